@@ -1,0 +1,57 @@
+"""ctypes loader for libflashqla_sm100.so (the C ABI declared in include/flashqla.h).
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libflashqla_sm100.so")
+
+_lock = threading.Lock()
+_lib = None
+
+_i32, _f32, _vp, _cp = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_char_p
+
+# name -> argtypes; every entry point returns int unless listed in _RESTYPES
+SIGNATURES = {
+    "fq_version": [],
+    "fq_last_error": [],
+    "fq_chunk_cumsum": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp],
+    "fq_kkt_solve": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _vp],
+    "fq_selftest_umma": [_vp, _vp, _vp, _i32, _vp, _vp],
+}
+_RESTYPES = {"fq_last_error": _cp}
+
+
+class FlashQLAError(RuntimeError):
+    pass
+
+
+def load():
+    """Return the loaded library, loading it on first use."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(LIB_PATH):
+                raise FlashQLAError(
+                    f"{LIB_PATH} not found: build it with `python -m flashqla_b200.build` "
+                    "(there is no fallback implementation)")
+            lib = ctypes.CDLL(LIB_PATH)
+            for name, argtypes in SIGNATURES.items():
+                fn = getattr(lib, name)  # AttributeError if the symbol is missing
+                fn.argtypes = argtypes
+                fn.restype = _RESTYPES.get(name, _i32)
+            _lib = lib
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = load().fq_last_error()
+        raise FlashQLAError(f"{what} failed with code {rc}: {msg.decode() if msg else ''}")

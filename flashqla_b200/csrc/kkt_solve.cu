@@ -1,0 +1,287 @@
+// A = (I + strictly_lower(diag(beta) K K^T))^-1 for every (chunk, V-head).
+//
+// One CTA (4 warps) owns one (chunk, QK-head): it loads the 64x128 K tile once, forms K K^T once
+// with warp-level bf16 MMA and then, for each of the G V-heads that share the QK head, inverts the
+// unit lower-triangular 64x64 matrix:
+//   1. the four 16x16 diagonal blocks by column-parallel forward substitution in fp32,
+//   2. the two 16x16 blocks next to the diagonal:  X10 = -D1 (L10 D0),  X32 = -D3 (L32 D2),
+//   3. the 32x32 block below:  X_lo_hi = -X_hi (L_hl X_lo),
+// steps 2 and 3 on tensor cores with split-TF32 (hi + lo) operands so the products keep fp32
+// accuracy.  The unit costs 24 KB of HBM traffic for ~1.4 MFLOP, i.e. it is HBM-bound, which is
+// why the legacy warp-level MMA path is enough here.
+#include "flashqla.h"
+#include "host.cuh"
+#include "seq.cuh"
+
+namespace fq {
+
+constexpr int kKLd = 136;  // bf16 elements per K-tile row in shared memory (pad: conflict-free fragments)
+constexpr int kFLd = 68;   // fp32 elements per row of the 64x64 work matrices
+constexpr int kTLd = 36;   // fp32 elements per row of the 32x32 scratch
+
+struct KktSmem {
+  __nv_bfloat16 k[kChunk * kKLd];
+  float kk[kChunk * kFLd];
+  float x[kChunk * kFLd];
+  float t[32 * kTLd];
+  float beta[kChunk];
+};
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void mma_tf32_1688(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(v));
+  const float r = v - __uint_as_float(hi);
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
+}
+// c += a * b with a, b given in fp32; three TF32 MMAs (hi*hi + hi*lo + lo*hi).
+__device__ __forceinline__ void mma_tf32x3(float (&c)[4], const float (&a)[4], const float (&b)[2]) {
+  uint32_t ah[4], al[4], bh[2], bl[2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) split_tf32(a[i], ah[i], al[i]);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) split_tf32(b[i], bh[i], bl[i]);
+  mma_tf32_1688(c, al, bh);
+  mma_tf32_1688(c, ah, bl);
+  mma_tf32_1688(c, ah, bh);
+}
+
+__global__ void __launch_bounds__(128) kkt_solve_kernel(const __nv_bfloat16* __restrict__ k,
+                                                       const float* __restrict__ beta,
+                                                       __nv_bfloat16* __restrict__ A, int H, int Hg, SeqArgs sa) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  KktSmem& s = *reinterpret_cast<KktSmem*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int hg = blockIdx.y;
+  const int G = H / Hg;
+  const ChunkPos p = chunk_lookup(sa, blockIdx.x);
+
+  // ---- K tile -> shared (rows past the sequence end are zero) and clear the X work matrix
+  {
+    const __nv_bfloat16* src = k + (static_cast<size_t>(p.tok0) * Hg + hg) * kDim;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int idx = it * 128 + tid;  // 16-byte piece index: 16 per row
+      const int row = idx >> 4, piece = idx & 15;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (row < p.len) v = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(row) * Hg * kDim) + piece);
+      *reinterpret_cast<uint4*>(&s.k[row * kKLd + piece * 8]) = v;
+    }
+    for (int i = tid; i < kChunk * kFLd; i += 128) s.x[i] = 0.f;
+  }
+  __syncthreads();
+
+  // ---- K K^T (lower block-triangle) with bf16 MMA, fp32 result in shared
+  {
+    const int m0 = warp * 16;
+    const int ntiles = 2 * warp + 2;
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+#pragma unroll
+    for (int k0 = 0; k0 < kDim; k0 += 16) {
+      uint32_t a[4];
+      a[0] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g) * kKLd + k0 + 2 * t]);
+      a[1] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g + 8) * kKLd + k0 + 2 * t]);
+      a[2] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g) * kKLd + k0 + 8 + 2 * t]);
+      a[3] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g + 8) * kKLd + k0 + 8 + 2 * t]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j < ntiles) {
+          uint32_t b[2];
+          b[0] = *reinterpret_cast<const uint32_t*>(&s.k[(j * 8 + g) * kKLd + k0 + 2 * t]);
+          b[1] = *reinterpret_cast<const uint32_t*>(&s.k[(j * 8 + g) * kKLd + k0 + 8 + 2 * t]);
+          mma_bf16_16816(acc[j], a, b);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (j < ntiles) {
+        *reinterpret_cast<float2*>(&s.kk[(m0 + g) * kFLd + j * 8 + 2 * t]) = make_float2(acc[j][0], acc[j][1]);
+        *reinterpret_cast<float2*>(&s.kk[(m0 + g + 8) * kFLd + j * 8 + 2 * t]) = make_float2(acc[j][2], acc[j][3]);
+      }
+    }
+  }
+
+  for (int hi = 0; hi < G; ++hi) {
+    const int hv = hg * G + hi;
+    __syncthreads();  // kk complete (first pass) / previous head's stores done
+    if (tid < kChunk) s.beta[tid] = (tid < p.len) ? __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hv) : 0.f;
+    __syncthreads();
+
+    // ---- step 1: inverse of the four 16x16 diagonal blocks, one column per thread
+    if (tid < kChunk) {
+      const int b0 = (tid >> 4) * 16, j = tid & 15;
+      float xcol[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float acc = 0.f;
+#pragma unroll
+        for (int m = 0; m < i; ++m) acc += s.kk[(b0 + i) * kFLd + b0 + m] * xcol[m];
+        xcol[i] = (i == j) ? 1.f : -s.beta[b0 + i] * acc;
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) s.x[(b0 + i) * kFLd + b0 + j] = xcol[i];
+    }
+    __syncthreads();
+
+    // ---- step 2: X10 = -D1 (L10 D0) and X32 = -D3 (L32 D2); warp = (block pair, 8-column half)
+    {
+      const int blk = warp >> 1, nt = warp & 1;
+      const int r0 = 16 * (2 * blk + 1), c0 = 16 * (2 * blk);
+      float* ts = &s.t[warp * 16 * 9];  // private 16 x 8 scratch (row stride 9)
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int k0 = 0; k0 < 16; k0 += 8) {
+        float a[4], b[2];
+        const float bg = s.beta[r0 + g], bg8 = s.beta[r0 + g + 8];
+        a[0] = bg * s.kk[(r0 + g) * kFLd + c0 + k0 + t];
+        a[1] = bg8 * s.kk[(r0 + g + 8) * kFLd + c0 + k0 + t];
+        a[2] = bg * s.kk[(r0 + g) * kFLd + c0 + k0 + t + 4];
+        a[3] = bg8 * s.kk[(r0 + g + 8) * kFLd + c0 + k0 + t + 4];
+        b[0] = s.x[(c0 + k0 + t) * kFLd + c0 + 8 * nt + g];
+        b[1] = s.x[(c0 + k0 + t + 4) * kFLd + c0 + 8 * nt + g];
+        mma_tf32x3(c, a, b);
+      }
+      ts[g * 9 + 2 * t] = c[0];
+      ts[g * 9 + 2 * t + 1] = c[1];
+      ts[(g + 8) * 9 + 2 * t] = c[2];
+      ts[(g + 8) * 9 + 2 * t + 1] = c[3];
+      __syncwarp();
+      float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int k0 = 0; k0 < 16; k0 += 8) {
+        float a[4], b[2];
+        a[0] = s.x[(r0 + g) * kFLd + r0 + k0 + t];
+        a[1] = s.x[(r0 + g + 8) * kFLd + r0 + k0 + t];
+        a[2] = s.x[(r0 + g) * kFLd + r0 + k0 + t + 4];
+        a[3] = s.x[(r0 + g + 8) * kFLd + r0 + k0 + t + 4];
+        b[0] = ts[(k0 + t) * 9 + g];
+        b[1] = ts[(k0 + t + 4) * 9 + g];
+        mma_tf32x3(d, a, b);
+      }
+      __syncthreads();  // every warp has read its diagonal blocks; the scratch is free again
+      *reinterpret_cast<float2*>(&s.x[(r0 + g) * kFLd + c0 + 8 * nt + 2 * t]) = make_float2(-d[0], -d[1]);
+      *reinterpret_cast<float2*>(&s.x[(r0 + g + 8) * kFLd + c0 + 8 * nt + 2 * t]) = make_float2(-d[2], -d[3]);
+    }
+    __syncthreads();
+
+    // ---- step 3: X[32:64, 0:32] = -X_hi (L_hl X_lo); warp = 16x16 quadrant
+    {
+      const int wr = warp >> 1, wc = warp & 1;
+      float c[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
+      const float bg = s.beta[32 + 16 * wr + g], bg8 = s.beta[32 + 16 * wr + g + 8];
+#pragma unroll
+      for (int k0 = 0; k0 < 32; k0 += 8) {
+        float a[4];
+        a[0] = bg * s.kk[(32 + 16 * wr + g) * kFLd + k0 + t];
+        a[1] = bg8 * s.kk[(32 + 16 * wr + g + 8) * kFLd + k0 + t];
+        a[2] = bg * s.kk[(32 + 16 * wr + g) * kFLd + k0 + t + 4];
+        a[3] = bg8 * s.kk[(32 + 16 * wr + g + 8) * kFLd + k0 + t + 4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+          float b[2];
+          b[0] = s.x[(k0 + t) * kFLd + 16 * wc + 8 * n + g];
+          b[1] = s.x[(k0 + t + 4) * kFLd + 16 * wc + 8 * n + g];
+          mma_tf32x3(c[n], a, b);
+        }
+      }
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        *reinterpret_cast<float2*>(&s.t[(16 * wr + g) * kTLd + 16 * wc + 8 * n + 2 * t]) = make_float2(c[n][0], c[n][1]);
+        *reinterpret_cast<float2*>(&s.t[(16 * wr + g + 8) * kTLd + 16 * wc + 8 * n + 2 * t]) =
+            make_float2(c[n][2], c[n][3]);
+      }
+      __syncthreads();
+      float d[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n) d[n][0] = d[n][1] = d[n][2] = d[n][3] = 0.f;
+#pragma unroll
+      for (int k0 = 0; k0 < 32; k0 += 8) {
+        float a[4];
+        a[0] = s.x[(32 + 16 * wr + g) * kFLd + 32 + k0 + t];
+        a[1] = s.x[(32 + 16 * wr + g + 8) * kFLd + 32 + k0 + t];
+        a[2] = s.x[(32 + 16 * wr + g) * kFLd + 32 + k0 + t + 4];
+        a[3] = s.x[(32 + 16 * wr + g + 8) * kFLd + 32 + k0 + t + 4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+          float b[2];
+          b[0] = s.t[(k0 + t) * kTLd + 16 * wc + 8 * n + g];
+          b[1] = s.t[(k0 + t + 4) * kTLd + 16 * wc + 8 * n + g];
+          mma_tf32x3(d[n], a, b);
+        }
+      }
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        *reinterpret_cast<float2*>(&s.x[(32 + 16 * wr + g) * kFLd + 16 * wc + 8 * n + 2 * t]) =
+            make_float2(-d[n][0], -d[n][1]);
+        *reinterpret_cast<float2*>(&s.x[(32 + 16 * wr + g + 8) * kFLd + 16 * wc + 8 * n + 2 * t]) =
+            make_float2(-d[n][2], -d[n][3]);
+      }
+    }
+    __syncthreads();
+
+    // ---- store A (bf16), 128 contiguous bytes per token row
+    {
+      __nv_bfloat16* dst = A + (static_cast<size_t>(p.tok0) * H + hv) * kChunk;
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int row = it * 16 + (tid >> 3), piece = tid & 7;
+        if (row < p.len) {
+          const float* xr = &s.x[row * kFLd + piece * 8];
+          uint4 v;
+          v.x = pack_bf16(xr[0], xr[1]);
+          v.y = pack_bf16(xr[2], xr[3]);
+          v.z = pack_bf16(xr[4], xr[5]);
+          v.w = pack_bf16(xr[6], xr[7]);
+          *(reinterpret_cast<uint4*>(dst + static_cast<size_t>(row) * H * kChunk) + piece) = v;
+        }
+      }
+    }
+  }
+}
+
+}  // namespace fq
+
+extern "C" FQ_API int fq_kkt_solve(const void* k, const float* beta, void* A, int B, int T, int H, int Hg,
+                                   const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
+                                   int total_chunks, void* stream) {
+  using namespace fq;
+  FQ_CHECK_ARG(k && beta && A, "fq_kkt_solve: null tensor");
+  FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0,
+               "fq_kkt_solve: bad sizes");
+  FQ_CHECK_ARG(Hg <= 65535, "fq_kkt_solve: too many QK heads");
+  FQ_CHECK_ARG((cu_seqlens == nullptr) == (chunk_offsets == nullptr),
+               "fq_kkt_solve: cu_seqlens and chunk_offsets must be given together");
+  FQ_CHECK_ARG(cu_seqlens == nullptr || B == 1, "fq_kkt_solve: packed batches need B == 1");
+  FQ_CHECK_ARG(cu_seqlens != nullptr || n_seq == B, "fq_kkt_solve: dense batches need n_seq == B");
+  if (total_chunks == 0) return FQ_OK;
+  SeqArgs sa{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  FQ_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    FQ_CHECK_CUDA(cudaFuncSetAttribute(kkt_solve_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(sizeof(KktSmem))));
+    attr_set[dev] = true;
+  }
+  dim3 grid(total_chunks, Hg);
+  kkt_solve_kernel<<<grid, 128, sizeof(KktSmem), static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(k), beta, static_cast<__nv_bfloat16*>(A), H, Hg, sa);
+  FQ_CHECK_CUDA(cudaGetLastError());
+  return FQ_OK;
+}

@@ -1,0 +1,81 @@
+"""Thin torch-tensor wrappers over the C ABI (one function per entry point).
+
+All tensors must live on the current CUDA device; work is enqueued on the current stream.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .planner import SeqPlan, plan_dense, plan_packed
+
+CHUNK = 64
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise _lib.FlashQLAError("flashqla_b200 kernels need CUDA tensors (there is no CPU path)")
+
+
+def make_plan(B: int, T: int, cu_seqlens, device) -> SeqPlan:
+    if cu_seqlens is None:
+        return plan_dense(B, T)
+    if B != 1:
+        raise ValueError(
+            f"The batch size is expected to be 1 rather than {B} when using `cu_seqlens`."
+            f"Please flatten variable-length inputs before processing.")
+    return plan_packed(cu_seqlens, device)
+
+
+def chunk_local_cumsum(g: torch.Tensor, chunk_size: int = CHUNK, reverse: bool = False, cu_seqlens=None,
+                       plan: SeqPlan | None = None) -> torch.Tensor:
+    """Chunk-local cumulative sum of g [B,T,H] (fp32 result)."""
+    assert chunk_size == CHUNK, "chunk size is fixed at 64"
+    _require_cuda(g)
+    B, T, H = g.shape
+    plan = plan or make_plan(B, T, cu_seqlens, g.device)
+    gin = g.contiguous() if g.dtype == torch.float32 else g.float().contiguous()
+    out = torch.empty_like(gin)
+    cu_p, off_p = plan.ptrs()
+    rc = _lib.load().fq_chunk_cumsum(gin.data_ptr(), out.data_ptr(), B, T, H, cu_p, off_p, plan.n_seq,
+                                     plan.total_chunks, int(reverse), _stream())
+    _lib.check(rc, "fq_chunk_cumsum")
+    return out
+
+
+def kkt_solve(k: torch.Tensor, b: torch.Tensor, cu_seqlens=None, plan: SeqPlan | None = None) -> torch.Tensor:
+    """A = (I + tril(diag(b) K K^T, -1))^-1, bf16 [B,T,H,64] (gate-free)."""
+    _require_cuda(k, b)
+    if k.dtype != torch.bfloat16:
+        raise _lib.FlashQLAError("kkt_solve: only bfloat16 keys are supported")
+    B, T, Hg, K = k.shape
+    H = b.shape[-1]
+    assert K == 128, "head dim must be 128"
+    plan = plan or make_plan(B, T, cu_seqlens, k.device)
+    k = k.contiguous()
+    bf = b.contiguous() if b.dtype == torch.float32 else b.float().contiguous()
+    # rows of partial tail chunks are never written by the kernel -> start from zeros
+    A = torch.zeros(B, T, H, CHUNK, dtype=k.dtype, device=k.device) if T % CHUNK or plan.packed else \
+        torch.empty(B, T, H, CHUNK, dtype=k.dtype, device=k.device)
+    cu_p, off_p = plan.ptrs()
+    rc = _lib.load().fq_kkt_solve(k.data_ptr(), bf.data_ptr(), A.data_ptr(), B, T, H, Hg, cu_p, off_p, plan.n_seq,
+                                  plan.total_chunks, _stream())
+    _lib.check(rc, "fq_kkt_solve")
+    return A
+
+
+def selftest_umma(a: torch.Tensor, b: torch.Tensor, mode: int) -> torch.Tensor:
+    _require_cuda(a, b)
+    d = torch.zeros(128, 128, dtype=torch.float32, device=a.device)
+    status = torch.zeros(1, dtype=torch.int32, device=a.device)
+    rc = _lib.load().fq_selftest_umma(a.data_ptr(), b.data_ptr(), d.data_ptr(), mode, status.data_ptr(), _stream())
+    _lib.check(rc, "fq_selftest_umma")
+    st = int(status.item())
+    if st != 0:
+        raise _lib.FlashQLAError(f"fq_selftest_umma: device wait timed out (code {st:#x})")
+    return d

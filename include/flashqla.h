@@ -1,0 +1,79 @@
+/*
+ * flashqla.h — C ABI of libflashqla_sm100.so: the chunked gated-delta-rule (GDN) kernels for
+ * NVIDIA B200 (sm_100a).
+ *
+ * The reference project (FlashQLA) has no native interface: its kernels are JIT-generated from
+ * Python and called through small torch wrappers.  Each entry point below replaces one of those
+ * wrappers; the file:line given with it is the wrapper's location inside the FlashQLA project.
+ *
+ * Conventions (all entry points):
+ *   - every pointer is a DEVICE pointer unless its name ends in `_host`;
+ *   - tensors are dense row-major: q,k [B,T,Hg,128], v,o,do,dv [B,T,H,128], g,beta [B,T,H],
+ *     A [B,T,H,64], states [n_seq,H,128,128] (K index before V index), h [total_chunks,H,128,128];
+ *   - q/k/v/o/A/h are bfloat16, gates/beta fp32, states fp32;
+ *   - variable-length batches: B == 1, `cu_seqlens` = int32 [n_seq+1] token offsets,
+ *     `chunk_offsets` = int32 [n_seq+1] prefix sums of ceil(len/64); both NULL for dense batches
+ *     (then n_seq == B and every sequence has T tokens);
+ *   - the work is enqueued on `stream` (a cudaStream_t); nothing synchronises, nothing is
+ *     allocated, no global mutable state is kept apart from per-device constant caches;
+ *   - return value: 0 on success, negative FQ_ERR_* otherwise; fq_last_error() gives a message
+ *     for the calling thread;
+ *   - `status_dev` (may be NULL): int32 in device memory, must be 0 on entry; a kernel whose
+ *     bounded wait expires stores a non-zero code there and drains instead of hanging.
+ */
+#ifndef FLASHQLA_H_
+#define FLASHQLA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define FQ_API __attribute__((visibility("default")))
+#else
+#define FQ_API
+#endif
+
+#define FQ_OK 0
+#define FQ_ERR_INVALID (-1)
+#define FQ_ERR_CUDA (-2)
+#define FQ_ERR_UNSUPPORTED (-3)
+#define FQ_ERR_WORKSPACE (-4)
+#define FQ_ERR_TIMEOUT (-5)
+
+/* Library version (major*100 + minor). */
+FQ_API int fq_version(void);
+/* Message of the last error raised on the calling thread. */
+FQ_API const char* fq_last_error(void);
+
+/*
+ * Chunk-local (64-token) inclusive prefix sum of the log-gate, or suffix sum when reverse != 0.
+ * Replaces chunk_local_cumsum, flash_qla/ops/utils/cumsum.py:131-165.
+ * g, out: fp32 [B,T,H].  `out` may alias `g`.
+ */
+FQ_API int fq_chunk_cumsum(const float* g, float* out, int B, int T, int H, const int32_t* cu_seqlens,
+                           const int32_t* chunk_offsets, int n_seq, int total_chunks, int reverse, void* stream);
+
+/*
+ * A = (I + strictly_lower(diag(beta) K K^T))^-1 per (chunk, V-head); gate-free, bf16 [B,T,H,64].
+ * Rows of a partial tail chunk beyond the sequence end are not written.
+ * Replaces kkt_solve, flash_qla/ops/gated_delta_rule/chunk/hopper/kkt_solve.py:305-345.
+ */
+FQ_API int fq_kkt_solve(const void* k, const float* beta, void* A, int B, int T, int H, int Hg,
+                        const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq, int total_chunks,
+                        void* stream);
+
+/*
+ * Self-test of the tensor-core plumbing (TMA 128B-swizzled tiles -> UMMA -> TMEM -> registers).
+ * a, b: bf16 [128,128] row-major; d: fp32 [128,128].  `mode` selects the operand forms, see
+ * csrc/selftest.cu.  No counterpart in the reference; used by the GPU tests only.
+ */
+FQ_API int fq_selftest_umma(const void* a, const void* b, float* d, int mode, int32_t* status_dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHQLA_H_ */
