@@ -22,6 +22,7 @@ SIGNATURES = {
     "fq_last_error": [],
     "fq_chunk_cumsum": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp],
     "fq_kkt_solve": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _vp],
+    "fq_gdr_fwd": [_vp] * 11 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "fq_selftest_umma": [_vp, _vp, _vp, _i32, _vp, _vp],
 }
 _RESTYPES = {"fq_last_error": _cp}

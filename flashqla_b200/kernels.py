@@ -79,3 +79,51 @@ def selftest_umma(a: torch.Tensor, b: torch.Tensor, mode: int) -> torch.Tensor:
     if st != 0:
         raise _lib.FlashQLAError(f"fq_selftest_umma: device wait timed out (code {st:#x})")
     return d
+
+
+def _status_tensor(device) -> torch.Tensor:
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def check_status(status: torch.Tensor, what: str) -> None:
+    """Raise if a kernel's bounded wait expired (costs a device sync; used by tests and debug mode)."""
+    st = int(status.item())
+    if st != 0:
+        raise _lib.FlashQLAError(f"{what}: device-side wait timed out (code {st:#x})")
+
+
+def fused_gdr_fwd(q, k, v, a, g, b, scale, initial_state=None, output_final_state=True, output_h=False,
+                  output_o=True, plan: SeqPlan | None = None, ht_index=None, n_out=None, status=None):
+    """Fused forward recurrence.  g is the chunk-local cumsum, a the gate-free inverse from kkt_solve.
+
+    Returns (o or None, h or None, final_state or None)."""
+    _require_cuda(q, k, v, a, g, b)
+    if q.dtype != torch.bfloat16:
+        raise _lib.FlashQLAError("fused_gdr_fwd: only bfloat16 q/k/v are supported")
+    B, T, Hg, K = k.shape
+    H, V = v.shape[2], v.shape[3]
+    assert K == 128 and V == 128, "head dims must be 128"
+    plan = plan or plan_dense(B, T)
+    dev = q.device
+    q, k, v, a = q.contiguous(), k.contiguous(), v.contiguous(), a.contiguous()
+    g = g.contiguous() if g.dtype == torch.float32 else g.float().contiguous()
+    b = b.contiguous() if b.dtype == torch.float32 else b.float().contiguous()
+    h0 = None
+    if initial_state is not None:
+        h0 = initial_state.contiguous() if initial_state.dtype == torch.float32 else initial_state.float().contiguous()
+        assert h0.shape == (plan.n_seq, H, K, V), f"initial_state shape {tuple(h0.shape)} != {(plan.n_seq, H, K, V)}"
+    o = torch.empty(B, T, H, V, dtype=q.dtype, device=dev) if output_o else None
+    h = torch.empty(1 if plan.packed else B, plan.total_chunks // (1 if plan.packed else B), H, K, V, dtype=q.dtype,
+                    device=dev) if output_h else None
+    ht = None
+    if output_final_state:
+        ht = torch.empty(plan.n_seq if n_out is None else n_out, H, K, V, dtype=torch.float32, device=dev)
+    cu_p, off_p = plan.ptrs()
+    rc = _lib.load().fq_gdr_fwd(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), g.data_ptr(), b.data_ptr(),
+        None if h0 is None else h0.data_ptr(), None if ht is None else ht.data_ptr(),
+        None if ht_index is None else ht_index.data_ptr(), None if o is None else o.data_ptr(),
+        None if h is None else h.data_ptr(), B, T, H, Hg, cu_p, off_p, plan.n_seq, plan.total_chunks, float(scale),
+        None if status is None else status.data_ptr(), _stream())
+    _lib.check(rc, "fq_gdr_fwd")
+    return o, h, ht

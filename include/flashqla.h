@@ -67,6 +67,23 @@ FQ_API int fq_kkt_solve(const void* k, const float* beta, void* A, int B, int T,
                         void* stream);
 
 /*
+ * Fused forward recurrence: per (sequence, V-head) walks the chunks, carries the fp32 K x V state
+ * and writes o = scale*exp(g) o (Q S) + P_g V_d per chunk.
+ * Replaces fused_gdr_fwd, flash_qla/ops/gated_delta_rule/chunk/hopper/fused_fwd.py:535-658
+ * (and, with o == NULL and h_out != NULL, the state-only fused_gdr_h of hopper/prepare_h.py:461-558).
+ *   q,k [B,T,Hg,128] bf16; v [B,T,H,128] bf16; A [B,T,H,64] bf16 from fq_kkt_solve;
+ *   g_cumsum, beta [B,T,H] fp32 (g_cumsum from fq_chunk_cumsum);
+ *   h0   [n_seq,H,128,128] fp32 initial states, or NULL for zeros;
+ *   ht   [*,H,128,128] fp32 final states, or NULL; sequence i writes slot ht_index[i]
+ *        (negative = skip; ht_index == NULL means slot i);
+ *   o    [B,T,H,128] bf16 or NULL;   h_out [total_chunks,H,128,128] bf16 (state BEFORE each chunk) or NULL.
+ */
+FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, const void* A, const float* g_cumsum,
+                      const float* beta, const float* h0, float* ht, const int32_t* ht_index, void* o, void* h_out,
+                      int B, int T, int H, int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
+                      int total_chunks, float scale, int32_t* status_dev, void* stream);
+
+/*
  * Self-test of the tensor-core plumbing (TMA 128B-swizzled tiles -> UMMA -> TMEM -> registers).
  * a, b: bf16 [128,128] row-major; d: fp32 [128,128].  `mode` selects the operand forms, see
  * csrc/selftest.cu.  No counterpart in the reference; used by the GPU tests only.

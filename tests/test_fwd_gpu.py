@@ -1,0 +1,104 @@
+"""GPU parity of the forward path against the CPU oracle and the golden fixtures.
+
+Tolerance (stated): max|x - ref| <= 1e-2 * max|ref| for bf16 outputs and <= 5e-3 * max|ref| for
+fp32 outputs, against the fp32 oracle on the same bf16-rounded inputs.  The reference's own
+acceptance bound is 2e-2 (tests/test_gdr.py:203-235 of the reference).
+"""
+import os
+
+import pytest
+import torch
+
+from conftest import load_golden
+from oracle import gdr_oracle as orc
+
+pytestmark = pytest.mark.gpu
+os.environ.setdefault("FLASHQLA_CHECK_STATUS", "1")
+
+TOL_BF16 = 1e-2
+TOL_FP32 = 5e-3
+
+
+def make_inputs(seed, B, T, Hq, Hv, dist="baseline", n_seq=None):
+    torch.manual_seed(seed)
+    N = B if n_seq is None else n_seq
+    q = orc.l2norm(torch.randn(B, T, Hq, 128)).bfloat16()
+    k = orc.l2norm(torch.randn(B, T, Hq, 128)).bfloat16()
+    v = torch.randn(B, T, Hv, 128).bfloat16()
+    g = torch.nn.functional.logsigmoid(torch.randn(B, T, Hv))
+    beta = torch.randn(B, T, Hv).sigmoid()
+    if dist == "baseline":
+        h0 = 0.1 * torch.randn(N, Hv, 128, 128)
+    else:
+        g = g / 16
+        g[:, :, -1] = 0.0
+        h0 = torch.randn(N, Hv, 128, 128)
+    return q, k, v, g, beta, h0
+
+
+def run_fwd(q, k, v, g, beta, h0, cu, output_h=False):
+    from flashqla_b200 import ops
+    dev = "cuda"
+    out = ops.chunk_gated_delta_rule_fwd(q.to(dev), k.to(dev), v.to(dev), g.to(dev), beta.to(dev), None,
+                                         None if h0 is None else h0.to(dev), None if cu is None else cu.to(dev),
+                                         True, output_h, False)
+    torch.cuda.synchronize()
+    return out
+
+
+FWD_CASES = [
+    # B, T, Hq, Hv, cu, dist, use_h0
+    (1, 64, 1, 1, None, "baseline", False),
+    (1, 128, 1, 1, None, "baseline", True),
+    (1, 512, 4, 4, None, "baseline", True),
+    (2, 200, 2, 4, None, "baseline", True),
+    (1, 33, 2, 2, None, "reftest", True),
+    (1, 1000, 2, 4, [0, 1, 64, 65, 300, 300, 777, 1000], "reftest", True),
+    (1, 2048, 2, 2, None, "reftest", True),
+]
+
+
+@pytest.mark.parametrize("B,T,Hq,Hv,cu,dist,use_h0", FWD_CASES)
+def test_forward_vs_oracle(B, T, Hq, Hv, cu, dist, use_h0):
+    cu_t = None if cu is None else torch.tensor(cu, dtype=torch.int32)
+    q, k, v, g, beta, h0 = make_inputs(7, B, T, Hq, Hv, dist, None if cu is None else len(cu) - 1)
+    if not use_h0:
+        h0 = None
+    gc_r, A_r, o_r, h_r, fs_r = orc.gdr_fwd(q.float(), k.float(), v.float(), g, beta, None, h0, cu_t, output_h=True)
+    gc, A, o, h, fs = run_fwd(q, k, v, g, beta, h0, cu_t, output_h=True)
+    assert orc.rel_to_max(gc.cpu(), gc_r) < 1e-5
+    assert orc.rel_to_max(A.float().cpu(), A_r) < 6e-3
+    assert orc.rel_to_max(o.float().cpu(), o_r) < TOL_BF16, "o"
+    assert orc.rel_to_max(fs.cpu(), fs_r) < TOL_FP32, "final_state"
+    assert orc.rel_to_max(h.float().cpu().reshape(h_r.shape), h_r) < TOL_BF16, "h"
+
+
+@pytest.mark.parametrize("name", ["dense_tail_bf16", "varlen_gva_reftest_bf16"])
+def test_forward_vs_reference_fixture(name):
+    z = load_golden(name)
+    cu = z.get("cu_seqlens")
+    gc, A, o, h, fs = run_fwd(z["q"], z["k"], z["v"], z["g"], z["beta"], z["h0"], cu)
+    assert orc.rel_to_max(gc.cpu(), z["g_cumsum"]) < 1e-5
+    assert orc.rel_to_max(o.float().cpu(), z["o"]) < TOL_BF16
+    assert orc.rel_to_max(fs.cpu(), z["final_state"]) < TOL_FP32
+
+
+def test_forward_c1_fixture_bf16_inputs():
+    """BASELINE config 1 shapes; the fixture's fp32 inputs are rounded to bf16 for the GPU path, so
+    the comparison is against the oracle on the rounded inputs and (loosely) against the fixture."""
+    z = load_golden("c1_fwd_fp32")
+    q, k, v = z["q"].bfloat16(), z["k"].bfloat16(), z["v"].bfloat16()
+    _, _, o_r, _, fs_r = orc.gdr_fwd(q.float(), k.float(), v.float(), z["g"], z["beta"], z["scale"], z["h0"], None)
+    gc, A, o, h, fs = run_fwd(q, k, v, z["g"], z["beta"], z["h0"], None)
+    assert orc.rel_to_max(o.float().cpu(), o_r) < TOL_BF16
+    assert orc.rel_to_max(fs.cpu(), fs_r) < TOL_FP32
+    assert orc.rel_to_max(o.float().cpu(), z["o"]) < 2e-2
+    assert orc.rel_to_max(fs.cpu(), z["final_state"]) < 2e-2
+
+
+def test_forward_is_deterministic():
+    q, k, v, g, beta, h0 = make_inputs(3, 1, 1024, 2, 2)
+    a = run_fwd(q, k, v, g, beta, h0, None)
+    for _ in range(5):
+        b = run_fwd(q, k, v, g, beta, h0, None)
+        assert torch.equal(a[2], b[2]) and torch.equal(a[4], b[4])
