@@ -1,0 +1,300 @@
+#!/usr/bin/env python
+"""Benchmark of the chunked gated-delta-rule (GDN) hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3]
+
+One "step" = one pass of the hot path over one synthetic batch.  The default workload is the
+configuration the headline metric is quoted on: single-GPU forward prefill,
+B=1, T=32768, H_q=H_v=64, K=V=128, bf16 q/k/v, fp32 gates (``c2``).  ``c3`` adds the training
+forward+backward on B=4, T=8192, H_q=16, H_v=32.
+
+Prints ONE JSON line (rank 0).  ``value`` is device-timed throughput with the inputs resident in
+HBM; ``e2e`` is the same metric through the public operator with HOST (pinned) buffers, the
+host<->device copies inside the timed region.  Under torchrun every rank runs the same workload
+on its own GPU (the path shards by batch x head with no collective): weak scaling.
+
+``--impl reference`` times the reference's CPU implementation of the path (the PyTorch oracle
+port under oracle/, all host threads) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, T, Hq, Hv, backward)
+    "c2": dict(B=1, T=32768, Hq=64, Hv=64, bwd=False,
+               desc="fwd prefill B=1 T=32768 Hq=Hv=64 K=V=128 bf16, g=logsigmoid(randn) fp32, h0=zeros"),
+    "c2s": dict(B=1, T=16384, Hq=32, Hv=32, bwd=False,
+                desc="(profiling case) fwd B=1 T=16384 Hq=Hv=32 K=V=128 bf16"),
+    "c3": dict(B=4, T=8192, Hq=16, Hv=32, bwd=True,
+               desc="fwd+bwd B=4 T=8192 Hq=16 Hv=32 K=V=128 bf16, h0=0.1 randn, dht=0.01 randn"),
+}
+# algorithmic HBM bytes per (chunk, V-head) of the fused forward kernel at Hq == Hv:
+# q, k, v read + o write (4 x 16 KiB) + g, beta (2 x 256 B)
+FWD_BYTES_PER_UNIT = 4 * 16384 + 512
+
+
+def l2norm(x):
+    return x * torch.rsqrt((x * x).sum(-1, keepdim=True) + 1e-6)
+
+
+def make_inputs(w, device, seed=0, pin=False):
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    B, T, Hq, Hv = w["B"], w["T"], w["Hq"], w["Hv"]
+
+    def rn(*shape):
+        return torch.randn(*shape, generator=gen)
+
+    host = dict(
+        q=l2norm(rn(B, T, Hq, 128)).bfloat16(), k=l2norm(rn(B, T, Hq, 128)).bfloat16(), v=rn(B, T, Hv, 128).bfloat16(),
+        g=torch.nn.functional.logsigmoid(rn(B, T, Hv)), beta=rn(B, T, Hv).sigmoid(),
+        h0=(0.1 * rn(B, Hv, 128, 128)) if w["bwd"] else torch.zeros(B, Hv, 128, 128))
+    if w["bwd"]:
+        host["do"] = rn(B, T, Hv, 128).bfloat16()
+        host["dht"] = 0.01 * rn(B, Hv, 128, 128)
+    if pin:
+        host = {k_: v_.pin_memory() for k_, v_ in host.items()}
+    if device is None:
+        return host, None
+    return host, {k_: v_.to(device, non_blocking=True) for k_, v_ in host.items()}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        if not sm:
+            return None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower() == "active" for r in self.rows)]
+        smax = max(int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit())
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": smax, "reasons": reasons, "samples": len(sm)}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d, "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def cpu_oracle_sample(w, threads):
+    """Time the CPU oracle port on a bounded sample: same distribution, T and H cut down.
+    Cost is linear in T*H, so tokens/s at the full head count = T_s * (H_s / Hv) / time."""
+    from oracle import gdr_oracle as orc
+    torch.set_num_threads(threads)
+    Ts, Hs = 8192, 16
+    Hqs = max(1, Hs * w["Hq"] // w["Hv"])
+    sw = dict(B=1, T=Ts, Hq=Hqs, Hv=Hs, bwd=w["bwd"])
+    host, _ = make_inputs(sw, None, seed=1)
+    f = {k_: v_.float() for k_, v_ in host.items()}
+    t0 = time.perf_counter()
+    gc, A, o, h, fs = orc.gdr_fwd(f["q"], f["k"], f["v"], f["g"], f["beta"], None, f["h0"], None)
+    if w["bwd"]:
+        orc.gdr_bwd(f["q"], f["k"], f["v"], gc, f["beta"], f["do"], f["dht"], None, f["h0"], None)
+    dt = time.perf_counter() - t0
+    tokens_equiv = Ts * Hs / w["Hv"]
+    return tokens_equiv / dt, dt, f"oracle port, B=1 T={Ts} Hq={Hqs} Hv={Hs} fp32, scaled by heads to Hv={w['Hv']}"
+
+
+def run_reference(args, w, rank, world):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    vals = []
+    for i in range(args.warmup + args.steps):
+        tps, dt, sample = cpu_oracle_sample(w, threads)
+        if i >= args.warmup:
+            vals.append((tps, dt))
+    tps = sum(v[0] for v in vals) / len(vals)
+    ms = 1e3 * sum(v[1] for v in vals) / len(vals)
+    line = {"impl": "reference", "metric": metric_name(w), "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+            "config": {"workload": w["desc"], "timing": "CPU wall clock per bounded sample"},
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def metric_name(w):
+    return "GDN fwd+bwd tokens/s per B200" if w["bwd"] else "GDN fwd tokens/s per B200"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if args.impl == "reference" and args.steps > 3:
+            args.steps, args.warmup = min(args.steps, 3), min(args.warmup, 1)
+        run_reference(args, w, rank, world)
+        return
+
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    import flashqla_b200 as fq
+    from flashqla_b200 import kernels
+    from flashqla_b200.planner import plan_dense
+
+    host, d = make_inputs(w, dev, seed=rank, pin=True)
+    torch.cuda.synchronize()
+    B, T, Hq, Hv = w["B"], w["T"], w["Hq"], w["Hv"]
+    tokens = B * T
+    scale = 128 ** -0.5
+    plan = plan_dense(B, T)
+    fwd_events = []
+
+    def step(record=False):
+        g_cum = kernels.chunk_local_cumsum(d["g"], plan=plan)
+        A = kernels.kkt_solve(d["k"], d["beta"], plan=plan)
+        if record:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        o, _, fs = kernels.fused_gdr_fwd(d["q"], d["k"], d["v"], A, g_cum, d["beta"], scale, initial_state=d["h0"],
+                                         plan=plan)
+        if record:
+            e1.record()
+            fwd_events.append((e0, e1))
+        if w["bwd"]:
+            fq.chunk_gated_delta_rule_bwd(d["q"], d["k"], d["v"], g_cum, d["beta"], A, d["do"], d["dht"], scale,
+                                          d["h0"], None)
+        return o, fs
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for _ in range(args.steps):
+        step(record=True)
+    t1.record()
+    barrier()
+    ms_total = t0.elapsed_time(t1)
+    fwd_ms = sum(a.elapsed_time(b) for a, b in fwd_events) / len(fwd_events)
+
+    # ---- end to end through the public operator with host buffers
+    def e2e_step():
+        dd = {k_: host[k_].to(dev, non_blocking=True) for k_ in ("q", "k", "v", "g", "beta", "h0")}
+        _, _, o, _, fs = fq.chunk_gated_delta_rule_fwd(dd["q"], dd["k"], dd["v"], dd["g"], dd["beta"], scale, dd["h0"],
+                                                       None, True, False, True)
+        if w["bwd"]:
+            raise NotImplementedError
+        return o.to("cpu", non_blocking=True), fs.to("cpu", non_blocking=True)
+
+    e2e = None
+    if not w["bwd"]:
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        n_e2e = max(3, min(args.steps, 5))
+        w0 = time.perf_counter()
+        for _ in range(n_e2e):
+            e2e_step()
+        barrier()
+        e2e_ms = 1e3 * (time.perf_counter() - w0) / n_e2e
+        h2d = sum(host[k_].numel() * host[k_].element_size() for k_ in ("q", "k", "v", "g", "beta", "h0"))
+        d2h = tokens * Hv * 128 * 2 + B * Hv * 128 * 128 * 4
+    clocks = sampler.stop() if sampler else None
+
+    ms = torch.tensor([ms_total / args.steps, fwd_ms, e2e_ms if not w["bwd"] else 0.0], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_step, fwd_ms, e2e_ms = (float(x) for x in ms.tolist())
+
+    if rank == 0:
+        peaks, how = measured_peaks()
+        units = plan.total_chunks * Hv
+        q_bytes = FWD_BYTES_PER_UNIT - 2 * 16384 + 2 * 16384 * Hq // Hv  # q,k are shared by Hv/Hq V-heads
+        alg_bytes = units * q_bytes + 2 * B * Hv * 128 * 128 * 4          # + h0 read, final state write
+        achieved = alg_bytes / (fwd_ms * 1e-3) / 1e9
+        line = {
+            "metric": metric_name(w), "value": world * tokens / (ms_step * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["desc"], "l2": "inputs (1.5 GB) exceed the 126 MB L2; no flush needed",
+                       "kernels_per_step": ["chunk_cumsum", "kkt_solve", "gdr_fwd"]},
+            "gpu_launches": (3 + (0 if not w["bwd"] else 0)) * args.steps,
+            "roofline": {"kernel": "gdr_fwd_kernel", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": how + " (of measured copy bandwidth)" if how == "measured" else how,
+                         "kernel_ms": fwd_ms, "algorithmic_bytes": alg_bytes, "traffic": None},
+            "clocks": clocks,
+        }
+        if not w["bwd"]:
+            line["e2e"] = {"value": world * tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+        if not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            tps, dt, sample = cpu_oracle_sample(w, threads)
+            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                    "sample": sample, "seconds": dt}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

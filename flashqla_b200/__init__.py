@@ -4,3 +4,11 @@ Same operator interface as FlashQLA's ``flash_qla`` package; the kernels are han
 sm_100a CUDA behind the C ABI of ``include/flashqla.h``.
 """
 __version__ = "0.1.0"
+
+from .ops import (  # noqa: E402
+    chunk_gated_delta_rule,
+    chunk_gated_delta_rule_bwd,
+    chunk_gated_delta_rule_fwd,
+)
+
+__all__ = ["chunk_gated_delta_rule_fwd", "chunk_gated_delta_rule_bwd", "chunk_gated_delta_rule"]

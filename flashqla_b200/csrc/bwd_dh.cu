@@ -1,0 +1,474 @@
+// Backward, serial part: the reverse recurrence of the state gradient dS, one persistent CTA per
+// (sequence, V-head), chunks visited last to first.  Same transposed-state layout as the forward
+// (dS^T in tensor memory: lane = v, column = k), so every product has M = 128:
+//
+//   PK   [128 x 64]  = [K;Q] K^T                 rows 64..127 -> P_g = scale * G o (Q K^T)
+//   D2   [128 x 64]  = dO^T P_g                   (state independent)
+//   D1   [128 x 64]  = dS^T_bf16 K^T
+//        dV'^T = rho o D1 + D2                    -> scratch dvp [tokens, H, 128]
+//   DW   [128 x 64]  = dV'^T A_g                  = dv^T  (aliases D1)
+//        dVg^T = -gamma o DW
+//   dS  <- gamma_last dS + dVg^T K + (scale*gamma o dO)^T Q
+//
+// The state BEFORE each update (the gradient w.r.t. the state after the chunk) is written as bf16
+// to dh [chunks, H, 128, 128]; the chunk-parallel kernel (bwd_chunk.cu) consumes it.
+#include "flashqla.h"
+#include "host.cuh"
+#include "seq.cuh"
+
+namespace fq {
+
+constexpr int kDhThreads = 512;
+constexpr int kDhGateStages = 4;
+constexpr uint32_t kDhStageBytes = 32768 + 16384 + 8192;
+
+constexpr uint32_t kDhColS = 0;     // fp32 dS^T
+constexpr uint32_t kDhColD1 = 128;  // D1, later DW
+constexpr uint32_t kDhColD2 = 192;
+constexpr uint32_t kDhColPK = 256;
+
+struct BwdDhSmem {
+  unsigned char kq[2][32768];    // k rows 0-63 | q rows 64-127, two 128-row regions (d 0-63 | 64-127)
+  unsigned char dout[2][16384];  // dO tile [64 c][128 v] as two 64-row regions
+  unsigned char a[2][8192];      // A tile, rewritten in place as A_g
+  unsigned char dsbf[32768];     // bf16 dS^T [128 v][128 k]
+  unsigned char dvp[16384];      // dV'^T [128 v][64 c]
+  unsigned char dvg[16384];      // dVg^T [128 v][64 c]
+  unsigned char dos[16384];      // (scale*gamma o dO)^T [128 v][64 c]
+  unsigned char pg[8192];        // P_g [64 i][64 j]
+  float gate[kDhGateStages][4][kChunk];
+  uint64_t full[2], empty[2], gate_full[kDhGateStages], gate_empty[kDhGateStages];
+  uint64_t pk_done, d2_done, d1_done, dw_done, ds_done;
+  uint64_t ds_ready, ds_scaled, dvp_ready, dvg_ready, ag_ready, pg_ready, dos_ready;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct BwdDhParams {
+  const float* g_cum;
+  const float* beta;
+  const float* dht;        // [n_seq, H, 128, 128] or nullptr
+  float* dh0;              // [n_seq, H, 128, 128] or nullptr
+  __nv_bfloat16* dh_out;   // [total_chunks, H, 128, 128]
+  __nv_bfloat16* dvp_out;  // [rows, H, 128]
+  __nv_bfloat16* dv_out;   // [rows, H, 128]
+  int H, Hg;
+  float scale;
+  SeqArgs sa;
+  int* status_dev;
+};
+
+__device__ __forceinline__ uint32_t dh_koff(int kk) { return (kk >> 2) * 16384 + (kk & 3) * 32; }
+
+// Stores a [128 v][64 c] tile held as 32 packed bf16 pairs per thread (thread = v) to the
+// token-major global tensor: element (c, v) goes to base[c * row_stride + v].
+__device__ __forceinline__ void store_cols_bf16(unsigned short* base, size_t row_stride, const uint32_t (&packed)[32],
+                                                int len) {
+#pragma unroll
+  for (int c = 0; c < kChunk; c += 2) {
+    if (c < len) base[c * row_stride] = static_cast<unsigned short>(packed[c >> 1] & 0xFFFFu);
+    if (c + 1 < len) base[(c + 1) * row_stride] = static_cast<unsigned short>(packed[c >> 1] >> 16);
+  }
+}
+
+__global__ void __launch_bounds__(kDhThreads, 1)
+gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                  const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_a,
+                  const BwdDhParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  BwdDhSmem& s = *reinterpret_cast<BwdDhSmem*>(
+      reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int seq = blockIdx.x / p.H, h = blockIdx.x - seq * p.H;
+  const int hg = h / (p.H / p.Hg);
+  int tok_begin, seq_len, chunk_off;
+  if (p.sa.cu_seqlens == nullptr) {
+    tok_begin = seq * p.sa.T;
+    seq_len = p.sa.T;
+    chunk_off = seq * p.sa.nc_dense;
+  } else {
+    tok_begin = __ldg(p.sa.cu_seqlens + seq);
+    seq_len = __ldg(p.sa.cu_seqlens + seq + 1) - tok_begin;
+    chunk_off = __ldg(p.sa.chunk_offsets + seq);
+  }
+  const int nchunks = (seq_len + kChunk - 1) / kChunk;
+  WaitCtx wc{&s.abort_flag, p.status_dev};
+
+  if (tid == 0) {
+    s.abort_flag = 0;
+    for (int i = 0; i < 2; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 5); }
+    for (int i = 0; i < kDhGateStages; ++i) { mbar_init(&s.gate_full[i], 64); mbar_init(&s.gate_empty[i], 12); }
+    mbar_init(&s.pk_done, 1); mbar_init(&s.d2_done, 1); mbar_init(&s.d1_done, 1); mbar_init(&s.dw_done, 1);
+    mbar_init(&s.ds_done, 1);
+    mbar_init(&s.ds_ready, 4); mbar_init(&s.ds_scaled, 4); mbar_init(&s.dvp_ready, 4); mbar_init(&s.dvg_ready, 4);
+    mbar_init(&s.dos_ready, 4); mbar_init(&s.ag_ready, 2); mbar_init(&s.pg_ready, 2);
+    fence_mbar_init();
+    tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_a);
+  }
+  if (warp == 1) {
+    tmem_alloc(&s.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = s.tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int it = 0; it < nchunks; ++it) {
+        const int n = nchunks - 1 - it, st = it & 1;
+        if (it >= 2 && !mbar_wait(wc, &s.empty[st], ((it >> 1) + 1) & 1, 1)) break;
+        mbar_arrive_expect_tx(&s.full[st], kDhStageBytes);
+        const int row = tok_begin + n * kChunk;
+        tma_load_3d(s.kq[st], &map_k, &s.full[st], 0, hg, row);
+        tma_load_3d(s.kq[st] + 16384, &map_k, &s.full[st], 64, hg, row);
+        tma_load_3d(s.kq[st] + 8192, &map_q, &s.full[st], 0, hg, row);
+        tma_load_3d(s.kq[st] + 24576, &map_q, &s.full[st], 64, hg, row);
+        tma_load_3d(s.dout[st], &map_do, &s.full[st], 0, h, row);
+        tma_load_3d(s.dout[st] + 8192, &map_do, &s.full[st], 64, h, row);
+        tma_load_3d(s.a[st], &map_a, &s.full[st], 0, h, row);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ UMMA issuer
+    if (lane == 0) {
+      constexpr uint32_t id64 = umma_idesc(128, 64, false, false, true);
+      constexpr uint32_t id64_bmn = umma_idesc(128, 64, false, true, true);
+      constexpr uint32_t id64_abmn = umma_idesc(128, 64, true, true, true);
+      constexpr uint32_t id128_bmn = umma_idesc(128, 128, false, true, true);
+      const uint32_t sds = smem_u32(s.dsbf), sdvp = smem_u32(s.dvp), sdvg = smem_u32(s.dvg), sdos = smem_u32(s.dos),
+                     spg = smem_u32(s.pg);
+      for (int it = 0; it < nchunks; ++it) {
+        const int st = it & 1;
+        const uint32_t ph = it & 1;
+        const uint32_t skq = smem_u32(s.kq[st]), sa = smem_u32(s.a[st]), sdo = smem_u32(s.dout[st]);
+        if (!mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(tm + kDhColPK, umma_desc_sw128(skq + dh_koff(kk), 16, 1024), umma_desc_sw128(skq + dh_koff(kk), 16, 1024),
+                  id64, kk > 0);
+        umma_commit(&s.pk_done);
+        if (!mbar_wait(wc, &s.pg_ready, ph, 3)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss(tm + kDhColD2, umma_desc_sw128(sdo + kk * 2048, 8192, 1024), umma_desc_sw128(spg + kk * 2048, 8192, 1024),
+                  id64_abmn, kk > 0);
+        umma_commit(&s.d2_done);
+        if (!mbar_wait(wc, &s.ds_ready, ph, 4)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(tm + kDhColD1, umma_desc_sw128(sds + dh_koff(kk), 16, 1024), umma_desc_sw128(skq + dh_koff(kk), 16, 1024),
+                  id64, kk > 0);
+        umma_commit(&s.d1_done);
+        if (!mbar_wait(wc, &s.dvp_ready, ph, 5)) break;
+        if (!mbar_wait(wc, &s.ag_ready, ph, 6)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss(tm + kDhColD1, umma_desc_sw128(sdvp + kk * 32, 16, 1024), umma_desc_sw128(sa + kk * 2048, 8192, 1024),
+                  id64_bmn, kk > 0);
+        umma_commit(&s.dw_done);
+        if (!mbar_wait(wc, &s.dvg_ready, ph, 7)) break;
+        if (!mbar_wait(wc, &s.dos_ready, ph, 8)) break;
+        if (!mbar_wait(wc, &s.ds_scaled, ph, 9)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss(tm + kDhColS, umma_desc_sw128(sdvg + kk * 32, 16, 1024), umma_desc_sw128(skq + kk * 2048, 16384, 1024),
+                  id128_bmn, 1);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss(tm + kDhColS, umma_desc_sw128(sdos + kk * 32, 16, 1024),
+                  umma_desc_sw128(skq + 8192 + kk * 2048, 16384, 1024), id128_bmn, 1);
+        umma_commit(&s.ds_done);
+        umma_commit(&s.empty[st]);
+      }
+    }
+  } else if (warp < 4) {
+    // ------------------------------------------------------------------ gate loader
+    const int t = tid - 64;
+    for (int it = 0; it < nchunks; ++it) {
+      const int n = nchunks - 1 - it, gs = it & (kDhGateStages - 1);
+      if (it >= kDhGateStages && !mbar_wait(wc, &s.gate_empty[gs], ((it >> 2) + 1) & 1, 10)) break;
+      const int len = min(kChunk, seq_len - n * kChunk);
+      const size_t row = static_cast<size_t>(tok_begin) + n * kChunk;
+      const float gl = __ldg(p.g_cum + (row + len - 1) * p.H + h);
+      float gi = gl, bi = 0.f;
+      if (t < len) {
+        gi = __ldg(p.g_cum + (row + t) * p.H + h);
+        bi = __ldg(p.beta + (row + t) * p.H + h);
+      }
+      s.gate[gs][0][t] = gi;
+      s.gate[gs][1][t] = fast_exp(gi);
+      s.gate[gs][2][t] = (t < len) ? fast_exp(gl - gi) : 0.f;
+      s.gate[gs][3][t] = bi;
+      mbar_arrive(&s.gate_full[gs]);
+    }
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ dV', dv, dVg (critical chain)
+    const int v = tid - 128;
+    const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32;
+    const size_t rs = static_cast<size_t>(p.H) * kDim;
+    for (int it = 0; it < nchunks; ++it) {
+      const int n = nchunks - 1 - it, gs = it & (kDhGateStages - 1);
+      const uint32_t ph = it & 1;
+      const int len = min(kChunk, seq_len - n * kChunk);
+      const size_t goff = (static_cast<size_t>(tok_begin) + n * kChunk) * rs + static_cast<size_t>(h) * kDim + v;
+      if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 11)) break;
+      if (!mbar_wait(wc, &s.d2_done, ph, 12)) break;
+      if (!mbar_wait(wc, &s.d1_done, ph, 13)) break;
+      tc_fence_after();
+      uint32_t packed[32];
+#pragma unroll
+      for (int qd = 0; qd < 4; ++qd) {
+        uint32_t d1[16], d2[16];
+        tmem_ld16(tmem_addr(tm, lane_base, kDhColD1 + qd * 16), d1);
+        tmem_ld16(tmem_addr(tm, lane_base, kDhColD2 + qd * 16), d2);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) {
+          const int c = qd * 16 + e;
+          const float x0 = s.gate[gs][2][c] * __uint_as_float(d1[e]) + __uint_as_float(d2[e]);
+          const float x1 = s.gate[gs][2][c + 1] * __uint_as_float(d1[e + 1]) + __uint_as_float(d2[e + 1]);
+          packed[c >> 1] = pack_bf16(x0, x1);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(s.dvp + sw128(v, j * 16)) = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+      tc_fence_before();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.dvp_ready);
+      store_cols_bf16(reinterpret_cast<unsigned short*>(p.dvp_out) + goff, rs, packed, len);
+      if (!mbar_wait(wc, &s.dw_done, ph, 14)) break;
+      tc_fence_after();
+      uint32_t pg2[32];
+#pragma unroll
+      for (int qd = 0; qd < 4; ++qd) {
+        uint32_t dw[16];
+        tmem_ld16(tmem_addr(tm, lane_base, kDhColD1 + qd * 16), dw);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) {
+          const int c = qd * 16 + e;
+          const float w0 = __uint_as_float(dw[e]), w1 = __uint_as_float(dw[e + 1]);
+          packed[c >> 1] = pack_bf16(w0, w1);
+          pg2[c >> 1] = pack_bf16(-s.gate[gs][1][c] * w0, -s.gate[gs][1][c + 1] * w1);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(s.dvg + sw128(v, j * 16)) = make_uint4(pg2[4 * j], pg2[4 * j + 1], pg2[4 * j + 2], pg2[4 * j + 3]);
+      tc_fence_before();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(&s.dvg_ready); mbar_arrive(&s.gate_empty[gs]); }
+      store_cols_bf16(reinterpret_cast<unsigned short*>(p.dv_out) + goff, rs, packed, len);
+    }
+  } else if (warp < 12) {
+    // ------------------------------------------------------------------ state gradient: TMEM <-> bf16 operand, decay, dh
+    const int v = tid - 256;
+    const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32;
+    {
+      const float* src = p.dht ? p.dht + (static_cast<size_t>(seq) * p.H + h) * kDim * kDim + v : nullptr;
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t r[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = src ? __float_as_uint(__ldg(src + static_cast<size_t>(cb * 32 + i) * kDim)) : 0u;
+        tmem_st32(tmem_addr(tm, lane_base, kDhColS + cb * 32), r);
+      }
+      tmem_wait_st();
+    }
+    bool alive = true;
+    for (int it = 0; it < nchunks && alive; ++it) {
+      const int n = nchunks - 1 - it, gs = it & (kDhGateStages - 1);
+      if (it > 0) {
+        if (!mbar_wait(wc, &s.ds_done, (it - 1) & 1, 15)) { alive = false; break; }
+        tc_fence_after();
+      }
+      if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 16)) { alive = false; break; }
+      const float gL = s.gate[gs][1][kChunk - 1];
+      __nv_bfloat16* hdst = p.dh_out + (static_cast<size_t>(chunk_off + n) * p.H + h) * kDim * kDim + v;
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tm, lane_base, kDhColS + cb * 32), r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 q4;
+          q4.x = pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+          q4.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+          q4.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+          q4.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+          *reinterpret_cast<uint4*>(s.dsbf + (cb >> 1) * 16384 + sw128(v, (cb & 1) * 64 + j * 16)) = q4;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) hdst[static_cast<size_t>(cb * 32 + i) * kDim] = __float2bfloat16(__uint_as_float(r[i]));
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * gL);
+        tmem_st32(tmem_addr(tm, lane_base, kDhColS + cb * 32), r);
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.ds_ready);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(&s.ds_scaled); mbar_arrive(&s.gate_empty[gs]); }
+    }
+    if (alive && nchunks > 0) {
+      alive = mbar_wait(wc, &s.ds_done, (nchunks - 1) & 1, 17);
+      tc_fence_after();
+    }
+    if (alive && p.dh0) {
+      float* dst = p.dh0 + (static_cast<size_t>(seq) * p.H + h) * kDim * kDim + v;
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tm, lane_base, kDhColS + cb * 32), r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) dst[static_cast<size_t>(cb * 32 + i) * kDim] = __uint_as_float(r[i]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ A_g, P_g, scaled dO^T
+    const int wid = warp - 12;
+    const int v = tid - 384;
+    const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32;
+    for (int it = 0; it < nchunks; ++it) {
+      const int n = nchunks - 1 - it, st = it & 1, gs = it & (kDhGateStages - 1);
+      const uint32_t ph = it & 1;
+      const int len = min(kChunk, seq_len - n * kChunk);
+      if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 18)) break;
+      if (!mbar_wait(wc, &s.full[st], (it >> 1) & 1, 19)) break;
+      if (wid < 2) {
+        const int i = wid * 32 + lane;
+        const float gi = s.gate[gs][0][i];
+#pragma unroll
+        for (int j8 = 0; j8 < 8; ++j8) {
+          uint4* ptr = reinterpret_cast<uint4*>(s.a[st] + sw128(i, j8 * 16));
+          uint4 a4 = *ptr;
+          uint32_t* aw = reinterpret_cast<uint32_t*>(&a4);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = j8 * 8 + 2 * e;
+            const float x0 = (j <= i) ? bf16_lo(aw[e]) * fast_exp(gi - s.gate[gs][0][j]) * s.gate[gs][3][j] : 0.f;
+            const float x1 = (j + 1 <= i) ? bf16_hi(aw[e]) * fast_exp(gi - s.gate[gs][0][j + 1]) * s.gate[gs][3][j + 1] : 0.f;
+            aw[e] = pack_bf16(x0, x1);
+          }
+          *ptr = a4;
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.ag_ready);
+      } else {
+        if (!mbar_wait(wc, &s.pk_done, ph, 20)) break;
+        tc_fence_after();
+        const int i = (wid - 2) * 32 + lane;
+        const float gi = s.gate[gs][0][i];
+        const bool row_ok = i < len;  // rows past the sequence end hold another sequence's tokens
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld32(tmem_addr(tm, lane_base, kDhColPK + half * 32), r);
+          tmem_wait_ld();
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const int j = half * 32 + e;
+            const float x0 = (row_ok && j <= i) ? p.scale * fast_exp(gi - s.gate[gs][0][j]) * __uint_as_float(r[e]) : 0.f;
+            const float x1 = (row_ok && j + 1 <= i) ? p.scale * fast_exp(gi - s.gate[gs][0][j + 1]) * __uint_as_float(r[e + 1]) : 0.f;
+            pk[e >> 1] = pack_bf16(x0, x1);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(s.pg + sw128(i, half * 64 + j * 16)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+        }
+        tc_fence_before();
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.pg_ready);
+      }
+      // (scale * gamma_c * dO[c][v])^T; the previous iteration's state update must have consumed the buffer
+      if (it > 0 && !mbar_wait(wc, &s.ds_done, (it - 1) & 1, 21)) break;
+      {
+        const unsigned char* dt = s.dout[st] + (v >> 6) * 8192;
+        const uint32_t vb = (v & 63) * 2;
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < kChunk; c += 2) {
+          const float x0 = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(dt + sw128(c, vb))) << 16);
+          const float x1 = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(dt + sw128(c + 1, vb))) << 16);
+          const float s0 = (c < len) ? p.scale * s.gate[gs][1][c] * x0 : 0.f;
+          const float s1 = (c + 1 < len) ? p.scale * s.gate[gs][1][c + 1] * x1 : 0.f;
+          pk[c >> 1] = pack_bf16(s0, s1);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(s.dos + sw128(v, j * 16)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(&s.dos_ready); mbar_arrive(&s.empty[st]); mbar_arrive(&s.gate_empty[gs]); }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tm, 512);
+}
+
+}  // namespace fq
+
+extern "C" FQ_API int fq_gdr_bwd_dh(const void* q, const void* k, const void* A, const void* dout, const float* g_cumsum,
+                                    const float* beta, const float* dht, float* dh0, void* dh_out, void* dvp_out,
+                                    void* dv_out, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
+                                    const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
+                                    int32_t* status_dev, void* stream) {
+  using namespace fq;
+  FQ_CHECK_ARG(q && k && A && dout && g_cumsum && beta && dh_out && dvp_out && dv_out, "fq_gdr_bwd_dh: null tensor");
+  FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0,
+               "fq_gdr_bwd_dh: bad sizes");
+  FQ_CHECK_ARG((cu_seqlens == nullptr) == (chunk_offsets == nullptr),
+               "fq_gdr_bwd_dh: cu_seqlens and chunk_offsets must be given together");
+  FQ_CHECK_ARG(cu_seqlens == nullptr || B == 1, "fq_gdr_bwd_dh: packed batches need B == 1");
+  FQ_CHECK_ARG(cu_seqlens != nullptr || n_seq == B, "fq_gdr_bwd_dh: dense batches need n_seq == B");
+  const uint64_t rows = static_cast<uint64_t>(B) * static_cast<uint64_t>(T);
+  FQ_CHECK_ARG(rows > 0 && rows < (1ull << 31), "fq_gdr_bwd_dh: token count out of range");
+  CUtensorMap mq, mk, mdo, ma;
+  int rc;
+  if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdo, dout, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&ma, A, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
+  BwdDhParams p;
+  p.g_cum = g_cumsum; p.beta = beta; p.dht = dht; p.dh0 = dh0;
+  p.dh_out = static_cast<__nv_bfloat16*>(dh_out);
+  p.dvp_out = static_cast<__nv_bfloat16*>(dvp_out);
+  p.dv_out = static_cast<__nv_bfloat16*>(dv_out);
+  p.H = H; p.Hg = Hg; p.scale = scale;
+  p.sa = SeqArgs{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
+  p.status_dev = status_dev;
+  const size_t smem = sizeof(BwdDhSmem) + 1024;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  FQ_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    FQ_CHECK_CUDA(cudaFuncSetAttribute(gdr_bwd_dh_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    attr_set[dev] = true;
+  }
+  const long long ctas = static_cast<long long>(n_seq) * H;
+  FQ_CHECK_ARG(ctas < (1ll << 31), "fq_gdr_bwd_dh: too many (sequence, head) pairs");
+  gdr_bwd_dh_kernel<<<static_cast<unsigned>(ctas), kDhThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mdo, ma, p);
+  FQ_CHECK_CUDA(cudaGetLastError());
+  return FQ_OK;
+}

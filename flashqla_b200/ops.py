@@ -40,3 +40,65 @@ def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None,
     if status is not None:
         kernels.check_status(status, "fq_gdr_fwd")
     return g_cum, A, o, h, final_state
+
+
+def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, initial_state=None, cu_seqlens=None):
+    """Backward pipeline (chunk/__init__.py:70-113).  ``g`` is the cumsum returned by the forward,
+    ``A`` the tensor returned by the forward.  Returns ``(dq, dk, dv, db, dg, dh0)``."""
+    from . import bwd  # the backward kernels live in their own module
+    return bwd.chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht, scale, initial_state, cu_seqlens)
+
+
+class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
+    """Autograd glue (chunk/__init__.py:116-180): saves (q, k, v, g_cumsum, beta, A, h0, cu_seqlens);
+    neither o nor the per-chunk states are kept."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
+    def forward(ctx, q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None):
+        g_cum, A, o, _, final_state = chunk_gated_delta_rule_fwd(
+            q=q, k=k, v=v, g=g, beta=beta, scale=scale, initial_state=initial_state,
+            output_final_state=output_final_state, output_h=False, cu_seqlens=cu_seqlens)
+        ctx.save_for_backward(q, k, v, g_cum, beta, A, initial_state, cu_seqlens)
+        ctx.scale = scale
+        ctx.g_dtype = g.dtype
+        ctx.beta_dtype = beta.dtype
+        return o.to(q.dtype), final_state
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, do, dht):
+        q, k, v, g_cum, beta, A, initial_state, cu_seqlens = ctx.saved_tensors
+        dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(
+            q=q, k=k, v=v, g=g_cum, beta=beta, A=A, do=do, dht=dht, scale=ctx.scale,
+            initial_state=initial_state, cu_seqlens=cu_seqlens)
+        return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dg.to(ctx.g_dtype), db.to(ctx.beta_dtype),
+                None, dh0, None, None)
+
+
+@torch.compiler.disable
+def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
+                           use_qk_l2norm_in_kernel=False, cu_seqlens=None, head_first=False):
+    """Public, differentiable entry (chunk/__init__.py:183-237).  Returns ``(o, final_state)``."""
+    assert q.dtype == k.dtype == v.dtype
+    assert q.dtype != torch.float32, (
+        "ChunkGatedDeltaRuleFunction does not support float32. Please use bfloat16 or float16.")
+    assert not head_first, "head_first=True is not supported."
+    assert v.shape[2] % k.shape[2] == 0, "num_qk_heads must be divisible to num_v_heads."
+    if q.dtype != torch.bfloat16:
+        raise _lib.FlashQLAError("the sm_100a kernels take bfloat16 q/k/v; float16 is not built")
+    if cu_seqlens is not None:
+        if q.shape[0] != 1:
+            raise ValueError(
+                f"The batch size is expected to be 1 rather than {q.shape[0]} when using `cu_seqlens`."
+                f"Please flatten variable-length inputs before processing.")
+        if initial_state is not None and initial_state.shape[0] != len(cu_seqlens) - 1:
+            raise ValueError(
+                f"The number of initial states is expected to be equal to the number of input sequences, "
+                f"i.e., {len(cu_seqlens) - 1} rather than {initial_state.shape[0]}.")
+    if scale is None:
+        scale = k.shape[-1] ** -0.5
+    if use_qk_l2norm_in_kernel:
+        q = l2norm(q)
+        k = l2norm(k)
+    return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens)
