@@ -1,0 +1,77 @@
+"""Backward orchestration (flash_qla/ops/gated_delta_rule/chunk/__init__.py:70-113 of the reference):
+state recompute -> reverse dS recurrence -> chunk-parallel gradients -> GVA head sum -> reverse cumsum."""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from . import _lib, kernels
+from .kernels import make_plan
+
+
+def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, initial_state=None, cu_seqlens=None):
+    kernels._require_cuda(q, k, v, g, beta, A, do)
+    if q.dtype != torch.bfloat16:
+        raise _lib.FlashQLAError("chunk_gated_delta_rule_bwd: only bfloat16 q/k/v are supported")
+    B, T, Hg, K = k.shape
+    H, V = v.shape[2], v.shape[3]
+    if scale is None:
+        scale = K ** -0.5
+    dev = q.device
+    plan = make_plan(B, T, cu_seqlens, dev)
+    check = os.environ.get("FLASHQLA_CHECK_STATUS", "0") == "1"
+    status = kernels._status_tensor(dev) if check else None
+    st_p = None if status is None else status.data_ptr()
+    q, k, v, A, do = q.contiguous(), k.contiguous(), v.contiguous(), A.contiguous(), do.contiguous()
+    if do.dtype != q.dtype:
+        do = do.to(q.dtype)
+    g = g.contiguous() if g.dtype == torch.float32 else g.float().contiguous()
+    bt = beta.contiguous() if beta.dtype == torch.float32 else beta.float().contiguous()
+    h0 = None
+    if initial_state is not None:
+        h0 = initial_state.contiguous() if initial_state.dtype == torch.float32 else initial_state.float().contiguous()
+    dht_c = None
+    if dht is not None:
+        dht_c = dht.contiguous() if dht.dtype == torch.float32 else dht.float().contiguous()
+
+    # 1. state before every chunk (bf16), recomputed with the forward recurrence kernel
+    _, h, _ = kernels.fused_gdr_fwd(q, k, v, A, g, bt, scale, initial_state=h0, output_final_state=False,
+                                    output_h=True, output_o=False, plan=plan, status=status)
+    # 2. reverse recurrence of the state gradient
+    dh = torch.empty_like(h)
+    dvp = torch.empty_like(v)
+    dv = torch.empty_like(v)
+    want_dh0 = (dht is not None) or (initial_state is not None)
+    dh0 = torch.empty(plan.n_seq, H, K, V, dtype=torch.float32, device=dev) if want_dh0 else None
+    cu_p, off_p = plan.ptrs()
+    lib = _lib.load()
+    rc = lib.fq_gdr_bwd_dh(q.data_ptr(), k.data_ptr(), A.data_ptr(), do.data_ptr(), g.data_ptr(), bt.data_ptr(),
+                           None if dht_c is None else dht_c.data_ptr(), None if dh0 is None else dh0.data_ptr(),
+                           dh.data_ptr(), dvp.data_ptr(), dv.data_ptr(), B, T, H, Hg, cu_p, off_p, plan.n_seq,
+                           plan.total_chunks, float(scale), st_p, kernels._stream())
+    _lib.check(rc, "fq_gdr_bwd_dh")
+    # 3. chunk-parallel gradients
+    dq_h = torch.empty(B, T, H, K, dtype=q.dtype, device=dev)
+    dk_h = torch.empty(B, T, H, K, dtype=q.dtype, device=dev)
+    dg_c = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+    db = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+    rc = lib.fq_gdr_bwd_chunk(q.data_ptr(), k.data_ptr(), v.data_ptr(), A.data_ptr(), do.data_ptr(), dvp.data_ptr(),
+                              dv.data_ptr(), h.data_ptr(), dh.data_ptr(), g.data_ptr(), bt.data_ptr(), dq_h.data_ptr(),
+                              dk_h.data_ptr(), dg_c.data_ptr(), db.data_ptr(), B, T, H, Hg, cu_p, off_p, plan.n_seq,
+                              plan.total_chunks, float(scale), st_p, kernels._stream())
+    _lib.check(rc, "fq_gdr_bwd_chunk")
+    # 4. sum the V-heads of every QK head
+    if Hg < H:
+        dq = torch.empty(B, T, Hg, K, dtype=q.dtype, device=dev)
+        dk = torch.empty(B, T, Hg, K, dtype=q.dtype, device=dev)
+        for src, dst in ((dq_h, dq), (dk_h, dk)):
+            rc = lib.fq_group_reduce(src.data_ptr(), dst.data_ptr(), B * T, H, Hg, kernels._stream())
+            _lib.check(rc, "fq_group_reduce")
+    else:
+        dq, dk = dq_h, dk_h
+    # 5. d/d(cumsum) -> d/d(raw gate)
+    dg = kernels.chunk_local_cumsum(dg_c, reverse=True, plan=plan)
+    if status is not None:
+        kernels.check_status(status, "backward kernels")
+    return dq, dk, dv, db, dg, dh0

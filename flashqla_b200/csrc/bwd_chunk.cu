@@ -1,0 +1,729 @@
+// Backward, chunk-parallel part: given the state before each chunk (h, from the forward
+// recurrence), the state gradient after each chunk (dh) and dV' / dv (from bwd_dh.cu), every
+// (chunk, V-head) unit is independent.  A persistent CTA walks units; per unit it runs six rounds
+// of tcgen05 MMAs (M = 64: row = token of the chunk) with CUDA-core epilogues in between:
+//
+//   round 1  U = K S0 | QK = Q K^T | accQ = dO S0^T | accK = dVg S0^T          (dVg = -gamma o dv)
+//            -> W = V - gamma o U, P_g, A_g, accQ *= scale*gamma, dg += rowsum(Q o accQ) + rowsum(K o accK)
+//   round 2  V' = A_g W
+//   round 3  K1 = V' dS^T | dPg = dO V'^T | dAg = dV' W^T
+//            -> accK += rho o K1, dg -= rowsum(K o rho K1); dP = scale G o dPg; dA = (G o dAg) beta_col;
+//               dg += rowsum - colsum of (dPg o P_g + dAb o A_b); dbeta += colsum(dAb o A)
+//   round 4  accQ += dP K | accK += dP^T Q | X1 = A^T dA          -> dq
+//   round 5  X2 = X1 A^T | KK = K K^T
+//            -> dL = -strict_lower(X2); dbeta += rowsum(dL o KK); dAs = beta_row dL + (beta_row dL)^T
+//   round 6  accK += dAs K                                        -> dk, dg, dbeta
+//
+// dg is the gradient w.r.t. the chunk-local cumsum of the gate; the caller applies the reverse
+// chunk cumsum.  dq / dk are written per V-head (bf16); the caller sums the heads of a QK group.
+#include "flashqla.h"
+#include "host.cuh"
+#include "seq.cuh"
+
+namespace fq {
+
+constexpr int kBcThreads = 256;
+constexpr uint32_t kBcLoadBytes = 6 * 16384 + 8192 + 2 * 32768;
+
+constexpr uint32_t kBcColU = 0;    // 128: U, then V', then K1, then X1 (0-63) / X2 (64-127)
+constexpr uint32_t kBcColQK = 128; // 64: QK^T, then dPg, then KK^T
+constexpr uint32_t kBcColX = 192;  // 64: dAg
+constexpr uint32_t kBcColQ = 256;  // 128: accQ
+constexpr uint32_t kBcColK = 384;  // 128: accK
+
+struct BwdChunkSmem {
+  unsigned char kt[16384];   // K  [64 c][128 k]  (two 64-row regions: k 0-63 | 64-127)
+  unsigned char qt[16384];   // Q
+  unsigned char wt[16384];   // V, rewritten as W
+  unsigned char dot[16384];  // dO
+  unsigned char dvp[16384];  // dV'
+  unsigned char dvg[16384];  // dv, rewritten as dVg
+  unsigned char vp[16384];   // V'
+  unsigned char s0[32768];   // S0 [128 k][128 v] (two 128-row regions: v 0-63 | 64-127)
+  unsigned char ds[32768];   // dS
+  unsigned char at[8192];    // A   [64 i][64 j]
+  unsigned char ag[8192];    // A_g -> dA -> dAs
+  unsigned char pg[8192];    // P_g -> dP -> X1
+  float g[kChunk], gam[kChunk], rho[kChunk], beta[kChunk];
+  float dg_s[kChunk], db_s[kChunk];
+  float dgl_s;
+  uint64_t bar_tma, bar_mma;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct BwdChunkParams {
+  const float* g_cum;
+  const float* beta;
+  __nv_bfloat16* dq;  // [rows, H, 128]
+  __nv_bfloat16* dk;  // [rows, H, 128]
+  float* dg;          // [rows, H]
+  float* db;          // [rows, H]
+  int H, Hg, total_chunks;
+  float scale;
+  SeqArgs sa;
+  int* status_dev;
+};
+
+__device__ __forceinline__ uint32_t off64(int kk) { return (kk >> 2) * 8192 + (kk & 3) * 32; }
+__device__ __forceinline__ uint32_t off128(int kk) { return (kk >> 2) * 16384 + (kk & 3) * 32; }
+
+// sum over the 16 lanes of a half warp (lanes 0-15 and 16-31 reduce separately)
+__device__ __forceinline__ float half_warp_sum(float x) {
+  x += __shfl_xor_sync(0xffffffffu, x, 8);
+  x += __shfl_xor_sync(0xffffffffu, x, 4);
+  x += __shfl_xor_sync(0xffffffffu, x, 2);
+  x += __shfl_xor_sync(0xffffffffu, x, 1);
+  return x;
+}
+
+__global__ void __launch_bounds__(kBcThreads, 1)
+gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                     const __grid_constant__ CUtensorMap map_dvp, const __grid_constant__ CUtensorMap map_dv,
+                     const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_h,
+                     const __grid_constant__ CUtensorMap map_dh, const BwdChunkParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  BwdChunkSmem& s = *reinterpret_cast<BwdChunkSmem*>(
+      reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int q4 = warp & 3, hf = warp >> 2;
+  const bool active = lane < 16;
+  const int row = active ? (16 * q4 + lane) : 0;
+  const uint32_t lane_base = static_cast<uint32_t>(q4) * 32;
+  WaitCtx wc{&s.abort_flag, p.status_dev, 3};
+
+  if (tid == 0) {
+    s.abort_flag = 0;
+    mbar_init(&s.bar_tma, 1);
+    mbar_init(&s.bar_mma, 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); tma_prefetch_desc(&map_do);
+    tma_prefetch_desc(&map_dvp); tma_prefetch_desc(&map_dv); tma_prefetch_desc(&map_a); tma_prefetch_desc(&map_h);
+    tma_prefetch_desc(&map_dh);
+  }
+  if (warp == 0) {
+    tmem_alloc(&s.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = s.tmem_base;
+  const uint32_t skt = smem_u32(s.kt), sqt = smem_u32(s.qt), swt = smem_u32(s.wt), sdot = smem_u32(s.dot),
+                 sdvp = smem_u32(s.dvp), sdvg = smem_u32(s.dvg), svp = smem_u32(s.vp), ss0 = smem_u32(s.s0),
+                 sds = smem_u32(s.ds), sat = smem_u32(s.at), sag = smem_u32(s.ag), spg = smem_u32(s.pg);
+  constexpr uint32_t id64_128_kk = umma_idesc(64, 128, false, false, true);
+  constexpr uint32_t id64_128_kmn = umma_idesc(64, 128, false, true, true);
+  constexpr uint32_t id64_128_mnmn = umma_idesc(64, 128, true, true, true);
+  constexpr uint32_t id64_64_kk = umma_idesc(64, 64, false, false, true);
+  constexpr uint32_t id64_64_mnmn = umma_idesc(64, 64, true, true, true);
+
+  uint32_t tma_phase = 0, mma_phase = 0;
+  const long long n_units = static_cast<long long>(p.total_chunks) * p.H;
+  bool alive = true;
+
+  for (long long unit = blockIdx.x; unit < n_units && alive; unit += gridDim.x) {
+    const int chunk = static_cast<int>(unit / p.H), h = static_cast<int>(unit - static_cast<long long>(chunk) * p.H);
+    const int hg = h / (p.H / p.Hg);
+    const ChunkPos cp = chunk_lookup(p.sa, chunk);
+    const int len = cp.len;
+    __syncthreads();  // the previous unit's shared-memory reads are complete
+
+    if (tid == 0) {
+      mbar_arrive_expect_tx(&s.bar_tma, kBcLoadBytes);
+      const int r0 = cp.tok0;
+      tma_load_3d(s.kt, &map_k, &s.bar_tma, 0, hg, r0);
+      tma_load_3d(s.kt + 8192, &map_k, &s.bar_tma, 64, hg, r0);
+      tma_load_3d(s.qt, &map_q, &s.bar_tma, 0, hg, r0);
+      tma_load_3d(s.qt + 8192, &map_q, &s.bar_tma, 64, hg, r0);
+      tma_load_3d(s.wt, &map_v, &s.bar_tma, 0, h, r0);
+      tma_load_3d(s.wt + 8192, &map_v, &s.bar_tma, 64, h, r0);
+      tma_load_3d(s.dot, &map_do, &s.bar_tma, 0, h, r0);
+      tma_load_3d(s.dot + 8192, &map_do, &s.bar_tma, 64, h, r0);
+      tma_load_3d(s.dvp, &map_dvp, &s.bar_tma, 0, h, r0);
+      tma_load_3d(s.dvp + 8192, &map_dvp, &s.bar_tma, 64, h, r0);
+      tma_load_3d(s.dvg, &map_dv, &s.bar_tma, 0, h, r0);
+      tma_load_3d(s.dvg + 8192, &map_dv, &s.bar_tma, 64, h, r0);
+      tma_load_3d(s.at, &map_a, &s.bar_tma, 0, h, r0);
+      const int hr = static_cast<int>((static_cast<long long>(chunk) * p.H + h) * kDim);
+      tma_load_3d(s.s0, &map_h, &s.bar_tma, 0, 0, hr);
+      tma_load_3d(s.s0 + 16384, &map_h, &s.bar_tma, 64, 0, hr);
+      tma_load_3d(s.ds, &map_dh, &s.bar_tma, 0, 0, hr);
+      tma_load_3d(s.ds + 16384, &map_dh, &s.bar_tma, 64, 0, hr);
+    }
+    if (tid < kChunk) {
+      const size_t base = static_cast<size_t>(cp.tok0) * p.H + h;
+      const float gl = __ldg(p.g_cum + base + static_cast<size_t>(len - 1) * p.H);
+      float gi = gl, bi = 0.f;
+      if (tid < len) {
+        gi = __ldg(p.g_cum + base + static_cast<size_t>(tid) * p.H);
+        bi = __ldg(p.beta + base + static_cast<size_t>(tid) * p.H);
+      }
+      s.g[tid] = gi;
+      s.gam[tid] = fast_exp(gi);
+      s.rho[tid] = (tid < len) ? fast_exp(gl - gi) : 0.f;
+      s.beta[tid] = bi;
+      s.dg_s[tid] = 0.f;
+      s.db_s[tid] = 0.f;
+      if (tid == 0) s.dgl_s = 0.f;
+    }
+    __syncthreads();
+    if (!mbar_wait(wc, &s.bar_tma, tma_phase, 1)) { alive = false; break; }
+    tma_phase ^= 1;
+
+    // ---- pre-pass on shared memory: zero the rows past the sequence end, dVg = -gamma o dv,
+    //      and the scalar gamma_last * sum(dS o S0)
+    if (len < kChunk) {
+      unsigned char* tiles[6] = {s.kt, s.qt, s.wt, s.dot, s.dvp, s.dvg};
+      const int nrows = kChunk - len;
+      for (int idx = tid; idx < nrows * 16; idx += kBcThreads) {
+        const int r = len + (idx >> 4), pc = idx & 15;
+        const uint32_t off = (pc >> 3) * 8192 + r * 128 + (pc & 7) * 16;
+#pragma unroll
+        for (int t6 = 0; t6 < 6; ++t6) *reinterpret_cast<uint4*>(tiles[t6] + off) = make_uint4(0, 0, 0, 0);
+        if (pc < 8) *reinterpret_cast<uint4*>(s.at + r * 128 + pc * 16) = make_uint4(0, 0, 0, 0);
+      }
+      __syncthreads();
+    }
+    {
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const uint32_t off = (it * kBcThreads + tid) * 16;
+        const int r = (off & 8191) >> 7;
+        const float f = -s.gam[r];
+        uint4* ptr = reinterpret_cast<uint4*>(s.dvg + off);
+        uint4 x = *ptr;
+        uint32_t* xw = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) xw[e] = pack_bf16(f * bf16_lo(xw[e]), f * bf16_hi(xw[e]));
+        *ptr = x;
+      }
+      float acc = 0.f;
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const uint32_t off = (it * kBcThreads + tid) * 16;
+        const uint4 a = *reinterpret_cast<const uint4*>(s.s0 + off);
+        const uint4 b = *reinterpret_cast<const uint4*>(s.ds + off);
+        const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
+        const uint32_t* bw = reinterpret_cast<const uint32_t*>(&b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc += bf16_lo(aw[e]) * bf16_lo(bw[e]) + bf16_hi(aw[e]) * bf16_hi(bw[e]);
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+      acc = half_warp_sum(acc);
+      if (lane == 0) atomicAdd(&s.dgl_s, acc * s.gam[kChunk - 1]);
+    }
+    fence_async_smem();
+    __syncthreads();
+
+    const float g_r = s.g[row], gam_r = s.gam[row], rho_r = s.rho[row], beta_r = s.beta[row];
+
+    // ================================================================== round 1
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)
+        umma_ss(tm + kBcColU, umma_desc_sw128(skt + off64(kk), 16, 1024), umma_desc_sw128(ss0 + kk * 2048, 16384, 1024),
+                id64_128_kmn, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)
+        umma_ss(tm + kBcColQK, umma_desc_sw128(sqt + off64(kk), 16, 1024), umma_desc_sw128(skt + off64(kk), 16, 1024),
+                id64_64_kk, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)
+        umma_ss(tm + kBcColQ, umma_desc_sw128(sdot + off64(kk), 16, 1024), umma_desc_sw128(ss0 + off128(kk), 16, 1024),
+                id64_128_kk, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)
+        umma_ss(tm + kBcColK, umma_desc_sw128(sdvg + off64(kk), 16, 1024), umma_desc_sw128(ss0 + off128(kk), 16, 1024),
+                id64_128_kk, kk > 0);
+      umma_commit(&s.bar_mma);
+    }
+    __syncwarp();
+    if (!mbar_wait(wc, &s.bar_mma, mma_phase, 2)) { alive = false; break; }
+    mma_phase ^= 1;
+    tc_fence_after();
+    {
+      // W = V - gamma o U (in place over V)
+#pragma unroll
+      for (int pc = 0; pc < 2; ++pc) {
+        uint32_t u[32];
+        tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 64 * hf + 32 * pc), u);
+        tmem_wait_ld();
+        if (active) {
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint4* ptr = reinterpret_cast<uint4*>(s.wt + hf * 8192 + sw128(row, (4 * pc + ch) * 16));
+            uint4 x = *ptr;
+            uint32_t* xw = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              xw[e] = pack_bf16(bf16_lo(xw[e]) - gam_r * __uint_as_float(u[8 * ch + 2 * e]),
+                                bf16_hi(xw[e]) - gam_r * __uint_as_float(u[8 * ch + 2 * e + 1]));
+            *ptr = x;
+          }
+        }
+      }
+      // P_g and A_g
+      {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tm, lane_base, kBcColQK + 32 * hf), r);
+        tmem_wait_ld();
+        if (active) {
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            const uint32_t so = sw128(row, (4 * hf + ch) * 16);
+            const uint4 av = *reinterpret_cast<const uint4*>(s.at + so);
+            const uint32_t* aw = reinterpret_cast<const uint32_t*>(&av);
+            uint4 pv, gv;
+            uint32_t* pw = reinterpret_cast<uint32_t*>(&pv);
+            uint32_t* gw = reinterpret_cast<uint32_t*>(&gv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int j = 32 * hf + 8 * ch + 2 * e;
+              const float G0 = (j <= row) ? fast_exp(g_r - s.g[j]) : 0.f;
+              const float G1 = (j + 1 <= row) ? fast_exp(g_r - s.g[j + 1]) : 0.f;
+              pw[e] = pack_bf16(p.scale * G0 * __uint_as_float(r[8 * ch + 2 * e]),
+                                p.scale * G1 * __uint_as_float(r[8 * ch + 2 * e + 1]));
+              gw[e] = pack_bf16(bf16_lo(aw[e]) * G0 * s.beta[j], bf16_hi(aw[e]) * G1 * s.beta[j + 1]);
+            }
+            *reinterpret_cast<uint4*>(s.pg + so) = pv;
+            *reinterpret_cast<uint4*>(s.ag + so) = gv;
+          }
+        }
+      }
+      // accQ *= scale * gamma (written back); dg += rowsum(Q o accQ) + rowsum(K o accK)
+      float part = 0.f;
+#pragma unroll
+      for (int pc = 0; pc < 2; ++pc) {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tm, lane_base, kBcColQ + 64 * hf + 32 * pc), r);
+        tmem_wait_ld();
+        const float f = p.scale * gam_r;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const uint4 qv = *reinterpret_cast<const uint4*>(s.qt + hf * 8192 + sw128(row, (4 * pc + ch) * 16));
+          const uint32_t* qw = reinterpret_cast<const uint32_t*>(&qv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float x0 = f * __uint_as_float(r[8 * ch + 2 * e]), x1 = f * __uint_as_float(r[8 * ch + 2 * e + 1]);
+            part += bf16_lo(qw[e]) * x0 + bf16_hi(qw[e]) * x1;
+            r[8 * ch + 2 * e] = __float_as_uint(x0);
+            r[8 * ch + 2 * e + 1] = __float_as_uint(x1);
+          }
+        }
+        tmem_st32(tmem_addr(tm, lane_base, kBcColQ + 64 * hf + 32 * pc), r);
+      }
+#pragma unroll
+      for (int pc = 0; pc < 2; ++pc) {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tm, lane_base, kBcColK + 64 * hf + 32 * pc), r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const uint4 kv = *reinterpret_cast<const uint4*>(s.kt + hf * 8192 + sw128(row, (4 * pc + ch) * 16));
+          const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            part += bf16_lo(kw[e]) * __uint_as_float(r[8 * ch + 2 * e]) + bf16_hi(kw[e]) * __uint_as_float(r[8 * ch + 2 * e + 1]);
+        }
+      }
+      if (active) atomicAdd(&s.dg_s[row], part);
+      tmem_wait_st();
+    }
+    tc_fence_before();
+    fence_async_smem();
+    __syncthreads();
+
+    // ================================================================== round 2: V' = A_g W
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        umma_ss(tm + kBcColU, umma_desc_sw128(sag + kk * 32, 16, 1024), umma_desc_sw128(swt + kk * 2048, 8192, 1024),
+                id64_128_kmn, kk > 0);
+      umma_commit(&s.bar_mma);
+    }
+    __syncwarp();
+    if (!mbar_wait(wc, &s.bar_mma, mma_phase, 3)) { alive = false; break; }
+    mma_phase ^= 1;
+    tc_fence_after();
+#pragma unroll
+    for (int pc = 0; pc < 2; ++pc) {
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 64 * hf + 32 * pc), r);
+      tmem_wait_ld();
+      if (active) {
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint4 x;
+          x.x = pack_bf16(__uint_as_float(r[8 * ch]), __uint_as_float(r[8 * ch + 1]));
+          x.y = pack_bf16(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
+          x.z = pack_bf16(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
+          x.w = pack_bf16(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
+          *reinterpret_cast<uint4*>(s.vp + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = x;
+        }
+      }
+    }
+    tc_fence_before();
+    fence_async_smem();
+    __syncthreads();
+
+    // ================================================================== round 3
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)
+        umma_ss(tm + kBcColU, umma_desc_sw128(svp + off64(kk), 16, 1024), umma_desc_sw128(sds + off128(kk), 16, 1024),
+                id64_128_kk, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)
+        umma_ss(tm + kBcColQK, umma_desc_sw128(sdot + off64(kk), 16, 1024), umma_desc_sw128(svp + off64(kk), 16, 1024),
+                id64_64_kk, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)
+        umma_ss(tm + kBcColX, umma_desc_sw128(sdvp + off64(kk), 16, 1024), umma_desc_sw128(swt + off64(kk), 16, 1024),
+                id64_64_kk, kk > 0);
+      umma_commit(&s.bar_mma);
+    }
+    __syncwarp();
+    if (!mbar_wait(wc, &s.bar_mma, mma_phase, 4)) { alive = false; break; }
+    mma_phase ^= 1;
+    tc_fence_after();
+    {
+      // accK += rho o K1 ; kk = rowsum(K o rho K1)
+      float kkp = 0.f;
+#pragma unroll
+      for (int pc = 0; pc < 2; ++pc) {
+        uint32_t r[32], a2[32];
+        tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 64 * hf + 32 * pc), r);
+        tmem_ld32(tmem_addr(tm, lane_base, kBcColK + 64 * hf + 32 * pc), a2);
+        tmem_wait_ld();
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const uint4 kv = *reinterpret_cast<const uint4*>(s.kt + hf * 8192 + sw128(row, (4 * pc + ch) * 16));
+          const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float x0 = rho_r * __uint_as_float(r[8 * ch + 2 * e]), x1 = rho_r * __uint_as_float(r[8 * ch + 2 * e + 1]);
+            kkp += bf16_lo(kw[e]) * x0 + bf16_hi(kw[e]) * x1;
+            a2[8 * ch + 2 * e] = __float_as_uint(__uint_as_float(a2[8 * ch + 2 * e]) + x0);
+            a2[8 * ch + 2 * e + 1] = __float_as_uint(__uint_as_float(a2[8 * ch + 2 * e + 1]) + x1);
+          }
+        }
+        tmem_st32(tmem_addr(tm, lane_base, kBcColK + 64 * hf + 32 * pc), a2);
+      }
+      if (!active) kkp = 0.f;
+      if (active) atomicAdd(&s.dg_s[row], -kkp);
+      const float kks = half_warp_sum(kkp);
+      if (lane == 0) atomicAdd(&s.dgl_s, kks);
+      // dPg and dAg: dP, dA tiles; row sums and column sums for dg, column sums for dbeta
+      uint32_t r1[32], r2[32];
+      tmem_ld32(tmem_addr(tm, lane_base, kBcColQK + 32 * hf), r1);
+      tmem_ld32(tmem_addr(tm, lane_base, kBcColX + 32 * hf), r2);
+      tmem_wait_ld();
+      float rows = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        const uint32_t so = sw128(row, (4 * hf + ch) * 16);
+        const uint4 pgv = *reinterpret_cast<const uint4*>(s.pg + so);
+        const uint4 av = *reinterpret_cast<const uint4*>(s.at + so);
+        const uint32_t* pw = reinterpret_cast<const uint32_t*>(&pgv);
+        const uint32_t* aw = reinterpret_cast<const uint32_t*>(&av);
+        uint4 dpv, dav;
+        uint32_t* dpw = reinterpret_cast<uint32_t*>(&dpv);
+        uint32_t* daw = reinterpret_cast<uint32_t*>(&dav);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float dpo[2], dao[2];
+#pragma unroll
+          for (int z = 0; z < 2; ++z) {
+            const int j = 32 * hf + 8 * ch + 2 * e + z;
+            const bool keep = active && (j <= row);
+            const float G = keep ? fast_exp(g_r - s.g[j]) : 0.f;
+            const float pgx = z ? bf16_hi(pw[e]) : bf16_lo(pw[e]);
+            const float ax = z ? bf16_hi(aw[e]) : bf16_lo(aw[e]);
+            const float dpg = __uint_as_float(r1[8 * ch + 2 * e + z]);
+            const float dab = G * __uint_as_float(r2[8 * ch + 2 * e + z]);
+            const float bj = s.beta[j];
+            const float t12 = keep ? (dpg * pgx + dab * ax * bj) : 0.f;
+            rows += t12;
+            const float cs = half_warp_sum(t12);
+            const float cb = half_warp_sum(dab * ax);
+            if (lane == 0) {
+              atomicAdd(&s.dg_s[j], -cs);
+              atomicAdd(&s.db_s[j], cb);
+            }
+            dpo[z] = p.scale * G * dpg;
+            dao[z] = dab * bj;
+          }
+          dpw[e] = pack_bf16(dpo[0], dpo[1]);
+          daw[e] = pack_bf16(dao[0], dao[1]);
+        }
+        if (active) {
+          *reinterpret_cast<uint4*>(s.pg + so) = dpv;
+          *reinterpret_cast<uint4*>(s.ag + so) = dav;
+        }
+      }
+      if (active) atomicAdd(&s.dg_s[row], rows);
+      tmem_wait_st();
+    }
+    tc_fence_before();
+    fence_async_smem();
+    __syncthreads();
+
+    // ================================================================== round 4
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        umma_ss(tm + kBcColQ, umma_desc_sw128(spg + kk * 32, 16, 1024), umma_desc_sw128(skt + kk * 2048, 8192, 1024),
+                id64_128_kmn, 1);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        umma_ss(tm + kBcColK, umma_desc_sw128(spg + kk * 2048, 8192, 1024), umma_desc_sw128(sqt + kk * 2048, 8192, 1024),
+                id64_128_mnmn, 1);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        umma_ss(tm + kBcColU, umma_desc_sw128(sat + kk * 2048, 8192, 1024), umma_desc_sw128(sag + kk * 2048, 8192, 1024),
+                id64_64_mnmn, kk > 0);
+      umma_commit(&s.bar_mma);
+    }
+    __syncwarp();
+    if (!mbar_wait(wc, &s.bar_mma, mma_phase, 5)) { alive = false; break; }
+    mma_phase ^= 1;
+    tc_fence_after();
+    {
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 32 * hf), r);
+      tmem_wait_ld();
+      if (active) {
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint4 x;
+          x.x = pack_bf16(__uint_as_float(r[8 * ch]), __uint_as_float(r[8 * ch + 1]));
+          x.y = pack_bf16(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
+          x.z = pack_bf16(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
+          x.w = pack_bf16(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
+          *reinterpret_cast<uint4*>(s.pg + sw128(row, (4 * hf + ch) * 16)) = x;
+        }
+      }
+      // dq
+      __nv_bfloat16* dst = p.dq + (static_cast<size_t>(cp.tok0 + row) * p.H + h) * kDim + 64 * hf;
+#pragma unroll
+      for (int pc = 0; pc < 2; ++pc) {
+        tmem_ld32(tmem_addr(tm, lane_base, kBcColQ + 64 * hf + 32 * pc), r);
+        tmem_wait_ld();
+        if (active && row < len) {
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint4 x;
+            x.x = pack_bf16(__uint_as_float(r[8 * ch]), __uint_as_float(r[8 * ch + 1]));
+            x.y = pack_bf16(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
+            x.z = pack_bf16(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
+            x.w = pack_bf16(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
+            *reinterpret_cast<uint4*>(dst + 32 * pc + 8 * ch) = x;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+    fence_async_smem();
+    __syncthreads();
+
+    // ================================================================== round 5
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        umma_ss(tm + kBcColU + 64, umma_desc_sw128(spg + kk * 32, 16, 1024), umma_desc_sw128(sat + kk * 32, 16, 1024),
+                id64_64_kk, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)
+        umma_ss(tm + kBcColQK, umma_desc_sw128(skt + off64(kk), 16, 1024), umma_desc_sw128(skt + off64(kk), 16, 1024),
+                id64_64_kk, kk > 0);
+      umma_commit(&s.bar_mma);
+    }
+    __syncwarp();
+    if (!mbar_wait(wc, &s.bar_mma, mma_phase, 6)) { alive = false; break; }
+    mma_phase ^= 1;
+    tc_fence_after();
+    {
+      uint32_t x2[32], kk2[32];
+      tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 64 + 32 * hf), x2);
+      tmem_ld32(tmem_addr(tm, lane_base, kBcColQK + 32 * hf), kk2);
+      tmem_wait_ld();
+      if (active) {
+        float dbr = 0.f;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int j = 32 * hf + e;
+          if (j < row) {
+            const float dL = -__uint_as_float(x2[e]);
+            dbr += dL * __uint_as_float(kk2[e]);
+            const unsigned short bits = __bfloat16_as_ushort(__float2bfloat16(beta_r * dL));
+            *reinterpret_cast<unsigned short*>(s.ag + sw128(row, j * 2)) = bits;
+            *reinterpret_cast<unsigned short*>(s.ag + sw128(j, row * 2)) = bits;
+          } else if (j == row) {
+            *reinterpret_cast<unsigned short*>(s.ag + sw128(row, j * 2)) = 0;
+          }
+        }
+        atomicAdd(&s.db_s[row], dbr);
+      }
+    }
+    tc_fence_before();
+    fence_async_smem();
+    __syncthreads();
+
+    // ================================================================== round 6
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        umma_ss(tm + kBcColK, umma_desc_sw128(sag + kk * 32, 16, 1024), umma_desc_sw128(skt + kk * 2048, 8192, 1024),
+                id64_128_kmn, 1);
+      umma_commit(&s.bar_mma);
+    }
+    __syncwarp();
+    if (!mbar_wait(wc, &s.bar_mma, mma_phase, 7)) { alive = false; break; }
+    mma_phase ^= 1;
+    tc_fence_after();
+    {
+      __nv_bfloat16* dst = p.dk + (static_cast<size_t>(cp.tok0 + row) * p.H + h) * kDim + 64 * hf;
+#pragma unroll
+      for (int pc = 0; pc < 2; ++pc) {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tm, lane_base, kBcColK + 64 * hf + 32 * pc), r);
+        tmem_wait_ld();
+        if (active && row < len) {
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint4 x;
+            x.x = pack_bf16(__uint_as_float(r[8 * ch]), __uint_as_float(r[8 * ch + 1]));
+            x.y = pack_bf16(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
+            x.z = pack_bf16(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
+            x.w = pack_bf16(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
+            *reinterpret_cast<uint4*>(dst + 32 * pc + 8 * ch) = x;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (tid < kChunk) {
+      // the padded rows of a tail chunk share the gate of the last valid token
+      float dgv = s.dg_s[tid];
+      if (tid == len - 1) {
+        for (int t2 = len; t2 < kChunk; ++t2) dgv += s.dg_s[t2];
+        dgv += s.dgl_s;
+      }
+      if (tid < len) {
+        const size_t o = static_cast<size_t>(cp.tok0 + tid) * p.H + h;
+        p.dg[o] = dgv;
+        p.db[o] = s.db_s[tid];
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, 512);
+}
+
+// Sum of the G V-heads of every QK head: in [rows, H, 128] bf16 -> out [rows, Hg, 128] bf16 (fp32 accumulate).
+__global__ void __launch_bounds__(256) group_reduce_kernel(const __nv_bfloat16* __restrict__ in,
+                                                          __nv_bfloat16* __restrict__ out, long long rows, int H, int Hg) {
+  const int G = H / Hg;
+  const long long total = rows * Hg * (kDim / 8);
+  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int piece = static_cast<int>(idx % (kDim / 8));
+    const long long rh = idx / (kDim / 8);
+    const int hg = static_cast<int>(rh % Hg);
+    const long long r = rh / Hg;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int i = 0; i < G; ++i) {
+      const uint4 x = __ldg(reinterpret_cast<const uint4*>(in + ((r * H + hg * G + i) * kDim)) + piece);
+      const uint32_t* xw = reinterpret_cast<const uint32_t*>(&x);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        acc[2 * e] += bf16_lo(xw[e]);
+        acc[2 * e + 1] += bf16_hi(xw[e]);
+      }
+    }
+    uint4 y;
+    y.x = pack_bf16(acc[0], acc[1]);
+    y.y = pack_bf16(acc[2], acc[3]);
+    y.z = pack_bf16(acc[4], acc[5]);
+    y.w = pack_bf16(acc[6], acc[7]);
+    *(reinterpret_cast<uint4*>(out + (r * Hg + hg) * kDim) + piece) = y;
+  }
+}
+
+}  // namespace fq
+
+extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void* v, const void* A, const void* dout,
+                                       const void* dvp, const void* dv, const void* h, const void* dh,
+                                       const float* g_cumsum, const float* beta, void* dq, void* dk, float* dg, float* db,
+                                       int B, int T, int H, int Hg, const int32_t* cu_seqlens,
+                                       const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
+                                       int32_t* status_dev, void* stream) {
+  using namespace fq;
+  FQ_CHECK_ARG(q && k && v && A && dout && dvp && dv && h && dh && g_cumsum && beta && dq && dk && dg && db,
+               "fq_gdr_bwd_chunk: null tensor");
+  FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0,
+               "fq_gdr_bwd_chunk: bad sizes");
+  FQ_CHECK_ARG((cu_seqlens == nullptr) == (chunk_offsets == nullptr),
+               "fq_gdr_bwd_chunk: cu_seqlens and chunk_offsets must be given together");
+  FQ_CHECK_ARG(cu_seqlens == nullptr || B == 1, "fq_gdr_bwd_chunk: packed batches need B == 1");
+  FQ_CHECK_ARG(cu_seqlens != nullptr || n_seq == B, "fq_gdr_bwd_chunk: dense batches need n_seq == B");
+  if (total_chunks == 0) return FQ_OK;
+  const uint64_t rows = static_cast<uint64_t>(B) * static_cast<uint64_t>(T);
+  const uint64_t hrows = static_cast<uint64_t>(total_chunks) * H * kDim;
+  FQ_CHECK_ARG(rows > 0 && rows < (1ull << 31) && hrows < (1ull << 31), "fq_gdr_bwd_chunk: sizes out of range");
+  CUtensorMap mq, mk, mv, mdo, mdvp, mdv, ma, mh, mdh;
+  int rc;
+  if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mv, v, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdo, dout, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdvp, dvp, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdv, dv, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&ma, A, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mh, h, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdh, dh, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
+  BwdChunkParams p;
+  p.g_cum = g_cumsum; p.beta = beta;
+  p.dq = static_cast<__nv_bfloat16*>(dq); p.dk = static_cast<__nv_bfloat16*>(dk); p.dg = dg; p.db = db;
+  p.H = H; p.Hg = Hg; p.total_chunks = total_chunks; p.scale = scale;
+  p.sa = SeqArgs{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
+  p.status_dev = status_dev;
+  const size_t smem = sizeof(BwdChunkSmem) + 1024;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  FQ_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    FQ_CHECK_CUDA(cudaFuncSetAttribute(gdr_bwd_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    attr_set[dev] = true;
+  }
+  const long long units = static_cast<long long>(total_chunks) * H;
+  const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
+  gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mdo, mdvp, mdv, ma, mh,
+                                                                                      mdh, p);
+  FQ_CHECK_CUDA(cudaGetLastError());
+  return FQ_OK;
+}
+
+extern "C" FQ_API int fq_group_reduce(const void* in, void* out, long long rows, int H, int Hg, void* stream) {
+  using namespace fq;
+  FQ_CHECK_ARG(in && out && rows >= 0 && H > 0 && Hg > 0 && H % Hg == 0, "fq_group_reduce: bad arguments");
+  if (rows == 0) return FQ_OK;
+  const long long total = rows * Hg * (kDim / 8);
+  const long long blocks = (total + 255) / 256;
+  const int grid = static_cast<int>(blocks < 148LL * 16 ? blocks : 148LL * 16);
+  group_reduce_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(in),
+                                                                          static_cast<__nv_bfloat16*>(out), rows, H, Hg);
+  FQ_CHECK_CUDA(cudaGetLastError());
+  return FQ_OK;
+}

@@ -39,7 +39,8 @@ struct BwdDhSmem {
   float gate[kDhGateStages][4][kChunk];
   uint64_t full[2], empty[2], gate_full[kDhGateStages], gate_empty[kDhGateStages];
   uint64_t pk_done, d2_done, d1_done, dw_done, ds_done;
-  uint64_t ds_ready, ds_scaled, dvp_ready, dvg_ready, ag_ready, pg_ready, dos_ready;
+  uint64_t ds_ready, ds_scaled, dvp_ready, dvg_ready, pg_ready, dos_ready;
+  uint64_t ag_ready[2];  // per stage: the A_g warps may run one iteration ahead of the UMMA issuer
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -92,7 +93,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     chunk_off = __ldg(p.sa.chunk_offsets + seq);
   }
   const int nchunks = (seq_len + kChunk - 1) / kChunk;
-  WaitCtx wc{&s.abort_flag, p.status_dev};
+  WaitCtx wc{&s.abort_flag, p.status_dev, 2};
 
   if (tid == 0) {
     s.abort_flag = 0;
@@ -101,7 +102,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     mbar_init(&s.pk_done, 1); mbar_init(&s.d2_done, 1); mbar_init(&s.d1_done, 1); mbar_init(&s.dw_done, 1);
     mbar_init(&s.ds_done, 1);
     mbar_init(&s.ds_ready, 4); mbar_init(&s.ds_scaled, 4); mbar_init(&s.dvp_ready, 4); mbar_init(&s.dvg_ready, 4);
-    mbar_init(&s.dos_ready, 4); mbar_init(&s.ag_ready, 2); mbar_init(&s.pg_ready, 2);
+    mbar_init(&s.dos_ready, 4); mbar_init(&s.ag_ready[0], 2); mbar_init(&s.ag_ready[1], 2); mbar_init(&s.pg_ready, 2);
     fence_mbar_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_a);
   }
@@ -166,7 +167,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                   id64, kk > 0);
         umma_commit(&s.d1_done);
         if (!mbar_wait(wc, &s.dvp_ready, ph, 5)) break;
-        if (!mbar_wait(wc, &s.ag_ready, ph, 6)) break;
+        if (!mbar_wait(wc, &s.ag_ready[st], (it >> 1) & 1, 6)) break;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
@@ -369,7 +370,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
         fence_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&s.ag_ready);
+        if (lane == 0) mbar_arrive(&s.ag_ready[st]);
       } else {
         if (!mbar_wait(wc, &s.pk_done, ph, 20)) break;
         tc_fence_after();

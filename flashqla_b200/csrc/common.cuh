@@ -53,6 +53,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 struct WaitCtx {
   volatile int* abort_flag;  // shared memory
   int* status_dev;           // global memory, may be nullptr
+  int kernel_id;             // reported in bits 12.. of the status code
 };
 
 __device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint64_t* bar, uint32_t parity, int where) {
@@ -63,7 +64,7 @@ __device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint64_t* bar, uint3
     if (*w.abort_flag) return false;
     if (clock64() - t0 > kWaitLimitCycles) {
       *w.abort_flag = 1;
-      if (w.status_dev) atomicCAS(w.status_dev, 0, 0x1000 + where);
+      if (w.status_dev) atomicCAS(w.status_dev, 0, (w.kernel_id << 12) + where);
       return false;
     }
   }

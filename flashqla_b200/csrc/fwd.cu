@@ -80,7 +80,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     chunk_off = __ldg(p.sa.chunk_offsets + seq);
   }
   const int nchunks = (seq_len + kChunk - 1) / kChunk;
-  WaitCtx wc{&s.abort_flag, p.status_dev};
+  WaitCtx wc{&s.abort_flag, p.status_dev, 1};
 
   if (tid == 0) {
     s.abort_flag = 0;

@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
   SelfTestSmem& s = *reinterpret_cast<SelfTestSmem*>(
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  WaitCtx wc{&s.abort_flag, status_dev};
+  WaitCtx wc{&s.abort_flag, status_dev, 15};
   constexpr uint32_t kCols = 256;
 
   if (tid == 0) {

@@ -84,6 +84,37 @@ FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, const void* A
                       int total_chunks, float scale, int32_t* status_dev, void* stream);
 
 /*
+ * Backward, serial part: reverse recurrence of the state gradient per (sequence, V-head).
+ * Together with fq_gdr_bwd_chunk it replaces fused_gdr_bwd,
+ * flash_qla/ops/gated_delta_rule/chunk/hopper/fused_bwd.py:900-985.
+ *   dout [B,T,H,128] bf16 (gradient of o); dht [n_seq,H,128,128] fp32 or NULL (gradient of the final state);
+ *   dh0  [n_seq,H,128,128] fp32 or NULL (gradient of the initial state);
+ *   dh_out [total_chunks,H,128,128] bf16: gradient w.r.t. the state AFTER each chunk (scratch for
+ *   fq_gdr_bwd_chunk); dvp_out [B,T,H,128] bf16 scratch (dV'); dv_out [B,T,H,128] bf16 = gradient of v.
+ */
+FQ_API int fq_gdr_bwd_dh(const void* q, const void* k, const void* A, const void* dout, const float* g_cumsum,
+                         const float* beta, const float* dht, float* dh0, void* dh_out, void* dvp_out, void* dv_out,
+                         int B, int T, int H, int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets,
+                         int n_seq, int total_chunks, float scale, int32_t* status_dev, void* stream);
+
+/*
+ * Backward, chunk-parallel part: dq, dk (per V-head, bf16 [B,T,H,128]), dg w.r.t. the gate cumsum
+ * and dbeta (fp32 [B,T,H]) from h (state before each chunk, from fq_gdr_fwd with h_out), dh, dvp and dv
+ * (from fq_gdr_bwd_dh).  Second half of the replacement of hopper/fused_bwd.py:900-985.
+ */
+FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void* v, const void* A, const void* dout,
+                            const void* dvp, const void* dv, const void* h, const void* dh, const float* g_cumsum,
+                            const float* beta, void* dq, void* dk, float* dg, float* db, int B, int T, int H, int Hg,
+                            const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq, int total_chunks,
+                            float scale, int32_t* status_dev, void* stream);
+
+/*
+ * out[r, hg, :] = sum of in[r, hg*G .. hg*G+G-1, :] (G = H / Hg), bf16 in/out, fp32 accumulation.
+ * Replaces group_reduce_vector, flash_qla/ops/utils/group_reduce.py:60-79.
+ */
+FQ_API int fq_group_reduce(const void* in, void* out, long long rows, int H, int Hg, void* stream);
+
+/*
  * Self-test of the tensor-core plumbing (TMA 128B-swizzled tiles -> UMMA -> TMEM -> registers).
  * a, b: bf16 [128,128] row-major; d: fp32 [128,128].  `mode` selects the operand forms, see
  * csrc/selftest.cu.  No counterpart in the reference; used by the GPU tests only.

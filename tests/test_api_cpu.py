@@ -1,0 +1,84 @@
+"""CPU-side checks: the C-ABI library loads and exports every declared symbol, the host planner,
+argument validation of the public operator, and the autograd arity."""
+import ast
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "flashqla.h")).read()
+    return sorted(set(re.findall(r"FQ_API\s+[\w\s\*]+?\b(fq_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from flashqla_b200 import _lib
+    if not os.path.exists(_lib.LIB_PATH):
+        from flashqla_b200 import build
+        build.build()
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    names = _declared_symbols()
+    assert len(names) >= 8
+    for n in names:
+        assert hasattr(lib, n), n
+    assert set(names) == set(_lib.SIGNATURES), "ctypes table and header disagree"
+    assert _lib.load().fq_version() >= 100
+
+
+def test_argument_errors_are_reported_without_a_gpu():
+    from flashqla_b200 import _lib
+    lib = _lib.load()
+    rc = lib.fq_chunk_cumsum(None, None, 1, 64, 1, None, None, 1, 1, 0, None)
+    assert rc == -1 and b"null tensor" in lib.fq_last_error()
+
+
+def test_planner_chunk_tables():
+    from flashqla_b200 import planner
+    cu = torch.tensor([0, 1, 64, 65, 300, 300, 777, 1000], dtype=torch.int32)
+    plan = planner.plan_packed(cu, "cpu")
+    assert plan.offsets_host == [0, 1, 2, 3, 7, 7, 15, 19] and plan.total_chunks == 19 and plan.n_seq == 7
+    assert planner.plan_packed(cu, "cpu") is plan  # cached by tensor identity
+    idx = planner.prepare_chunk_indices(cu)
+    assert idx.shape == (19, 2) and idx[3].tolist() == [3, 0] and idx[6].tolist() == [3, 3] and idx[7].tolist() == [5, 0]
+    off, total = planner.prepare_chunk_offsets(cu)
+    assert off.tolist() == plan.offsets_host and total == 19
+    with pytest.raises(ValueError):
+        planner.plan_packed(torch.tensor([0, 5, 3], dtype=torch.int32), "cpu")
+    d = planner.plan_dense(3, 200)
+    assert (d.n_seq, d.total_chunks, d.max_chunks) == (3, 12, 4)
+
+
+def test_public_operator_validation():
+    import flash_qla
+    q = torch.zeros(2, 64, 2, 128, dtype=torch.bfloat16)
+    g = torch.zeros(2, 64, 2)
+    with pytest.raises(AssertionError):
+        flash_qla.chunk_gated_delta_rule(q.float(), q.float(), q.float(), g, g)
+    with pytest.raises(AssertionError):
+        flash_qla.chunk_gated_delta_rule(q, q, q, g, g, head_first=True)
+    with pytest.raises(AssertionError):
+        flash_qla.chunk_gated_delta_rule(q, q, q[:, :, :1].repeat(1, 1, 3, 1), g, g)
+    with pytest.raises(ValueError):
+        flash_qla.chunk_gated_delta_rule(q, q, q, g, g, cu_seqlens=torch.tensor([0, 64], dtype=torch.int32))
+    with pytest.raises(ValueError):
+        flash_qla.chunk_gated_delta_rule(q[:1], q[:1], q[:1], g[:1], g[:1], initial_state=torch.zeros(3, 2, 128, 128),
+                                         cu_seqlens=torch.tensor([0, 32, 64], dtype=torch.int32))
+    # no CPU path: CPU tensors are refused by the kernels
+    from flashqla_b200._lib import FlashQLAError
+    with pytest.raises(FlashQLAError):
+        flash_qla.chunk_gated_delta_rule(q, q, q, g, g)
+
+
+def test_autograd_backward_arity():
+    """backward returns one gradient per forward input (tests/test_function_signature.py of the reference)."""
+    src = open(os.path.join(ROOT, "flashqla_b200", "ops.py")).read()
+    cls = next(n for n in ast.parse(src).body if isinstance(n, ast.ClassDef) and n.name == "ChunkGatedDeltaRuleFunction")
+    fwd = next(n for n in cls.body if isinstance(n, ast.FunctionDef) and n.name == "forward")
+    bwd = next(n for n in cls.body if isinstance(n, ast.FunctionDef) and n.name == "backward")
+    ret = [n for n in ast.walk(bwd) if isinstance(n, ast.Return)][-1]
+    assert len(ret.value.elts) == len(fwd.args.args) - 1
