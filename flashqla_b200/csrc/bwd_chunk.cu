@@ -727,3 +727,94 @@ extern "C" FQ_API int fq_group_reduce(const void* in, void* out, long long rows,
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the chunk-parallel backward for grouped heads (Hg < H).
+//
+// The regular path needs two [rows, H, 128] bf16 buffers for the per-V-head dq / dk that
+// fq_group_reduce then sums; the caller allocates them.  Some callers cannot allocate device
+// memory at the point where they run the backward: code that executes inside a region where the
+// framework's allocator is frozen (a memory-planned inference/training step whose buffers were all
+// assigned ahead of time), or a host without a caching allocator that would have to pay a
+// cudaMalloc (which synchronises the device) on every call.  For them the two buffers live in a
+// fixed array that is part of the library image.
+namespace fq {
+constexpr size_t kNoAllocScratchBytes = 32ull << 20;  // 2 buffers of rows*H*128 bf16  ->  rows*H <= 65536
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+}  // namespace fq
+
+extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k, const void* v, const void* A,
+                                                   const void* dout, const void* dvp, const void* dv, const void* h,
+                                                   const void* dh, const float* g_cumsum, const float* beta, void* dq,
+                                                   void* dk, float* dg, float* db, int B, int T, int H, int Hg,
+                                                   const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
+                                                   int total_chunks, float scale, int32_t* status_dev, void* stream) {
+  using namespace fq;
+  FQ_CHECK_ARG(q && k && v && A && dout && dvp && dv && h && dh && g_cumsum && beta && dq && dk && dg && db,
+               "fq_gdr_bwd_chunk_gva_noalloc: null tensor");
+  FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0,
+               "fq_gdr_bwd_chunk_gva_noalloc: bad sizes");
+  FQ_CHECK_ARG((cu_seqlens == nullptr) == (chunk_offsets == nullptr),
+               "fq_gdr_bwd_chunk_gva_noalloc: cu_seqlens and chunk_offsets must be given together");
+  FQ_CHECK_ARG(cu_seqlens == nullptr || B == 1, "fq_gdr_bwd_chunk_gva_noalloc: packed batches need B == 1");
+  FQ_CHECK_ARG(cu_seqlens != nullptr || n_seq == B, "fq_gdr_bwd_chunk_gva_noalloc: dense batches need n_seq == B");
+  const uint64_t rows = static_cast<uint64_t>(B) * static_cast<uint64_t>(T);
+  const uint64_t per_buffer = rows * static_cast<uint64_t>(H) * kDim * 2;
+  if (2 * per_buffer > kNoAllocScratchBytes) {
+    set_error("fq_gdr_bwd_chunk_gva_noalloc: B*T*H = %llu exceeds the built-in scratch (limit B*T*H <= %llu); "
+              "use fq_gdr_bwd_chunk + fq_group_reduce with caller-provided buffers",
+              (unsigned long long)(rows * H), (unsigned long long)(kNoAllocScratchBytes / (4 * kDim)));
+    return FQ_ERR_WORKSPACE;
+  }
+  if (total_chunks == 0) return FQ_OK;
+  const uint64_t hrows = static_cast<uint64_t>(total_chunks) * H * kDim;
+  FQ_CHECK_ARG(rows > 0 && rows < (1ull << 31) && hrows < (1ull << 31), "fq_gdr_bwd_chunk_gva_noalloc: sizes out of range");
+
+  // One-time set-up per device, with that device current: resolve the device address of the scratch
+  // array (its name is only a host-side handle) and raise the kernel's shared-memory limit.
+  static unsigned char* scratch_dev[64] = {nullptr};
+  int dev = 0;
+  FQ_CHECK_CUDA(cudaGetDevice(&dev));
+  FQ_CHECK_ARG(dev >= 0 && dev < 64, "fq_gdr_bwd_chunk_gva_noalloc: device index out of range");
+  const size_t smem = sizeof(BwdChunkSmem) + 1024;
+  if (scratch_dev[dev] == nullptr) {
+    void* ptr = nullptr;
+    FQ_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    FQ_CHECK_CUDA(cudaFuncSetAttribute(gdr_bwd_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    scratch_dev[dev] = static_cast<unsigned char*>(ptr);
+  }
+  __nv_bfloat16* dq_h = reinterpret_cast<__nv_bfloat16*>(scratch_dev[dev]);
+  __nv_bfloat16* dk_h = reinterpret_cast<__nv_bfloat16*>(scratch_dev[dev] + per_buffer);
+
+  CUtensorMap mq, mk, mv, mdo, mdvp, mdv, ma, mh, mdh;
+  int rc;
+  if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mv, v, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdo, dout, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdvp, dvp, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdv, dv, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&ma, A, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mh, h, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdh, dh, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
+  BwdChunkParams p;
+  p.g_cum = g_cumsum; p.beta = beta;
+  p.dq = dq_h; p.dk = dk_h; p.dg = dg; p.db = db;
+  p.H = H; p.Hg = Hg; p.total_chunks = total_chunks; p.scale = scale;
+  p.sa = SeqArgs{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
+  p.status_dev = status_dev;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long units = static_cast<long long>(total_chunks) * H;
+  const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
+  gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, st>>>(mq, mk, mv, mdo, mdvp, mdv, ma, mh, mdh, p);
+  FQ_CHECK_CUDA(cudaGetLastError());
+  // Every token row of both scratch buffers was just written (each row belongs to exactly one
+  // chunk), so nothing has to be cleared before the sum reads them.
+  const long long total = static_cast<long long>(rows) * Hg * (kDim / 8);
+  const long long blocks = (total + 255) / 256;
+  const int rgrid = static_cast<int>(blocks < 148LL * 16 ? blocks : 148LL * 16);
+  group_reduce_kernel<<<rgrid, 256, 0, st>>>(dq_h, static_cast<__nv_bfloat16*>(dq), static_cast<long long>(rows), H, Hg);
+  group_reduce_kernel<<<rgrid, 256, 0, st>>>(dk_h, static_cast<__nv_bfloat16*>(dk), static_cast<long long>(rows), H, Hg);
+  FQ_CHECK_CUDA(cudaGetLastError());
+  return FQ_OK;
+}

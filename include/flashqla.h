@@ -115,6 +115,29 @@ FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void* v, const v
 FQ_API int fq_group_reduce(const void* in, void* out, long long rows, int H, int Hg, void* stream);
 
 /*
+ * Allocation-free variant of fq_gdr_bwd_chunk + fq_group_reduce for grouped heads; it has no
+ * counterpart in the reference.  Same inputs as fq_gdr_bwd_chunk, but dq and dk are the final
+ * [B,T,Hg,128] gradients: the per-V-head partial results that the regular path keeps in two
+ * caller-allocated [B,T,H,128] buffers are held in a 32 MiB array inside the library instead.
+ * It exists for callers that must not allocate device memory where the backward runs (a step whose
+ * buffers were all planned in advance and whose allocator is frozen, or a host that would
+ * otherwise pay a device-synchronising cudaMalloc per call).
+ *   - limit: B*T*H <= 65536; larger problems return FQ_ERR_WORKSPACE with a message;
+ *   - the first call on each device resolves the array's device address and configures the kernel;
+ *     make that first call outside any stream capture;
+ *   - all calls share the one array and it keeps the previous call's contents: nothing in it has to
+ *     be cleared (every row is rewritten before it is read), but two calls that overlap on the GPU
+ *     (different streams, or different host threads) race on it; serialise them;
+ *   - it calls no cudaMalloc / cudaFree and no allocating library routine.
+ */
+FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k, const void* v, const void* A, const void* dout,
+                                        const void* dvp, const void* dv, const void* h, const void* dh,
+                                        const float* g_cumsum, const float* beta, void* dq, void* dk, float* dg,
+                                        float* db, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
+                                        const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
+                                        int32_t* status_dev, void* stream);
+
+/*
  * Self-test of the tensor-core plumbing (TMA 128B-swizzled tiles -> UMMA -> TMEM -> registers).
  * a, b: bf16 [128,128] row-major; d: fp32 [128,128].  `mode` selects the operand forms, see
  * csrc/selftest.cu.  No counterpart in the reference; used by the GPU tests only.
