@@ -9,7 +9,7 @@ import os
 import threading
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libflashqla_sm100.so")
+LIB_PATH = os.environ.get("FLASHQLA_LIB", os.path.join(_PKG, "libflashqla_sm100.so"))
 
 _lock = threading.Lock()
 _lib = None
@@ -23,6 +23,8 @@ SIGNATURES = {
     "fq_chunk_cumsum": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp],
     "fq_kkt_solve": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _vp],
     "fq_gdr_fwd": [_vp] * 11 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
+    "fq_gdr_fwd_cp": [_vp] * 13 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
+    "fq_cp_warmup": [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _f32, _i32, _vp],
     "fq_gdr_bwd_dh": [_vp] * 11 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "fq_gdr_bwd_chunk": [_vp] * 15 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "fq_gdr_bwd_chunk_gva_noalloc": [_vp] * 15 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],

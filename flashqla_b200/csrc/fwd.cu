@@ -1,16 +1,23 @@
 // Fused GDN forward: inter-chunk state recurrence + chunk outputs, one persistent CTA per
-// (sequence, V-head).  All contractions run on tcgen05 with the state kept TRANSPOSED in tensor
-// memory (S^T: lane = v, column = k), so that every product has M = 128:
+// (sequence piece, V-head).  All contractions run on tcgen05 with the state kept TRANSPOSED in
+// tensor memory (S^T: lane = v, column = k), so that every product has M = 128:
 //
 //   PK   [128 x 64]  = [K;Q] K^T            rows 64..127 give Q K^T            (state independent)
-//   UQ   [128 x 128] = S^T_bf16 [K;Q]^T     cols 0..63 = U^T, cols 64..127 = (Q S)^T
-//   VD   [128 x 64]  = W^T A_g^T            W = V - gamma o U                  (aliases U^T)
-//   OX   [128 x 64]  = V_d^T P_g^T
+//   U    [128 x 64]  = S^T_bf16 K^T
+//   VD   [128 x 64]  = V^T A_g^T - (gamma o U)^T A_g^T   = V_d^T; the V term is state independent
+//   O    [64 x 128]  = Q~ S + P_g V_d        natural orientation (row = token), Q~ = scale*gamma o Q
 //   S   += V'^T K                           V' = rho o V_d; S was pre-scaled by gamma_last
 //
 // Per chunk:  o = scale*gamma o (Q S) + P_g V_d,   S <- gamma_last S + K^T V'.
-// Warp roles (16 warps): 0 TMA producer, 1 UMMA issuer, 2-3 gate loader, 4-7 W / V_d / V'
-// (critical chain), 8-11 state (TMEM -> bf16 operand, decay), 12-15 A_g / P_g and output.
+// Warp roles (16 warps): 0 TMA producer, 1 UMMA issuer, 2-3 gate loader, 4-11 chain group
+// (TMEM state -> bf16 operand + decay, then -gamma o U, then V_d / V'), 12-15 A_g / P_g / Q~ and the
+// output tile (row-contiguous stores straight from the accumulator).
+//
+// Context parallel: a CTA may own a piece of a sequence.  It then first replays `w` whole chunks
+// that precede the piece (state only, nothing stored) starting from a zero state - or from the
+// sequence's initial state when the replay reaches the sequence start.  `w` comes from the gate
+// scan (cp.cu): the decay accumulated over the replayed chunks makes older history negligible.
+//
 // Every wait on an mbarrier is bounded; on expiry the CTA drains and reports through status_dev.
 #include "flashqla.h"
 #include "host.cuh"
@@ -18,28 +25,38 @@
 
 namespace fq {
 
+#ifdef FQ_TRACE
+// Debug builds only: clock64 stamps of one CTA for a few chunks, read back with fq_trace_read.
+__device__ long long g_trace[8][32];
+#define FQ_TS(n, id) do { if (blockIdx.x == 0 && (n) >= 16 && (n) < 24) g_trace[(n) - 16][id] = clock64(); } while (0)
+#else
+#define FQ_TS(n, id) do { } while (0)
+#endif
+
 constexpr int kFwdThreads = 512;
 constexpr int kGateStages = 4;
 constexpr uint32_t kStageBytes = 32768 + 16384 + 8192;
 
 // TMEM column map (512 columns allocated)
 constexpr uint32_t kColS = 0;     // fp32 state S^T, 128 columns
-constexpr uint32_t kColUQ = 128;  // U^T | (QS)^T, 128 columns; V_d^T reuses the first 64
+constexpr uint32_t kColUQ = 128;  // U^T, 64 columns
+constexpr uint32_t kColVD = 192;  // V_d^T, 64 columns
 constexpr uint32_t kColPK = 256;  // [K;Q] K^T, 64 columns
-constexpr uint32_t kColOX = 320;  // (P_g V_d)^T, 64 columns
+constexpr uint32_t kColO = 320;   // O [64 x 128] (M = 64: rows in lanes 0-15 of every 32-lane quarter)
 
 struct FwdSmem {
   unsigned char kq[2][32768];  // per stage, two 128-row x 128-byte regions (d 0-63 | d 64-127); rows 0-63 k, 64-127 q
   unsigned char v[2][16384];   // per stage, two 64-row x 128-byte regions (v 0-63 | v 64-127)
   unsigned char a[2][8192];    // per stage, A tile [64 i][64 j]; rewritten in place as A_g
   unsigned char sbf[32768];    // bf16 S^T [128 v][128 k] as two 128-row regions
-  unsigned char w[16384];      // W^T, later V'^T   [128 v][64 c]
+  unsigned char w[16384];      // -(gamma o U)^T, later V'^T   [128 v][64 c]
   unsigned char vd[16384];     // V_d^T             [128 v][64 i]
   unsigned char pg[8192];      // P_g               [64 i][64 j]
+  unsigned char qs[16384];     // Q~ = scale*gamma o Q  [64 c][128 k] (two 64-row regions)
   float gate[kGateStages][4][kChunk];  // g, exp(g), exp(g_last - g), beta
   uint64_t full[2], empty[2], gate_full[kGateStages], gate_empty[kGateStages];
-  uint64_t pk_done, uq_done, vd_done, s_done;
-  uint64_t s_ready, s_scaled, w_ready, vp_ready, ag_ready, pg_ready, o_free;
+  uint64_t pk_done, uq_done, vd_done, s_done, o_done;
+  uint64_t s_ready, s_scaled, w_ready, vp_ready, ag_ready, pg_ready, qs_ready, o_free;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -47,9 +64,12 @@ struct FwdSmem {
 struct FwdParams {
   const float* g_cum;   // [rows, H] chunk-local cumsum of the log gate
   const float* beta;    // [rows, H]
-  const float* h0;      // [n_seq, H, 128, 128] or nullptr
+  const float* h0;      // [n_h0, H, 128, 128] or nullptr
   float* ht;            // [n_out, H, 128, 128] or nullptr
-  const int* ht_index;  // [n_seq] slot in ht per sequence (negative: do not write) or nullptr (= sequence index)
+  const int* ht_index;  // [n_seq] slot in ht per piece (negative: do not write) or nullptr (= piece index)
+  const int* h0_index;  // [n_seq] slot in h0 per piece or nullptr (= piece index)
+  const int* warmup;    // [n_seq, H] chunks to replay before the piece; bit 30 set = the replay starts at the
+                        //            sequence start (use h0), else start from zero.  nullptr = {0 | bit 30}
   __nv_bfloat16* o;     // [rows, H, 128] or nullptr
   __nv_bfloat16* h_out; // [total_chunks, H, 128, 128] state before each chunk, or nullptr
   int H, Hg;
@@ -59,10 +79,13 @@ struct FwdParams {
 };
 
 __device__ __forceinline__ uint32_t kq_off(int kk) { return (kk >> 2) * 16384 + (kk & 3) * 32; }
+// Descriptor with the start address advanced by `bytes` (the address field holds addr >> 4).
+__device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t bytes) { return d + (bytes >> 4); }
 
 __global__ void __launch_bounds__(kFwdThreads, 1)
 gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-               const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_a, const FwdParams p) {
+               const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_a,
+               const __grid_constant__ CUtensorMap map_o, const FwdParams p) {
   extern __shared__ unsigned char smem_dyn[];
   FwdSmem& s = *reinterpret_cast<FwdSmem*>(
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
@@ -80,14 +103,19 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     chunk_off = __ldg(p.sa.chunk_offsets + seq);
   }
   const int nchunks = (seq_len + kChunk - 1) / kChunk;
+  const int warm_code = p.warmup ? __ldg(p.warmup + static_cast<size_t>(seq) * p.H + h) : (1 << 30);
+  const int warm = warm_code & 0xFFFFFF;
+  const bool use_h0 = (warm_code >> 30) & 1;
+  const int total = nchunks > 0 ? warm + nchunks : 0;  // iterations; iteration `it` handles chunk n = it - warm
   WaitCtx wc{&s.abort_flag, p.status_dev, 1};
 
   if (tid == 0) {
     s.abort_flag = 0;
-    for (int i = 0; i < 2; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 5); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
     for (int i = 0; i < kGateStages; ++i) { mbar_init(&s.gate_full[i], 64); mbar_init(&s.gate_empty[i], 12); }
     mbar_init(&s.pk_done, 1); mbar_init(&s.uq_done, 1); mbar_init(&s.vd_done, 1); mbar_init(&s.s_done, 1);
-    mbar_init(&s.s_ready, 4); mbar_init(&s.s_scaled, 4); mbar_init(&s.w_ready, 4); mbar_init(&s.vp_ready, 4);
+    mbar_init(&s.o_done, 1); mbar_init(&s.qs_ready, 4);
+    mbar_init(&s.s_ready, 8); mbar_init(&s.s_scaled, 8); mbar_init(&s.w_ready, 8); mbar_init(&s.vp_ready, 8);
     mbar_init(&s.o_free, 4); mbar_init(&s.ag_ready, 2); mbar_init(&s.pg_ready, 2);
     fence_mbar_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); tma_prefetch_desc(&map_a);
@@ -104,11 +132,11 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      for (int n = 0; n < nchunks; ++n) {
-        const int st = n & 1;
-        if (n >= 2 && !mbar_wait(wc, &s.empty[st], ((n >> 1) + 1) & 1, 1)) break;
+      for (int it = 0; it < total; ++it) {
+        const int st = it & 1;
+        if (it >= 2 && !mbar_wait(wc, &s.empty[st], ((it >> 1) + 1) & 1, 1)) break;
         mbar_arrive_expect_tx(&s.full[st], kStageBytes);
-        const int row = tok_begin + n * kChunk;
+        const int row = tok_begin + (it - warm) * kChunk;
         tma_load_3d(s.kq[st], &map_k, &s.full[st], 0, hg, row);
         tma_load_3d(s.kq[st] + 16384, &map_k, &s.full[st], 64, hg, row);
         tma_load_3d(s.kq[st] + 8192, &map_q, &s.full[st], 0, hg, row);
@@ -121,61 +149,89 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer
     if (lane == 0) {
-      constexpr uint32_t id128 = umma_idesc(128, 128, false, false, true);
       constexpr uint32_t id64 = umma_idesc(128, 64, false, false, true);
+      constexpr uint32_t id64_amn = umma_idesc(128, 64, true, false, true);
       constexpr uint32_t id128_bmn = umma_idesc(128, 128, false, true, true);
-      const uint32_t sbf = smem_u32(s.sbf), sw = smem_u32(s.w), svd = smem_u32(s.vd), spg = smem_u32(s.pg);
-      for (int n = 0; n < nchunks; ++n) {
-        const int st = n & 1;
-        const uint32_t ph = n & 1;
-        const uint32_t skq = smem_u32(s.kq[st]), sa = smem_u32(s.a[st]);
-        if (!mbar_wait(wc, &s.full[st], (n >> 1) & 1, 2)) break;
+      constexpr uint32_t id_o = umma_idesc(64, 128, false, false, true);
+      const uint64_t d_sbf = umma_desc_sw128(smem_u32(s.sbf), 16, 1024);
+      const uint64_t d_w = umma_desc_sw128(smem_u32(s.w), 16, 1024);
+      const uint64_t d_vd = umma_desc_sw128(smem_u32(s.vd), 16, 1024);
+      const uint64_t d_pg = umma_desc_sw128(smem_u32(s.pg), 16, 1024);
+      const uint64_t d_qs = umma_desc_sw128(smem_u32(s.qs), 16, 1024);
+      uint64_t d_kq[2], d_kmn[2], d_a[2], d_vmn[2];
+      for (int i = 0; i < 2; ++i) {
+        d_vmn[i] = umma_desc_sw128(smem_u32(s.v[i]), 8192, 1024);
+        d_kq[i] = umma_desc_sw128(smem_u32(s.kq[i]), 16, 1024);
+        d_kmn[i] = umma_desc_sw128(smem_u32(s.kq[i]), 16384, 1024);
+        d_a[i] = umma_desc_sw128(smem_u32(s.a[i]), 16, 1024);
+      }
+      for (int it = 0; it < total; ++it) {
+        const int st = it & 1;
+        const uint32_t ph = it & 1;
+        if (!mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2)) break;
+        FQ_TS(it, 0);
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tm + kColPK, umma_desc_sw128(skq + kq_off(kk), 16, 1024), umma_desc_sw128(skq + kq_off(kk), 16, 1024),
-                  id64, kk > 0);
+        for (int kk = 0; kk < 8; ++kk)  // PK = [K;Q] K^T
+          umma_ss(tm + kColPK, desc_add(d_kq[st], kq_off(kk)), desc_add(d_kq[st], kq_off(kk)), id64, kk > 0);
         umma_commit(&s.pk_done);
         if (!mbar_wait(wc, &s.s_ready, ph, 3)) break;
-        if (n > 0 && !mbar_wait(wc, &s.o_free, (n - 1) & 1, 4)) break;
+        FQ_TS(it, 1);
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)  // U^T = S^T K^T
+          umma_ss(tm + kColUQ, desc_add(d_sbf, kq_off(kk)), desc_add(d_kq[st], kq_off(kk)), id64, kk > 0);
+        umma_commit(&s.uq_done);
+        FQ_TS(it, 3);
+        if (!mbar_wait(wc, &s.ag_ready, ph, 6)) break;
+        FQ_TS(it, 5);
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)  // V_d^T = V^T A_g^T (A operand = the V tile as loaded, MN-major)
+          umma_ss(tm + kColVD, desc_add(d_vmn[st], kk * 2048), desc_add(d_a[st], kk * 32), id64_amn, kk > 0);
+        // O = Q~ S: needs the output accumulator of the previous chunk to be drained and Q~ of this chunk
+        if (it > 0 && !mbar_wait(wc, &s.o_free, (it - 1) & 1, 4)) break;
+        if (!mbar_wait(wc, &s.qs_ready, ph, 22)) break;
+        FQ_TS(it, 2);
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tm + kColUQ, umma_desc_sw128(sbf + kq_off(kk), 16, 1024), umma_desc_sw128(skq + kq_off(kk), 16, 1024),
-                  id128, kk > 0);
-        umma_commit(&s.uq_done);
+          umma_ss(tm + kColO, desc_add(d_qs, (kk >> 2) * 8192 + (kk & 3) * 32), desc_add(d_sbf, kq_off(kk)), id_o, kk > 0);
         if (!mbar_wait(wc, &s.w_ready, ph, 5)) break;
-        if (!mbar_wait(wc, &s.ag_ready, ph, 6)) break;
+        FQ_TS(it, 4);
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tm + kColUQ, umma_desc_sw128(sw + kk * 32, 16, 1024), umma_desc_sw128(sa + kk * 32, 16, 1024), id64,
-                  kk > 0);
+        for (int kk = 0; kk < 4; ++kk)  // V_d^T -= (gamma o U)^T A_g^T
+          umma_ss(tm + kColVD, desc_add(d_w, kk * 32), desc_add(d_a[st], kk * 32), id64, 1);
         umma_commit(&s.vd_done);
+        FQ_TS(it, 6);
         if (!mbar_wait(wc, &s.vp_ready, ph, 7)) break;
-        if (!mbar_wait(wc, &s.pg_ready, ph, 8)) break;
+        FQ_TS(it, 7);
         if (!mbar_wait(wc, &s.s_scaled, ph, 9)) break;
+        FQ_TS(it, 8);
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tm + kColOX, umma_desc_sw128(svd + kk * 32, 16, 1024), umma_desc_sw128(spg + kk * 32, 16, 1024), id64,
-                  kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tm + kColS, umma_desc_sw128(sw + kk * 32, 16, 1024), umma_desc_sw128(skq + kk * 2048, 16384, 1024),
-                  id128_bmn, 1);
+        for (int kk = 0; kk < 4; ++kk)  // S^T += V'^T K
+          umma_ss(tm + kColS, desc_add(d_w, kk * 32), desc_add(d_kmn[st], kk * 2048), id128_bmn, 1);
         umma_commit(&s.s_done);
+        FQ_TS(it, 9);
+        if (!mbar_wait(wc, &s.pg_ready, ph, 8)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)  // O += P_g V_d
+          umma_ss(tm + kColO, desc_add(d_pg, kk * 32), desc_add(d_vd, kk * 32), id_o, 1);
+        umma_commit(&s.o_done);
         umma_commit(&s.empty[st]);
       }
     }
   } else if (warp < 4) {
     // ------------------------------------------------------------------ gate loader
     const int t = tid - 64;
-    for (int n = 0; n < nchunks; ++n) {
-      const int gs = n & (kGateStages - 1);
-      if (n >= kGateStages && !mbar_wait(wc, &s.gate_empty[gs], ((n >> 2) + 1) & 1, 10)) break;
-      const int len = min(kChunk, seq_len - n * kChunk);
-      const size_t row = static_cast<size_t>(tok_begin) + n * kChunk;
+    for (int it = 0; it < total; ++it) {
+      const int n = it - warm, gs = it & (kGateStages - 1);
+      if (it >= kGateStages && !mbar_wait(wc, &s.gate_empty[gs], ((it >> 2) + 1) & 1, 10)) break;
+      const int len = min(kChunk, seq_len - n * kChunk);  // replayed chunks (n < 0) are always whole
+      const long long row = static_cast<long long>(tok_begin) + static_cast<long long>(n) * kChunk;
       const float gl = __ldg(p.g_cum + (row + len - 1) * p.H + h);
       float gi = gl, bi = 0.f;
       if (t < len) {
@@ -188,162 +244,196 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       s.gate[gs][3][t] = bi;
       mbar_arrive(&s.gate_full[gs]);
     }
-  } else if (warp < 8) {
-    // ------------------------------------------------------------------ W, V_d, V' (critical chain)
-    const int v = tid - 128;
-    const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32;
-    for (int n = 0; n < nchunks; ++n) {
-      const int st = n & 1, gs = n & (kGateStages - 1);
-      const uint32_t ph = n & 1;
-      if (!mbar_wait(wc, &s.full[st], (n >> 1) & 1, 11)) break;
-      if (!mbar_wait(wc, &s.gate_full[gs], (n >> 2) & 1, 12)) break;
-      if (!mbar_wait(wc, &s.uq_done, ph, 13)) break;
-      tc_fence_after();
-      const unsigned char* vt = s.v[st] + (v >> 6) * 8192;
-      const uint32_t vb = (v & 63) * 2;
+  } else if (warp < 12) {
+    // ------------------------------------------------------------------ chain group (8 warps): per chunk
+    //   state: TMEM -> bf16 operand (+ h), decay in TMEM;  W = V - gamma o U;  V_d and V' = rho o V_d
+    // Warp w owns TMEM lanes 32*(w&3).. and, of every tile, the column half hf = (w-4)>>2.
+    const int q4 = warp & 3, hf = (warp - 4) >> 2;
+    const int v = q4 * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(q4) * 32;
+    {
+      const int slot = p.h0_index ? __ldg(p.h0_index + seq) : seq;
+      const float* src = (p.h0 && use_h0) ? p.h0 + (static_cast<size_t>(slot) * p.H + h) * kDim * kDim + v : nullptr;
+#pragma unroll 1
+      for (int pc = 0; pc < 2; ++pc) {
+        uint32_t r[32];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
+        for (int i = 0; i < 32; ++i)
+          r[i] = src ? __float_as_uint(__ldg(src + static_cast<size_t>(64 * hf + 32 * pc + i) * kDim)) : 0u;
+        tmem_st32(tmem_addr(tm, lane_base, kColS + 64 * hf + 32 * pc), r);
+      }
+      tmem_wait_st();
+    }
+    bool alive = true;
+    for (int it = 0; it < total; ++it) {
+      const int n = it - warm, st = it & 1, gs = it & (kGateStages - 1);
+      const uint32_t ph = it & 1;
+      // ---- state -> bf16 operand, optional h, decay
+      if (it > 0) {
+        if (!mbar_wait(wc, &s.s_done, (it - 1) & 1, 15)) { alive = false; break; }
+        tc_fence_after();
+      }
+      if (tid == 128) FQ_TS(it, 14);
+      if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 16)) { alive = false; break; }
+      {
+        const float gL = s.gate[gs][1][kChunk - 1];
+        __nv_bfloat16* hdst = (p.h_out && n >= 0)
+                                  ? p.h_out + (static_cast<size_t>(chunk_off + n) * p.H + h) * kDim * kDim + v
+                                  : nullptr;
+#pragma unroll
+        for (int pc = 0; pc < 2; ++pc) {
+          uint32_t r[32];
+          tmem_ld32(tmem_addr(tm, lane_base, kColS + 64 * hf + 32 * pc), r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 q4v;
+            q4v.x = pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+            q4v.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+            q4v.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+            q4v.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            *reinterpret_cast<uint4*>(s.sbf + hf * 16384 + sw128(v, pc * 64 + j * 16)) = q4v;
+          }
+          if (hdst) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              hdst[static_cast<size_t>(64 * hf + 32 * pc + i) * kDim] = __float2bfloat16(__uint_as_float(r[i]));
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * gL);
+          tmem_st32(tmem_addr(tm, lane_base, kColS + 64 * hf + 32 * pc), r);
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.s_ready);
+        if (tid == 128) FQ_TS(it, 15);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.s_scaled);
+      }
+      // ---- -(gamma_c U^T[v][c]) for c in [32 hf, 32 hf + 32): the state-dependent half of W = V - gamma o U
+      if (!mbar_wait(wc, &s.uq_done, ph, 13)) { alive = false; break; }
+      if (tid == 128) FQ_TS(it, 10);
+      tc_fence_after();
+      {
         uint32_t u[32];
-        tmem_ld32(tmem_addr(tm, lane_base, kColUQ + half * 32), u);
+        tmem_ld32(tmem_addr(tm, lane_base, kColUQ + 32 * hf), u);
         tmem_wait_ld();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const int c = half * 32 + i;
-          const float v0 = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(vt + sw128(c, vb))) << 16);
-          const float v1 = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(vt + sw128(c + 1, vb))) << 16);
-          const float w0 = v0 - s.gate[gs][1][c] * __uint_as_float(u[i]);
-          const float w1 = v1 - s.gate[gs][1][c + 1] * __uint_as_float(u[i + 1]);
-          pk[i >> 1] = pack_bf16(w0, w1);
+          const int c = 32 * hf + i;
+          pk[i >> 1] = pack_bf16(-s.gate[gs][1][c] * __uint_as_float(u[i]), -s.gate[gs][1][c + 1] * __uint_as_float(u[i + 1]));
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(s.w + sw128(v, half * 64 + j * 16)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+          *reinterpret_cast<uint4*>(s.w + sw128(v, hf * 64 + j * 16)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
       }
       tc_fence_before();
       fence_async_smem();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(&s.w_ready); mbar_arrive(&s.empty[st]); }
-      if (!mbar_wait(wc, &s.vd_done, ph, 14)) break;
+      if (lane == 0) mbar_arrive(&s.w_ready);
+      if (tid == 128) FQ_TS(it, 11);
+      // ---- V_d^T and V'^T = rho o V_d^T
+      if (!mbar_wait(wc, &s.vd_done, ph, 14)) { alive = false; break; }
+      if (tid == 128) FQ_TS(it, 12);
       tc_fence_after();
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
         uint32_t d[32];
-        tmem_ld32(tmem_addr(tm, lane_base, kColUQ + half * 32), d);
+        tmem_ld32(tmem_addr(tm, lane_base, kColVD + 32 * hf), d);
         tmem_wait_ld();
         uint32_t pd[16], pp[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const int c = half * 32 + i;
+          const int c = 32 * hf + i;
           const float d0 = __uint_as_float(d[i]), d1 = __uint_as_float(d[i + 1]);
           pd[i >> 1] = pack_bf16(d0, d1);
           pp[i >> 1] = pack_bf16(s.gate[gs][2][c] * d0, s.gate[gs][2][c + 1] * d1);
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          *reinterpret_cast<uint4*>(s.vd + sw128(v, half * 64 + j * 16)) = make_uint4(pd[4 * j], pd[4 * j + 1], pd[4 * j + 2], pd[4 * j + 3]);
-          *reinterpret_cast<uint4*>(s.w + sw128(v, half * 64 + j * 16)) = make_uint4(pp[4 * j], pp[4 * j + 1], pp[4 * j + 2], pp[4 * j + 3]);
+          *reinterpret_cast<uint4*>(s.vd + sw128(v, hf * 64 + j * 16)) = make_uint4(pd[4 * j], pd[4 * j + 1], pd[4 * j + 2], pd[4 * j + 3]);
+          *reinterpret_cast<uint4*>(s.w + sw128(v, hf * 64 + j * 16)) = make_uint4(pp[4 * j], pp[4 * j + 1], pp[4 * j + 2], pp[4 * j + 3]);
         }
       }
       tc_fence_before();
       fence_async_smem();
       __syncwarp();
       if (lane == 0) { mbar_arrive(&s.vp_ready); mbar_arrive(&s.gate_empty[gs]); }
+      if (tid == 128) FQ_TS(it, 13);
     }
-  } else if (warp < 12) {
-    // ------------------------------------------------------------------ state: TMEM <-> bf16 operand, decay, h / final state
-    const int v = tid - 256;
-    const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32;
-    {
-      const float* src = p.h0 ? p.h0 + (static_cast<size_t>(seq) * p.H + h) * kDim * kDim + v : nullptr;
-#pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
-        uint32_t r[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) r[i] = src ? __float_as_uint(__ldg(src + static_cast<size_t>(cb * 32 + i) * kDim)) : 0u;
-        tmem_st32(tmem_addr(tm, lane_base, kColS + cb * 32), r);
-      }
-      tmem_wait_st();
-    }
-    bool alive = true;
-    for (int n = 0; n < nchunks && alive; ++n) {
-      const int gs = n & (kGateStages - 1);
-      if (n > 0) {
-        if (!mbar_wait(wc, &s.s_done, (n - 1) & 1, 15)) { alive = false; break; }
-        tc_fence_after();
-      }
-      if (!mbar_wait(wc, &s.gate_full[gs], (n >> 2) & 1, 16)) { alive = false; break; }
-      const float gL = s.gate[gs][1][kChunk - 1];
-      __nv_bfloat16* hdst = p.h_out ? p.h_out + (static_cast<size_t>(chunk_off + n) * p.H + h) * kDim * kDim + v : nullptr;
-#pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
-        uint32_t r[32];
-        tmem_ld32(tmem_addr(tm, lane_base, kColS + cb * 32), r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 q4;
-          q4.x = pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
-          q4.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-          q4.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-          q4.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-          *reinterpret_cast<uint4*>(s.sbf + (cb >> 1) * 16384 + sw128(v, (cb & 1) * 64 + j * 16)) = q4;
-        }
-        if (hdst) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) hdst[static_cast<size_t>(cb * 32 + i) * kDim] = __float2bfloat16(__uint_as_float(r[i]));
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * gL);
-        tmem_st32(tmem_addr(tm, lane_base, kColS + cb * 32), r);
-      }
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s.s_ready);
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) { mbar_arrive(&s.s_scaled); mbar_arrive(&s.gate_empty[gs]); }
-    }
-    if (alive && nchunks > 0) {
-      alive = mbar_wait(wc, &s.s_done, (nchunks - 1) & 1, 17);
+    // ---- final state
+    if (alive && total > 0) {
+      alive = mbar_wait(wc, &s.s_done, (total - 1) & 1, 17);
       tc_fence_after();
     }
     const int slot = p.ht_index ? __ldg(p.ht_index + seq) : seq;
     if (alive && p.ht && slot >= 0) {
       float* dst = p.ht + (static_cast<size_t>(slot) * p.H + h) * kDim * kDim + v;
 #pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
+      for (int pc = 0; pc < 2; ++pc) {
         uint32_t r[32];
-        tmem_ld32(tmem_addr(tm, lane_base, kColS + cb * 32), r);
+        tmem_ld32(tmem_addr(tm, lane_base, kColS + 64 * hf + 32 * pc), r);
         tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) dst[static_cast<size_t>(cb * 32 + i) * kDim] = __uint_as_float(r[i]);
+        for (int i = 0; i < 32; ++i) dst[static_cast<size_t>(64 * hf + 32 * pc + i) * kDim] = __uint_as_float(r[i]);
       }
     }
   } else {
-    // ------------------------------------------------------------------ A_g, P_g and the output tile
+    // ------------------------------------------------------------------ A_g, P_g, Q~ and the output tile
+    // Order per iteration: drain the finished output accumulator (row-contiguous stores), release it,
+    // then prepare Q~ / A_g / P_g of the NEXT chunk (the chain needs them early).
     const int wid = warp - 12;
-    const int v = tid - 384;
+    const int ta = tid - 384;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32;
-    for (int n = 0; n < nchunks; ++n) {
-      const int st = n & 1, gs = n & (kGateStages - 1);
-      const uint32_t ph = n & 1;
-      if (!mbar_wait(wc, &s.gate_full[gs], (n >> 2) & 1, 18)) break;
-      if (wid < 2) {
-        if (!mbar_wait(wc, &s.full[st], (n >> 1) & 1, 19)) break;
+    bool ok = true;
+
+    auto prepare = [&](int it) -> bool {
+      const int st = it & 1, gs = it & (kGateStages - 1);
+      if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 18)) return false;
+      if (!mbar_wait(wc, &s.full[st], (it >> 1) & 1, 19)) return false;
+      {  // Q~[c][:] = scale * gamma_c * q[c][:]; thread = (row, 64-column half)
+        const int r = ta >> 1, hq = ta & 1;
+        const float f = p.scale * s.gate[gs][1][r];
+        const unsigned char* src = s.kq[st] + hq * 16384 + 8192;
+        unsigned char* dst = s.qs + hq * 8192;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t so = sw128(r, j * 16);
+          uint4 x = *reinterpret_cast<const uint4*>(src + so);
+          uint32_t* xw = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) xw[e] = pack_bf16(f * bf16_lo(xw[e]), f * bf16_hi(xw[e]));
+          *reinterpret_cast<uint4*>(dst + so) = x;
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.qs_ready);
+      }
+      if (wid < 2) {  // A_g = A o G o beta_col, in place; 16-byte pieces above the diagonal are just zeroed
         const int i = wid * 32 + lane;
         const float gi = s.gate[gs][0][i];
 #pragma unroll
         for (int j8 = 0; j8 < 8; ++j8) {
           uint4* ptr = reinterpret_cast<uint4*>(s.a[st] + sw128(i, j8 * 16));
+          if (j8 * 8 > wid * 32 + 31) {  // whole warp is above the diagonal here
+            *ptr = make_uint4(0, 0, 0, 0);
+            continue;
+          }
           uint4 a4 = *ptr;
           uint32_t* aw = reinterpret_cast<uint32_t*>(&a4);
+          const float4 g0 = *reinterpret_cast<const float4*>(&s.gate[gs][0][j8 * 8]);
+          const float4 g1 = *reinterpret_cast<const float4*>(&s.gate[gs][0][j8 * 8 + 4]);
+          const float4 b0 = *reinterpret_cast<const float4*>(&s.gate[gs][3][j8 * 8]);
+          const float4 b1 = *reinterpret_cast<const float4*>(&s.gate[gs][3][j8 * 8 + 4]);
+          const float gj[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+          const float bj[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int j = j8 * 8 + 2 * e;
-            const float x0 = (j <= i) ? bf16_lo(aw[e]) * fast_exp(gi - s.gate[gs][0][j]) * s.gate[gs][3][j] : 0.f;
-            const float x1 = (j + 1 <= i) ? bf16_hi(aw[e]) * fast_exp(gi - s.gate[gs][0][j + 1]) * s.gate[gs][3][j + 1] : 0.f;
+            const float x0 = (j <= i) ? bf16_lo(aw[e]) * fast_exp(gi - gj[2 * e]) * bj[2 * e] : 0.f;
+            const float x1 = (j + 1 <= i) ? bf16_hi(aw[e]) * fast_exp(gi - gj[2 * e + 1]) * bj[2 * e + 1] : 0.f;
             aw[e] = pack_bf16(x0, x1);
           }
           *ptr = a4;
@@ -351,23 +441,34 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s.ag_ready);
-      } else {
-        if (!mbar_wait(wc, &s.pk_done, ph, 20)) break;
+      } else {  // P_g = scale * G o (Q K^T) from TMEM lanes 64..127
+        if (!mbar_wait(wc, &s.pk_done, it & 1, 20)) return false;
         tc_fence_after();
-        const int i = (wid - 2) * 32 + lane;
+        const int w2 = wid - 2;
+        const int i = w2 * 32 + lane;
         const float gi = s.gate[gs][0][i];
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          uint32_t r[32];
-          tmem_ld32(tmem_addr(tm, lane_base, kColPK + half * 32), r);
-          tmem_wait_ld();
           uint32_t pk[16];
+          if (half > w2) {  // columns 32..63 for rows 0..31: above the diagonal
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const int j = half * 32 + e;
-            const float x0 = (j <= i) ? p.scale * fast_exp(gi - s.gate[gs][0][j]) * __uint_as_float(r[e]) : 0.f;
-            const float x1 = (j + 1 <= i) ? p.scale * fast_exp(gi - s.gate[gs][0][j + 1]) * __uint_as_float(r[e + 1]) : 0.f;
-            pk[e >> 1] = pack_bf16(x0, x1);
+            for (int e = 0; e < 16; ++e) pk[e] = 0u;
+          } else {
+            uint32_t r[32];
+            tmem_ld32(tmem_addr(tm, lane_base, kColPK + half * 32), r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+              const float4 g4 = *reinterpret_cast<const float4*>(&s.gate[gs][0][half * 32 + e]);
+              const float gj[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+              for (int z = 0; z < 4; z += 2) {
+                const int j = half * 32 + e + z;
+                const float x0 = (j <= i) ? p.scale * fast_exp(gi - gj[z]) * __uint_as_float(r[e + z]) : 0.f;
+                const float x1 = (j + 1 <= i) ? p.scale * fast_exp(gi - gj[z + 1]) * __uint_as_float(r[e + z + 1]) : 0.f;
+                pk[(e + z) >> 1] = pack_bf16(x0, x1);
+              }
+            }
           }
 #pragma unroll
           for (int j = 0; j < 4; ++j)
@@ -377,39 +478,48 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s.pg_ready);
+        if (tid == 448) FQ_TS(it, 17);
       }
-      // output tile: o[c][v] = scale * gamma_c * (Q S)[c][v] + (P_g V_d)[c][v]
-      if (!mbar_wait(wc, &s.s_done, ph, 21)) break;
+      return true;
+    };
+
+    if (total > 0) ok = prepare(0);
+    for (int it = 0; it < total && ok; ++it) {
+      const int n = it - warm, gs = it & (kGateStages - 1);
+      const uint32_t ph = it & 1;
+      // ---- output tile O[c][v]: thread (lane < 16) owns token row c = 16 * quarter + lane
+      if (!mbar_wait(wc, &s.o_done, ph, 21)) break;
+      if (tid == 384) FQ_TS(it, 18);
       tc_fence_after();
-      uint32_t packed[32];
+      if (p.o != nullptr && n >= 0) {
+        const int c = 16 * (warp & 3) + lane;
+        const int len = min(kChunk, seq_len - n * kChunk);
+        const bool wr = (lane < 16) && (c < len);
+        __nv_bfloat16* dst = p.o + (static_cast<size_t>(tok_begin + n * kChunk + (wr ? c : 0)) * p.H + h) * kDim;
 #pragma unroll
-      for (int qd = 0; qd < 4; ++qd) {
-        uint32_t oi[16], ox[16];
-        tmem_ld16(tmem_addr(tm, lane_base, kColUQ + 64 + qd * 16), oi);
-        tmem_ld16(tmem_addr(tm, lane_base, kColOX + qd * 16), ox);
-        tmem_wait_ld();
+        for (int pc = 0; pc < 4; ++pc) {
+          uint32_t r[32];
+          tmem_ld32(tmem_addr(tm, lane_base, kColO + 32 * pc), r);
+          tmem_wait_ld();
+          if (wr) {
 #pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          const int c = qd * 16 + e;
-          const float o0 = p.scale * s.gate[gs][1][c] * __uint_as_float(oi[e]) + __uint_as_float(ox[e]);
-          const float o1 = p.scale * s.gate[gs][1][c + 1] * __uint_as_float(oi[e + 1]) + __uint_as_float(ox[e + 1]);
-          packed[c >> 1] = pack_bf16(o0, o1);
+            for (int j = 0; j < 4; ++j) {
+              uint4 x;
+              x.x = pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+              x.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+              x.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+              x.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+              *reinterpret_cast<uint4*>(dst + 32 * pc + 8 * j) = x;
+            }
+          }
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) { mbar_arrive(&s.o_free); mbar_arrive(&s.gate_empty[gs]); }
-      if (p.o) {
-        const int len = min(kChunk, seq_len - n * kChunk);
-        unsigned short* dst = reinterpret_cast<unsigned short*>(p.o) +
-                              (static_cast<size_t>(tok_begin) + n * kChunk) * p.H * kDim + static_cast<size_t>(h) * kDim + v;
-        const size_t rs = static_cast<size_t>(p.H) * kDim;
-#pragma unroll
-        for (int c = 0; c < kChunk; c += 2) {
-          if (c < len) dst[c * rs] = static_cast<unsigned short>(packed[c >> 1] & 0xFFFFu);
-          if (c + 1 < len) dst[(c + 1) * rs] = static_cast<unsigned short>(packed[c >> 1] >> 16);
-        }
-      }
+      if (tid == 384) FQ_TS(it, 19);
+      // ---- next chunk's Q~ / A_g / P_g.  The buffers are free: every UMMA that read them finished before o_done.
+      if (it + 1 < total) ok = prepare(it + 1);
     }
   }
 
@@ -425,6 +535,15 @@ extern "C" FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, co
                                  void* h_out, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
                                  const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
                                  int32_t* status_dev, void* stream) {
+  return fq_gdr_fwd_cp(q, k, v, A, g_cumsum, beta, h0, ht, ht_index, nullptr, nullptr, o, h_out, B, T, H, Hg, cu_seqlens,
+                       chunk_offsets, n_seq, total_chunks, scale, status_dev, stream);
+}
+
+extern "C" FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v, const void* A, const float* g_cumsum,
+                                    const float* beta, const float* h0, float* ht, const int32_t* ht_index,
+                                    const int32_t* h0_index, const int32_t* warmup, void* o, void* h_out, int B, int T,
+                                    int H, int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
+                                    int total_chunks, float scale, int32_t* status_dev, void* stream) {
   using namespace fq;
   FQ_CHECK_ARG(q && k && v && A && g_cumsum && beta, "fq_gdr_fwd: null input tensor");
   FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0, "fq_gdr_fwd: bad sizes");
@@ -432,16 +551,20 @@ extern "C" FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, co
                "fq_gdr_fwd: cu_seqlens and chunk_offsets must be given together");
   FQ_CHECK_ARG(cu_seqlens == nullptr || B == 1, "fq_gdr_fwd: packed batches need B == 1");
   FQ_CHECK_ARG(cu_seqlens != nullptr || n_seq == B, "fq_gdr_fwd: dense batches need n_seq == B");
+  FQ_CHECK_ARG(warmup == nullptr || cu_seqlens != nullptr, "fq_gdr_fwd: warm-up tables need piece boundaries (cu_seqlens)");
   const uint64_t rows = static_cast<uint64_t>(B) * static_cast<uint64_t>(T);
   FQ_CHECK_ARG(rows > 0 && rows < (1ull << 31), "fq_gdr_fwd: token count out of range");
-  CUtensorMap mq, mk, mv, ma;
+  CUtensorMap mq, mk, mv, ma, mo;
   int rc;
   if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mv, v, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&ma, A, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
+  // the output map is only dereferenced when o != NULL; v stands in to keep the descriptor valid otherwise
+  if ((rc = make_tmap_rows_heads_dim(&mo, o ? o : v, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   FwdParams p;
-  p.g_cum = g_cumsum; p.beta = beta; p.h0 = h0; p.ht = ht; p.ht_index = ht_index;
+  p.g_cum = g_cumsum; p.beta = beta; p.h0 = h0; p.ht = ht; p.ht_index = ht_index; p.h0_index = h0_index;
+  p.warmup = warmup;
   p.o = static_cast<__nv_bfloat16*>(o); p.h_out = static_cast<__nv_bfloat16*>(h_out);
   p.H = H; p.Hg = Hg; p.scale = scale;
   p.sa = SeqArgs{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
@@ -456,7 +579,13 @@ extern "C" FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, co
   }
   const long long ctas = static_cast<long long>(n_seq) * H;
   FQ_CHECK_ARG(ctas < (1ll << 31), "fq_gdr_fwd: too many (sequence, head) pairs");
-  gdr_fwd_kernel<<<static_cast<unsigned>(ctas), kFwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, ma, p);
+  gdr_fwd_kernel<<<static_cast<unsigned>(ctas), kFwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, ma, mo, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }
+
+#ifdef FQ_TRACE
+extern "C" FQ_API int fq_trace_read(long long* out_host) {
+  return cudaMemcpyFromSymbol(out_host, fq::g_trace, sizeof(long long) * 8 * 32) == cudaSuccess ? 0 : -2;
+}
+#endif

@@ -95,3 +95,106 @@ def prepare_chunk_offsets(cu_seqlens: torch.Tensor, chunk_size: int = CHUNK):
     assert chunk_size == CHUNK
     plan = plan_packed(cu_seqlens)
     return plan.chunk_offsets.to(cu_seqlens.dtype), plan.total_chunks
+
+
+# --------------------------------------------------------------------------- context parallel
+@dataclass
+class CpPlan:
+    """Split of the sequences of a batch into pieces that run as independent CTAs.
+
+    Counterpart of `_calc_cp_seqs` (flash_qla/ops/gated_delta_rule/chunk/cp_context.py:32-103).  Pieces
+    of one sequence are contiguous, every piece but the last of a sequence holds `piece_chunks`
+    whole chunks, so chunk boundaries (and with them the cumsum, A and h tensors) are the same with
+    and without the split.  All tensors are int32 on the device.
+    """
+    n_pieces: int
+    piece_chunks: int
+    total_chunks: int
+    cu_seqlens: torch.Tensor        # [P+1] piece token boundaries in the flattened [B*T] token axis
+    chunk_offsets: torch.Tensor     # [P+1] prefix sums of chunks per piece
+    seq_index: torch.Tensor         # [P] raw sequence of each piece (slot of h0 / dht)
+    out_index_fwd: torch.Tensor     # [P] raw sequence for the LAST piece of a sequence, else -1 (slot of ht)
+    out_index_bwd: torch.Tensor     # [P] raw sequence for the FIRST piece of a sequence, else -1 (slot of dh0)
+    piece_start: torch.Tensor       # [P] first token of the piece
+    piece_end: torch.Tensor         # [P] first token after the piece
+    chunks_before: torch.Tensor     # [P] chunks of the sequence that precede the piece
+    chunks_after: torch.Tensor      # [P] chunks of the sequence that follow the piece
+    last_chunk_len: torch.Tensor    # [P] tokens in the last chunk of the piece's sequence
+
+
+def choose_piece_chunks(n_chunks: list, H: int, n_sm: int, overhead: int = 6) -> int | None:
+    """Chunks per piece, or None to run un-split.
+
+    Cost model in units of one chunk step of one CTA: a CTA costs (chunks + overhead) where the
+    overhead stands for the replayed chunks and the CTA start-up; the kernel keeps one CTA per SM, so
+    the run takes about max(longest CTA, total work / n_sm).  The reference's rule
+    (cp_context.py:52-57, 86-87) was fitted to 132 SMs with up to two CTAs each; this one follows
+    from the one-CTA-per-SM kernel.
+    """
+    longest = max(n_chunks) if n_chunks else 0
+    if longest <= 8:
+        return None
+
+    def cost(L):
+        pieces = [min(L, c - i) for c in n_chunks for i in range(0, c, L)] if L < longest else list(n_chunks)
+        work = sum((x + overhead) for x in pieces if x > 0) * H
+        return max(max(pieces) + overhead, work / n_sm)
+
+    base = cost(longest)
+    best_L, best = None, base
+    L = 1 << (longest - 1).bit_length()
+    while L >= 8:
+        for cand in (L, (3 * L) // 4):
+            if 8 <= cand < longest:
+                c = cost(cand)
+                if c < best * 0.999:
+                    best_L, best = cand, c
+        L //= 2
+    if best_L is None or best > 0.9 * base:
+        return None
+    return best_L
+
+
+_CP_CACHE: "OrderedDict[tuple, CpPlan | None]" = OrderedDict()
+
+
+def plan_cp(plan: SeqPlan, B: int, T: int, H: int, n_sm: int, device, piece_chunks: int | None = None):
+    """CpPlan for a batch, or None when splitting does not pay.  Dense batches are treated as packed
+    ones over the flattened token axis (row b*T + t)."""
+    key = (id(plan), B, T, H, n_sm, str(device), piece_chunks)
+    if key in _CP_CACHE and _CP_CACHE[key] is not None and _CP_CACHE[key][0] is plan:
+        return _CP_CACHE[key][1]
+    cu = plan.cu_host if plan.packed else [b * T for b in range(B + 1)]
+    n_chunks = [(cu[i + 1] - cu[i] + CHUNK - 1) // CHUNK for i in range(len(cu) - 1)]
+    L = piece_chunks if piece_chunks is not None else choose_piece_chunks(n_chunks, H, n_sm)
+    result = None
+    if L is not None and L >= 1 and max(n_chunks, default=0) > L:
+        starts, ends, seq_idx, before, after, lastlen, out_f, out_b = [], [], [], [], [], [], [], []
+        for i, nc in enumerate(n_chunks):
+            s, e = cu[i], cu[i + 1]
+            if nc == 0:  # empty sequence: one empty piece so that its final state / dh0 still gets written
+                starts.append(s); ends.append(e); seq_idx.append(i); before.append(0); after.append(0)
+                lastlen.append(0); out_f.append(i); out_b.append(i)
+                continue
+            ll = (e - s) - (nc - 1) * CHUNK
+            for c0 in range(0, nc, L):
+                c1 = min(nc, c0 + L)
+                starts.append(s + c0 * CHUNK)
+                ends.append(min(e, s + c1 * CHUNK))
+                seq_idx.append(i); before.append(c0); after.append(nc - c1); lastlen.append(ll)
+                out_f.append(i if c1 == nc else -1)
+                out_b.append(i if c0 == 0 else -1)
+        bounds = starts + [cu[-1]]
+        offs = [0]
+        for a_, b_ in zip(starts, ends):
+            offs.append(offs[-1] + (b_ - a_ + CHUNK - 1) // CHUNK)
+
+        def t(x):
+            return torch.tensor(x, dtype=torch.int32, device=device)
+
+        result = CpPlan(len(starts), L, offs[-1], t(bounds), t(offs), t(seq_idx), t(out_f), t(out_b), t(starts), t(ends),
+                        t(before), t(after), t(lastlen))
+    _CP_CACHE[key] = (plan, result)
+    if len(_CP_CACHE) > _CACHE_SIZE:
+        _CP_CACHE.popitem(last=False)
+    return result

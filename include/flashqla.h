@@ -84,6 +84,40 @@ FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, const void* A
                       int total_chunks, float scale, int32_t* status_dev, void* stream);
 
 /*
+ * fq_gdr_fwd with context-parallel pieces: `cu_seqlens` holds PIECE boundaries (pieces of one
+ * sequence are contiguous and start on 64-token boundaries of their sequence).  Per piece:
+ *   h0_index[i]  slot of h0 to start from when the replay reaches the sequence start (NULL = i);
+ *   ht_index[i]  slot of ht to write, negative for non-terminal pieces (NULL = i);
+ *   warmup[i*H+h] = w | (1<<30 if the replay starts at the sequence start): the CTA first replays the
+ *                 w whole chunks before the piece (nothing stored) from h0 (bit 30) or from zero.
+ * Replaces intra_card_cp_preprocess + correct_initial_states,
+ * flash_qla/ops/gated_delta_rule/chunk/cp_context.py:106-163 and chunk/hopper/cp_fwd.py:256-309:
+ * instead of computing per-piece end states in a separate pass and chaining them, every piece
+ * warms its own state up inside the fused kernel.
+ */
+FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v, const void* A, const float* g_cumsum,
+                         const float* beta, const float* h0, float* ht, const int32_t* ht_index,
+                         const int32_t* h0_index, const int32_t* warmup, void* o, void* h_out, int B, int T, int H,
+                         int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq, int total_chunks,
+                         float scale, int32_t* status_dev, void* stream);
+
+/*
+ * Gate scan for context-parallel pieces (counterpart of get_warmup_chunks,
+ * flash_qla/ops/gated_delta_rule/chunk/hopper/cp_fwd.py:69-101).  For every (piece, head) returns in
+ * warmup[piece*H+h] the number of whole chunks adjacent to the piece that must be replayed so that
+ * older history has decayed below exp(threshold); bit 30 is set when the replay reaches the end of
+ * the sequence (then it is exact and starts from the sequence's boundary state).
+ *   reverse == 0 (forward state): piece_edge = first token of the piece, piece_aux = chunks that
+ *                precede the piece in its sequence; piece_chunks_after unused.
+ *   reverse != 0 (state gradient): piece_edge = first token after the piece, piece_chunks_after =
+ *                chunks that follow the piece in its sequence, piece_aux = token count of the
+ *                sequence's last chunk.
+ */
+FQ_API int fq_cp_warmup(const float* g_cumsum, const int32_t* piece_edge, const int32_t* piece_aux,
+                        const int32_t* piece_chunks_after, int32_t* warmup, int n_pieces, int H, float threshold,
+                        int reverse, void* stream);
+
+/*
  * Backward, serial part: reverse recurrence of the state gradient per (sequence, V-head).
  * Together with fq_gdr_bwd_chunk it replaces fused_gdr_bwd,
  * flash_qla/ops/gated_delta_rule/chunk/hopper/fused_bwd.py:900-985.
