@@ -197,16 +197,18 @@ def main():
     tokens = B * T
     scale = 128 ** -0.5
     plan = plan_dense(B, T)
+    from flashqla_b200.planner import plan_cp
+    cp = plan_cp(plan, B, T, Hv, kernels.sm_count(dev), dev)
     fwd_events = []
 
     def step(record=False):
         g_cum = kernels.chunk_local_cumsum(d["g"], plan=plan)
-        A = kernels.kkt_solve(d["k"], d["beta"], plan=plan)
+        A, Ag, Pg = kernels.kkt_solve_gated(d["k"], d["q"], d["beta"], g_cum, scale, plan)
         if record:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-        o, _, fs = kernels.fused_gdr_fwd(d["q"], d["k"], d["v"], A, g_cum, d["beta"], scale, initial_state=d["h0"],
-                                         plan=plan)
+        o, _, fs = kernels.fused_gdr_fwd(d["q"], d["k"], d["v"], Ag, Pg, g_cum, d["beta"], scale, initial_state=d["h0"],
+                                         plan=plan, cp=cp, warmup=kernels.cp_warmup(g_cum, cp, Hv) if cp is not None else None)
         if record:
             e1.record()
             fwd_events.append((e0, e1))

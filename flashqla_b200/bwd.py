@@ -8,6 +8,7 @@ import torch
 
 from . import _lib, kernels
 from .kernels import make_plan
+from .planner import plan_cp
 
 
 def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, initial_state=None, cu_seqlens=None):
@@ -35,9 +36,14 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
     if dht is not None:
         dht_c = dht.contiguous() if dht.dtype == torch.float32 else dht.float().contiguous()
 
-    # 1. state before every chunk (bf16), recomputed with the forward recurrence kernel
-    _, h, _ = kernels.fused_gdr_fwd(q, k, v, A, g, bt, scale, initial_state=h0, output_final_state=False,
-                                    output_h=True, output_o=False, plan=plan, status=status)
+    # 1. gated tiles from the given A, then the state before every chunk (bf16) with the forward
+    #    recurrence kernel in state-only mode (context parallel like the forward)
+    _, Ag, Pg = kernels.kkt_solve_gated(k, q, bt, g, scale, plan, A=A)
+    from . import ops as _ops
+    cp = plan_cp(plan, B, T, H, kernels.sm_count(dev), dev, piece_chunks=_ops._FORCE_PIECE_CHUNKS)
+    warm = kernels.cp_warmup(g, cp, H) if cp is not None else None
+    _, h, _ = kernels.fused_gdr_fwd(q, k, v, Ag, None, g, bt, scale, initial_state=h0, output_final_state=False,
+                                    output_h=True, output_o=False, plan=plan, cp=cp, warmup=warm, status=status)
     # 2. reverse recurrence of the state gradient
     dh = torch.empty_like(h)
     dvp = torch.empty_like(v)
@@ -46,10 +52,19 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
     dh0 = torch.empty(plan.n_seq, H, K, V, dtype=torch.float32, device=dev) if want_dh0 else None
     cu_p, off_p = plan.ptrs()
     lib = _lib.load()
-    rc = lib.fq_gdr_bwd_dh(q.data_ptr(), k.data_ptr(), A.data_ptr(), do.data_ptr(), g.data_ptr(), bt.data_ptr(),
-                           None if dht_c is None else dht_c.data_ptr(), None if dh0 is None else dh0.data_ptr(),
-                           dh.data_ptr(), dvp.data_ptr(), dv.data_ptr(), B, T, H, Hg, cu_p, off_p, plan.n_seq,
-                           plan.total_chunks, float(scale), st_p, kernels._stream())
+    pp = lambda t: None if t is None else t.data_ptr()
+    if cp is None:
+        rc = lib.fq_gdr_bwd_dh(q.data_ptr(), k.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), do.data_ptr(), g.data_ptr(),
+                               bt.data_ptr(), pp(dht_c), pp(dh0), dh.data_ptr(), dvp.data_ptr(), dv.data_ptr(), B, T, H, Hg,
+                               cu_p, off_p, plan.n_seq, plan.total_chunks, float(scale), st_p, kernels._stream())
+    else:
+        warm_r = kernels.cp_warmup(g, cp, H, reverse=True)
+        rc = lib.fq_gdr_bwd_dh_cp(q.data_ptr(), k.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), do.data_ptr(), g.data_ptr(),
+                                  bt.data_ptr(), pp(dht_c), pp(dh0), dh.data_ptr(), dvp.data_ptr(), dv.data_ptr(),
+                                  cp.seq_index.data_ptr(), cp.out_index_bwd.data_ptr(), cp.seq_end.data_ptr(),
+                                  warm_r.data_ptr(), 1, B * T, H, Hg, cp.cu_seqlens.data_ptr(),
+                                  cp.chunk_offsets.data_ptr(), cp.n_pieces, cp.total_chunks, float(scale), st_p,
+                                  kernels._stream())
     _lib.check(rc, "fq_gdr_bwd_dh")
     # 3. chunk-parallel gradients
     dq_h = torch.empty(B, T, H, K, dtype=q.dtype, device=dev)

@@ -2,8 +2,7 @@
 // (sequence, V-head), chunks visited last to first.  Same transposed-state layout as the forward
 // (dS^T in tensor memory: lane = v, column = k), so every product has M = 128:
 //
-//   PK   [128 x 64]  = [K;Q] K^T                 rows 64..127 -> P_g = scale * G o (Q K^T)
-//   D2   [128 x 64]  = dO^T P_g                   (state independent)
+//   D2   [128 x 64]  = dO^T P_g                   (state independent; A_g and P_g come from kkt_solve.cu)
 //   D1   [128 x 64]  = dS^T_bf16 K^T
 //        dV'^T = rho o D1 + D2                    -> scratch dvp [tokens, H, 128]
 //   DW   [128 x 64]  = dV'^T A_g                  = dv^T  (aliases D1)
@@ -20,27 +19,26 @@ namespace fq {
 
 constexpr int kDhThreads = 512;
 constexpr int kDhGateStages = 4;
-constexpr uint32_t kDhStageBytes = 32768 + 16384 + 8192;
+constexpr uint32_t kDhStageBytes = 32768 + 16384 + 8192 + 8192;
 
 constexpr uint32_t kDhColS = 0;     // fp32 dS^T
 constexpr uint32_t kDhColD1 = 128;  // D1, later DW
 constexpr uint32_t kDhColD2 = 192;
-constexpr uint32_t kDhColPK = 256;
 
 struct BwdDhSmem {
   unsigned char kq[2][32768];    // k rows 0-63 | q rows 64-127, two 128-row regions (d 0-63 | 64-127)
   unsigned char dout[2][16384];  // dO tile [64 c][128 v] as two 64-row regions
-  unsigned char a[2][8192];      // A tile, rewritten in place as A_g
+  unsigned char a[2][8192];      // A_g tile [64 i][64 j]
+  unsigned char pg[2][8192];     // P_g tile [64 i][64 j]
   unsigned char dsbf[32768];     // bf16 dS^T [128 v][128 k]
   unsigned char dvp[16384];      // dV'^T [128 v][64 c]
   unsigned char dvg[16384];      // dVg^T [128 v][64 c]
   unsigned char dos[16384];      // (scale*gamma o dO)^T [128 v][64 c]
-  unsigned char pg[8192];        // P_g [64 i][64 j]
   float gate[kDhGateStages][4][kChunk];
   uint64_t full[2], empty[2], gate_full[kDhGateStages], gate_empty[kDhGateStages];
-  uint64_t pk_done, d2_done, d1_done, dw_done, ds_done;
-  uint64_t ds_ready, ds_scaled, dvp_ready, dvg_ready, pg_ready, dos_ready;
-  uint64_t ag_ready[2];  // per stage: the A_g warps may run one iteration ahead of the UMMA issuer
+  uint64_t d2_done, d1_done, dw_done, ds_done;
+  uint64_t ds_ready, ds_scaled, dvp_ready, dvg_ready, dos_ready;
+  uint64_t pg_ready[2];  // per stage: the aux warps may run one iteration ahead of the UMMA issuer
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -53,6 +51,13 @@ struct BwdDhParams {
   __nv_bfloat16* dh_out;   // [total_chunks, H, 128, 128]
   __nv_bfloat16* dvp_out;  // [rows, H, 128]
   __nv_bfloat16* dv_out;   // [rows, H, 128]
+  // context parallel (all nullptr for whole sequences): per piece the slot of dht / dh0 and the first
+  // token after the piece's sequence; per (piece, head) the chunks to replay AFTER the piece
+  // (bit 30: the replay starts at the sequence end, i.e. from dht).
+  const int* dht_index;
+  const int* dh0_index;
+  const int* seq_end;
+  const int* warmup;
   int H, Hg;
   float scale;
   SeqArgs sa;
@@ -75,7 +80,7 @@ __device__ __forceinline__ void store_cols_bf16(unsigned short* base, size_t row
 __global__ void __launch_bounds__(kDhThreads, 1)
 gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_a,
-                  const BwdDhParams p) {
+                  const __grid_constant__ CUtensorMap map_pg, const BwdDhParams p) {
   extern __shared__ unsigned char smem_dyn[];
   BwdDhSmem& s = *reinterpret_cast<BwdDhSmem*>(
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
@@ -93,18 +98,25 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     chunk_off = __ldg(p.sa.chunk_offsets + seq);
   }
   const int nchunks = (seq_len + kChunk - 1) / kChunk;
+  const int warm_code = p.warmup ? __ldg(p.warmup + static_cast<size_t>(seq) * p.H + h) : (1 << 30);
+  const int warm = warm_code & 0xFFFFFF;
+  const bool use_dht = (warm_code >> 30) & 1;
+  const int total = nchunks > 0 ? nchunks + warm : 0;  // iteration `it` handles chunk n = total - 1 - it of the piece
+  // tokens available from the piece start to the end of its sequence (bounds the length of replayed chunks)
+  const int avail = p.seq_end ? __ldg(p.seq_end + seq) - tok_begin : seq_len;
   WaitCtx wc{&s.abort_flag, p.status_dev, 2};
 
   if (tid == 0) {
     s.abort_flag = 0;
     for (int i = 0; i < 2; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 5); }
     for (int i = 0; i < kDhGateStages; ++i) { mbar_init(&s.gate_full[i], 64); mbar_init(&s.gate_empty[i], 12); }
-    mbar_init(&s.pk_done, 1); mbar_init(&s.d2_done, 1); mbar_init(&s.d1_done, 1); mbar_init(&s.dw_done, 1);
+    mbar_init(&s.d2_done, 1); mbar_init(&s.d1_done, 1); mbar_init(&s.dw_done, 1);
     mbar_init(&s.ds_done, 1);
     mbar_init(&s.ds_ready, 4); mbar_init(&s.ds_scaled, 4); mbar_init(&s.dvp_ready, 4); mbar_init(&s.dvg_ready, 4);
-    mbar_init(&s.dos_ready, 4); mbar_init(&s.ag_ready[0], 2); mbar_init(&s.ag_ready[1], 2); mbar_init(&s.pg_ready, 2);
+    mbar_init(&s.dos_ready, 4); mbar_init(&s.pg_ready[0], 4); mbar_init(&s.pg_ready[1], 4);
     fence_mbar_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_pg);
   }
   if (warp == 1) {
     tmem_alloc(&s.tmem_base, 512);
@@ -118,8 +130,8 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      for (int it = 0; it < nchunks; ++it) {
-        const int n = nchunks - 1 - it, st = it & 1;
+      for (int it = 0; it < total; ++it) {
+        const int n = total - 1 - it, st = it & 1;
         if (it >= 2 && !mbar_wait(wc, &s.empty[st], ((it >> 1) + 1) & 1, 1)) break;
         mbar_arrive_expect_tx(&s.full[st], kDhStageBytes);
         const int row = tok_begin + n * kChunk;
@@ -130,6 +142,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         tma_load_3d(s.dout[st], &map_do, &s.full[st], 0, h, row);
         tma_load_3d(s.dout[st] + 8192, &map_do, &s.full[st], 64, h, row);
         tma_load_3d(s.a[st], &map_a, &s.full[st], 0, h, row);
+        tma_load_3d(s.pg[st], &map_pg, &s.full[st], 0, h, row);
       }
     }
   } else if (warp == 1) {
@@ -139,20 +152,14 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       constexpr uint32_t id64_bmn = umma_idesc(128, 64, false, true, true);
       constexpr uint32_t id64_abmn = umma_idesc(128, 64, true, true, true);
       constexpr uint32_t id128_bmn = umma_idesc(128, 128, false, true, true);
-      const uint32_t sds = smem_u32(s.dsbf), sdvp = smem_u32(s.dvp), sdvg = smem_u32(s.dvg), sdos = smem_u32(s.dos),
-                     spg = smem_u32(s.pg);
-      for (int it = 0; it < nchunks; ++it) {
+      const uint32_t sds = smem_u32(s.dsbf), sdvp = smem_u32(s.dvp), sdvg = smem_u32(s.dvg), sdos = smem_u32(s.dos);
+      for (int it = 0; it < total; ++it) {
         const int st = it & 1;
         const uint32_t ph = it & 1;
-        const uint32_t skq = smem_u32(s.kq[st]), sa = smem_u32(s.a[st]), sdo = smem_u32(s.dout[st]);
+        const uint32_t skq = smem_u32(s.kq[st]), sa = smem_u32(s.a[st]), sdo = smem_u32(s.dout[st]), spg = smem_u32(s.pg[st]);
         if (!mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2)) break;
         tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tm + kDhColPK, umma_desc_sw128(skq + dh_koff(kk), 16, 1024), umma_desc_sw128(skq + dh_koff(kk), 16, 1024),
-                  id64, kk > 0);
-        umma_commit(&s.pk_done);
-        if (!mbar_wait(wc, &s.pg_ready, ph, 3)) break;
+        if (!mbar_wait(wc, &s.pg_ready[st], (it >> 1) & 1, 3)) break;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
@@ -167,7 +174,6 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                   id64, kk > 0);
         umma_commit(&s.d1_done);
         if (!mbar_wait(wc, &s.dvp_ready, ph, 5)) break;
-        if (!mbar_wait(wc, &s.ag_ready[st], (it >> 1) & 1, 6)) break;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
@@ -193,10 +199,10 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   } else if (warp < 4) {
     // ------------------------------------------------------------------ gate loader
     const int t = tid - 64;
-    for (int it = 0; it < nchunks; ++it) {
-      const int n = nchunks - 1 - it, gs = it & (kDhGateStages - 1);
+    for (int it = 0; it < total; ++it) {
+      const int n = total - 1 - it, gs = it & (kDhGateStages - 1);
       if (it >= kDhGateStages && !mbar_wait(wc, &s.gate_empty[gs], ((it >> 2) + 1) & 1, 10)) break;
-      const int len = min(kChunk, seq_len - n * kChunk);
+      const int len = min(kChunk, avail - n * kChunk);
       const size_t row = static_cast<size_t>(tok_begin) + n * kChunk;
       const float gl = __ldg(p.g_cum + (row + len - 1) * p.H + h);
       float gi = gl, bi = 0.f;
@@ -215,10 +221,10 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int v = tid - 128;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32;
     const size_t rs = static_cast<size_t>(p.H) * kDim;
-    for (int it = 0; it < nchunks; ++it) {
-      const int n = nchunks - 1 - it, gs = it & (kDhGateStages - 1);
+    for (int it = 0; it < total; ++it) {
+      const int n = total - 1 - it, gs = it & (kDhGateStages - 1);
       const uint32_t ph = it & 1;
-      const int len = min(kChunk, seq_len - n * kChunk);
+      const int len = min(kChunk, avail - n * kChunk);
       const size_t goff = (static_cast<size_t>(tok_begin) + n * kChunk) * rs + static_cast<size_t>(h) * kDim + v;
       if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 11)) break;
       if (!mbar_wait(wc, &s.d2_done, ph, 12)) break;
@@ -246,7 +252,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.dvp_ready);
-      store_cols_bf16(reinterpret_cast<unsigned short*>(p.dvp_out) + goff, rs, packed, len);
+      if (n < nchunks) store_cols_bf16(reinterpret_cast<unsigned short*>(p.dvp_out) + goff, rs, packed, len);
       if (!mbar_wait(wc, &s.dw_done, ph, 14)) break;
       tc_fence_after();
       uint32_t pg2[32];
@@ -270,14 +276,15 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       fence_async_smem();
       __syncwarp();
       if (lane == 0) { mbar_arrive(&s.dvg_ready); mbar_arrive(&s.gate_empty[gs]); }
-      store_cols_bf16(reinterpret_cast<unsigned short*>(p.dv_out) + goff, rs, packed, len);
+      if (n < nchunks) store_cols_bf16(reinterpret_cast<unsigned short*>(p.dv_out) + goff, rs, packed, len);
     }
   } else if (warp < 12) {
     // ------------------------------------------------------------------ state gradient: TMEM <-> bf16 operand, decay, dh
     const int v = tid - 256;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32;
     {
-      const float* src = p.dht ? p.dht + (static_cast<size_t>(seq) * p.H + h) * kDim * kDim + v : nullptr;
+      const int in_slot = p.dht_index ? __ldg(p.dht_index + seq) : seq;
+      const float* src = (p.dht && use_dht) ? p.dht + (static_cast<size_t>(in_slot) * p.H + h) * kDim * kDim + v : nullptr;
 #pragma unroll 1
       for (int cb = 0; cb < 4; ++cb) {
         uint32_t r[32];
@@ -288,15 +295,15 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       tmem_wait_st();
     }
     bool alive = true;
-    for (int it = 0; it < nchunks && alive; ++it) {
-      const int n = nchunks - 1 - it, gs = it & (kDhGateStages - 1);
+    for (int it = 0; it < total && alive; ++it) {
+      const int n = total - 1 - it, gs = it & (kDhGateStages - 1);
       if (it > 0) {
         if (!mbar_wait(wc, &s.ds_done, (it - 1) & 1, 15)) { alive = false; break; }
         tc_fence_after();
       }
       if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 16)) { alive = false; break; }
       const float gL = s.gate[gs][1][kChunk - 1];
-      __nv_bfloat16* hdst = p.dh_out + (static_cast<size_t>(chunk_off + n) * p.H + h) * kDim * kDim + v;
+      __nv_bfloat16* hdst = (n < nchunks) ? p.dh_out + (static_cast<size_t>(chunk_off + n) * p.H + h) * kDim * kDim + v : nullptr;
 #pragma unroll 1
       for (int cb = 0; cb < 4; ++cb) {
         uint32_t r[32];
@@ -311,8 +318,10 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           q4.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
           *reinterpret_cast<uint4*>(s.dsbf + (cb >> 1) * 16384 + sw128(v, (cb & 1) * 64 + j * 16)) = q4;
         }
+        if (hdst) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) hdst[static_cast<size_t>(cb * 32 + i) * kDim] = __float2bfloat16(__uint_as_float(r[i]));
+          for (int i = 0; i < 32; ++i) hdst[static_cast<size_t>(cb * 32 + i) * kDim] = __float2bfloat16(__uint_as_float(r[i]));
+        }
 #pragma unroll
         for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * gL);
         tmem_st32(tmem_addr(tm, lane_base, kDhColS + cb * 32), r);
@@ -325,12 +334,13 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       __syncwarp();
       if (lane == 0) { mbar_arrive(&s.ds_scaled); mbar_arrive(&s.gate_empty[gs]); }
     }
-    if (alive && nchunks > 0) {
-      alive = mbar_wait(wc, &s.ds_done, (nchunks - 1) & 1, 17);
+    if (alive && total > 0) {
+      alive = mbar_wait(wc, &s.ds_done, (total - 1) & 1, 17);
       tc_fence_after();
     }
-    if (alive && p.dh0) {
-      float* dst = p.dh0 + (static_cast<size_t>(seq) * p.H + h) * kDim * kDim + v;
+    const int out_slot = p.dh0_index ? __ldg(p.dh0_index + seq) : seq;
+    if (alive && p.dh0 && out_slot >= 0) {
+      float* dst = p.dh0 + (static_cast<size_t>(out_slot) * p.H + h) * kDim * kDim + v;
 #pragma unroll 1
       for (int cb = 0; cb < 4; ++cb) {
         uint32_t r[32];
@@ -341,64 +351,25 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
     }
   } else {
-    // ------------------------------------------------------------------ A_g, P_g, scaled dO^T
-    const int wid = warp - 12;
+    // ------------------------------------------------------------------ tail fix of P_g, scaled dO^T
     const int v = tid - 384;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32;
-    for (int it = 0; it < nchunks; ++it) {
-      const int n = nchunks - 1 - it, st = it & 1, gs = it & (kDhGateStages - 1);
+    for (int it = 0; it < total; ++it) {
+      const int n = total - 1 - it, st = it & 1, gs = it & (kDhGateStages - 1);
       const uint32_t ph = it & 1;
-      const int len = min(kChunk, seq_len - n * kChunk);
+      const int len = min(kChunk, avail - n * kChunk);
       if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 18)) break;
       if (!mbar_wait(wc, &s.full[st], (it >> 1) & 1, 19)) break;
-      if (wid < 2) {
-        const int i = wid * 32 + lane;
-        const float gi = s.gate[gs][0][i];
-#pragma unroll
-        for (int j8 = 0; j8 < 8; ++j8) {
-          uint4* ptr = reinterpret_cast<uint4*>(s.a[st] + sw128(i, j8 * 16));
-          uint4 a4 = *ptr;
-          uint32_t* aw = reinterpret_cast<uint32_t*>(&a4);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int j = j8 * 8 + 2 * e;
-            const float x0 = (j <= i) ? bf16_lo(aw[e]) * fast_exp(gi - s.gate[gs][0][j]) * s.gate[gs][3][j] : 0.f;
-            const float x1 = (j + 1 <= i) ? bf16_hi(aw[e]) * fast_exp(gi - s.gate[gs][0][j + 1]) * s.gate[gs][3][j + 1] : 0.f;
-            aw[e] = pack_bf16(x0, x1);
-          }
-          *ptr = a4;
+      // P_g rows past the sequence end were produced for the NEXT sequence's tokens: clear them
+      if (len < kChunk) {
+        for (int idx = v; idx < (kChunk - len) * 8; idx += 128) {
+          const int r = len + (idx >> 3), pc = idx & 7;
+          *reinterpret_cast<uint4*>(s.pg[st] + r * 128 + pc * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s.ag_ready[st]);
-      } else {
-        if (!mbar_wait(wc, &s.pk_done, ph, 20)) break;
-        tc_fence_after();
-        const int i = (wid - 2) * 32 + lane;
-        const float gi = s.gate[gs][0][i];
-        const bool row_ok = i < len;  // rows past the sequence end hold another sequence's tokens
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t r[32];
-          tmem_ld32(tmem_addr(tm, lane_base, kDhColPK + half * 32), r);
-          tmem_wait_ld();
-          uint32_t pk[16];
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const int j = half * 32 + e;
-            const float x0 = (row_ok && j <= i) ? p.scale * fast_exp(gi - s.gate[gs][0][j]) * __uint_as_float(r[e]) : 0.f;
-            const float x1 = (row_ok && j + 1 <= i) ? p.scale * fast_exp(gi - s.gate[gs][0][j + 1]) * __uint_as_float(r[e + 1]) : 0.f;
-            pk[e >> 1] = pack_bf16(x0, x1);
-          }
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<uint4*>(s.pg + sw128(i, half * 64 + j * 16)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-        }
-        tc_fence_before();
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s.pg_ready);
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.pg_ready[st]);
       // (scale * gamma_c * dO[c][v])^T; the previous iteration's state update must have consumed the buffer
       if (it > 0 && !mbar_wait(wc, &s.ds_done, (it - 1) & 1, 21)) break;
       {
@@ -430,13 +401,23 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
 }  // namespace fq
 
-extern "C" FQ_API int fq_gdr_bwd_dh(const void* q, const void* k, const void* A, const void* dout, const float* g_cumsum,
-                                    const float* beta, const float* dht, float* dh0, void* dh_out, void* dvp_out,
-                                    void* dv_out, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
-                                    const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
-                                    int32_t* status_dev, void* stream) {
+extern "C" FQ_API int fq_gdr_bwd_dh(const void* q, const void* k, const void* Ag, const void* Pg, const void* dout,
+                                    const float* g_cumsum, const float* beta, const float* dht, float* dh0,
+                                    void* dh_out, void* dvp_out, void* dv_out, int B, int T, int H, int Hg,
+                                    const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
+                                    int total_chunks, float scale, int32_t* status_dev, void* stream) {
+  return fq_gdr_bwd_dh_cp(q, k, Ag, Pg, dout, g_cumsum, beta, dht, dh0, dh_out, dvp_out, dv_out, nullptr, nullptr, nullptr,
+                          nullptr, B, T, H, Hg, cu_seqlens, chunk_offsets, n_seq, total_chunks, scale, status_dev, stream);
+}
+
+extern "C" FQ_API int fq_gdr_bwd_dh_cp(const void* q, const void* k, const void* Ag, const void* Pg, const void* dout,
+                                       const float* g_cumsum, const float* beta, const float* dht, float* dh0,
+                                       void* dh_out, void* dvp_out, void* dv_out, const int32_t* dht_index,
+                                       const int32_t* dh0_index, const int32_t* seq_end, const int32_t* warmup, int B,
+                                       int T, int H, int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets,
+                                       int n_seq, int total_chunks, float scale, int32_t* status_dev, void* stream) {
   using namespace fq;
-  FQ_CHECK_ARG(q && k && A && dout && g_cumsum && beta && dh_out && dvp_out && dv_out, "fq_gdr_bwd_dh: null tensor");
+  FQ_CHECK_ARG(q && k && Ag && Pg && dout && g_cumsum && beta && dh_out && dvp_out && dv_out, "fq_gdr_bwd_dh: null tensor");
   FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0,
                "fq_gdr_bwd_dh: bad sizes");
   FQ_CHECK_ARG((cu_seqlens == nullptr) == (chunk_offsets == nullptr),
@@ -445,17 +426,20 @@ extern "C" FQ_API int fq_gdr_bwd_dh(const void* q, const void* k, const void* A,
   FQ_CHECK_ARG(cu_seqlens != nullptr || n_seq == B, "fq_gdr_bwd_dh: dense batches need n_seq == B");
   const uint64_t rows = static_cast<uint64_t>(B) * static_cast<uint64_t>(T);
   FQ_CHECK_ARG(rows > 0 && rows < (1ull << 31), "fq_gdr_bwd_dh: token count out of range");
-  CUtensorMap mq, mk, mdo, ma;
+  CUtensorMap mq, mk, mdo, ma, mpg;
   int rc;
   if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdo, dout, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
-  if ((rc = make_tmap_rows_heads_dim(&ma, A, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&ma, Ag, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mpg, Pg, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
   BwdDhParams p;
   p.g_cum = g_cumsum; p.beta = beta; p.dht = dht; p.dh0 = dh0;
   p.dh_out = static_cast<__nv_bfloat16*>(dh_out);
   p.dvp_out = static_cast<__nv_bfloat16*>(dvp_out);
   p.dv_out = static_cast<__nv_bfloat16*>(dv_out);
+  p.dht_index = dht_index; p.dh0_index = dh0_index; p.seq_end = seq_end; p.warmup = warmup;
+  p.dht_index = dht_index; p.dh0_index = dh0_index; p.seq_end = seq_end; p.warmup = warmup;
   p.H = H; p.Hg = Hg; p.scale = scale;
   p.sa = SeqArgs{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
   p.status_dev = status_dev;
@@ -469,7 +453,7 @@ extern "C" FQ_API int fq_gdr_bwd_dh(const void* q, const void* k, const void* A,
   }
   const long long ctas = static_cast<long long>(n_seq) * H;
   FQ_CHECK_ARG(ctas < (1ll << 31), "fq_gdr_bwd_dh: too many (sequence, head) pairs");
-  gdr_bwd_dh_kernel<<<static_cast<unsigned>(ctas), kDhThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mdo, ma, p);
+  gdr_bwd_dh_kernel<<<static_cast<unsigned>(ctas), kDhThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mdo, ma, mpg, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }

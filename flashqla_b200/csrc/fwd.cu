@@ -1,17 +1,19 @@
 // Fused GDN forward: inter-chunk state recurrence + chunk outputs, one persistent CTA per
-// (sequence piece, V-head).  All contractions run on tcgen05 with the state kept TRANSPOSED in
-// tensor memory (S^T: lane = v, column = k), so that every product has M = 128:
+// (sequence piece, V-head).  The chunk-parallel operand tiles A_g = A o G o beta_col and
+// P_g = scale * G o (Q K^T) come from the pre-kernel (kkt_solve.cu); this kernel carries only what is
+// serial.  The state is kept TRANSPOSED in tensor memory (S^T: lane = v, column = k), so the
+// products on the critical chain have M = 128:
 //
-//   PK   [128 x 64]  = [K;Q] K^T            rows 64..127 give Q K^T            (state independent)
 //   U    [128 x 64]  = S^T_bf16 K^T
-//   VD   [128 x 64]  = V^T A_g^T - (gamma o U)^T A_g^T   = V_d^T; the V term is state independent
-//   O    [64 x 128]  = Q~ S + P_g V_d        natural orientation (row = token), Q~ = scale*gamma o Q
-//   S   += V'^T K                           V' = rho o V_d; S was pre-scaled by gamma_last
+//   VD   [128 x 64]  = V^T A_g^T - (gamma o U)^T A_g^T = V_d^T     (the V term is state independent:
+//                                                                  its A operand is the V tile as loaded)
+//   S   += V'^T K                                                  V' = rho o V_d; S pre-scaled by gamma_last
+//   OI   [64 x 128]  = Q S,   OX [64 x 128] = P_g V_d              natural orientation (row = token)
 //
-// Per chunk:  o = scale*gamma o (Q S) + P_g V_d,   S <- gamma_last S + K^T V'.
+// Per chunk:  o = scale*gamma o OI + OX,   S <- gamma_last S + K^T V'.
 // Warp roles (16 warps): 0 TMA producer, 1 UMMA issuer, 2-3 gate loader, 4-11 chain group
-// (TMEM state -> bf16 operand + decay, then -gamma o U, then V_d / V'), 12-15 A_g / P_g / Q~ and the
-// output tile (row-contiguous stores straight from the accumulator).
+// (TMEM state -> bf16 operand + decay, then -gamma o U, then V_d / V'), 12-15 output tile
+// (row-contiguous stores straight from the accumulators).
 //
 // Context parallel: a CTA may own a piece of a sequence.  It then first replays `w` whole chunks
 // that precede the piece (state only, nothing stored) starting from a zero state - or from the
@@ -35,28 +37,27 @@ __device__ long long g_trace[8][32];
 
 constexpr int kFwdThreads = 512;
 constexpr int kGateStages = 4;
-constexpr uint32_t kStageBytes = 32768 + 16384 + 8192;
+constexpr uint32_t kStageBytes = 32768 + 16384 + 8192 + 8192;
 
 // TMEM column map (512 columns allocated)
 constexpr uint32_t kColS = 0;     // fp32 state S^T, 128 columns
 constexpr uint32_t kColUQ = 128;  // U^T, 64 columns
 constexpr uint32_t kColVD = 192;  // V_d^T, 64 columns
-constexpr uint32_t kColPK = 256;  // [K;Q] K^T, 64 columns
-constexpr uint32_t kColO = 320;   // O [64 x 128] (M = 64: rows in lanes 0-15 of every 32-lane quarter)
+constexpr uint32_t kColOI = 256;  // Q S      [64 x 128] (M = 64: rows in lanes 0-15 of every 32-lane quarter)
+constexpr uint32_t kColOX = 384;  // P_g V_d  [64 x 128]
 
 struct FwdSmem {
   unsigned char kq[2][32768];  // per stage, two 128-row x 128-byte regions (d 0-63 | d 64-127); rows 0-63 k, 64-127 q
   unsigned char v[2][16384];   // per stage, two 64-row x 128-byte regions (v 0-63 | v 64-127)
-  unsigned char a[2][8192];    // per stage, A tile [64 i][64 j]; rewritten in place as A_g
+  unsigned char a[2][8192];    // per stage, A_g tile [64 i][64 j]
+  unsigned char pg[2][8192];   // per stage, P_g tile [64 i][64 j]
   unsigned char sbf[32768];    // bf16 S^T [128 v][128 k] as two 128-row regions
   unsigned char w[16384];      // -(gamma o U)^T, later V'^T   [128 v][64 c]
   unsigned char vd[16384];     // V_d^T             [128 v][64 i]
-  unsigned char pg[8192];      // P_g               [64 i][64 j]
-  unsigned char qs[16384];     // Q~ = scale*gamma o Q  [64 c][128 k] (two 64-row regions)
   float gate[kGateStages][4][kChunk];  // g, exp(g), exp(g_last - g), beta
   uint64_t full[2], empty[2], gate_full[kGateStages], gate_empty[kGateStages];
-  uint64_t pk_done, uq_done, vd_done, s_done, o_done;
-  uint64_t s_ready, s_scaled, w_ready, vp_ready, ag_ready, pg_ready, qs_ready, o_free;
+  uint64_t uq_done, vd_done, s_done, o_done;
+  uint64_t s_ready, s_scaled, w_ready, vp_ready, o_free;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -85,7 +86,7 @@ __device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t bytes) { retur
 __global__ void __launch_bounds__(kFwdThreads, 1)
 gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_a,
-               const __grid_constant__ CUtensorMap map_o, const FwdParams p) {
+               const __grid_constant__ CUtensorMap map_pg, const FwdParams p) {
   extern __shared__ unsigned char smem_dyn[];
   FwdSmem& s = *reinterpret_cast<FwdSmem*>(
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
@@ -113,12 +114,12 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     s.abort_flag = 0;
     for (int i = 0; i < 2; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
     for (int i = 0; i < kGateStages; ++i) { mbar_init(&s.gate_full[i], 64); mbar_init(&s.gate_empty[i], 12); }
-    mbar_init(&s.pk_done, 1); mbar_init(&s.uq_done, 1); mbar_init(&s.vd_done, 1); mbar_init(&s.s_done, 1);
-    mbar_init(&s.o_done, 1); mbar_init(&s.qs_ready, 4);
+    mbar_init(&s.uq_done, 1); mbar_init(&s.vd_done, 1); mbar_init(&s.s_done, 1); mbar_init(&s.o_done, 1);
     mbar_init(&s.s_ready, 8); mbar_init(&s.s_scaled, 8); mbar_init(&s.w_ready, 8); mbar_init(&s.vp_ready, 8);
-    mbar_init(&s.o_free, 4); mbar_init(&s.ag_ready, 2); mbar_init(&s.pg_ready, 2);
+    mbar_init(&s.o_free, 4);
     fence_mbar_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_pg);
   }
   if (warp == 1) {
     tmem_alloc(&s.tmem_base, 512);
@@ -144,6 +145,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tma_load_3d(s.v[st], &map_v, &s.full[st], 0, h, row);
         tma_load_3d(s.v[st] + 8192, &map_v, &s.full[st], 64, h, row);
         tma_load_3d(s.a[st], &map_a, &s.full[st], 0, h, row);
+        tma_load_3d(s.pg[st], &map_pg, &s.full[st], 0, h, row);
       }
     }
   } else if (warp == 1) {
@@ -153,56 +155,51 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       constexpr uint32_t id64_amn = umma_idesc(128, 64, true, false, true);
       constexpr uint32_t id128_bmn = umma_idesc(128, 128, false, true, true);
       constexpr uint32_t id_o = umma_idesc(64, 128, false, false, true);
+      const bool want_o = p.o != nullptr;
       const uint64_t d_sbf = umma_desc_sw128(smem_u32(s.sbf), 16, 1024);
       const uint64_t d_w = umma_desc_sw128(smem_u32(s.w), 16, 1024);
       const uint64_t d_vd = umma_desc_sw128(smem_u32(s.vd), 16, 1024);
-      const uint64_t d_pg = umma_desc_sw128(smem_u32(s.pg), 16, 1024);
-      const uint64_t d_qs = umma_desc_sw128(smem_u32(s.qs), 16, 1024);
-      uint64_t d_kq[2], d_kmn[2], d_a[2], d_vmn[2];
-      for (int i = 0; i < 2; ++i) {
-        d_vmn[i] = umma_desc_sw128(smem_u32(s.v[i]), 8192, 1024);
-        d_kq[i] = umma_desc_sw128(smem_u32(s.kq[i]), 16, 1024);
-        d_kmn[i] = umma_desc_sw128(smem_u32(s.kq[i]), 16384, 1024);
-        d_a[i] = umma_desc_sw128(smem_u32(s.a[i]), 16, 1024);
-      }
+      // stage-0 descriptors; stage 1 adds the stage stride to the address field (kept in registers)
+      const uint64_t d_vmn0 = umma_desc_sw128(smem_u32(s.v[0]), 8192, 1024);
+      const uint64_t d_kq0 = umma_desc_sw128(smem_u32(s.kq[0]), 16, 1024);
+      const uint64_t d_kmn0 = umma_desc_sw128(smem_u32(s.kq[0]), 16384, 1024);
+      const uint64_t d_a0 = umma_desc_sw128(smem_u32(s.a[0]), 16, 1024);
+      const uint64_t d_pg0 = umma_desc_sw128(smem_u32(s.pg[0]), 16, 1024);
       for (int it = 0; it < total; ++it) {
         const int st = it & 1;
         const uint32_t ph = it & 1;
+        const bool do_o = want_o && it >= warm;
+        const uint64_t d_vmn = desc_add(d_vmn0, st * 16384), d_kq = desc_add(d_kq0, st * 32768),
+                       d_kmn = desc_add(d_kmn0, st * 32768), d_a = desc_add(d_a0, st * 8192),
+                       d_pg = desc_add(d_pg0, st * 8192);
         if (!mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2)) break;
         FQ_TS(it, 0);
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)  // PK = [K;Q] K^T
-          umma_ss(tm + kColPK, desc_add(d_kq[st], kq_off(kk)), desc_add(d_kq[st], kq_off(kk)), id64, kk > 0);
-        umma_commit(&s.pk_done);
+        for (int kk = 0; kk < 4; ++kk)  // V_d^T = V^T A_g^T (A operand = the V tile as loaded, MN-major)
+          umma_ss(tm + kColVD, desc_add(d_vmn, kk * 2048), desc_add(d_a, kk * 32), id64_amn, kk > 0);
         if (!mbar_wait(wc, &s.s_ready, ph, 3)) break;
         FQ_TS(it, 1);
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)  // U^T = S^T K^T
-          umma_ss(tm + kColUQ, desc_add(d_sbf, kq_off(kk)), desc_add(d_kq[st], kq_off(kk)), id64, kk > 0);
+          umma_ss(tm + kColUQ, desc_add(d_sbf, kq_off(kk)), desc_add(d_kq, kq_off(kk)), id64, kk > 0);
         umma_commit(&s.uq_done);
         FQ_TS(it, 3);
-        if (!mbar_wait(wc, &s.ag_ready, ph, 6)) break;
-        FQ_TS(it, 5);
-        tc_fence_after();
+        if (do_o) {  // OI = Q S: the accumulators of the previous chunk must have been drained
+          if (it > 0 && !mbar_wait(wc, &s.o_free, (it - 1) & 1, 4)) break;
+          FQ_TS(it, 2);
+          tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)  // V_d^T = V^T A_g^T (A operand = the V tile as loaded, MN-major)
-          umma_ss(tm + kColVD, desc_add(d_vmn[st], kk * 2048), desc_add(d_a[st], kk * 32), id64_amn, kk > 0);
-        // O = Q~ S: needs the output accumulator of the previous chunk to be drained and Q~ of this chunk
-        if (it > 0 && !mbar_wait(wc, &s.o_free, (it - 1) & 1, 4)) break;
-        if (!mbar_wait(wc, &s.qs_ready, ph, 22)) break;
-        FQ_TS(it, 2);
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tm + kColO, desc_add(d_qs, (kk >> 2) * 8192 + (kk & 3) * 32), desc_add(d_sbf, kq_off(kk)), id_o, kk > 0);
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(tm + kColOI, desc_add(d_kq, 8192 + kq_off(kk)), desc_add(d_sbf, kq_off(kk)), id_o, kk > 0);
+        }
         if (!mbar_wait(wc, &s.w_ready, ph, 5)) break;
         FQ_TS(it, 4);
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // V_d^T -= (gamma o U)^T A_g^T
-          umma_ss(tm + kColVD, desc_add(d_w, kk * 32), desc_add(d_a[st], kk * 32), id64, 1);
+          umma_ss(tm + kColVD, desc_add(d_w, kk * 32), desc_add(d_a, kk * 32), id64, 1);
         umma_commit(&s.vd_done);
         FQ_TS(it, 6);
         if (!mbar_wait(wc, &s.vp_ready, ph, 7)) break;
@@ -212,14 +209,14 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // S^T += V'^T K
-          umma_ss(tm + kColS, desc_add(d_w, kk * 32), desc_add(d_kmn[st], kk * 2048), id128_bmn, 1);
+          umma_ss(tm + kColS, desc_add(d_w, kk * 32), desc_add(d_kmn, kk * 2048), id128_bmn, 1);
         umma_commit(&s.s_done);
         FQ_TS(it, 9);
-        if (!mbar_wait(wc, &s.pg_ready, ph, 8)) break;
-        tc_fence_after();
+        if (do_o) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)  // O += P_g V_d
-          umma_ss(tm + kColO, desc_add(d_pg, kk * 32), desc_add(d_vd, kk * 32), id_o, 1);
+          for (int kk = 0; kk < 4; ++kk)  // OX = P_g V_d
+            umma_ss(tm + kColOX, desc_add(d_pg, kk * 32), desc_add(d_vd, kk * 32), id_o, kk > 0);
+        }
         umma_commit(&s.o_done);
         umma_commit(&s.empty[st]);
       }
@@ -381,134 +378,40 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------------ A_g, P_g, Q~ and the output tile
-    // Order per iteration: drain the finished output accumulator (row-contiguous stores), release it,
-    // then prepare Q~ / A_g / P_g of the NEXT chunk (the chain needs them early).
-    const int wid = warp - 12;
-    const int ta = tid - 384;
+    // ------------------------------------------------------------------ output tile
+    // o[c][:] = scale * gamma_c * OI[c][:] + OX[c][:]; thread (lane < 16) owns token row c = 16 * quarter + lane
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32;
-    bool ok = true;
-
-    auto prepare = [&](int it) -> bool {
-      const int st = it & 1, gs = it & (kGateStages - 1);
-      if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 18)) return false;
-      if (!mbar_wait(wc, &s.full[st], (it >> 1) & 1, 19)) return false;
-      {  // Q~[c][:] = scale * gamma_c * q[c][:]; thread = (row, 64-column half)
-        const int r = ta >> 1, hq = ta & 1;
-        const float f = p.scale * s.gate[gs][1][r];
-        const unsigned char* src = s.kq[st] + hq * 16384 + 8192;
-        unsigned char* dst = s.qs + hq * 8192;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t so = sw128(r, j * 16);
-          uint4 x = *reinterpret_cast<const uint4*>(src + so);
-          uint32_t* xw = reinterpret_cast<uint32_t*>(&x);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) xw[e] = pack_bf16(f * bf16_lo(xw[e]), f * bf16_hi(xw[e]));
-          *reinterpret_cast<uint4*>(dst + so) = x;
-        }
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s.qs_ready);
-      }
-      if (wid < 2) {  // A_g = A o G o beta_col, in place; 16-byte pieces above the diagonal are just zeroed
-        const int i = wid * 32 + lane;
-        const float gi = s.gate[gs][0][i];
-#pragma unroll
-        for (int j8 = 0; j8 < 8; ++j8) {
-          uint4* ptr = reinterpret_cast<uint4*>(s.a[st] + sw128(i, j8 * 16));
-          if (j8 * 8 > wid * 32 + 31) {  // whole warp is above the diagonal here
-            *ptr = make_uint4(0, 0, 0, 0);
-            continue;
-          }
-          uint4 a4 = *ptr;
-          uint32_t* aw = reinterpret_cast<uint32_t*>(&a4);
-          const float4 g0 = *reinterpret_cast<const float4*>(&s.gate[gs][0][j8 * 8]);
-          const float4 g1 = *reinterpret_cast<const float4*>(&s.gate[gs][0][j8 * 8 + 4]);
-          const float4 b0 = *reinterpret_cast<const float4*>(&s.gate[gs][3][j8 * 8]);
-          const float4 b1 = *reinterpret_cast<const float4*>(&s.gate[gs][3][j8 * 8 + 4]);
-          const float gj[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-          const float bj[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int j = j8 * 8 + 2 * e;
-            const float x0 = (j <= i) ? bf16_lo(aw[e]) * fast_exp(gi - gj[2 * e]) * bj[2 * e] : 0.f;
-            const float x1 = (j + 1 <= i) ? bf16_hi(aw[e]) * fast_exp(gi - gj[2 * e + 1]) * bj[2 * e + 1] : 0.f;
-            aw[e] = pack_bf16(x0, x1);
-          }
-          *ptr = a4;
-        }
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s.ag_ready);
-      } else {  // P_g = scale * G o (Q K^T) from TMEM lanes 64..127
-        if (!mbar_wait(wc, &s.pk_done, it & 1, 20)) return false;
-        tc_fence_after();
-        const int w2 = wid - 2;
-        const int i = w2 * 32 + lane;
-        const float gi = s.gate[gs][0][i];
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t pk[16];
-          if (half > w2) {  // columns 32..63 for rows 0..31: above the diagonal
-#pragma unroll
-            for (int e = 0; e < 16; ++e) pk[e] = 0u;
-          } else {
-            uint32_t r[32];
-            tmem_ld32(tmem_addr(tm, lane_base, kColPK + half * 32), r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 32; e += 4) {
-              const float4 g4 = *reinterpret_cast<const float4*>(&s.gate[gs][0][half * 32 + e]);
-              const float gj[4] = {g4.x, g4.y, g4.z, g4.w};
-#pragma unroll
-              for (int z = 0; z < 4; z += 2) {
-                const int j = half * 32 + e + z;
-                const float x0 = (j <= i) ? p.scale * fast_exp(gi - gj[z]) * __uint_as_float(r[e + z]) : 0.f;
-                const float x1 = (j + 1 <= i) ? p.scale * fast_exp(gi - gj[z + 1]) * __uint_as_float(r[e + z + 1]) : 0.f;
-                pk[(e + z) >> 1] = pack_bf16(x0, x1);
-              }
-            }
-          }
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<uint4*>(s.pg + sw128(i, half * 64 + j * 16)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-        }
-        tc_fence_before();
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s.pg_ready);
-        if (tid == 448) FQ_TS(it, 17);
-      }
-      return true;
-    };
-
-    if (total > 0) ok = prepare(0);
-    for (int it = 0; it < total && ok; ++it) {
+    const int c = 16 * (warp & 3) + (lane & 15);
+    for (int it = 0; it < total; ++it) {
       const int n = it - warm, gs = it & (kGateStages - 1);
       const uint32_t ph = it & 1;
-      // ---- output tile O[c][v]: thread (lane < 16) owns token row c = 16 * quarter + lane
+      if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 18)) break;
       if (!mbar_wait(wc, &s.o_done, ph, 21)) break;
       if (tid == 384) FQ_TS(it, 18);
       tc_fence_after();
       if (p.o != nullptr && n >= 0) {
-        const int c = 16 * (warp & 3) + lane;
         const int len = min(kChunk, seq_len - n * kChunk);
         const bool wr = (lane < 16) && (c < len);
+        const float f = p.scale * s.gate[gs][1][c];
         __nv_bfloat16* dst = p.o + (static_cast<size_t>(tok_begin + n * kChunk + (wr ? c : 0)) * p.H + h) * kDim;
 #pragma unroll
         for (int pc = 0; pc < 4; ++pc) {
-          uint32_t r[32];
-          tmem_ld32(tmem_addr(tm, lane_base, kColO + 32 * pc), r);
+          uint32_t oi[32], ox[32];
+          tmem_ld32(tmem_addr(tm, lane_base, kColOI + 32 * pc), oi);
+          tmem_ld32(tmem_addr(tm, lane_base, kColOX + 32 * pc), ox);
           tmem_wait_ld();
           if (wr) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 x;
-              x.x = pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
-              x.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-              x.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-              x.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+              x.x = pack_bf16(f * __uint_as_float(oi[8 * j]) + __uint_as_float(ox[8 * j]),
+                              f * __uint_as_float(oi[8 * j + 1]) + __uint_as_float(ox[8 * j + 1]));
+              x.y = pack_bf16(f * __uint_as_float(oi[8 * j + 2]) + __uint_as_float(ox[8 * j + 2]),
+                              f * __uint_as_float(oi[8 * j + 3]) + __uint_as_float(ox[8 * j + 3]));
+              x.z = pack_bf16(f * __uint_as_float(oi[8 * j + 4]) + __uint_as_float(ox[8 * j + 4]),
+                              f * __uint_as_float(oi[8 * j + 5]) + __uint_as_float(ox[8 * j + 5]));
+              x.w = pack_bf16(f * __uint_as_float(oi[8 * j + 6]) + __uint_as_float(ox[8 * j + 6]),
+                              f * __uint_as_float(oi[8 * j + 7]) + __uint_as_float(ox[8 * j + 7]));
               *reinterpret_cast<uint4*>(dst + 32 * pc + 8 * j) = x;
             }
           }
@@ -518,8 +421,6 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       __syncwarp();
       if (lane == 0) { mbar_arrive(&s.o_free); mbar_arrive(&s.gate_empty[gs]); }
       if (tid == 384) FQ_TS(it, 19);
-      // ---- next chunk's Q~ / A_g / P_g.  The buffers are free: every UMMA that read them finished before o_done.
-      if (it + 1 < total) ok = prepare(it + 1);
     }
   }
 
@@ -530,22 +431,24 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
 }  // namespace fq
 
-extern "C" FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, const void* A, const float* g_cumsum,
-                                 const float* beta, const float* h0, float* ht, const int32_t* ht_index, void* o,
-                                 void* h_out, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
-                                 const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
-                                 int32_t* status_dev, void* stream) {
-  return fq_gdr_fwd_cp(q, k, v, A, g_cumsum, beta, h0, ht, ht_index, nullptr, nullptr, o, h_out, B, T, H, Hg, cu_seqlens,
-                       chunk_offsets, n_seq, total_chunks, scale, status_dev, stream);
+extern "C" FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, const void* Ag, const void* Pg,
+                                 const float* g_cumsum, const float* beta, const float* h0, float* ht,
+                                 const int32_t* ht_index, void* o, void* h_out, int B, int T, int H, int Hg,
+                                 const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq, int total_chunks,
+                                 float scale, int32_t* status_dev, void* stream) {
+  return fq_gdr_fwd_cp(q, k, v, Ag, Pg, g_cumsum, beta, h0, ht, ht_index, nullptr, nullptr, o, h_out, B, T, H, Hg,
+                       cu_seqlens, chunk_offsets, n_seq, total_chunks, scale, status_dev, stream);
 }
 
-extern "C" FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v, const void* A, const float* g_cumsum,
-                                    const float* beta, const float* h0, float* ht, const int32_t* ht_index,
+extern "C" FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v, const void* Ag, const void* Pg,
+                                    const float* g_cumsum, const float* beta, const float* h0, float* ht,
+                                    const int32_t* ht_index,
                                     const int32_t* h0_index, const int32_t* warmup, void* o, void* h_out, int B, int T,
                                     int H, int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
                                     int total_chunks, float scale, int32_t* status_dev, void* stream) {
   using namespace fq;
-  FQ_CHECK_ARG(q && k && v && A && g_cumsum && beta, "fq_gdr_fwd: null input tensor");
+  FQ_CHECK_ARG(q && k && v && Ag && g_cumsum && beta, "fq_gdr_fwd: null input tensor");
+  FQ_CHECK_ARG(o == nullptr || Pg != nullptr, "fq_gdr_fwd: P_g is needed when o is requested");
   FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0, "fq_gdr_fwd: bad sizes");
   FQ_CHECK_ARG((cu_seqlens == nullptr) == (chunk_offsets == nullptr),
                "fq_gdr_fwd: cu_seqlens and chunk_offsets must be given together");
@@ -554,14 +457,14 @@ extern "C" FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v,
   FQ_CHECK_ARG(warmup == nullptr || cu_seqlens != nullptr, "fq_gdr_fwd: warm-up tables need piece boundaries (cu_seqlens)");
   const uint64_t rows = static_cast<uint64_t>(B) * static_cast<uint64_t>(T);
   FQ_CHECK_ARG(rows > 0 && rows < (1ull << 31), "fq_gdr_fwd: token count out of range");
-  CUtensorMap mq, mk, mv, ma, mo;
+  CUtensorMap mq, mk, mv, ma, mpg;
   int rc;
   if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mv, v, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
-  if ((rc = make_tmap_rows_heads_dim(&ma, A, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
-  // the output map is only dereferenced when o != NULL; v stands in to keep the descriptor valid otherwise
-  if ((rc = make_tmap_rows_heads_dim(&mo, o ? o : v, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&ma, Ag, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
+  // in state-only mode (o == NULL) the P_g tile is loaded but never used; A_g stands in for a missing P_g
+  if ((rc = make_tmap_rows_heads_dim(&mpg, Pg ? Pg : Ag, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
   FwdParams p;
   p.g_cum = g_cumsum; p.beta = beta; p.h0 = h0; p.ht = ht; p.ht_index = ht_index; p.h0_index = h0_index;
   p.warmup = warmup;
@@ -579,7 +482,7 @@ extern "C" FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v,
   }
   const long long ctas = static_cast<long long>(n_seq) * H;
   FQ_CHECK_ARG(ctas < (1ll << 31), "fq_gdr_fwd: too many (sequence, head) pairs");
-  gdr_fwd_kernel<<<static_cast<unsigned>(ctas), kFwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, ma, mo, p);
+  gdr_fwd_kernel<<<static_cast<unsigned>(ctas), kFwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, ma, mpg, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }

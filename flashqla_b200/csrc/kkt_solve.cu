@@ -9,6 +9,12 @@
 // steps 2 and 3 on tensor cores with split-TF32 (hi + lo) operands so the products keep fp32
 // accuracy.  The unit costs 24 KB of HBM traffic for ~1.4 MFLOP, i.e. it is HBM-bound, which is
 // why the legacy warp-level MMA path is enough here.
+//
+// Optionally (Ag / Pg given) the same CTA also emits the two gated, chunk-parallel operand tiles
+// of the recurrences, so that the serial kernels carry only serial work:
+//   A_g[i][j] = A[i][j] * exp(g_i - g_j) * beta_j   (j <= i)
+//   P_g[i][j] = scale * exp(g_i - g_j) * (q_i . k_j) (j <= i)
+// with g the chunk-local cumsum of the log gate (padded rows use the last valid value).
 #include "flashqla.h"
 #include "host.cuh"
 #include "seq.cuh"
@@ -20,11 +26,15 @@ constexpr int kFLd = 68;   // fp32 elements per row of the 64x64 work matrices
 constexpr int kTLd = 36;   // fp32 elements per row of the 32x32 scratch
 
 struct KktSmem {
+  union {  // the Q tile is only read while Q K^T is formed; K K^T (fp32) then takes its place
+    __nv_bfloat16 q[kChunk * kKLd];
+    float kk[kChunk * kFLd];
+  };
   __nv_bfloat16 k[kChunk * kKLd];
-  float kk[kChunk * kFLd];
   float x[kChunk * kFLd];
   float t[32 * kTLd];
   float beta[kChunk];
+  float g[kChunk];
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
@@ -58,7 +68,11 @@ __device__ __forceinline__ void mma_tf32x3(float (&c)[4], const float (&a)[4], c
 
 __global__ void __launch_bounds__(128) kkt_solve_kernel(const __nv_bfloat16* __restrict__ k,
                                                        const float* __restrict__ beta,
-                                                       __nv_bfloat16* __restrict__ A, int H, int Hg, SeqArgs sa) {
+                                                       __nv_bfloat16* __restrict__ A, int H, int Hg, SeqArgs sa,
+                                                       const __nv_bfloat16* __restrict__ q,
+                                                       const float* __restrict__ g_cum,
+                                                       __nv_bfloat16* __restrict__ Ag, __nv_bfloat16* __restrict__ Pg,
+                                                       float scale, const __nv_bfloat16* __restrict__ A_in) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   KktSmem& s = *reinterpret_cast<KktSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -79,11 +93,48 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __nv_bfloat16* __r
       *reinterpret_cast<uint4*>(&s.k[row * kKLd + piece * 8]) = v;
     }
     for (int i = tid; i < kChunk * kFLd; i += 128) s.x[i] = 0.f;
+    if (Pg) {
+      const __nv_bfloat16* qsrc = q + (static_cast<size_t>(p.tok0) * Hg + hg) * kDim;
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int idx = it * 128 + tid;
+        const int row = idx >> 4, piece = idx & 15;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < p.len) v = __ldg(reinterpret_cast<const uint4*>(qsrc + static_cast<size_t>(row) * Hg * kDim) + piece);
+        *reinterpret_cast<uint4*>(&s.q[row * kKLd + piece * 8]) = v;
+      }
+    }
   }
   __syncthreads();
 
-  // ---- K K^T (lower block-triangle) with bf16 MMA, fp32 result in shared
-  {
+  // ---- Q K^T (lower block-triangle) kept in registers for all V-heads of the group
+  float qk[8][4];
+  if (Pg) {
+    const int m0 = warp * 16;
+    const int ntiles = 2 * warp + 2;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) qk[j][0] = qk[j][1] = qk[j][2] = qk[j][3] = 0.f;
+#pragma unroll
+    for (int k0 = 0; k0 < kDim; k0 += 16) {
+      uint32_t a[4];
+      a[0] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g) * kKLd + k0 + 2 * t]);
+      a[1] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g + 8) * kKLd + k0 + 2 * t]);
+      a[2] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g) * kKLd + k0 + 8 + 2 * t]);
+      a[3] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g + 8) * kKLd + k0 + 8 + 2 * t]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j < ntiles) {
+          uint32_t b[2];
+          b[0] = *reinterpret_cast<const uint32_t*>(&s.k[(j * 8 + g) * kKLd + k0 + 2 * t]);
+          b[1] = *reinterpret_cast<const uint32_t*>(&s.k[(j * 8 + g) * kKLd + k0 + 8 + 2 * t]);
+          mma_bf16_16816(qk[j], a, b);
+        }
+      }
+    }
+  }
+
+  // ---- K K^T (lower block-triangle) with bf16 MMA, fp32 result in shared (skipped when A is given)
+  if (A_in == nullptr) {
     const int m0 = warp * 16;
     const int ntiles = 2 * warp + 2;
     float acc[8][4];
@@ -106,6 +157,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __nv_bfloat16* __r
         }
       }
     }
+    __syncthreads();  // every warp is done reading the Q tile that shares storage with kk
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       if (j < ntiles) {
@@ -118,9 +170,30 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __nv_bfloat16* __r
   for (int hi = 0; hi < G; ++hi) {
     const int hv = hg * G + hi;
     __syncthreads();  // kk complete (first pass) / previous head's stores done
-    if (tid < kChunk) s.beta[tid] = (tid < p.len) ? __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hv) : 0.f;
+    if (tid < kChunk) {
+      s.beta[tid] = (tid < p.len) ? __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hv) : 0.f;
+      if (Ag || Pg) s.g[tid] = __ldg(g_cum + static_cast<size_t>(p.tok0 + min(tid, p.len - 1)) * H + hv);
+    }
     __syncthreads();
 
+    if (A_in != nullptr) {
+      // A was computed earlier (backward pass): fetch it instead of solving again
+      const __nv_bfloat16* asrc = A_in + (static_cast<size_t>(p.tok0) * H + hv) * kChunk;
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int row = it * 16 + (tid >> 3), piece = tid & 7;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < p.len) v = __ldg(reinterpret_cast<const uint4*>(asrc + static_cast<size_t>(row) * H * kChunk) + piece);
+        const uint32_t* vw = reinterpret_cast<const uint32_t*>(&v);
+        float* xr = &s.x[row * kFLd + piece * 8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          xr[2 * e] = bf16_lo(vw[e]);
+          xr[2 * e + 1] = bf16_hi(vw[e]);
+        }
+      }
+      __syncthreads();
+    } else {
     // ---- step 1: inverse of the four 16x16 diagonal blocks, one column per thread
     if (tid < kChunk) {
       const int b0 = (tid >> 4) * 16, j = tid & 15;
@@ -235,20 +308,60 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __nv_bfloat16* __r
     }
     __syncthreads();
 
-    // ---- store A (bf16), 128 contiguous bytes per token row
+    }
+    // ---- store A (bf16) and, if asked, A_g; 128 contiguous bytes per token row
     {
       __nv_bfloat16* dst = A + (static_cast<size_t>(p.tok0) * H + hv) * kChunk;
+      __nv_bfloat16* dstg = Ag ? Ag + (static_cast<size_t>(p.tok0) * H + hv) * kChunk : nullptr;
 #pragma unroll
       for (int it = 0; it < 4; ++it) {
         const int row = it * 16 + (tid >> 3), piece = tid & 7;
         if (row < p.len) {
           const float* xr = &s.x[row * kFLd + piece * 8];
           uint4 v;
-          v.x = pack_bf16(xr[0], xr[1]);
-          v.y = pack_bf16(xr[2], xr[3]);
-          v.z = pack_bf16(xr[4], xr[5]);
-          v.w = pack_bf16(xr[6], xr[7]);
-          *(reinterpret_cast<uint4*>(dst + static_cast<size_t>(row) * H * kChunk) + piece) = v;
+          if (A_in == nullptr) {
+            v.x = pack_bf16(xr[0], xr[1]);
+            v.y = pack_bf16(xr[2], xr[3]);
+            v.z = pack_bf16(xr[4], xr[5]);
+            v.w = pack_bf16(xr[6], xr[7]);
+            *(reinterpret_cast<uint4*>(dst + static_cast<size_t>(row) * H * kChunk) + piece) = v;
+          }
+          if (dstg) {
+            const float gi = s.g[row];
+            float y[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int j = piece * 8 + e;
+              y[e] = (j <= row) ? xr[e] * fast_exp(gi - s.g[j]) * s.beta[j] : 0.f;
+            }
+            v.x = pack_bf16(y[0], y[1]);
+            v.y = pack_bf16(y[2], y[3]);
+            v.z = pack_bf16(y[4], y[5]);
+            v.w = pack_bf16(y[6], y[7]);
+            *(reinterpret_cast<uint4*>(dstg + static_cast<size_t>(row) * H * kChunk) + piece) = v;
+          }
+        }
+      }
+    }
+    // ---- P_g straight from the Q K^T fragments (rows m0+g and m0+g+8, column pairs 8j+2t)
+    if (Pg) {
+      const int m0 = warp * 16;
+      __nv_bfloat16* dstp = Pg + (static_cast<size_t>(p.tok0) * H + hv) * kChunk;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int row = m0 + g + 8 * half;
+        if (row < p.len) {
+          const float gi = s.g[row];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int c0 = j * 8 + 2 * t;
+            float y0 = 0.f, y1 = 0.f;
+            if (j < 2 * warp + 2) {
+              if (c0 <= row) y0 = scale * fast_exp(gi - s.g[c0]) * qk[j][2 * half];
+              if (c0 + 1 <= row) y1 = scale * fast_exp(gi - s.g[c0 + 1]) * qk[j][2 * half + 1];
+            }
+            *reinterpret_cast<uint32_t*>(dstp + static_cast<size_t>(row) * H * kChunk + c0) = pack_bf16(y0, y1);
+          }
         }
       }
     }
@@ -257,11 +370,14 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __nv_bfloat16* __r
 
 }  // namespace fq
 
-extern "C" FQ_API int fq_kkt_solve(const void* k, const float* beta, void* A, int B, int T, int H, int Hg,
-                                   const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
-                                   int total_chunks, void* stream) {
+extern "C" FQ_API int fq_kkt_solve_gated(const void* k, const void* q, const float* beta, const float* g_cumsum, void* A,
+                                         void* Ag, void* Pg, int a_is_input, int B, int T, int H, int Hg,
+                                         const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
+                                         int total_chunks, float scale, void* stream) {
   using namespace fq;
   FQ_CHECK_ARG(k && beta && A, "fq_kkt_solve: null tensor");
+  FQ_CHECK_ARG((Ag == nullptr && Pg == nullptr) || (g_cumsum != nullptr), "fq_kkt_solve: A_g / P_g need the gate cumsum");
+  FQ_CHECK_ARG(Pg == nullptr || q != nullptr, "fq_kkt_solve: P_g needs q");
   FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0,
                "fq_kkt_solve: bad sizes");
   FQ_CHECK_ARG(Hg <= 65535, "fq_kkt_solve: too many QK heads");
@@ -281,7 +397,16 @@ extern "C" FQ_API int fq_kkt_solve(const void* k, const float* beta, void* A, in
   }
   dim3 grid(total_chunks, Hg);
   kkt_solve_kernel<<<grid, 128, sizeof(KktSmem), static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(k), beta, static_cast<__nv_bfloat16*>(A), H, Hg, sa);
+      static_cast<const __nv_bfloat16*>(k), beta, static_cast<__nv_bfloat16*>(A), H, Hg, sa,
+      static_cast<const __nv_bfloat16*>(q), g_cumsum, static_cast<__nv_bfloat16*>(Ag), static_cast<__nv_bfloat16*>(Pg),
+      scale, a_is_input ? static_cast<const __nv_bfloat16*>(A) : nullptr);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
+}
+
+extern "C" FQ_API int fq_kkt_solve(const void* k, const float* beta, void* A, int B, int T, int H, int Hg,
+                                   const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
+                                   int total_chunks, void* stream) {
+  return fq_kkt_solve_gated(k, nullptr, beta, nullptr, A, nullptr, nullptr, 0, B, T, H, Hg, cu_seqlens, chunk_offsets, n_seq,
+                            total_chunks, 0.f, stream);
 }

@@ -92,12 +92,56 @@ def check_status(status: torch.Tensor, what: str) -> None:
         raise _lib.FlashQLAError(f"{what}: device-side wait timed out (code {st:#x})")
 
 
-def fused_gdr_fwd(q, k, v, a, g, b, scale, initial_state=None, output_final_state=True, output_h=False,
-                  output_o=True, plan: SeqPlan | None = None, ht_index=None, n_out=None, status=None):
-    """Fused forward recurrence.  g is the chunk-local cumsum, a the gate-free inverse from kkt_solve.
+def kkt_solve_gated(k, q, b, g_cum, scale, plan: SeqPlan, A=None, want_pg=True):
+    """A (gate-free inverse, computed unless given), A_g and P_g tiles, bf16 [B,T,H,64] each."""
+    _require_cuda(k, q, b, g_cum)
+    if k.dtype != torch.bfloat16:
+        raise _lib.FlashQLAError("kkt_solve_gated: only bfloat16 keys are supported")
+    B, T, Hg, K = k.shape
+    H = b.shape[-1]
+    assert K == 128, "head dim must be 128"
+    k, q = k.contiguous(), q.contiguous()
+    bf = b.contiguous() if b.dtype == torch.float32 else b.float().contiguous()
+    a_is_input = A is not None
+    if A is None:
+        A = torch.empty(B, T, H, CHUNK, dtype=k.dtype, device=k.device)
+    else:
+        A = A.contiguous()
+    Ag = torch.empty(B, T, H, CHUNK, dtype=k.dtype, device=k.device)
+    Pg = torch.empty(B, T, H, CHUNK, dtype=k.dtype, device=k.device) if want_pg else None
+    cu_p, off_p = plan.ptrs()
+    rc = _lib.load().fq_kkt_solve_gated(k.data_ptr(), q.data_ptr(), bf.data_ptr(), g_cum.data_ptr(), A.data_ptr(),
+                                        Ag.data_ptr(), None if Pg is None else Pg.data_ptr(), int(a_is_input), B, T, H,
+                                        Hg, cu_p, off_p, plan.n_seq, plan.total_chunks, float(scale), _stream())
+    _lib.check(rc, "fq_kkt_solve_gated")
+    return A, Ag, Pg
+
+
+def sm_count(device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+def cp_warmup(g_cum, cp, H, threshold=-16.0, reverse=False):
+    """Chunks to replay per (piece, head) for a context-parallel run (see csrc/cp.cu)."""
+    out = torch.empty(cp.n_pieces, H, dtype=torch.int32, device=g_cum.device)
+    if not reverse:
+        rc = _lib.load().fq_cp_warmup(g_cum.data_ptr(), cp.piece_start.data_ptr(), cp.chunks_before.data_ptr(), None,
+                                      out.data_ptr(), cp.n_pieces, H, float(threshold), 0, _stream())
+    else:
+        rc = _lib.load().fq_cp_warmup(g_cum.data_ptr(), cp.piece_end.data_ptr(), cp.last_chunk_len.data_ptr(),
+                                      cp.chunks_after.data_ptr(), out.data_ptr(), cp.n_pieces, H, float(threshold), 1,
+                                      _stream())
+    _lib.check(rc, "fq_cp_warmup")
+    return out
+
+
+def fused_gdr_fwd(q, k, v, ag, pg, g, b, scale, initial_state=None, output_final_state=True, output_h=False,
+                  output_o=True, plan: SeqPlan | None = None, cp=None, warmup=None, status=None):
+    """Fused forward recurrence.  g is the chunk-local cumsum, ag / pg the gated tiles from kkt_solve_gated.
+    With a CpPlan `cp` (and its `warmup` table) every piece of a sequence runs as its own CTA.
 
     Returns (o or None, h or None, final_state or None)."""
-    _require_cuda(q, k, v, a, g, b)
+    _require_cuda(q, k, v, ag, g, b)
     if q.dtype != torch.bfloat16:
         raise _lib.FlashQLAError("fused_gdr_fwd: only bfloat16 q/k/v are supported")
     B, T, Hg, K = k.shape
@@ -105,7 +149,7 @@ def fused_gdr_fwd(q, k, v, a, g, b, scale, initial_state=None, output_final_stat
     assert K == 128 and V == 128, "head dims must be 128"
     plan = plan or plan_dense(B, T)
     dev = q.device
-    q, k, v, a = q.contiguous(), k.contiguous(), v.contiguous(), a.contiguous()
+    q, k, v, ag = q.contiguous(), k.contiguous(), v.contiguous(), ag.contiguous()
     g = g.contiguous() if g.dtype == torch.float32 else g.float().contiguous()
     b = b.contiguous() if b.dtype == torch.float32 else b.float().contiguous()
     h0 = None
@@ -115,15 +159,18 @@ def fused_gdr_fwd(q, k, v, a, g, b, scale, initial_state=None, output_final_stat
     o = torch.empty(B, T, H, V, dtype=q.dtype, device=dev) if output_o else None
     h = torch.empty(1 if plan.packed else B, plan.total_chunks // (1 if plan.packed else B), H, K, V, dtype=q.dtype,
                     device=dev) if output_h else None
-    ht = None
-    if output_final_state:
-        ht = torch.empty(plan.n_seq if n_out is None else n_out, H, K, V, dtype=torch.float32, device=dev)
-    cu_p, off_p = plan.ptrs()
-    rc = _lib.load().fq_gdr_fwd(
-        q.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), g.data_ptr(), b.data_ptr(),
-        None if h0 is None else h0.data_ptr(), None if ht is None else ht.data_ptr(),
-        None if ht_index is None else ht_index.data_ptr(), None if o is None else o.data_ptr(),
-        None if h is None else h.data_ptr(), B, T, H, Hg, cu_p, off_p, plan.n_seq, plan.total_chunks, float(scale),
-        None if status is None else status.data_ptr(), _stream())
+    ht = torch.empty(plan.n_seq, H, K, V, dtype=torch.float32, device=dev) if output_final_state else None
+    p = lambda t: None if t is None else t.data_ptr()
+    if cp is None:
+        cu_p, off_p = plan.ptrs()
+        rc = _lib.load().fq_gdr_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), ag.data_ptr(), p(pg), g.data_ptr(),
+                                    b.data_ptr(), p(h0), p(ht), None, p(o), p(h), B, T, H, Hg, cu_p, off_p, plan.n_seq,
+                                    plan.total_chunks, float(scale), p(status), _stream())
+    else:
+        rc = _lib.load().fq_gdr_fwd_cp(q.data_ptr(), k.data_ptr(), v.data_ptr(), ag.data_ptr(), p(pg), g.data_ptr(),
+                                       b.data_ptr(), p(h0), p(ht), cp.out_index_fwd.data_ptr(), cp.seq_index.data_ptr(),
+                                       warmup.data_ptr(), p(o), p(h), 1, B * T, H, Hg, cp.cu_seqlens.data_ptr(),
+                                       cp.chunk_offsets.data_ptr(), cp.n_pieces, cp.total_chunks, float(scale),
+                                       p(status), _stream())
     _lib.check(rc, "fq_gdr_fwd")
     return o, h, ht

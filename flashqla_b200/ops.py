@@ -9,8 +9,11 @@ import torch
 
 from . import _lib, kernels
 from .kernels import make_plan
+from .planner import plan_cp
 
 _DEBUG_STATUS = os.environ.get("FLASHQLA_CHECK_STATUS", "0") == "1"
+# testing hook: force a piece length (in chunks) for the context-parallel split
+_FORCE_PIECE_CHUNKS = int(os.environ["FLASHQLA_PIECE_CHUNKS"]) if "FLASHQLA_PIECE_CHUNKS" in os.environ else None
 
 
 def l2norm(x: torch.Tensor, dim: int = -1, eps: float = 1e-6) -> torch.Tensor:
@@ -22,21 +25,27 @@ def l2norm(x: torch.Tensor, dim: int = -1, eps: float = 1e-6) -> torch.Tensor:
 
 def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None, cu_seqlens=None,
                                output_final_state=True, output_h=False, auto_cp=True):
-    """Forward pipeline (chunk/__init__.py:17-67): cumsum -> K K^T + solve -> fused recurrence.
+    """Forward pipeline (chunk/__init__.py:17-67): cumsum -> K K^T + solve (+ gated tiles) -> fused recurrence.
 
     Returns ``(g_cumsum, A, o, h, final_state)``; ``A`` is the gate-free inverse (opaque, only
-    meant to be passed back to ``chunk_gated_delta_rule_bwd``)."""
+    meant to be passed back to ``chunk_gated_delta_rule_bwd``).  With ``auto_cp`` long sequences are
+    split into pieces that run as independent CTAs (context parallel inside the GPU)."""
     B, T, Hg, K = k.shape
     H = v.shape[2]
     if scale is None:
         scale = K ** -0.5
     plan = make_plan(B, T, cu_seqlens, q.device)
     g_cum = kernels.chunk_local_cumsum(g, cu_seqlens=cu_seqlens, plan=plan)
-    A = kernels.kkt_solve(k, beta, plan=plan)
+    A, Ag, Pg = kernels.kkt_solve_gated(k, q, beta, g_cum, scale, plan)
     status = kernels._status_tensor(q.device) if _DEBUG_STATUS else None
-    o, h, final_state = kernels.fused_gdr_fwd(q, k, v, A, g_cum, beta, scale, initial_state=initial_state,
+    cp = warm = None
+    if auto_cp:
+        cp = plan_cp(plan, B, T, H, kernels.sm_count(q.device), q.device, piece_chunks=_FORCE_PIECE_CHUNKS)
+        if cp is not None:
+            warm = kernels.cp_warmup(g_cum, cp, H)
+    o, h, final_state = kernels.fused_gdr_fwd(q, k, v, Ag, Pg, g_cum, beta, scale, initial_state=initial_state,
                                               output_final_state=output_final_state, output_h=output_h,
-                                              plan=plan, status=status)
+                                              plan=plan, cp=cp, warmup=warm, status=status)
     if status is not None:
         kernels.check_status(status, "fq_gdr_fwd")
     return g_cum, A, o, h, final_state

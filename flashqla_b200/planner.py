@@ -120,6 +120,7 @@ class CpPlan:
     chunks_before: torch.Tensor     # [P] chunks of the sequence that precede the piece
     chunks_after: torch.Tensor      # [P] chunks of the sequence that follow the piece
     last_chunk_len: torch.Tensor    # [P] tokens in the last chunk of the piece's sequence
+    seq_end: torch.Tensor           # [P] first token after the piece's sequence
 
 
 def choose_piece_chunks(n_chunks: list, H: int, n_sm: int, overhead: int = 6) -> int | None:
@@ -169,12 +170,12 @@ def plan_cp(plan: SeqPlan, B: int, T: int, H: int, n_sm: int, device, piece_chun
     L = piece_chunks if piece_chunks is not None else choose_piece_chunks(n_chunks, H, n_sm)
     result = None
     if L is not None and L >= 1 and max(n_chunks, default=0) > L:
-        starts, ends, seq_idx, before, after, lastlen, out_f, out_b = [], [], [], [], [], [], [], []
+        starts, ends, seq_idx, before, after, lastlen, out_f, out_b, send = [], [], [], [], [], [], [], [], []
         for i, nc in enumerate(n_chunks):
             s, e = cu[i], cu[i + 1]
             if nc == 0:  # empty sequence: one empty piece so that its final state / dh0 still gets written
                 starts.append(s); ends.append(e); seq_idx.append(i); before.append(0); after.append(0)
-                lastlen.append(0); out_f.append(i); out_b.append(i)
+                lastlen.append(0); out_f.append(i); out_b.append(i); send.append(e)
                 continue
             ll = (e - s) - (nc - 1) * CHUNK
             for c0 in range(0, nc, L):
@@ -184,6 +185,7 @@ def plan_cp(plan: SeqPlan, B: int, T: int, H: int, n_sm: int, device, piece_chun
                 seq_idx.append(i); before.append(c0); after.append(nc - c1); lastlen.append(ll)
                 out_f.append(i if c1 == nc else -1)
                 out_b.append(i if c0 == 0 else -1)
+                send.append(e)
         bounds = starts + [cu[-1]]
         offs = [0]
         for a_, b_ in zip(starts, ends):
@@ -193,7 +195,7 @@ def plan_cp(plan: SeqPlan, B: int, T: int, H: int, n_sm: int, device, piece_chun
             return torch.tensor(x, dtype=torch.int32, device=device)
 
         result = CpPlan(len(starts), L, offs[-1], t(bounds), t(offs), t(seq_idx), t(out_f), t(out_b), t(starts), t(ends),
-                        t(before), t(after), t(lastlen))
+                        t(before), t(after), t(lastlen), t(send))
     _CP_CACHE[key] = (plan, result)
     if len(_CP_CACHE) > _CACHE_SIZE:
         _CP_CACHE.popitem(last=False)

@@ -67,21 +67,34 @@ FQ_API int fq_kkt_solve(const void* k, const float* beta, void* A, int B, int T,
                         void* stream);
 
 /*
+ * fq_kkt_solve that also emits the gated operand tiles of the recurrences (bf16 [B,T,H,64] each, NULL to skip):
+ *   Ag[i][j] = A[i][j] * exp(g_i - g_j) * beta_j,   Pg[i][j] = scale * exp(g_i - g_j) * (q_i . k_j),   j <= i.
+ * In the reference these products are formed inside the serial kernels
+ * (flash_qla/ops/gated_delta_rule/chunk/hopper/fused_fwd.py:300-350); they are chunk-parallel, so here
+ * they are produced by the chunk-parallel kernel.  g_cumsum: fp32 [B,T,H] from fq_chunk_cumsum.
+ * a_is_input != 0: A is read instead of computed (the backward pass re-derives Ag / Pg from the A it was given).
+ */
+FQ_API int fq_kkt_solve_gated(const void* k, const void* q, const float* beta, const float* g_cumsum, void* A, void* Ag,
+                              void* Pg, int a_is_input, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
+                              const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale, void* stream);
+
+/*
  * Fused forward recurrence: per (sequence, V-head) walks the chunks, carries the fp32 K x V state
  * and writes o = scale*exp(g) o (Q S) + P_g V_d per chunk.
  * Replaces fused_gdr_fwd, flash_qla/ops/gated_delta_rule/chunk/hopper/fused_fwd.py:535-658
  * (and, with o == NULL and h_out != NULL, the state-only fused_gdr_h of hopper/prepare_h.py:461-558).
- *   q,k [B,T,Hg,128] bf16; v [B,T,H,128] bf16; A [B,T,H,64] bf16 from fq_kkt_solve;
- *   g_cumsum, beta [B,T,H] fp32 (g_cumsum from fq_chunk_cumsum);
+ *   q,k [B,T,Hg,128] bf16; v [B,T,H,128] bf16; Ag, Pg [B,T,H,64] bf16 from fq_kkt_solve_gated
+ *   (Pg may be NULL when o is NULL); g_cumsum, beta [B,T,H] fp32 (g_cumsum from fq_chunk_cumsum);
  *   h0   [n_seq,H,128,128] fp32 initial states, or NULL for zeros;
  *   ht   [*,H,128,128] fp32 final states, or NULL; sequence i writes slot ht_index[i]
  *        (negative = skip; ht_index == NULL means slot i);
  *   o    [B,T,H,128] bf16 or NULL;   h_out [total_chunks,H,128,128] bf16 (state BEFORE each chunk) or NULL.
  */
-FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, const void* A, const float* g_cumsum,
-                      const float* beta, const float* h0, float* ht, const int32_t* ht_index, void* o, void* h_out,
-                      int B, int T, int H, int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
-                      int total_chunks, float scale, int32_t* status_dev, void* stream);
+FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, const void* Ag, const void* Pg,
+                      const float* g_cumsum, const float* beta, const float* h0, float* ht, const int32_t* ht_index,
+                      void* o, void* h_out, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
+                      const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale, int32_t* status_dev,
+                      void* stream);
 
 /*
  * fq_gdr_fwd with context-parallel pieces: `cu_seqlens` holds PIECE boundaries (pieces of one
@@ -95,8 +108,8 @@ FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, const void* A
  * instead of computing per-piece end states in a separate pass and chaining them, every piece
  * warms its own state up inside the fused kernel.
  */
-FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v, const void* A, const float* g_cumsum,
-                         const float* beta, const float* h0, float* ht, const int32_t* ht_index,
+FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v, const void* Ag, const void* Pg,
+                         const float* g_cumsum, const float* beta, const float* h0, float* ht, const int32_t* ht_index,
                          const int32_t* h0_index, const int32_t* warmup, void* o, void* h_out, int B, int T, int H,
                          int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq, int total_chunks,
                          float scale, int32_t* status_dev, void* stream);
@@ -121,15 +134,30 @@ FQ_API int fq_cp_warmup(const float* g_cumsum, const int32_t* piece_edge, const 
  * Backward, serial part: reverse recurrence of the state gradient per (sequence, V-head).
  * Together with fq_gdr_bwd_chunk it replaces fused_gdr_bwd,
  * flash_qla/ops/gated_delta_rule/chunk/hopper/fused_bwd.py:900-985.
+ *   Ag, Pg [B,T,H,64] bf16 from fq_kkt_solve_gated;
  *   dout [B,T,H,128] bf16 (gradient of o); dht [n_seq,H,128,128] fp32 or NULL (gradient of the final state);
  *   dh0  [n_seq,H,128,128] fp32 or NULL (gradient of the initial state);
  *   dh_out [total_chunks,H,128,128] bf16: gradient w.r.t. the state AFTER each chunk (scratch for
  *   fq_gdr_bwd_chunk); dvp_out [B,T,H,128] bf16 scratch (dV'); dv_out [B,T,H,128] bf16 = gradient of v.
  */
-FQ_API int fq_gdr_bwd_dh(const void* q, const void* k, const void* A, const void* dout, const float* g_cumsum,
-                         const float* beta, const float* dht, float* dh0, void* dh_out, void* dvp_out, void* dv_out,
+FQ_API int fq_gdr_bwd_dh(const void* q, const void* k, const void* Ag, const void* Pg, const void* dout,
+                         const float* g_cumsum, const float* beta, const float* dht, float* dh0, void* dh_out, void* dvp_out, void* dv_out,
                          int B, int T, int H, int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets,
                          int n_seq, int total_chunks, float scale, int32_t* status_dev, void* stream);
+
+/*
+ * fq_gdr_bwd_dh over context-parallel pieces (`cu_seqlens` = piece boundaries, see fq_gdr_fwd_cp):
+ *   dht_index[i] slot of dht used when the replay reaches the end of the sequence; dh0_index[i] slot of dh0
+ *   to write (negative for pieces that do not start their sequence); seq_end[i] first token after the
+ *   piece's sequence; warmup[i*H+h] chunks to replay AFTER the piece (from fq_cp_warmup, reverse != 0).
+ * The reference has no context parallelism in its backward.
+ */
+FQ_API int fq_gdr_bwd_dh_cp(const void* q, const void* k, const void* Ag, const void* Pg, const void* dout,
+                            const float* g_cumsum, const float* beta, const float* dht, float* dh0, void* dh_out,
+                            void* dvp_out, void* dv_out, const int32_t* dht_index, const int32_t* dh0_index,
+                            const int32_t* seq_end, const int32_t* warmup, int B, int T, int H, int Hg,
+                            const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq, int total_chunks,
+                            float scale, int32_t* status_dev, void* stream);
 
 /*
  * Backward, chunk-parallel part: dq, dk (per V-head, bf16 [B,T,H,128]), dg w.r.t. the gate cumsum

@@ -96,3 +96,25 @@ def test_autograd_entry():
     got = [leaves[0].grad, leaves[1].grad, leaves[2].grad, leaves[4].grad, leaves[3].grad, leaves[5].grad]
     errs = {n: orc.rel_to_max(x.float().cpu(), r) for n, x, r in zip(NAMES, got, ref)}
     assert all(e < TOL for e in errs.values()), str({k_: f'{v_:.2e}' for k_, v_ in errs.items()})
+
+
+CP_CASES = [
+    (1, 1024, 2, 2, None, "baseline", 4),
+    (1, 1024, 2, 2, None, "reftest", 4),   # the g = 0 head replays to the sequence end / start: exact
+    (2, 520, 1, 2, None, "baseline", 2),
+    (1, 1500, 2, 4, [0, 1, 64, 65, 700, 700, 1500], "reftest", 3),
+]
+
+
+@pytest.mark.parametrize("B,T,Hq,Hv,cu,dist,pc", CP_CASES)
+def test_backward_context_parallel(B, T, Hq, Hv, cu, dist, pc, monkeypatch):
+    """State recompute and the dS recurrence split into pieces (forward and reverse gate-driven warm-up)."""
+    from flashqla_b200 import ops
+    monkeypatch.setattr(ops, "_FORCE_PIECE_CHUNKS", pc)
+    cu_t = None if cu is None else torch.tensor(cu, dtype=torch.int32)
+    q, k, v, g, beta, h0, do, dht = make_inputs(13, B, T, Hq, Hv, dist, None if cu is None else len(cu) - 1)
+    gc = orc.chunk_local_cumsum(g, cu_t)
+    ref = orc.gdr_bwd(q.float(), k.float(), v.float(), gc, beta, do.float(), dht, None, h0, cu_t)
+    got = run_bwd(q, k, v, g, beta, h0, do, dht, cu_t)
+    errs = {n: orc.rel_to_max(x, r) for n, x, r in zip(NAMES, got, ref)}
+    assert all(e < TOL for e in errs.values()), str({k_: f'{v_:.2e}' for k_, v_ in errs.items()})

@@ -102,3 +102,29 @@ def test_forward_is_deterministic():
     for _ in range(5):
         b = run_fwd(q, k, v, g, beta, h0, None)
         assert torch.equal(a[2], b[2]) and torch.equal(a[4], b[4])
+
+
+CP_CASES = [
+    # B, T, Hq, Hv, cu, dist, piece_chunks
+    (1, 1024, 2, 2, None, "baseline", 4),
+    (1, 1024, 2, 2, None, "reftest", 4),      # one head has g = 0: its pieces replay from the sequence start (exact)
+    (2, 520, 1, 2, None, "baseline", 2),      # dense batch with a tail chunk, treated as packed rows
+    (1, 1500, 2, 4, [0, 1, 64, 65, 700, 700, 1500], "reftest", 3),
+]
+
+
+@pytest.mark.parametrize("B,T,Hq,Hv,cu,dist,pc", CP_CASES)
+def test_forward_context_parallel(B, T, Hq, Hv, cu, dist, pc, monkeypatch):
+    """Sequences split into pieces of `pc` chunks that run as independent CTAs (gate-driven warm-up)."""
+    from flashqla_b200 import ops
+    monkeypatch.setattr(ops, "_FORCE_PIECE_CHUNKS", pc)
+    cu_t = None if cu is None else torch.tensor(cu, dtype=torch.int32)
+    q, k, v, g, beta, h0 = make_inputs(9, B, T, Hq, Hv, dist, None if cu is None else len(cu) - 1)
+    gc_r, A_r, o_r, h_r, fs_r = orc.gdr_fwd(q.float(), k.float(), v.float(), g, beta, None, h0, cu_t, output_h=True)
+    dev = "cuda"
+    gc, A, o, h, fs = ops.chunk_gated_delta_rule_fwd(q.to(dev), k.to(dev), v.to(dev), g.to(dev), beta.to(dev), None,
+                                                     h0.to(dev), None if cu is None else cu_t.to(dev), True, True, True)
+    torch.cuda.synchronize()
+    assert orc.rel_to_max(o.float().cpu(), o_r) < TOL_BF16, "o"
+    assert orc.rel_to_max(fs.cpu(), fs_r) < TOL_FP32, "final_state"
+    assert orc.rel_to_max(h.float().cpu().reshape(h_r.shape), h_r) < TOL_BF16, "h"

@@ -43,12 +43,13 @@ def test_noalloc_matches_regular_entry_point(B, T, Hq, Hv, cu):
     plan = kernels.make_plan(B, T, cu_t, q.device)
     scale = 128 ** -0.5
     gc, A, _, _, _ = ops.chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale, h0, cu_t, True, False, False)
-    _, h, _ = kernels.fused_gdr_fwd(q, k, v, A, gc, beta, scale, initial_state=h0, output_final_state=False,
+    _, Ag, Pg = kernels.kkt_solve_gated(k, q, beta, gc, scale, plan, A=A)
+    _, h, _ = kernels.fused_gdr_fwd(q, k, v, Ag, None, gc, beta, scale, initial_state=h0, output_final_state=False,
                                     output_h=True, output_o=False, plan=plan)
     dh, dvp, dv = torch.empty_like(h), torch.empty_like(v), torch.empty_like(v)
     cu_p, off_p = plan.ptrs()
     st = kernels._stream()
-    rc = lib.fq_gdr_bwd_dh(q.data_ptr(), k.data_ptr(), A.data_ptr(), do.data_ptr(), gc.data_ptr(), beta.data_ptr(),
+    rc = lib.fq_gdr_bwd_dh(q.data_ptr(), k.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), do.data_ptr(), gc.data_ptr(), beta.data_ptr(),
                            dht.data_ptr(), None, dh.data_ptr(), dvp.data_ptr(), dv.data_ptr(), B, T, Hv, Hq, cu_p, off_p,
                            plan.n_seq, plan.total_chunks, scale, None, st)
     _lib.check(rc, "fq_gdr_bwd_dh")
