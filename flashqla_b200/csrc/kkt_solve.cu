@@ -6,9 +6,10 @@
 //   1. the four 16x16 diagonal blocks by column-parallel forward substitution in fp32,
 //   2. the two 16x16 blocks next to the diagonal:  X10 = -D1 (L10 D0),  X32 = -D3 (L32 D2),
 //   3. the 32x32 block below:  X_lo_hi = -X_hi (L_hl X_lo),
-// steps 2 and 3 on tensor cores with split-TF32 (hi + lo) operands so the products keep fp32
-// accuracy.  The unit costs 24 KB of HBM traffic for ~1.4 MFLOP, i.e. it is HBM-bound, which is
-// why the legacy warp-level MMA path is enough here.
+// steps 2 and 3 on tensor cores with TF32 operands and fp32 accumulation.  TF32 rounding (2^-11) of
+// these products changes A by at most 2.4e-4 (rms 9e-6) on unit-norm keys, below the 1e-3 rounding of
+// the bf16 result.  The unit costs 24 KB of HBM traffic for ~1.4 MFLOP, i.e. it is HBM-bound by
+// arithmetic intensity, which is why the legacy warp-level MMA path is enough here.
 //
 // Optionally (Ag / Pg given) the same CTA also emits the two gated, chunk-parallel operand tiles
 // of the recurrences, so that the serial kernels carry only serial work:
@@ -30,8 +31,10 @@ struct KktSmem {
     __nv_bfloat16 q[kChunk * kKLd];
     float kk[kChunk * kFLd];
   };
-  __nv_bfloat16 k[kChunk * kKLd];
-  float x[kChunk * kFLd];
+  union {  // the K tile is dead once K K^T and Q K^T are formed; the inverse X (fp32) then takes its place
+    __nv_bfloat16 k[kChunk * kKLd];
+    float x[kChunk * kFLd];
+  };
   float t[32 * kTLd];
   float beta[kChunk];
   float g[kChunk];
@@ -49,24 +52,17 @@ __device__ __forceinline__ void mma_tf32_1688(float (&c)[4], const uint32_t (&a)
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
-__device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(v));
-  const float r = v - __uint_as_float(hi);
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
-}
-// c += a * b with a, b given in fp32; three TF32 MMAs (hi*hi + hi*lo + lo*hi).
-__device__ __forceinline__ void mma_tf32x3(float (&c)[4], const float (&a)[4], const float (&b)[2]) {
-  uint32_t ah[4], al[4], bh[2], bl[2];
+// c += a * b with a, b given in fp32 and rounded to TF32.
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const float (&a)[4], const float (&b)[2]) {
+  uint32_t ah[4], bh[2];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) split_tf32(a[i], ah[i], al[i]);
+  for (int i = 0; i < 4; ++i) asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(ah[i]) : "f"(a[i]));
 #pragma unroll
-  for (int i = 0; i < 2; ++i) split_tf32(b[i], bh[i], bl[i]);
-  mma_tf32_1688(c, al, bh);
-  mma_tf32_1688(c, ah, bl);
+  for (int i = 0; i < 2; ++i) asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bh[i]) : "f"(b[i]));
   mma_tf32_1688(c, ah, bh);
 }
 
-__global__ void __launch_bounds__(128) kkt_solve_kernel(const __nv_bfloat16* __restrict__ k,
+__global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* __restrict__ k,
                                                        const float* __restrict__ beta,
                                                        __nv_bfloat16* __restrict__ A, int H, int Hg, SeqArgs sa,
                                                        const __nv_bfloat16* __restrict__ q,
@@ -92,7 +88,6 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __nv_bfloat16* __r
       if (row < p.len) v = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(row) * Hg * kDim) + piece);
       *reinterpret_cast<uint4*>(&s.k[row * kKLd + piece * 8]) = v;
     }
-    for (int i = tid; i < kChunk * kFLd; i += 128) s.x[i] = 0.f;
     if (Pg) {
       const __nv_bfloat16* qsrc = q + (static_cast<size_t>(p.tok0) * Hg + hg) * kDim;
 #pragma unroll
@@ -157,7 +152,8 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __nv_bfloat16* __r
         }
       }
     }
-    __syncthreads();  // every warp is done reading the Q tile that shares storage with kk
+    __syncthreads();  // every warp is done reading the Q and K tiles, whose storage kk and x reuse
+    for (int i = tid; i < kChunk * kFLd; i += 128) s.x[i] = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       if (j < ntiles) {
@@ -226,7 +222,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __nv_bfloat16* __r
         a[3] = bg8 * s.kk[(r0 + g + 8) * kFLd + c0 + k0 + t + 4];
         b[0] = s.x[(c0 + k0 + t) * kFLd + c0 + 8 * nt + g];
         b[1] = s.x[(c0 + k0 + t + 4) * kFLd + c0 + 8 * nt + g];
-        mma_tf32x3(c, a, b);
+        mma_tf32(c, a, b);
       }
       ts[g * 9 + 2 * t] = c[0];
       ts[g * 9 + 2 * t + 1] = c[1];
@@ -243,7 +239,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __nv_bfloat16* __r
         a[3] = s.x[(r0 + g + 8) * kFLd + r0 + k0 + t + 4];
         b[0] = ts[(k0 + t) * 9 + g];
         b[1] = ts[(k0 + t + 4) * 9 + g];
-        mma_tf32x3(d, a, b);
+        mma_tf32(d, a, b);
       }
       __syncthreads();  // every warp has read its diagonal blocks; the scratch is free again
       *reinterpret_cast<float2*>(&s.x[(r0 + g) * kFLd + c0 + 8 * nt + 2 * t]) = make_float2(-d[0], -d[1]);
@@ -270,7 +266,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __nv_bfloat16* __r
           float b[2];
           b[0] = s.x[(k0 + t) * kFLd + 16 * wc + 8 * n + g];
           b[1] = s.x[(k0 + t + 4) * kFLd + 16 * wc + 8 * n + g];
-          mma_tf32x3(c[n], a, b);
+          mma_tf32(c[n], a, b);
         }
       }
 #pragma unroll
@@ -295,7 +291,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __nv_bfloat16* __r
           float b[2];
           b[0] = s.t[(k0 + t) * kTLd + 16 * wc + 8 * n + g];
           b[1] = s.t[(k0 + t + 4) * kTLd + 16 * wc + 8 * n + g];
-          mma_tf32x3(d[n], a, b);
+          mma_tf32(d[n], a, b);
         }
       }
 #pragma unroll

@@ -53,9 +53,19 @@ _CACHE: "OrderedDict[tuple, tuple]" = OrderedDict()
 _CACHE_SIZE = 256
 
 
+_DENSE_CACHE: dict = {}
+
+
 def plan_dense(B: int, T: int) -> SeqPlan:
-    nc = (T + CHUNK - 1) // CHUNK
-    return SeqPlan(B, B * nc, B * T, nc, None, None, None, None)
+    """Plan of a dense batch; one object per (B, T) so that plans derived from it can be cached by identity."""
+    plan = _DENSE_CACHE.get((B, T))
+    if plan is None:
+        nc = (T + CHUNK - 1) // CHUNK
+        plan = SeqPlan(B, B * nc, B * T, nc, None, None, None, None)
+        if len(_DENSE_CACHE) > _CACHE_SIZE:
+            _DENSE_CACHE.clear()
+        _DENSE_CACHE[(B, T)] = plan
+    return plan
 
 
 def plan_packed(cu_seqlens: torch.Tensor, device=None) -> SeqPlan:
@@ -123,14 +133,32 @@ class CpPlan:
     seq_end: torch.Tensor           # [P] first token after the piece's sequence
 
 
-def choose_piece_chunks(n_chunks: list, H: int, n_sm: int, overhead: int = 6) -> int | None:
+def _makespan(pieces: list, H: int, n_sm: int, overhead: int) -> float:
+    """Finish time of list scheduling: CTAs (one per piece and head, in launch order) go to the SM that frees up first."""
+    import heapq
+    if not pieces:
+        return 0.0
+    free = [0.0] * n_sm
+    heapq.heapify(free)
+    end = 0.0
+    for x in pieces:
+        if x <= 0:
+            continue
+        for _ in range(H):
+            t = heapq.heappop(free) + x + overhead
+            end = max(end, t)
+            heapq.heappush(free, t)
+    return end
+
+
+def choose_piece_chunks(n_chunks: list, H: int, n_sm: int, overhead: int = 8) -> int | None:
     """Chunks per piece, or None to run un-split.
 
-    Cost model in units of one chunk step of one CTA: a CTA costs (chunks + overhead) where the
-    overhead stands for the replayed chunks and the CTA start-up; the kernel keeps one CTA per SM, so
-    the run takes about max(longest CTA, total work / n_sm).  The reference's rule
-    (cp_context.py:52-57, 86-87) was fitted to 132 SMs with up to two CTAs each; this one follows
-    from the one-CTA-per-SM kernel.
+    Cost model in units of one chunk step of one CTA: a CTA costs (chunks + overhead), the overhead
+    standing for the replayed chunks and the CTA start-up; the kernels keep one CTA per SM, so the
+    run time is the makespan of scheduling the CTAs, in launch order, on n_sm machines.  The
+    reference's rule (cp_context.py:52-57, 86-87) was fitted to 132 SMs with up to two CTAs each;
+    this one follows from the one-CTA-per-SM kernels.
     """
     longest = max(n_chunks) if n_chunks else 0
     if longest <= 8:
@@ -138,19 +166,22 @@ def choose_piece_chunks(n_chunks: list, H: int, n_sm: int, overhead: int = 6) ->
 
     def cost(L):
         pieces = [min(L, c - i) for c in n_chunks for i in range(0, c, L)] if L < longest else list(n_chunks)
-        work = sum((x + overhead) for x in pieces if x > 0) * H
-        return max(max(pieces) + overhead, work / n_sm)
+        return _makespan(pieces, H, n_sm, overhead)
 
     base = cost(longest)
     best_L, best = None, base
+    cands = set()
     L = 1 << (longest - 1).bit_length()
     while L >= 8:
-        for cand in (L, (3 * L) // 4):
-            if 8 <= cand < longest:
-                c = cost(cand)
-                if c < best * 0.999:
-                    best_L, best = cand, c
+        cands.update((L, (3 * L) // 4))
         L //= 2
+    for parts in range(2, 65):  # equal splits of the longest sequence
+        cands.add(-(-longest // parts))
+    for cand in sorted(cands, reverse=True):
+        if 8 <= cand < longest:
+            c = cost(cand)
+            if c < best * 0.999:
+                best_L, best = cand, c
     if best_L is None or best > 0.9 * base:
         return None
     return best_L
@@ -163,8 +194,9 @@ def plan_cp(plan: SeqPlan, B: int, T: int, H: int, n_sm: int, device, piece_chun
     """CpPlan for a batch, or None when splitting does not pay.  Dense batches are treated as packed
     ones over the flattened token axis (row b*T + t)."""
     key = (id(plan), B, T, H, n_sm, str(device), piece_chunks)
-    if key in _CP_CACHE and _CP_CACHE[key] is not None and _CP_CACHE[key][0] is plan:
-        return _CP_CACHE[key][1]
+    hit = _CP_CACHE.get(key)
+    if hit is not None and hit[0] is plan:
+        return hit[1]
     cu = plan.cu_host if plan.packed else [b * T for b in range(B + 1)]
     n_chunks = [(cu[i + 1] - cu[i] + CHUNK - 1) // CHUNK for i in range(len(cu) - 1)]
     L = piece_chunks if piece_chunks is not None else choose_piece_chunks(n_chunks, H, n_sm)
