@@ -189,7 +189,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     import flashqla_b200 as fq
     from flashqla_b200 import kernels
-    from flashqla_b200.planner import plan_dense
+    from flashqla_b200.planner import plan_cp, plan_dense
 
     host, d = make_inputs(w, dev, seed=rank, pin=True)
     torch.cuda.synchronize()
@@ -197,24 +197,36 @@ def main():
     tokens = B * T
     scale = 128 ** -0.5
     plan = plan_dense(B, T)
-    from flashqla_b200.planner import plan_cp
     cp = plan_cp(plan, B, T, Hv, kernels.sm_count(dev), dev)
-    fwd_events = []
+    stamps = []          # per step: list of (name, start_event, end_event) for the forward kernels
+    launches = [0]
+
+    def timed(name, fn, rec):
+        if rec is None:
+            return fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = fn()
+        e1.record()
+        rec.append((name, e0, e1))
+        return out
 
     def step(record=False):
-        g_cum = kernels.chunk_local_cumsum(d["g"], plan=plan)
-        A, Ag, Pg = kernels.kkt_solve_gated(d["k"], d["q"], d["beta"], g_cum, scale, plan)
-        if record:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-        o, _, fs = kernels.fused_gdr_fwd(d["q"], d["k"], d["v"], Ag, Pg, g_cum, d["beta"], scale, initial_state=d["h0"],
-                                         plan=plan, cp=cp, warmup=kernels.cp_warmup(g_cum, cp, Hv) if cp is not None else None)
-        if record:
-            e1.record()
-            fwd_events.append((e0, e1))
+        rec = [] if record else None
+        g_cum = timed("chunk_cumsum", lambda: kernels.chunk_local_cumsum(d["g"], plan=plan), rec)
+        A, Ag, Pg = timed("kkt_solve", lambda: kernels.kkt_solve_gated(d["k"], d["q"], d["beta"], g_cum, scale, plan), rec)
+        warm = timed("cp_warmup", lambda: kernels.cp_warmup(g_cum, cp, Hv), rec) if cp is not None else None
+        o, _, fs = timed("gdr_fwd", lambda: kernels.fused_gdr_fwd(d["q"], d["k"], d["v"], Ag, Pg, g_cum, d["beta"], scale,
+                                                                 initial_state=d["h0"], plan=plan, cp=cp, warmup=warm), rec)
+        n = 3 + (1 if cp is not None else 0)
         if w["bwd"]:
-            fq.chunk_gated_delta_rule_bwd(d["q"], d["k"], d["v"], g_cum, d["beta"], A, d["do"], d["dht"], scale,
-                                          d["h0"], None)
+            timed("backward", lambda: fq.chunk_gated_delta_rule_bwd(d["q"], d["k"], d["v"], g_cum, d["beta"], A, d["do"],
+                                                                     d["dht"], scale, d["h0"], None), rec)
+            # kkt(gated) + fwd(h) + bwd_dh + bwd_chunk + reverse cumsum (+ 2 warm-up scans, + 2 head sums)
+            n += 5 + (2 if cp is not None else 0) + (2 if Hq < Hv else 0)
+        if record:
+            stamps.append(rec)
+        launches[0] = n
         return o, fs
 
     def barrier():
@@ -236,33 +248,41 @@ def main():
     t1.record()
     barrier()
     ms_total = t0.elapsed_time(t1)
-    fwd_ms = sum(a.elapsed_time(b) for a, b in fwd_events) / len(fwd_events)
+    kernel_ms = {}
+    for rec in stamps:
+        for name, e0, e1 in rec:
+            kernel_ms[name] = kernel_ms.get(name, 0.0) + e0.elapsed_time(e1) / len(stamps)
+    fwd_ms = kernel_ms["gdr_fwd"]
 
-    # ---- end to end through the public operator with host buffers
+    # ---- end to end through the public operator with host buffers (pinned), copies inside the timed region
     def e2e_step():
-        dd = {k_: host[k_].to(dev, non_blocking=True) for k_ in ("q", "k", "v", "g", "beta", "h0")}
-        _, _, o, _, fs = fq.chunk_gated_delta_rule_fwd(dd["q"], dd["k"], dd["v"], dd["g"], dd["beta"], scale, dd["h0"],
-                                                       None, True, False, True)
-        if w["bwd"]:
-            raise NotImplementedError
-        return o.to("cpu", non_blocking=True), fs.to("cpu", non_blocking=True)
+        dd = {k_: host[k_].to(dev, non_blocking=True) for k_ in host}
+        if not w["bwd"]:
+            _, _, o, _, fs = fq.chunk_gated_delta_rule_fwd(dd["q"], dd["k"], dd["v"], dd["g"], dd["beta"], scale,
+                                                           dd["h0"], None, True, False, True)
+            return [o.to("cpu", non_blocking=True), fs.to("cpu", non_blocking=True)]
+        leaves = [dd[k_].requires_grad_() for k_ in ("q", "k", "v", "g", "beta", "h0")]
+        o, fs = fq.chunk_gated_delta_rule(leaves[0], leaves[1], leaves[2], leaves[3], leaves[4], scale=scale,
+                                          initial_state=leaves[5], output_final_state=True)
+        torch.autograd.backward([o, fs], [dd["do"], dd["dht"]])
+        return [x.grad.to("cpu", non_blocking=True) for x in leaves] + [o.detach().to("cpu", non_blocking=True)]
 
-    e2e = None
-    if not w["bwd"]:
-        for _ in range(2):
-            e2e_step()
-        barrier()
-        n_e2e = max(3, min(args.steps, 5))
-        w0 = time.perf_counter()
-        for _ in range(n_e2e):
-            e2e_step()
-        barrier()
-        e2e_ms = 1e3 * (time.perf_counter() - w0) / n_e2e
-        h2d = sum(host[k_].numel() * host[k_].element_size() for k_ in ("q", "k", "v", "g", "beta", "h0"))
-        d2h = tokens * Hv * 128 * 2 + B * Hv * 128 * 128 * 4
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    n_e2e = max(3, min(args.steps, 5))
+    w0 = time.perf_counter()
+    for _ in range(n_e2e):
+        e2e_step()
+    barrier()
+    e2e_ms = 1e3 * (time.perf_counter() - w0) / n_e2e
+    h2d = sum(host[k_].numel() * host[k_].element_size() for k_ in host)
+    d2h = tokens * Hv * 128 * 2 + B * Hv * 128 * 128 * 4
+    if w["bwd"]:
+        d2h = sum(host[k_].numel() * host[k_].element_size() for k_ in ("q", "k", "v", "g", "beta", "h0")) + tokens * Hv * 256
     clocks = sampler.stop() if sampler else None
 
-    ms = torch.tensor([ms_total / args.steps, fwd_ms, e2e_ms if not w["bwd"] else 0.0], device=dev, dtype=torch.float64)
+    ms = torch.tensor([ms_total / args.steps, fwd_ms, e2e_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms_step, fwd_ms, e2e_ms = (float(x) for x in ms.tolist())
@@ -270,24 +290,25 @@ def main():
     if rank == 0:
         peaks, how = measured_peaks()
         units = plan.total_chunks * Hv
-        q_bytes = FWD_BYTES_PER_UNIT - 2 * 16384 + 2 * 16384 * Hq // Hv  # q,k are shared by Hv/Hq V-heads
-        alg_bytes = units * q_bytes + 2 * B * Hv * 128 * 128 * 4          # + h0 read, final state write
+        unit_bytes = FWD_BYTES_PER_UNIT - 2 * 16384 + 2 * 16384 * Hq // Hv  # q,k are shared by Hv/Hq V-heads
+        alg_bytes = units * unit_bytes + 2 * B * Hv * 128 * 128 * 4          # + h0 read, final state write
         achieved = alg_bytes / (fwd_ms * 1e-3) / 1e9
         line = {
             "metric": metric_name(w), "value": world * tokens / (ms_step * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": w["desc"], "l2": "inputs (1.5 GB) exceed the 126 MB L2; no flush needed",
-                       "kernels_per_step": ["chunk_cumsum", "kkt_solve", "gdr_fwd"]},
-            "gpu_launches": (3 + (0 if not w["bwd"] else 0)) * args.steps,
+            "config": {"workload": w["desc"], "l2": "inputs exceed the 126 MB L2; no flush needed",
+                       "context_parallel_piece_chunks": None if cp is None else cp.piece_chunks,
+                       "kernel_ms": {k_: round(v_, 4) for k_, v_ in kernel_ms.items()}},
+            "gpu_launches": launches[0] * args.steps,
             "roofline": {"kernel": "gdr_fwd_kernel", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
-                         "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": how + " (of measured copy bandwidth)" if how == "measured" else how,
+                         "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                         "peak_source": "measured copy bandwidth (MEASURED_PEAKS.json)" if how == "measured" else "fallback",
                          "kernel_ms": fwd_ms, "algorithmic_bytes": alg_bytes, "traffic": None},
             "clocks": clocks,
+            "e2e": {"value": world * tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         }
-        if not w["bwd"]:
-            line["e2e"] = {"value": world * tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-                           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
         if not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             tps, dt, sample = cpu_oracle_sample(w, threads)
