@@ -37,6 +37,8 @@ WORKLOADS = {
                desc="fwd prefill B=1 T=32768 Hq=Hv=64 K=V=128 bf16, g=logsigmoid(randn) fp32, h0=zeros"),
     "c2s": dict(B=1, T=16384, Hq=32, Hv=32, bwd=False,
                 desc="(profiling case) fwd B=1 T=16384 Hq=Hv=32 K=V=128 bf16"),
+    "c5": dict(B=1, T=1048576, Hq=8, Hv=8, bwd=True, seq_parallel=True,
+               desc="fwd+bwd B=1 T=1048576 Hq=Hv=8 K=V=128 bf16, ONE sequence split contiguously over the GPUs"),
     "c3": dict(B=4, T=8192, Hq=16, Hv=32, bwd=True,
                desc="fwd+bwd B=4 T=8192 Hq=16 Hv=32 K=V=128 bf16, h0=0.1 randn, dht=0.01 randn"),
 }
@@ -122,7 +124,7 @@ def cpu_oracle_sample(w, threads):
     Cost is linear in T*H, so tokens/s at the full head count = T_s * (H_s / Hv) / time."""
     from oracle import gdr_oracle as orc
     torch.set_num_threads(threads)
-    Ts, Hs = 8192, 16
+    Ts, Hs = 32768, 32
     Hqs = max(1, Hs * w["Hq"] // w["Hv"])
     sw = dict(B=1, T=Ts, Hq=Hqs, Hv=Hs, bwd=w["bwd"])
     host, _ = make_inputs(sw, None, seed=1)
@@ -156,6 +158,66 @@ def run_reference(args, w, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_sequence_parallel(args, w, rank, world, local):
+    """Config 5: one long sequence, rank r owns tokens [r*T/N, (r+1)*T/N); halo exchange over NCCL."""
+    import torch.distributed as dist
+    from flashqla_b200 import dist as fqd
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl" if world > 1 else "gloo", device_id=dev if world > 1 else None,
+                                rank=rank, world_size=world,
+                                init_method=None if "MASTER_ADDR" in os.environ else "tcp://127.0.0.1:29533")
+    T, H = w["T"], w["Hv"]
+    b = fqd.shard_sequence(T, world)
+    Tl = b[rank + 1] - b[rank]
+    gen = torch.Generator(device="cpu").manual_seed(100 + rank)
+    rn = lambda *shape: torch.randn(*shape, generator=gen)
+    q = l2norm(rn(1, Tl, H, 128)).bfloat16().to(dev); k = l2norm(rn(1, Tl, H, 128)).bfloat16().to(dev)
+    v = rn(1, Tl, H, 128).bfloat16().to(dev); g = torch.nn.functional.logsigmoid(rn(1, Tl, H)).to(dev)
+    beta = rn(1, Tl, H).sigmoid().to(dev); do = rn(1, Tl, H, 128).bfloat16().to(dev)
+    scale = 128 ** -0.5
+
+    def step():
+        o, fs, info = fqd.cp_forward(q, k, v, g, beta, scale, None, None)
+        fqd.cp_backward(q, k, v, g, beta, do, None, scale, info["h_in"], None, mode=info["mode"])
+        return info
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        info = step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for _ in range(args.steps):
+        step()
+    t1.record()
+    barrier()
+    ms = torch.tensor([t0.elapsed_time(t1) / args.steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop() if sampler else None
+    if rank == 0:
+        ms_step = float(ms.item())
+        print(json.dumps({
+            "metric": "GDN fwd+bwd tokens/s, one 1M-token sequence split over the GPUs", "value": T / (ms_step * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["desc"], "exchange": info["mode"], "halo_chunks": info["halo_chunks"],
+                       "replayed_chunks": info["replayed"]},
+            "clocks": clocks}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def metric_name(w):
     return "GDN fwd+bwd tokens/s per B200" if w["bwd"] else "GDN fwd tokens/s per B200"
 
@@ -183,6 +245,9 @@ def main():
     import torch.distributed as dist
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    if w.get("seq_parallel"):
+        run_sequence_parallel(args, w, rank, world, local)
+        return
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:

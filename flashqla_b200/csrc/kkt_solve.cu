@@ -102,63 +102,54 @@ __global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* 
   }
   __syncthreads();
 
-  // ---- Q K^T (lower block-triangle) kept in registers for all V-heads of the group
+  // ---- Q K^T (kept in registers for all V-heads of the group) and K K^T (fp32, to shared), lower
+  //      block-triangle only; one pass over the K tile feeds both products (shared B fragments)
   float qk[8][4];
-  if (Pg) {
+  {
     const int m0 = warp * 16;
     const int ntiles = 2 * warp + 2;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) qk[j][0] = qk[j][1] = qk[j][2] = qk[j][3] = 0.f;
-#pragma unroll
-    for (int k0 = 0; k0 < kDim; k0 += 16) {
-      uint32_t a[4];
-      a[0] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g) * kKLd + k0 + 2 * t]);
-      a[1] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g + 8) * kKLd + k0 + 2 * t]);
-      a[2] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g) * kKLd + k0 + 8 + 2 * t]);
-      a[3] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g + 8) * kKLd + k0 + 8 + 2 * t]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (j < ntiles) {
-          uint32_t b[2];
-          b[0] = *reinterpret_cast<const uint32_t*>(&s.k[(j * 8 + g) * kKLd + k0 + 2 * t]);
-          b[1] = *reinterpret_cast<const uint32_t*>(&s.k[(j * 8 + g) * kKLd + k0 + 8 + 2 * t]);
-          mma_bf16_16816(qk[j], a, b);
-        }
-      }
-    }
-  }
-
-  // ---- K K^T (lower block-triangle) with bf16 MMA, fp32 result in shared (skipped when A is given)
-  if (A_in == nullptr) {
-    const int m0 = warp * 16;
-    const int ntiles = 2 * warp + 2;
+    const bool do_qk = Pg != nullptr, do_kk = A_in == nullptr;
     float acc[8][4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int j = 0; j < 8; ++j) {
+      qk[j][0] = qk[j][1] = qk[j][2] = qk[j][3] = 0.f;
+      acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    }
 #pragma unroll
     for (int k0 = 0; k0 < kDim; k0 += 16) {
-      uint32_t a[4];
-      a[0] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g) * kKLd + k0 + 2 * t]);
-      a[1] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g + 8) * kKLd + k0 + 2 * t]);
-      a[2] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g) * kKLd + k0 + 8 + 2 * t]);
-      a[3] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g + 8) * kKLd + k0 + 8 + 2 * t]);
+      uint32_t aq[4] = {0, 0, 0, 0}, ak[4] = {0, 0, 0, 0};
+      if (do_qk) {
+        aq[0] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g) * kKLd + k0 + 2 * t]);
+        aq[1] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g + 8) * kKLd + k0 + 2 * t]);
+        aq[2] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g) * kKLd + k0 + 8 + 2 * t]);
+        aq[3] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g + 8) * kKLd + k0 + 8 + 2 * t]);
+      }
+      if (do_kk) {
+        ak[0] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g) * kKLd + k0 + 2 * t]);
+        ak[1] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g + 8) * kKLd + k0 + 2 * t]);
+        ak[2] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g) * kKLd + k0 + 8 + 2 * t]);
+        ak[3] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g + 8) * kKLd + k0 + 8 + 2 * t]);
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         if (j < ntiles) {
-          uint32_t b[2];
-          b[0] = *reinterpret_cast<const uint32_t*>(&s.k[(j * 8 + g) * kKLd + k0 + 2 * t]);
-          b[1] = *reinterpret_cast<const uint32_t*>(&s.k[(j * 8 + g) * kKLd + k0 + 8 + 2 * t]);
-          mma_bf16_16816(acc[j], a, b);
+          uint32_t bfr[2];
+          bfr[0] = *reinterpret_cast<const uint32_t*>(&s.k[(j * 8 + g) * kKLd + k0 + 2 * t]);
+          bfr[1] = *reinterpret_cast<const uint32_t*>(&s.k[(j * 8 + g) * kKLd + k0 + 8 + 2 * t]);
+          if (do_qk) mma_bf16_16816(qk[j], aq, bfr);
+          if (do_kk) mma_bf16_16816(acc[j], ak, bfr);
         }
       }
     }
-    __syncthreads();  // every warp is done reading the Q and K tiles, whose storage kk and x reuse
-    for (int i = tid; i < kChunk * kFLd; i += 128) s.x[i] = 0.f;
+    if (do_kk) {
+      __syncthreads();  // every warp is done reading the Q and K tiles, whose storage kk and x reuse
+      for (int i = tid; i < kChunk * kFLd; i += 128) s.x[i] = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (j < ntiles) {
-        *reinterpret_cast<float2*>(&s.kk[(m0 + g) * kFLd + j * 8 + 2 * t]) = make_float2(acc[j][0], acc[j][1]);
-        *reinterpret_cast<float2*>(&s.kk[(m0 + g + 8) * kFLd + j * 8 + 2 * t]) = make_float2(acc[j][2], acc[j][3]);
+      for (int j = 0; j < 8; ++j) {
+        if (j < ntiles) {
+          *reinterpret_cast<float2*>(&s.kk[(m0 + g) * kFLd + j * 8 + 2 * t]) = make_float2(acc[j][0], acc[j][1]);
+          *reinterpret_cast<float2*>(&s.kk[(m0 + g + 8) * kFLd + j * 8 + 2 * t]) = make_float2(acc[j][2], acc[j][3]);
+        }
       }
     }
   }
@@ -168,7 +159,8 @@ __global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* 
     __syncthreads();  // kk complete (first pass) / previous head's stores done
     if (tid < kChunk) {
       s.beta[tid] = (tid < p.len) ? __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hv) : 0.f;
-      if (Ag || Pg) s.g[tid] = __ldg(g_cum + static_cast<size_t>(p.tok0 + min(tid, p.len - 1)) * H + hv);
+      // log-gate cumsum times log2(e): exp(g_i - g_j) = exp2(g2_i - g2_j)
+      if (Ag || Pg) s.g[tid] = 1.4426950408889634f * __ldg(g_cum + static_cast<size_t>(p.tok0 + min(tid, p.len - 1)) * H + hv);
     }
     __syncthreads();
 
@@ -313,7 +305,9 @@ __global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* 
       for (int it = 0; it < 4; ++it) {
         const int row = it * 16 + (tid >> 3), piece = tid & 7;
         if (row < p.len) {
-          const float* xr = &s.x[row * kFLd + piece * 8];
+          const float4 x0 = *reinterpret_cast<const float4*>(&s.x[row * kFLd + piece * 8]);
+          const float4 x1 = *reinterpret_cast<const float4*>(&s.x[row * kFLd + piece * 8 + 4]);
+          const float xr[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
           uint4 v;
           if (A_in == nullptr) {
             v.x = pack_bf16(xr[0], xr[1]);
@@ -323,12 +317,18 @@ __global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* 
             *(reinterpret_cast<uint4*>(dst + static_cast<size_t>(row) * H * kChunk) + piece) = v;
           }
           if (dstg) {
-            const float gi = s.g[row];
-            float y[8];
+            float y[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (piece * 8 <= row) {  // pieces entirely above the diagonal stay zero
+              const float gi = s.g[row];
+              const float4 g0 = *reinterpret_cast<const float4*>(&s.g[piece * 8]);
+              const float4 g1 = *reinterpret_cast<const float4*>(&s.g[piece * 8 + 4]);
+              const float4 b0 = *reinterpret_cast<const float4*>(&s.beta[piece * 8]);
+              const float4 b1 = *reinterpret_cast<const float4*>(&s.beta[piece * 8 + 4]);
+              const float gj[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+              const float bj[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const int j = piece * 8 + e;
-              y[e] = (j <= row) ? xr[e] * fast_exp(gi - s.g[j]) * s.beta[j] : 0.f;
+              for (int e = 0; e < 8; ++e)
+                y[e] = (piece * 8 + e <= row) ? xr[e] * exp2f(gi - gj[e]) * bj[e] : 0.f;
             }
             v.x = pack_bf16(y[0], y[1]);
             v.y = pack_bf16(y[2], y[3]);
@@ -353,8 +353,9 @@ __global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* 
             const int c0 = j * 8 + 2 * t;
             float y0 = 0.f, y1 = 0.f;
             if (j < 2 * warp + 2) {
-              if (c0 <= row) y0 = scale * fast_exp(gi - s.g[c0]) * qk[j][2 * half];
-              if (c0 + 1 <= row) y1 = scale * fast_exp(gi - s.g[c0 + 1]) * qk[j][2 * half + 1];
+              const float2 gj = *reinterpret_cast<const float2*>(&s.g[c0]);
+              if (c0 <= row) y0 = scale * exp2f(gi - gj.x) * qk[j][2 * half];
+              if (c0 + 1 <= row) y1 = scale * exp2f(gi - gj.y) * qk[j][2 * half + 1];
             }
             *reinterpret_cast<uint32_t*>(dstp + static_cast<size_t>(row) * H * kChunk + c0) = pack_bf16(y0, y1);
           }
