@@ -71,7 +71,8 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
     dk_h = torch.empty(B, T, H, K, dtype=q.dtype, device=dev)
     dg_c = torch.empty(B, T, H, dtype=torch.float32, device=dev)
     db = torch.empty(B, T, H, dtype=torch.float32, device=dev)
-    rc = lib.fq_gdr_bwd_chunk(q.data_ptr(), k.data_ptr(), v.data_ptr(), A.data_ptr(), do.data_ptr(), dvp.data_ptr(),
+    rc = lib.fq_gdr_bwd_chunk(q.data_ptr(), k.data_ptr(), v.data_ptr(), A.data_ptr(), Ag.data_ptr(), Pg.data_ptr(),
+                              do.data_ptr(), dvp.data_ptr(),
                               dv.data_ptr(), h.data_ptr(), dh.data_ptr(), g.data_ptr(), bt.data_ptr(), dq_h.data_ptr(),
                               dk_h.data_ptr(), dg_c.data_ptr(), db.data_ptr(), B, T, H, Hg, cu_p, off_p, plan.n_seq,
                               plan.total_chunks, float(scale), st_p, kernels._stream())

@@ -3,13 +3,15 @@
 // (chunk, V-head) unit is independent.  A persistent CTA walks units; per unit it runs six rounds
 // of tcgen05 MMAs (M = 64: row = token of the chunk) with CUDA-core epilogues in between:
 //
-//   round 1  U = K S0 | QK = Q K^T | accQ = dO S0^T | accK = dVg S0^T          (dVg = -gamma o dv)
-//            -> W = V - gamma o U, P_g, A_g, accQ *= scale*gamma, dg += rowsum(Q o accQ) + rowsum(K o accK)
+//   round 1  U = K S0 | accQ = dO S0^T | accK = dVg S0^T                       (dVg = -gamma o dv)
+//            -> W = V - gamma o U, accQ *= scale*gamma, dg += rowsum(Q o accQ) + rowsum(K o accK)
+//            (A_g and P_g tiles come from kkt_solve.cu)
 //   round 2  V' = A_g W
 //   round 3  K1 = V' dS^T | dPg = dO V'^T | dAg = dV' W^T
 //            -> accK += rho o K1, dg -= rowsum(K o rho K1); dP = scale G o dPg; dA = (G o dAg) beta_col;
-//               dg += rowsum - colsum of (dPg o P_g + dAb o A_b); dbeta += colsum(dAb o A)
-//   round 4  accQ += dP K | accK += dP^T Q | X1 = A^T dA          -> dq
+//               dg += rowsum of T = dPg o P_g + dAb o A_b; tiles T and T3 = dAb o A kept for the column sums
+//   round 4  accQ += dP K | accK += dP^T Q | X1 = A^T dA | column sums T^T 1, T3^T 1 (ones-vector MMAs)
+//            -> dq, dg -= colsum(T), dbeta += colsum(T3)
 //   round 5  X2 = X1 A^T | KK = K K^T
 //            -> dL = -strict_lower(X2); dbeta += rowsum(dL o KK); dAs = beta_row dL + (beta_row dL)^T
 //   round 6  accK += dAs K                                        -> dk, dg, dbeta
@@ -23,7 +25,7 @@
 namespace fq {
 
 constexpr int kBcThreads = 256;
-constexpr uint32_t kBcLoadBytes = 6 * 16384 + 8192 + 2 * 32768;
+constexpr uint32_t kBcLoadBytes = 6 * 16384 + 3 * 8192 + 2 * 32768;
 
 constexpr uint32_t kBcColU = 0;    // 128: U, then V', then K1, then X1 (0-63) / X2 (64-127)
 constexpr uint32_t kBcColQK = 128; // 64: QK^T, then dPg, then KK^T
@@ -44,6 +46,9 @@ struct BwdChunkSmem {
   unsigned char at[8192];    // A   [64 i][64 j]
   unsigned char ag[8192];    // A_g -> dA -> dAs
   unsigned char pg[8192];    // P_g -> dP -> X1
+  unsigned char t12[8192];   // T  = dPg o P_g + dAb o A_b   [64 i][64 j]
+  unsigned char t3[8192];    // T3 = dAb o A                 [64 i][64 j]
+  unsigned char ones[2048];  // 16 x 64 bf16 ones: B operand that turns an MMA into a column sum
   float g[kChunk], gam[kChunk], rho[kChunk], beta[kChunk];
   float dg_s[kChunk], db_s[kChunk];
   float dgl_s;
@@ -81,7 +86,8 @@ __global__ void __launch_bounds__(kBcThreads, 1)
 gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                      const __grid_constant__ CUtensorMap map_dvp, const __grid_constant__ CUtensorMap map_dv,
-                     const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_h,
+                     const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_ag,
+                     const __grid_constant__ CUtensorMap map_pg, const __grid_constant__ CUtensorMap map_h,
                      const __grid_constant__ CUtensorMap map_dh, const BwdChunkParams p) {
   extern __shared__ unsigned char smem_dyn[];
   BwdChunkSmem& s = *reinterpret_cast<BwdChunkSmem*>(
@@ -100,8 +106,10 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     fence_mbar_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); tma_prefetch_desc(&map_do);
     tma_prefetch_desc(&map_dvp); tma_prefetch_desc(&map_dv); tma_prefetch_desc(&map_a); tma_prefetch_desc(&map_h);
-    tma_prefetch_desc(&map_dh);
+    tma_prefetch_desc(&map_dh); tma_prefetch_desc(&map_ag); tma_prefetch_desc(&map_pg);
   }
+  for (int i = tid; i < 512; i += kBcThreads) reinterpret_cast<uint32_t*>(s.ones)[i] = 0x3F803F80u;
+  fence_async_smem();
   if (warp == 0) {
     tmem_alloc(&s.tmem_base, 512);
     tmem_relinquish();
@@ -112,12 +120,14 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   const uint32_t tm = s.tmem_base;
   const uint32_t skt = smem_u32(s.kt), sqt = smem_u32(s.qt), swt = smem_u32(s.wt), sdot = smem_u32(s.dot),
                  sdvp = smem_u32(s.dvp), sdvg = smem_u32(s.dvg), svp = smem_u32(s.vp), ss0 = smem_u32(s.s0),
-                 sds = smem_u32(s.ds), sat = smem_u32(s.at), sag = smem_u32(s.ag), spg = smem_u32(s.pg);
+                 sds = smem_u32(s.ds), sat = smem_u32(s.at), sag = smem_u32(s.ag), spg = smem_u32(s.pg),
+                 st12 = smem_u32(s.t12), st3 = smem_u32(s.t3), sones = smem_u32(s.ones);
   constexpr uint32_t id64_128_kk = umma_idesc(64, 128, false, false, true);
   constexpr uint32_t id64_128_kmn = umma_idesc(64, 128, false, true, true);
   constexpr uint32_t id64_128_mnmn = umma_idesc(64, 128, true, true, true);
   constexpr uint32_t id64_64_kk = umma_idesc(64, 64, false, false, true);
   constexpr uint32_t id64_64_mnmn = umma_idesc(64, 64, true, true, true);
+  constexpr uint32_t id64_16_mnk = umma_idesc(64, 16, true, false, true);
 
   uint32_t tma_phase = 0, mma_phase = 0;
   const long long n_units = static_cast<long long>(p.total_chunks) * p.H;
@@ -146,6 +156,8 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       tma_load_3d(s.dvg, &map_dv, &s.bar_tma, 0, h, r0);
       tma_load_3d(s.dvg + 8192, &map_dv, &s.bar_tma, 64, h, r0);
       tma_load_3d(s.at, &map_a, &s.bar_tma, 0, h, r0);
+      tma_load_3d(s.ag, &map_ag, &s.bar_tma, 0, h, r0);
+      tma_load_3d(s.pg, &map_pg, &s.bar_tma, 0, h, r0);
       const int hr = static_cast<int>((static_cast<long long>(chunk) * p.H + h) * kDim);
       tma_load_3d(s.s0, &map_h, &s.bar_tma, 0, 0, hr);
       tma_load_3d(s.s0 + 16384, &map_h, &s.bar_tma, 64, 0, hr);
@@ -182,7 +194,11 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const uint32_t off = (pc >> 3) * 8192 + r * 128 + (pc & 7) * 16;
 #pragma unroll
         for (int t6 = 0; t6 < 6; ++t6) *reinterpret_cast<uint4*>(tiles[t6] + off) = make_uint4(0, 0, 0, 0);
-        if (pc < 8) *reinterpret_cast<uint4*>(s.at + r * 128 + pc * 16) = make_uint4(0, 0, 0, 0);
+        if (pc < 8) {
+          *reinterpret_cast<uint4*>(s.at + r * 128 + pc * 16) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(s.ag + r * 128 + pc * 16) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(s.pg + r * 128 + pc * 16) = make_uint4(0, 0, 0, 0);
+        }
       }
       __syncthreads();
     }
@@ -217,7 +233,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     fence_async_smem();
     __syncthreads();
 
-    const float g_r = s.g[row], gam_r = s.gam[row], rho_r = s.rho[row], beta_r = s.beta[row];
+    const float gam_r = s.gam[row], rho_r = s.rho[row];
 
     // ================================================================== round 1
     if (tid == 0) {
@@ -226,10 +242,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       for (int kk = 0; kk < 8; ++kk)
         umma_ss(tm + kBcColU, umma_desc_sw128(skt + off64(kk), 16, 1024), umma_desc_sw128(ss0 + kk * 2048, 16384, 1024),
                 id64_128_kmn, kk > 0);
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        umma_ss(tm + kBcColQK, umma_desc_sw128(sqt + off64(kk), 16, 1024), umma_desc_sw128(skt + off64(kk), 16, 1024),
-                id64_64_kk, kk > 0);
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk)
         umma_ss(tm + kBcColQ, umma_desc_sw128(sdot + off64(kk), 16, 1024), umma_desc_sw128(ss0 + off128(kk), 16, 1024),
@@ -262,34 +274,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
               xw[e] = pack_bf16(bf16_lo(xw[e]) - gam_r * __uint_as_float(u[8 * ch + 2 * e]),
                                 bf16_hi(xw[e]) - gam_r * __uint_as_float(u[8 * ch + 2 * e + 1]));
             *ptr = x;
-          }
-        }
-      }
-      // P_g and A_g
-      {
-        uint32_t r[32];
-        tmem_ld32(tmem_addr(tm, lane_base, kBcColQK + 32 * hf), r);
-        tmem_wait_ld();
-        if (active) {
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            const uint32_t so = sw128(row, (4 * hf + ch) * 16);
-            const uint4 av = *reinterpret_cast<const uint4*>(s.at + so);
-            const uint32_t* aw = reinterpret_cast<const uint32_t*>(&av);
-            uint4 pv, gv;
-            uint32_t* pw = reinterpret_cast<uint32_t*>(&pv);
-            uint32_t* gw = reinterpret_cast<uint32_t*>(&gv);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j = 32 * hf + 8 * ch + 2 * e;
-              const float G0 = (j <= row) ? fast_exp(g_r - s.g[j]) : 0.f;
-              const float G1 = (j + 1 <= row) ? fast_exp(g_r - s.g[j + 1]) : 0.f;
-              pw[e] = pack_bf16(p.scale * G0 * __uint_as_float(r[8 * ch + 2 * e]),
-                                p.scale * G1 * __uint_as_float(r[8 * ch + 2 * e + 1]));
-              gw[e] = pack_bf16(bf16_lo(aw[e]) * G0 * s.beta[j], bf16_hi(aw[e]) * G1 * s.beta[j + 1]);
-            }
-            *reinterpret_cast<uint4*>(s.pg + so) = pv;
-            *reinterpret_cast<uint4*>(s.ag + so) = gv;
           }
         }
       }
@@ -418,54 +402,75 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (active) atomicAdd(&s.dg_s[row], -kkp);
       const float kks = half_warp_sum(kkp);
       if (lane == 0) atomicAdd(&s.dgl_s, kks);
-      // dPg and dAg: dP, dA tiles; row sums and column sums for dg, column sums for dbeta
+      // dPg and dAg -> dP, dA, T, T3 tiles and the row sums of T.  Only lanes 0-15 hold accumulator rows
+      // (M = 64), so each of them hands half of its 32 columns to lane + 16: all 32 lanes work on 16 columns.
       uint32_t r1[32], r2[32];
       tmem_ld32(tmem_addr(tm, lane_base, kBcColQK + 32 * hf), r1);
       tmem_ld32(tmem_addr(tm, lane_base, kBcColX + 32 * hf), r2);
       tmem_wait_ld();
+      const int up = lane >> 4;                 // 0: columns 0-15 of the piece, 1: columns 16-31
+      const int row2 = 16 * q4 + (lane & 15);   // row served by this lane
+      const float g_r2 = s.g[row2];
+      float a1[16], a2[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t h1 = __shfl_sync(0xffffffffu, r1[16 + i], lane & 15);
+        const uint32_t h2 = __shfl_sync(0xffffffffu, r2[16 + i], lane & 15);
+        a1[i] = __uint_as_float(up ? h1 : r1[i]);
+        a2[i] = __uint_as_float(up ? h2 : r2[i]);
+      }
       float rows = 0.f;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        const uint32_t so = sw128(row, (4 * hf + ch) * 16);
+      for (int c2 = 0; c2 < 2; ++c2) {
+        const int ch = 2 * up + c2;  // 16-byte piece of the row's 64-byte half
+        const uint32_t so = sw128(row2, (4 * hf + ch) * 16);
         const uint4 pgv = *reinterpret_cast<const uint4*>(s.pg + so);
         const uint4 av = *reinterpret_cast<const uint4*>(s.at + so);
         const uint32_t* pw = reinterpret_cast<const uint32_t*>(&pgv);
         const uint32_t* aw = reinterpret_cast<const uint32_t*>(&av);
-        uint4 dpv, dav;
+        uint4 dpv, dav, t12v, t3v;
         uint32_t* dpw = reinterpret_cast<uint32_t*>(&dpv);
         uint32_t* daw = reinterpret_cast<uint32_t*>(&dav);
+        uint32_t* t12w = reinterpret_cast<uint32_t*>(&t12v);
+        uint32_t* t3w = reinterpret_cast<uint32_t*>(&t3v);
+        const int jb = 32 * hf + 8 * ch;
+        const float4 gj0 = *reinterpret_cast<const float4*>(&s.g[jb]);
+        const float4 gj1 = *reinterpret_cast<const float4*>(&s.g[jb + 4]);
+        const float4 bj0 = *reinterpret_cast<const float4*>(&s.beta[jb]);
+        const float4 bj1 = *reinterpret_cast<const float4*>(&s.beta[jb + 4]);
+        const float gj[8] = {gj0.x, gj0.y, gj0.z, gj0.w, gj1.x, gj1.y, gj1.z, gj1.w};
+        const float bjv[8] = {bj0.x, bj0.y, bj0.z, bj0.w, bj1.x, bj1.y, bj1.z, bj1.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          float dpo[2], dao[2];
+          float dpo[2], dao[2], t12o[2], t3o[2];
 #pragma unroll
           for (int z = 0; z < 2; ++z) {
-            const int j = 32 * hf + 8 * ch + 2 * e + z;
-            const bool keep = active && (j <= row);
-            const float G = keep ? fast_exp(g_r - s.g[j]) : 0.f;
+            const int j = jb + 2 * e + z;
+            const bool keep = j <= row2;
+            const float G = keep ? fast_exp(g_r2 - gj[2 * e + z]) : 0.f;
             const float pgx = z ? bf16_hi(pw[e]) : bf16_lo(pw[e]);
             const float ax = z ? bf16_hi(aw[e]) : bf16_lo(aw[e]);
-            const float dpg = __uint_as_float(r1[8 * ch + 2 * e + z]);
-            const float dab = G * __uint_as_float(r2[8 * ch + 2 * e + z]);
-            const float bj = s.beta[j];
-            const float t12 = keep ? (dpg * pgx + dab * ax * bj) : 0.f;
-            rows += t12;
-            const float cs = half_warp_sum(t12);
-            const float cb = half_warp_sum(dab * ax);
-            if (lane == 0) {
-              atomicAdd(&s.dg_s[j], -cs);
-              atomicAdd(&s.db_s[j], cb);
-            }
+            const float dpg = a1[8 * c2 + 2 * e + z];
+            const float dab = G * a2[8 * c2 + 2 * e + z];
+            const float bj = bjv[2 * e + z];
+            t12o[z] = keep ? (dpg * pgx + dab * ax * bj) : 0.f;
+            t3o[z] = dab * ax;
             dpo[z] = p.scale * G * dpg;
             dao[z] = dab * bj;
           }
           dpw[e] = pack_bf16(dpo[0], dpo[1]);
           daw[e] = pack_bf16(dao[0], dao[1]);
+          t12w[e] = pack_bf16(t12o[0], t12o[1]);
+          // the row sums use the rounded values that the column-sum MMA sees, so the diagonal terms cancel exactly
+          rows += bf16_lo(t12w[e]) + bf16_hi(t12w[e]);
+          t3w[e] = pack_bf16(t3o[0], t3o[1]);
         }
-        if (active) {
-          *reinterpret_cast<uint4*>(s.pg + so) = dpv;
-          *reinterpret_cast<uint4*>(s.ag + so) = dav;
-        }
+        *reinterpret_cast<uint4*>(s.pg + so) = dpv;
+        *reinterpret_cast<uint4*>(s.ag + so) = dav;
+        *reinterpret_cast<uint4*>(s.t12 + so) = t12v;
+        *reinterpret_cast<uint4*>(s.t3 + so) = t3v;
       }
+      rows += __shfl_xor_sync(0xffffffffu, rows, 16);
       if (active) atomicAdd(&s.dg_s[row], rows);
       tmem_wait_st();
     }
@@ -488,6 +493,14 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       for (int kk = 0; kk < 4; ++kk)
         umma_ss(tm + kBcColU, umma_desc_sw128(sat + kk * 2048, 8192, 1024), umma_desc_sw128(sag + kk * 2048, 8192, 1024),
                 id64_64_mnmn, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)  // column sums: D[j][:] = sum_i T[i][j]
+        umma_ss(tm + kBcColX, umma_desc_sw128(st12 + kk * 2048, 8192, 1024), umma_desc_sw128(sones + kk * 32, 16, 1024),
+                id64_16_mnk, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        umma_ss(tm + kBcColX + 16, umma_desc_sw128(st3 + kk * 2048, 8192, 1024), umma_desc_sw128(sones + kk * 32, 16, 1024),
+                id64_16_mnk, kk > 0);
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
@@ -507,6 +520,17 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           x.z = pack_bf16(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
           x.w = pack_bf16(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
           *reinterpret_cast<uint4*>(s.pg + sw128(row, (4 * hf + ch) * 16)) = x;
+        }
+      }
+      // column sums of T and T3 (every column of the small accumulators holds the same sum)
+      if (hf == 0) {
+        uint32_t c12[16], c3[16];
+        tmem_ld16(tmem_addr(tm, lane_base, kBcColX), c12);
+        tmem_ld16(tmem_addr(tm, lane_base, kBcColX + 16), c3);
+        tmem_wait_ld();
+        if (active) {
+          atomicAdd(&s.dg_s[row], -__uint_as_float(c12[0]));
+          atomicAdd(&s.db_s[row], __uint_as_float(c3[0]));
         }
       }
       // dq
@@ -554,23 +578,30 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 64 + 32 * hf), x2);
       tmem_ld32(tmem_addr(tm, lane_base, kBcColQK + 32 * hf), kk2);
       tmem_wait_ld();
-      if (active) {
-        float dbr = 0.f;
+      // as in round 3, lane + 16 takes over columns 16-31 of the row held by lane
+      const int up = lane >> 4;
+      const int row2 = 16 * q4 + (lane & 15);
+      const float beta_r2 = s.beta[row2];
+      float dbr = 0.f;
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int j = 32 * hf + e;
-          if (j < row) {
-            const float dL = -__uint_as_float(x2[e]);
-            dbr += dL * __uint_as_float(kk2[e]);
-            const unsigned short bits = __bfloat16_as_ushort(__float2bfloat16(beta_r * dL));
-            *reinterpret_cast<unsigned short*>(s.ag + sw128(row, j * 2)) = bits;
-            *reinterpret_cast<unsigned short*>(s.ag + sw128(j, row * 2)) = bits;
-          } else if (j == row) {
-            *reinterpret_cast<unsigned short*>(s.ag + sw128(row, j * 2)) = 0;
-          }
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t hx = __shfl_sync(0xffffffffu, x2[16 + i], lane & 15);
+        const uint32_t hk = __shfl_sync(0xffffffffu, kk2[16 + i], lane & 15);
+        const float xv = __uint_as_float(up ? hx : x2[i]);
+        const float kv = __uint_as_float(up ? hk : kk2[i]);
+        const int j = 32 * hf + 16 * up + i;
+        if (j < row2) {
+          const float dL = -xv;
+          dbr += dL * kv;
+          const unsigned short bits = __bfloat16_as_ushort(__float2bfloat16(beta_r2 * dL));
+          *reinterpret_cast<unsigned short*>(s.ag + sw128(row2, j * 2)) = bits;
+          *reinterpret_cast<unsigned short*>(s.ag + sw128(j, row2 * 2)) = bits;
+        } else if (j == row2) {
+          *reinterpret_cast<unsigned short*>(s.ag + sw128(row2, j * 2)) = 0;
         }
-        atomicAdd(&s.db_s[row], dbr);
       }
+      dbr += __shfl_xor_sync(0xffffffffu, dbr, 16);
+      if (active) atomicAdd(&s.db_s[row], dbr);
     }
     tc_fence_before();
     fence_async_smem();
@@ -663,14 +694,15 @@ __global__ void __launch_bounds__(256) group_reduce_kernel(const __nv_bfloat16* 
 
 }  // namespace fq
 
-extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void* v, const void* A, const void* dout,
+extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void* v, const void* A, const void* Ag,
+                                       const void* Pg, const void* dout,
                                        const void* dvp, const void* dv, const void* h, const void* dh,
                                        const float* g_cumsum, const float* beta, void* dq, void* dk, float* dg, float* db,
                                        int B, int T, int H, int Hg, const int32_t* cu_seqlens,
                                        const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
                                        int32_t* status_dev, void* stream) {
   using namespace fq;
-  FQ_CHECK_ARG(q && k && v && A && dout && dvp && dv && h && dh && g_cumsum && beta && dq && dk && dg && db,
+  FQ_CHECK_ARG(q && k && v && A && Ag && Pg && dout && dvp && dv && h && dh && g_cumsum && beta && dq && dk && dg && db,
                "fq_gdr_bwd_chunk: null tensor");
   FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0,
                "fq_gdr_bwd_chunk: bad sizes");
@@ -682,7 +714,7 @@ extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void*
   const uint64_t rows = static_cast<uint64_t>(B) * static_cast<uint64_t>(T);
   const uint64_t hrows = static_cast<uint64_t>(total_chunks) * H * kDim;
   FQ_CHECK_ARG(rows > 0 && rows < (1ull << 31) && hrows < (1ull << 31), "fq_gdr_bwd_chunk: sizes out of range");
-  CUtensorMap mq, mk, mv, mdo, mdvp, mdv, ma, mh, mdh;
+  CUtensorMap mq, mk, mv, mdo, mdvp, mdv, ma, mag, mpg, mh, mdh;
   int rc;
   if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
@@ -691,6 +723,8 @@ extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void*
   if ((rc = make_tmap_rows_heads_dim(&mdvp, dvp, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdv, dv, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&ma, A, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mag, Ag, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mpg, Pg, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mh, h, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdh, dh, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
   BwdChunkParams p;
@@ -709,8 +743,8 @@ extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void*
   }
   const long long units = static_cast<long long>(total_chunks) * H;
   const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
-  gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mdo, mdvp, mdv, ma, mh,
-                                                                                      mdh, p);
+  gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mdo, mdvp, mdv, ma, mag,
+                                                                                      mpg, mh, mdh, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }
@@ -744,13 +778,13 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratch
 }  // namespace fq
 
 extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k, const void* v, const void* A,
-                                                   const void* dout, const void* dvp, const void* dv, const void* h,
+                                                   const void* Ag, const void* Pg, const void* dout, const void* dvp, const void* dv, const void* h,
                                                    const void* dh, const float* g_cumsum, const float* beta, void* dq,
                                                    void* dk, float* dg, float* db, int B, int T, int H, int Hg,
                                                    const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
                                                    int total_chunks, float scale, int32_t* status_dev, void* stream) {
   using namespace fq;
-  FQ_CHECK_ARG(q && k && v && A && dout && dvp && dv && h && dh && g_cumsum && beta && dq && dk && dg && db,
+  FQ_CHECK_ARG(q && k && v && A && Ag && Pg && dout && dvp && dv && h && dh && g_cumsum && beta && dq && dk && dg && db,
                "fq_gdr_bwd_chunk_gva_noalloc: null tensor");
   FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0,
                "fq_gdr_bwd_chunk_gva_noalloc: bad sizes");
@@ -786,7 +820,7 @@ extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k,
   __nv_bfloat16* dq_h = reinterpret_cast<__nv_bfloat16*>(scratch_dev[dev]);
   __nv_bfloat16* dk_h = reinterpret_cast<__nv_bfloat16*>(scratch_dev[dev] + per_buffer);
 
-  CUtensorMap mq, mk, mv, mdo, mdvp, mdv, ma, mh, mdh;
+  CUtensorMap mq, mk, mv, mdo, mdvp, mdv, ma, mag, mpg, mh, mdh;
   int rc;
   if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
@@ -795,6 +829,8 @@ extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k,
   if ((rc = make_tmap_rows_heads_dim(&mdvp, dvp, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdv, dv, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&ma, A, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mag, Ag, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mpg, Pg, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mh, h, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdh, dh, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
   BwdChunkParams p;
@@ -806,7 +842,7 @@ extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long units = static_cast<long long>(total_chunks) * H;
   const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
-  gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, st>>>(mq, mk, mv, mdo, mdvp, mdv, ma, mh, mdh, p);
+  gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, st>>>(mq, mk, mv, mdo, mdvp, mdv, ma, mag, mpg, mh, mdh, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   // Every token row of both scratch buffers was just written (each row belongs to exactly one
   // chunk), so nothing has to be cleared before the sum reads them.

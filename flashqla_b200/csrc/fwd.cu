@@ -277,33 +277,43 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         __nv_bfloat16* hdst = (p.h_out && n >= 0)
                                   ? p.h_out + (static_cast<size_t>(chunk_off + n) * p.H + h) * kDim * kDim + v
                                   : nullptr;
+        // both 32-column pieces are loaded before anything is stored, so only one TMEM round trip is exposed
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tmem_addr(tm, lane_base, kColS + 64 * hf), r0);
+        tmem_ld32(tmem_addr(tm, lane_base, kColS + 64 * hf + 32), r1);
+        tmem_wait_ld();
 #pragma unroll
-        for (int pc = 0; pc < 2; ++pc) {
-          uint32_t r[32];
-          tmem_ld32(tmem_addr(tm, lane_base, kColS + 64 * hf + 32 * pc), r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 q4v;
-            q4v.x = pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
-            q4v.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-            q4v.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-            q4v.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-            *reinterpret_cast<uint4*>(s.sbf + hf * 16384 + sw128(v, pc * 64 + j * 16)) = q4v;
-          }
-          if (hdst) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              hdst[static_cast<size_t>(64 * hf + 32 * pc + i) * kDim] = __float2bfloat16(__uint_as_float(r[i]));
-          }
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * gL);
-          tmem_st32(tmem_addr(tm, lane_base, kColS + 64 * hf + 32 * pc), r);
+        for (int j = 0; j < 4; ++j) {
+          uint4 x0, x1;
+          x0.x = pack_bf16(__uint_as_float(r0[8 * j]), __uint_as_float(r0[8 * j + 1]));
+          x0.y = pack_bf16(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+          x0.z = pack_bf16(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+          x0.w = pack_bf16(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+          x1.x = pack_bf16(__uint_as_float(r1[8 * j]), __uint_as_float(r1[8 * j + 1]));
+          x1.y = pack_bf16(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+          x1.z = pack_bf16(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+          x1.w = pack_bf16(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+          *reinterpret_cast<uint4*>(s.sbf + hf * 16384 + sw128(v, j * 16)) = x0;
+          *reinterpret_cast<uint4*>(s.sbf + hf * 16384 + sw128(v, 64 + j * 16)) = x1;
         }
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s.s_ready);
         if (tid == 128) FQ_TS(it, 15);
+        if (hdst) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            hdst[static_cast<size_t>(64 * hf + i) * kDim] = __float2bfloat16(__uint_as_float(r0[i]));
+            hdst[static_cast<size_t>(64 * hf + 32 + i) * kDim] = __float2bfloat16(__uint_as_float(r1[i]));
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          r0[i] = __float_as_uint(__uint_as_float(r0[i]) * gL);
+          r1[i] = __float_as_uint(__uint_as_float(r1[i]) * gL);
+        }
+        tmem_st32(tmem_addr(tm, lane_base, kColS + 64 * hf), r0);
+        tmem_st32(tmem_addr(tm, lane_base, kColS + 64 * hf + 32), r1);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();

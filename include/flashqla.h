@@ -164,7 +164,8 @@ FQ_API int fq_gdr_bwd_dh_cp(const void* q, const void* k, const void* Ag, const 
  * and dbeta (fp32 [B,T,H]) from h (state before each chunk, from fq_gdr_fwd with h_out), dh, dvp and dv
  * (from fq_gdr_bwd_dh).  Second half of the replacement of hopper/fused_bwd.py:900-985.
  */
-FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void* v, const void* A, const void* dout,
+FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void* v, const void* A, const void* Ag,
+                            const void* Pg, const void* dout,
                             const void* dvp, const void* dv, const void* h, const void* dh, const float* g_cumsum,
                             const float* beta, void* dq, void* dk, float* dg, float* db, int B, int T, int H, int Hg,
                             const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq, int total_chunks,
@@ -192,7 +193,8 @@ FQ_API int fq_group_reduce(const void* in, void* out, long long rows, int H, int
  *     (different streams, or different host threads) race on it; serialise them;
  *   - it calls no cudaMalloc / cudaFree and no allocating library routine.
  */
-FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k, const void* v, const void* A, const void* dout,
+FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k, const void* v, const void* A, const void* Ag,
+                                        const void* Pg, const void* dout,
                                         const void* dvp, const void* dv, const void* h, const void* dh,
                                         const float* g_cumsum, const float* beta, void* dq, void* dk, float* dg,
                                         float* db, int B, int T, int H, int Hg, const int32_t* cu_seqlens,

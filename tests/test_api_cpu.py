@@ -82,3 +82,29 @@ def test_autograd_backward_arity():
     bwd = next(n for n in cls.body if isinstance(n, ast.FunctionDef) and n.name == "backward")
     ret = [n for n in ast.walk(bwd) if isinstance(n, ast.Return)][-1]
     assert len(ret.value.elts) == len(fwd.args.args) - 1
+
+
+def test_context_parallel_planner():
+    from flashqla_b200 import planner
+    # pieces tile every sequence, keep 64-token chunk boundaries and mark first / last pieces
+    cu = torch.tensor([0, 100, 100, 5000, 9000], dtype=torch.int32)
+    plan = planner.plan_packed(cu, "cpu")
+    cp = planner.plan_cp(plan, 1, 9000, 4, 148, "cpu", piece_chunks=16)
+    b = cp.cu_seqlens.tolist()
+    assert b[0] == 0 and b[-1] == 9000 and cp.n_pieces == len(b) - 1 == 11
+    assert all((s - cu_s) % 64 == 0 for s, cu_s in zip(cp.piece_start.tolist(), [0, 100, 100, 100, 100, 100, 100, 5000, 5000, 5000, 5000]))
+    assert cp.out_index_fwd.tolist() == [0, 1, -1, -1, -1, -1, 2, -1, -1, -1, 3]
+    assert cp.out_index_bwd.tolist() == [0, 1, 2, -1, -1, -1, -1, 3, -1, -1, -1]
+    assert cp.chunks_before.tolist() == [0, 0, 0, 16, 32, 48, 64, 0, 16, 32, 48]
+    assert cp.chunk_offsets.tolist()[-1] == plan.total_chunks == cp.total_chunks
+    assert cp.seq_end.tolist() == [100, 100, 5000, 5000, 5000, 5000, 5000, 9000, 9000, 9000, 9000]
+    # the split is chosen from a makespan model of one CTA per SM
+    assert planner.choose_piece_chunks([128] * 4, 32, 148) is None          # 128 CTAs already fill the GPU
+    L = planner.choose_piece_chunks([512], 64, 148)
+    assert L is not None and 8 <= L < 512
+    assert planner.choose_piece_chunks([4, 4, 4], 2, 148) is None           # too short to split
+    assert planner.plan_cp(planner.plan_dense(4, 8192), 4, 8192, 32, 148, "cpu") is None
+    # dense batches are split over the flattened token axis
+    cp2 = planner.plan_cp(planner.plan_dense(2, 1024), 2, 1024, 1, 148, "cpu", piece_chunks=4)
+    assert cp2.cu_seqlens.tolist() == [0, 256, 512, 768, 1024, 1280, 1536, 1792, 2048]
+    assert cp2.seq_index.tolist() == [0, 0, 0, 0, 1, 1, 1, 1]

@@ -55,7 +55,7 @@ def test_noalloc_matches_regular_entry_point(B, T, Hq, Hv, cu):
     _lib.check(rc, "fq_gdr_bwd_dh")
 
     def common_args(dq, dk, dg, db):
-        return (q.data_ptr(), k.data_ptr(), v.data_ptr(), A.data_ptr(), do.data_ptr(), dvp.data_ptr(), dv.data_ptr(),
+        return (q.data_ptr(), k.data_ptr(), v.data_ptr(), A.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), do.data_ptr(), dvp.data_ptr(), dv.data_ptr(),
                 h.data_ptr(), dh.data_ptr(), gc.data_ptr(), beta.data_ptr(), dq.data_ptr(), dk.data_ptr(),
                 dg.data_ptr(), db.data_ptr(), B, T, Hv, Hq, cu_p, off_p, plan.n_seq, plan.total_chunks, scale, None, st)
 
@@ -87,6 +87,6 @@ def test_noalloc_rejects_oversized_problem():
     lib = _lib.load()
     x = torch.zeros(16, device="cuda")
     p = x.data_ptr()
-    rc = lib.fq_gdr_bwd_chunk_gva_noalloc(p, p, p, p, p, p, p, p, p, p, p, p, p, p, p, 1, 65536, 2, 1, None, None, 1, 1024,
+    rc = lib.fq_gdr_bwd_chunk_gva_noalloc(p, p, p, p, p, p, p, p, p, p, p, p, p, p, p, p, p, 1, 65536, 2, 1, None, None, 1, 1024,
                                           0.1, None, None)
     assert rc == -4 and b"exceeds the built-in scratch" in lib.fq_last_error()
