@@ -25,10 +25,10 @@ SIGNATURES = {
     "fq_gdr_fwd": [_vp] * 12 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "fq_gdr_fwd_cp": [_vp] * 14 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "fq_cp_warmup": [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _f32, _i32, _vp],
-    "fq_gdr_bwd_dh": [_vp] * 12 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
-    "fq_gdr_bwd_dh_cp": [_vp] * 16 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
-    "fq_gdr_bwd_chunk": [_vp] * 17 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
-    "fq_gdr_bwd_chunk_gva_noalloc": [_vp] * 17 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
+    "fq_gdr_bwd_dh": [_vp] * 10 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
+    "fq_gdr_bwd_dh_cp": [_vp] * 14 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
+    "fq_gdr_bwd_chunk": [_vp] * 16 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
+    "fq_gdr_bwd_chunk_gva_noalloc": [_vp] * 16 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "fq_group_reduce": [_vp, _vp, ctypes.c_longlong, _i32, _i32, _vp],
     "fq_kkt_solve_gated": [_vp] * 7 + [_i32] * 5 + [_vp, _vp, _i32, _i32, _f32, _vp],
     "fq_selftest_umma": [_vp, _vp, _vp, _i32, _vp, _vp],

@@ -46,8 +46,6 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
                                     output_h=True, output_o=False, plan=plan, cp=cp, warmup=warm, status=status)
     # 2. reverse recurrence of the state gradient
     dh = torch.empty_like(h)
-    dvp = torch.empty_like(v)
-    dv = torch.empty_like(v)
     want_dh0 = (dht is not None) or (initial_state is not None)
     dh0 = torch.empty(plan.n_seq, H, K, V, dtype=torch.float32, device=dev) if want_dh0 else None
     cu_p, off_p = plan.ptrs()
@@ -55,12 +53,12 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
     pp = lambda t: None if t is None else t.data_ptr()
     if cp is None:
         rc = lib.fq_gdr_bwd_dh(q.data_ptr(), k.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), do.data_ptr(), g.data_ptr(),
-                               bt.data_ptr(), pp(dht_c), pp(dh0), dh.data_ptr(), dvp.data_ptr(), dv.data_ptr(), B, T, H, Hg,
+                               bt.data_ptr(), pp(dht_c), pp(dh0), dh.data_ptr(), B, T, H, Hg,
                                cu_p, off_p, plan.n_seq, plan.total_chunks, float(scale), st_p, kernels._stream())
     else:
         warm_r = kernels.cp_warmup(g, cp, H, reverse=True)
         rc = lib.fq_gdr_bwd_dh_cp(q.data_ptr(), k.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), do.data_ptr(), g.data_ptr(),
-                                  bt.data_ptr(), pp(dht_c), pp(dh0), dh.data_ptr(), dvp.data_ptr(), dv.data_ptr(),
+                                  bt.data_ptr(), pp(dht_c), pp(dh0), dh.data_ptr(),
                                   cp.seq_index.data_ptr(), cp.out_index_bwd.data_ptr(), cp.seq_end.data_ptr(),
                                   warm_r.data_ptr(), 1, B * T, H, Hg, cp.cu_seqlens.data_ptr(),
                                   cp.chunk_offsets.data_ptr(), cp.n_pieces, cp.total_chunks, float(scale), st_p,
@@ -71,10 +69,10 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
     dk_h = torch.empty(B, T, H, K, dtype=q.dtype, device=dev)
     dg_c = torch.empty(B, T, H, dtype=torch.float32, device=dev)
     db = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+    dv = torch.empty_like(v)
     rc = lib.fq_gdr_bwd_chunk(q.data_ptr(), k.data_ptr(), v.data_ptr(), A.data_ptr(), Ag.data_ptr(), Pg.data_ptr(),
-                              do.data_ptr(), dvp.data_ptr(),
-                              dv.data_ptr(), h.data_ptr(), dh.data_ptr(), g.data_ptr(), bt.data_ptr(), dq_h.data_ptr(),
-                              dk_h.data_ptr(), dg_c.data_ptr(), db.data_ptr(), B, T, H, Hg, cu_p, off_p, plan.n_seq,
+                              do.data_ptr(), h.data_ptr(), dh.data_ptr(), g.data_ptr(), bt.data_ptr(), dq_h.data_ptr(),
+                              dk_h.data_ptr(), dv.data_ptr(), dg_c.data_ptr(), db.data_ptr(), B, T, H, Hg, cu_p, off_p, plan.n_seq,
                               plan.total_chunks, float(scale), st_p, kernels._stream())
     _lib.check(rc, "fq_gdr_bwd_chunk")
     # 4. sum the V-heads of every QK head

@@ -1,21 +1,22 @@
 // Backward, chunk-parallel part: given the state before each chunk (h, from the forward
-// recurrence), the state gradient after each chunk (dh) and dV' / dv (from bwd_dh.cu), every
-// (chunk, V-head) unit is independent.  A persistent CTA walks units; per unit it runs six rounds
-// of tcgen05 MMAs (M = 64: row = token of the chunk) with CUDA-core epilogues in between:
+// recurrence) and the state gradient after each chunk (dh, from bwd_dh.cu), every (chunk, V-head)
+// unit is independent.  A persistent CTA walks units; per unit it runs six rounds of tcgen05 MMAs
+// (M = 64: row = token of the chunk) with CUDA-core epilogues in between:
 //
-//   round 1  U = K S0 | accQ = dO S0^T | accK = dVg S0^T                       (dVg = -gamma o dv)
-//            -> W = V - gamma o U, accQ *= scale*gamma, dg += rowsum(Q o accQ) + rowsum(K o accK)
-//            (A_g and P_g tiles come from kkt_solve.cu)
-//   round 2  V' = A_g W
-//   round 3  K1 = V' dS^T | dPg = dO V'^T | dAg = dV' W^T
-//            -> accK += rho o K1, dg -= rowsum(K o rho K1); dP = scale G o dPg; dA = (G o dAg) beta_col;
-//               dg += rowsum of T = dPg o P_g + dAb o A_b; tiles T and T3 = dAb o A kept for the column sums
+//   round 1  U = K S0 | D1 = K dS | D2 = P_g^T dO | accQ = dO S0^T
+//            -> W = V - gamma o U, dV' = rho o D1 + D2, accQ *= scale*gamma, dg += rowsum(Q o accQ)
+//   round 2  V' = A_g W | dW = A_g^T dV'
+//            -> dv = dW (output), dVg = -gamma o dW
+//   round 3  K1 = V' dS^T | dPg = dO V'^T | dAg = dV' W^T | accK = dVg S0^T
+//            -> dg += rowsum(K o accK); accK += rho o K1, dg -= rowsum(K o rho K1); dP = scale G o dPg;
+//               dA = (G o dAg) beta_col; dg += rowsum of T = dPg o P_g + dAb o A_b; tiles T, T3 = dAb o A
 //   round 4  accQ += dP K | accK += dP^T Q | X1 = A^T dA | column sums T^T 1, T3^T 1 (ones-vector MMAs)
 //            -> dq, dg -= colsum(T), dbeta += colsum(T3)
 //   round 5  X2 = X1 A^T | KK = K K^T
 //            -> dL = -strict_lower(X2); dbeta += rowsum(dL o KK); dAs = beta_row dL + (beta_row dL)^T
 //   round 6  accK += dAs K                                        -> dk, dg, dbeta
 //
+// A_g and P_g come from kkt_solve.cu; S0 and dS arrive transposed ([v][k]) as the recurrences store them.
 // dg is the gradient w.r.t. the chunk-local cumsum of the gate; the caller applies the reverse
 // chunk cumsum.  dq / dk are written per V-head (bf16); the caller sums the heads of a QK group.
 #include "flashqla.h"
@@ -25,24 +26,25 @@
 namespace fq {
 
 constexpr int kBcThreads = 256;
-constexpr uint32_t kBcLoadBytes = 6 * 16384 + 3 * 8192 + 2 * 32768;
+constexpr uint32_t kBcLoadBytes = 4 * 16384 + 3 * 8192 + 2 * 32768;
 
 constexpr uint32_t kBcColU = 0;    // 128: U, then V', then K1, then X1 (0-63) / X2 (64-127)
-constexpr uint32_t kBcColQK = 128; // 64: QK^T, then dPg, then KK^T
-constexpr uint32_t kBcColX = 192;  // 64: dAg
-constexpr uint32_t kBcColQ = 256;  // 128: accQ
-constexpr uint32_t kBcColK = 384;  // 128: accK
+constexpr uint32_t kBcColD1 = 128; // 128: D1 = K dS, then dW; later split into the two 64-column slots below
+constexpr uint32_t kBcColQK = 128; // 64: dPg, then KK^T
+constexpr uint32_t kBcColX = 192;  // 64: dAg, then the column sums
+constexpr uint32_t kBcColK = 256;  // 128: D2 = P_g^T dO, then accK
+constexpr uint32_t kBcColQ = 384;  // 128: accQ
 
 struct BwdChunkSmem {
   unsigned char kt[16384];   // K  [64 c][128 k]  (two 64-row regions: k 0-63 | 64-127)
   unsigned char qt[16384];   // Q
   unsigned char wt[16384];   // V, rewritten as W
   unsigned char dot[16384];  // dO
-  unsigned char dvp[16384];  // dV'
-  unsigned char dvg[16384];  // dv, rewritten as dVg
+  unsigned char dvp[16384];  // dV'  (computed)
+  unsigned char dvg[16384];  // dVg  (computed)
   unsigned char vp[16384];   // V'
-  unsigned char s0[32768];   // S0 [128 k][128 v] (two 128-row regions: v 0-63 | 64-127)
-  unsigned char ds[32768];   // dS
+  unsigned char s0[32768];   // S0^T [128 v][128 k] (two 128-row regions: k 0-63 | 64-127), as stored by the recurrences
+  unsigned char ds[32768];   // dS^T, same layout
   unsigned char at[8192];    // A   [64 i][64 j]
   unsigned char ag[8192];    // A_g -> dA -> dAs
   unsigned char pg[8192];    // P_g -> dP -> X1
@@ -64,6 +66,7 @@ struct BwdChunkParams {
   __nv_bfloat16* dk;  // [rows, H, 128]
   float* dg;          // [rows, H]
   float* db;          // [rows, H]
+  __nv_bfloat16* dv;  // [rows, H, 128]
   int H, Hg, total_chunks;
   float scale;
   SeqArgs sa;
@@ -85,7 +88,6 @@ __device__ __forceinline__ float half_warp_sum(float x) {
 __global__ void __launch_bounds__(kBcThreads, 1)
 gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                     const __grid_constant__ CUtensorMap map_dvp, const __grid_constant__ CUtensorMap map_dv,
                      const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_ag,
                      const __grid_constant__ CUtensorMap map_pg, const __grid_constant__ CUtensorMap map_h,
                      const __grid_constant__ CUtensorMap map_dh, const BwdChunkParams p) {
@@ -105,7 +107,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     mbar_init(&s.bar_mma, 1);
     fence_mbar_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); tma_prefetch_desc(&map_do);
-    tma_prefetch_desc(&map_dvp); tma_prefetch_desc(&map_dv); tma_prefetch_desc(&map_a); tma_prefetch_desc(&map_h);
+    tma_prefetch_desc(&map_a); tma_prefetch_desc(&map_h);
     tma_prefetch_desc(&map_dh); tma_prefetch_desc(&map_ag); tma_prefetch_desc(&map_pg);
   }
   for (int i = tid; i < 512; i += kBcThreads) reinterpret_cast<uint32_t*>(s.ones)[i] = 0x3F803F80u;
@@ -151,10 +153,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       tma_load_3d(s.wt + 8192, &map_v, &s.bar_tma, 64, h, r0);
       tma_load_3d(s.dot, &map_do, &s.bar_tma, 0, h, r0);
       tma_load_3d(s.dot + 8192, &map_do, &s.bar_tma, 64, h, r0);
-      tma_load_3d(s.dvp, &map_dvp, &s.bar_tma, 0, h, r0);
-      tma_load_3d(s.dvp + 8192, &map_dvp, &s.bar_tma, 64, h, r0);
-      tma_load_3d(s.dvg, &map_dv, &s.bar_tma, 0, h, r0);
-      tma_load_3d(s.dvg + 8192, &map_dv, &s.bar_tma, 64, h, r0);
       tma_load_3d(s.at, &map_a, &s.bar_tma, 0, h, r0);
       tma_load_3d(s.ag, &map_ag, &s.bar_tma, 0, h, r0);
       tma_load_3d(s.pg, &map_pg, &s.bar_tma, 0, h, r0);
@@ -184,16 +182,16 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     if (!mbar_wait(wc, &s.bar_tma, tma_phase, 1)) { alive = false; break; }
     tma_phase ^= 1;
 
-    // ---- pre-pass on shared memory: zero the rows past the sequence end, dVg = -gamma o dv,
+    // ---- pre-pass on shared memory: zero the rows past the sequence end
     //      and the scalar gamma_last * sum(dS o S0)
     if (len < kChunk) {
-      unsigned char* tiles[6] = {s.kt, s.qt, s.wt, s.dot, s.dvp, s.dvg};
+      unsigned char* tiles[4] = {s.kt, s.qt, s.wt, s.dot};
       const int nrows = kChunk - len;
       for (int idx = tid; idx < nrows * 16; idx += kBcThreads) {
         const int r = len + (idx >> 4), pc = idx & 15;
         const uint32_t off = (pc >> 3) * 8192 + r * 128 + (pc & 7) * 16;
 #pragma unroll
-        for (int t6 = 0; t6 < 6; ++t6) *reinterpret_cast<uint4*>(tiles[t6] + off) = make_uint4(0, 0, 0, 0);
+        for (int t6 = 0; t6 < 4; ++t6) *reinterpret_cast<uint4*>(tiles[t6] + off) = make_uint4(0, 0, 0, 0);
         if (pc < 8) {
           *reinterpret_cast<uint4*>(s.at + r * 128 + pc * 16) = make_uint4(0, 0, 0, 0);
           *reinterpret_cast<uint4*>(s.ag + r * 128 + pc * 16) = make_uint4(0, 0, 0, 0);
@@ -203,18 +201,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       __syncthreads();
     }
     {
-#pragma unroll
-      for (int it = 0; it < 4; ++it) {
-        const uint32_t off = (it * kBcThreads + tid) * 16;
-        const int r = (off & 8191) >> 7;
-        const float f = -s.gam[r];
-        uint4* ptr = reinterpret_cast<uint4*>(s.dvg + off);
-        uint4 x = *ptr;
-        uint32_t* xw = reinterpret_cast<uint32_t*>(&x);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) xw[e] = pack_bf16(f * bf16_lo(xw[e]), f * bf16_hi(xw[e]));
-        *ptr = x;
-      }
       float acc = 0.f;
 #pragma unroll
       for (int it = 0; it < 8; ++it) {
@@ -239,17 +225,21 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     if (tid == 0) {
       tc_fence_after();
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        umma_ss(tm + kBcColU, umma_desc_sw128(skt + off64(kk), 16, 1024), umma_desc_sw128(ss0 + kk * 2048, 16384, 1024),
+      for (int kk = 0; kk < 8; ++kk)  // U = K S0
+        umma_ss(tm + kBcColU, umma_desc_sw128(skt + off64(kk), 16, 1024), umma_desc_sw128(ss0 + off128(kk), 16, 1024),
+                id64_128_kk, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)  // D1 = K dS
+        umma_ss(tm + kBcColD1, umma_desc_sw128(skt + off64(kk), 16, 1024), umma_desc_sw128(sds + off128(kk), 16, 1024),
+                id64_128_kk, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)  // D2 = P_g^T dO
+        umma_ss(tm + kBcColK, umma_desc_sw128(spg + kk * 2048, 8192, 1024), umma_desc_sw128(sdot + kk * 2048, 8192, 1024),
+                id64_128_mnmn, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)  // accQ = dO S0^T
+        umma_ss(tm + kBcColQ, umma_desc_sw128(sdot + off64(kk), 16, 1024), umma_desc_sw128(ss0 + kk * 2048, 16384, 1024),
                 id64_128_kmn, kk > 0);
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        umma_ss(tm + kBcColQ, umma_desc_sw128(sdot + off64(kk), 16, 1024), umma_desc_sw128(ss0 + off128(kk), 16, 1024),
-                id64_128_kk, kk > 0);
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        umma_ss(tm + kBcColK, umma_desc_sw128(sdvg + off64(kk), 16, 1024), umma_desc_sw128(ss0 + off128(kk), 16, 1024),
-                id64_128_kk, kk > 0);
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
@@ -257,7 +247,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     mma_phase ^= 1;
     tc_fence_after();
     {
-      // W = V - gamma o U (in place over V)
+      // W = V - gamma o U (in place over V);  dV' = rho o D1 + D2
 #pragma unroll
       for (int pc = 0; pc < 2; ++pc) {
         uint32_t u[32];
@@ -276,8 +266,24 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             *ptr = x;
           }
         }
+        uint32_t d2[32];
+        tmem_ld32(tmem_addr(tm, lane_base, kBcColD1 + 64 * hf + 32 * pc), u);
+        tmem_ld32(tmem_addr(tm, lane_base, kBcColK + 64 * hf + 32 * pc), d2);
+        tmem_wait_ld();
+        if (active) {
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint4 x;
+            uint32_t* xw = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              xw[e] = pack_bf16(rho_r * __uint_as_float(u[8 * ch + 2 * e]) + __uint_as_float(d2[8 * ch + 2 * e]),
+                                rho_r * __uint_as_float(u[8 * ch + 2 * e + 1]) + __uint_as_float(d2[8 * ch + 2 * e + 1]));
+            *reinterpret_cast<uint4*>(s.dvp + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = x;
+          }
+        }
       }
-      // accQ *= scale * gamma (written back); dg += rowsum(Q o accQ) + rowsum(K o accK)
+      // accQ *= scale * gamma (written back); dg += rowsum(Q o accQ)
       float part = 0.f;
 #pragma unroll
       for (int pc = 0; pc < 2; ++pc) {
@@ -299,20 +305,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         tmem_st32(tmem_addr(tm, lane_base, kBcColQ + 64 * hf + 32 * pc), r);
       }
-#pragma unroll
-      for (int pc = 0; pc < 2; ++pc) {
-        uint32_t r[32];
-        tmem_ld32(tmem_addr(tm, lane_base, kBcColK + 64 * hf + 32 * pc), r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const uint4 kv = *reinterpret_cast<const uint4*>(s.kt + hf * 8192 + sw128(row, (4 * pc + ch) * 16));
-          const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kv);
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            part += bf16_lo(kw[e]) * __uint_as_float(r[8 * ch + 2 * e]) + bf16_hi(kw[e]) * __uint_as_float(r[8 * ch + 2 * e + 1]);
-        }
-      }
       if (active) atomicAdd(&s.dg_s[row], part);
       tmem_wait_st();
     }
@@ -320,33 +312,51 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     fence_async_smem();
     __syncthreads();
 
-    // ================================================================== round 2: V' = A_g W
+    // ================================================================== round 2: V' = A_g W, dW = A_g^T dV'
     if (tid == 0) {
       tc_fence_after();
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk)
         umma_ss(tm + kBcColU, umma_desc_sw128(sag + kk * 32, 16, 1024), umma_desc_sw128(swt + kk * 2048, 8192, 1024),
                 id64_128_kmn, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        umma_ss(tm + kBcColD1, umma_desc_sw128(sag + kk * 2048, 8192, 1024), umma_desc_sw128(sdvp + kk * 2048, 8192, 1024),
+                id64_128_mnmn, kk > 0);
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
     if (!mbar_wait(wc, &s.bar_mma, mma_phase, 3)) { alive = false; break; }
     mma_phase ^= 1;
     tc_fence_after();
+    {
+      __nv_bfloat16* dvdst = p.dv + (static_cast<size_t>(cp.tok0 + row) * p.H + h) * kDim + 64 * hf;
 #pragma unroll
-    for (int pc = 0; pc < 2; ++pc) {
-      uint32_t r[32];
-      tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 64 * hf + 32 * pc), r);
-      tmem_wait_ld();
-      if (active) {
+      for (int pc = 0; pc < 2; ++pc) {
+        uint32_t r[32], w2[32];
+        tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 64 * hf + 32 * pc), r);
+        tmem_ld32(tmem_addr(tm, lane_base, kBcColD1 + 64 * hf + 32 * pc), w2);
+        tmem_wait_ld();
+        if (active) {
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint4 x;
-          x.x = pack_bf16(__uint_as_float(r[8 * ch]), __uint_as_float(r[8 * ch + 1]));
-          x.y = pack_bf16(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
-          x.z = pack_bf16(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
-          x.w = pack_bf16(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
-          *reinterpret_cast<uint4*>(s.vp + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = x;
+          for (int ch = 0; ch < 4; ++ch) {
+            uint4 x, y, z;
+            x.x = pack_bf16(__uint_as_float(r[8 * ch]), __uint_as_float(r[8 * ch + 1]));
+            x.y = pack_bf16(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
+            x.z = pack_bf16(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
+            x.w = pack_bf16(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
+            *reinterpret_cast<uint4*>(s.vp + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = x;
+            uint32_t* yw = reinterpret_cast<uint32_t*>(&y);
+            uint32_t* zw = reinterpret_cast<uint32_t*>(&z);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float d0 = __uint_as_float(w2[8 * ch + 2 * e]), d1 = __uint_as_float(w2[8 * ch + 2 * e + 1]);
+              yw[e] = pack_bf16(d0, d1);                      // dv
+              zw[e] = pack_bf16(-gam_r * d0, -gam_r * d1);    // dVg
+            }
+            *reinterpret_cast<uint4*>(s.dvg + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = z;
+            if (row < len) *reinterpret_cast<uint4*>(dvdst + 32 * pc + 8 * ch) = y;
+          }
         }
       }
     }
@@ -359,8 +369,8 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       tc_fence_after();
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk)
-        umma_ss(tm + kBcColU, umma_desc_sw128(svp + off64(kk), 16, 1024), umma_desc_sw128(sds + off128(kk), 16, 1024),
-                id64_128_kk, kk > 0);
+        umma_ss(tm + kBcColU, umma_desc_sw128(svp + off64(kk), 16, 1024), umma_desc_sw128(sds + kk * 2048, 16384, 1024),
+                id64_128_kmn, kk > 0);
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk)
         umma_ss(tm + kBcColQK, umma_desc_sw128(sdot + off64(kk), 16, 1024), umma_desc_sw128(svp + off64(kk), 16, 1024),
@@ -369,6 +379,10 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       for (int kk = 0; kk < 8; ++kk)
         umma_ss(tm + kBcColX, umma_desc_sw128(sdvp + off64(kk), 16, 1024), umma_desc_sw128(swt + off64(kk), 16, 1024),
                 id64_64_kk, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)  // accK = dVg S0^T
+        umma_ss(tm + kBcColK, umma_desc_sw128(sdvg + off64(kk), 16, 1024), umma_desc_sw128(ss0 + kk * 2048, 16384, 1024),
+                id64_128_kmn, kk > 0);
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
@@ -376,8 +390,8 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     mma_phase ^= 1;
     tc_fence_after();
     {
-      // accK += rho o K1 ; kk = rowsum(K o rho K1)
-      float kkp = 0.f;
+      // dg += rowsum(K o accK); then accK += rho o K1 ; kk = rowsum(K o rho K1)
+      float kkp = 0.f, kap = 0.f;
 #pragma unroll
       for (int pc = 0; pc < 2; ++pc) {
         uint32_t r[32], a2[32];
@@ -391,6 +405,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float x0 = rho_r * __uint_as_float(r[8 * ch + 2 * e]), x1 = rho_r * __uint_as_float(r[8 * ch + 2 * e + 1]);
+            kap += bf16_lo(kw[e]) * __uint_as_float(a2[8 * ch + 2 * e]) + bf16_hi(kw[e]) * __uint_as_float(a2[8 * ch + 2 * e + 1]);
             kkp += bf16_lo(kw[e]) * x0 + bf16_hi(kw[e]) * x1;
             a2[8 * ch + 2 * e] = __float_as_uint(__uint_as_float(a2[8 * ch + 2 * e]) + x0);
             a2[8 * ch + 2 * e + 1] = __float_as_uint(__uint_as_float(a2[8 * ch + 2 * e + 1]) + x1);
@@ -399,7 +414,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         tmem_st32(tmem_addr(tm, lane_base, kBcColK + 64 * hf + 32 * pc), a2);
       }
       if (!active) kkp = 0.f;
-      if (active) atomicAdd(&s.dg_s[row], -kkp);
+      if (active) atomicAdd(&s.dg_s[row], kap - kkp);
       const float kks = half_warp_sum(kkp);
       if (lane == 0) atomicAdd(&s.dgl_s, kks);
       // dPg and dAg -> dP, dA, T, T3 tiles and the row sums of T.  Only lanes 0-15 hold accumulator rows
@@ -695,14 +710,14 @@ __global__ void __launch_bounds__(256) group_reduce_kernel(const __nv_bfloat16* 
 }  // namespace fq
 
 extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void* v, const void* A, const void* Ag,
-                                       const void* Pg, const void* dout,
-                                       const void* dvp, const void* dv, const void* h, const void* dh,
-                                       const float* g_cumsum, const float* beta, void* dq, void* dk, float* dg, float* db,
+                                       const void* Pg, const void* dout, const void* h, const void* dh,
+                                       const float* g_cumsum, const float* beta, void* dq, void* dk, void* dv, float* dg,
+                                       float* db,
                                        int B, int T, int H, int Hg, const int32_t* cu_seqlens,
                                        const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
                                        int32_t* status_dev, void* stream) {
   using namespace fq;
-  FQ_CHECK_ARG(q && k && v && A && Ag && Pg && dout && dvp && dv && h && dh && g_cumsum && beta && dq && dk && dg && db,
+  FQ_CHECK_ARG(q && k && v && A && Ag && Pg && dout && dv && h && dh && g_cumsum && beta && dq && dk && dg && db,
                "fq_gdr_bwd_chunk: null tensor");
   FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0,
                "fq_gdr_bwd_chunk: bad sizes");
@@ -714,14 +729,12 @@ extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void*
   const uint64_t rows = static_cast<uint64_t>(B) * static_cast<uint64_t>(T);
   const uint64_t hrows = static_cast<uint64_t>(total_chunks) * H * kDim;
   FQ_CHECK_ARG(rows > 0 && rows < (1ull << 31) && hrows < (1ull << 31), "fq_gdr_bwd_chunk: sizes out of range");
-  CUtensorMap mq, mk, mv, mdo, mdvp, mdv, ma, mag, mpg, mh, mdh;
+  CUtensorMap mq, mk, mv, mdo, ma, mag, mpg, mh, mdh;
   int rc;
   if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mv, v, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdo, dout, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
-  if ((rc = make_tmap_rows_heads_dim(&mdvp, dvp, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
-  if ((rc = make_tmap_rows_heads_dim(&mdv, dv, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&ma, A, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mag, Ag, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mpg, Pg, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
@@ -730,6 +743,7 @@ extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void*
   BwdChunkParams p;
   p.g_cum = g_cumsum; p.beta = beta;
   p.dq = static_cast<__nv_bfloat16*>(dq); p.dk = static_cast<__nv_bfloat16*>(dk); p.dg = dg; p.db = db;
+  p.dv = static_cast<__nv_bfloat16*>(dv);
   p.H = H; p.Hg = Hg; p.total_chunks = total_chunks; p.scale = scale;
   p.sa = SeqArgs{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
   p.status_dev = status_dev;
@@ -743,8 +757,8 @@ extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void*
   }
   const long long units = static_cast<long long>(total_chunks) * H;
   const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
-  gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mdo, mdvp, mdv, ma, mag,
-                                                                                      mpg, mh, mdh, p);
+  gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mdo, ma, mag, mpg, mh,
+                                                                                      mdh, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }
@@ -778,13 +792,13 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratch
 }  // namespace fq
 
 extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k, const void* v, const void* A,
-                                                   const void* Ag, const void* Pg, const void* dout, const void* dvp, const void* dv, const void* h,
+                                                   const void* Ag, const void* Pg, const void* dout, const void* h,
                                                    const void* dh, const float* g_cumsum, const float* beta, void* dq,
-                                                   void* dk, float* dg, float* db, int B, int T, int H, int Hg,
+                                                   void* dk, void* dv, float* dg, float* db, int B, int T, int H, int Hg,
                                                    const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
                                                    int total_chunks, float scale, int32_t* status_dev, void* stream) {
   using namespace fq;
-  FQ_CHECK_ARG(q && k && v && A && Ag && Pg && dout && dvp && dv && h && dh && g_cumsum && beta && dq && dk && dg && db,
+  FQ_CHECK_ARG(q && k && v && A && Ag && Pg && dout && dv && h && dh && g_cumsum && beta && dq && dk && dg && db,
                "fq_gdr_bwd_chunk_gva_noalloc: null tensor");
   FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0,
                "fq_gdr_bwd_chunk_gva_noalloc: bad sizes");
@@ -820,14 +834,12 @@ extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k,
   __nv_bfloat16* dq_h = reinterpret_cast<__nv_bfloat16*>(scratch_dev[dev]);
   __nv_bfloat16* dk_h = reinterpret_cast<__nv_bfloat16*>(scratch_dev[dev] + per_buffer);
 
-  CUtensorMap mq, mk, mv, mdo, mdvp, mdv, ma, mag, mpg, mh, mdh;
+  CUtensorMap mq, mk, mv, mdo, ma, mag, mpg, mh, mdh;
   int rc;
   if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mv, v, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdo, dout, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
-  if ((rc = make_tmap_rows_heads_dim(&mdvp, dvp, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
-  if ((rc = make_tmap_rows_heads_dim(&mdv, dv, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&ma, A, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mag, Ag, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mpg, Pg, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
@@ -836,13 +848,14 @@ extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k,
   BwdChunkParams p;
   p.g_cum = g_cumsum; p.beta = beta;
   p.dq = dq_h; p.dk = dk_h; p.dg = dg; p.db = db;
+  p.dv = static_cast<__nv_bfloat16*>(dv);
   p.H = H; p.Hg = Hg; p.total_chunks = total_chunks; p.scale = scale;
   p.sa = SeqArgs{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
   p.status_dev = status_dev;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long units = static_cast<long long>(total_chunks) * H;
   const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
-  gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, st>>>(mq, mk, mv, mdo, mdvp, mdv, ma, mag, mpg, mh, mdh, p);
+  gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, st>>>(mq, mk, mv, mdo, ma, mag, mpg, mh, mdh, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   // Every token row of both scratch buffers was just written (each row belongs to exactly one
   // chunk), so nothing has to be cleared before the sum reads them.

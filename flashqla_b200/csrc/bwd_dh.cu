@@ -4,13 +4,14 @@
 //
 //   D2   [128 x 64]  = dO^T P_g                   (state independent; A_g and P_g come from kkt_solve.cu)
 //   D1   [128 x 64]  = dS^T_bf16 K^T
-//        dV'^T = rho o D1 + D2                    -> scratch dvp [tokens, H, 128]
-//   DW   [128 x 64]  = dV'^T A_g                  = dv^T  (aliases D1)
+//        dV'^T = rho o D1 + D2
+//   DW   [128 x 64]  = dV'^T A_g                  (aliases D1)
 //        dVg^T = -gamma o DW
 //   dS  <- gamma_last dS + dVg^T K + (scale*gamma o dO)^T Q
 //
 // The state BEFORE each update (the gradient w.r.t. the state after the chunk) is written as bf16
-// to dh [chunks, H, 128, 128]; the chunk-parallel kernel (bwd_chunk.cu) consumes it.
+// (transposed, by TMA from the operand buffer) to dh [chunks, H, 128, 128]; the chunk-parallel kernel
+// (bwd_chunk.cu) consumes it and forms dv, dq, dk, dg, dbeta.  Nothing else is stored here.
 #include "flashqla.h"
 #include "host.cuh"
 #include "seq.cuh"
@@ -48,9 +49,7 @@ struct BwdDhParams {
   const float* beta;
   const float* dht;        // [n_seq, H, 128, 128] or nullptr
   float* dh0;              // [n_seq, H, 128, 128] or nullptr
-  __nv_bfloat16* dh_out;   // [total_chunks, H, 128, 128]
-  __nv_bfloat16* dvp_out;  // [rows, H, 128]
-  __nv_bfloat16* dv_out;   // [rows, H, 128]
+  __nv_bfloat16* dh_out;   // [total_chunks, H, 128(v), 128(k)] TRANSPOSED, written by TMA from the operand buffer
   // context parallel (all nullptr for whole sequences): per piece the slot of dht / dh0 and the first
   // token after the piece's sequence; per (piece, head) the chunks to replay AFTER the piece
   // (bit 30: the replay starts at the sequence end, i.e. from dht).
@@ -66,21 +65,11 @@ struct BwdDhParams {
 
 __device__ __forceinline__ uint32_t dh_koff(int kk) { return (kk >> 2) * 16384 + (kk & 3) * 32; }
 
-// Stores a [128 v][64 c] tile held as 32 packed bf16 pairs per thread (thread = v) to the
-// token-major global tensor: element (c, v) goes to base[c * row_stride + v].
-__device__ __forceinline__ void store_cols_bf16(unsigned short* base, size_t row_stride, const uint32_t (&packed)[32],
-                                                int len) {
-#pragma unroll
-  for (int c = 0; c < kChunk; c += 2) {
-    if (c < len) base[c * row_stride] = static_cast<unsigned short>(packed[c >> 1] & 0xFFFFu);
-    if (c + 1 < len) base[(c + 1) * row_stride] = static_cast<unsigned short>(packed[c >> 1] >> 16);
-  }
-}
-
 __global__ void __launch_bounds__(kDhThreads, 1)
 gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_a,
-                  const __grid_constant__ CUtensorMap map_pg, const BwdDhParams p) {
+                  const __grid_constant__ CUtensorMap map_pg, const __grid_constant__ CUtensorMap map_dh,
+                  const BwdDhParams p) {
   extern __shared__ unsigned char smem_dyn[];
   BwdDhSmem& s = *reinterpret_cast<BwdDhSmem*>(
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
@@ -116,7 +105,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     mbar_init(&s.dos_ready, 4); mbar_init(&s.pg_ready[0], 4); mbar_init(&s.pg_ready[1], 4);
     fence_mbar_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_a);
-    tma_prefetch_desc(&map_pg);
+    tma_prefetch_desc(&map_pg); tma_prefetch_desc(&map_dh);
   }
   if (warp == 1) {
     tmem_alloc(&s.tmem_base, 512);
@@ -220,12 +209,9 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // ------------------------------------------------------------------ dV', dv, dVg (critical chain)
     const int v = tid - 128;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32;
-    const size_t rs = static_cast<size_t>(p.H) * kDim;
     for (int it = 0; it < total; ++it) {
       const int n = total - 1 - it, gs = it & (kDhGateStages - 1);
       const uint32_t ph = it & 1;
-      const int len = min(kChunk, avail - n * kChunk);
-      const size_t goff = (static_cast<size_t>(tok_begin) + n * kChunk) * rs + static_cast<size_t>(h) * kDim + v;
       if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 11)) break;
       if (!mbar_wait(wc, &s.d2_done, ph, 12)) break;
       if (!mbar_wait(wc, &s.d1_done, ph, 13)) break;
@@ -252,7 +238,6 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.dvp_ready);
-      if (n < nchunks) store_cols_bf16(reinterpret_cast<unsigned short*>(p.dvp_out) + goff, rs, packed, len);
       if (!mbar_wait(wc, &s.dw_done, ph, 14)) break;
       tc_fence_after();
       uint32_t pg2[32];
@@ -265,7 +250,6 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         for (int e = 0; e < 16; e += 2) {
           const int c = qd * 16 + e;
           const float w0 = __uint_as_float(dw[e]), w1 = __uint_as_float(dw[e + 1]);
-          packed[c >> 1] = pack_bf16(w0, w1);
           pg2[c >> 1] = pack_bf16(-s.gate[gs][1][c] * w0, -s.gate[gs][1][c + 1] * w1);
         }
       }
@@ -276,7 +260,6 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       fence_async_smem();
       __syncwarp();
       if (lane == 0) { mbar_arrive(&s.dvg_ready); mbar_arrive(&s.gate_empty[gs]); }
-      if (n < nchunks) store_cols_bf16(reinterpret_cast<unsigned short*>(p.dv_out) + goff, rs, packed, len);
     }
   } else if (warp < 12) {
     // ------------------------------------------------------------------ state gradient: TMEM <-> bf16 operand, decay, dh
@@ -303,7 +286,9 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
       if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 16)) { alive = false; break; }
       const float gL = s.gate[gs][1][kChunk - 1];
-      __nv_bfloat16* hdst = (n < nchunks) ? p.dh_out + (static_cast<size_t>(chunk_off + n) * p.H + h) * kDim * kDim + v : nullptr;
+      const bool store_dh = n < nchunks;
+      if (tid == 256) tma_store_wait_read<0>();  // the previous chunk's TMA store has read the operand buffer
+      asm volatile("bar.sync 2, 128;" ::: "memory");
 #pragma unroll 1
       for (int cb = 0; cb < 4; ++cb) {
         uint32_t r[32];
@@ -318,10 +303,6 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           q4.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
           *reinterpret_cast<uint4*>(s.dsbf + (cb >> 1) * 16384 + sw128(v, (cb & 1) * 64 + j * 16)) = q4;
         }
-        if (hdst) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) hdst[static_cast<size_t>(cb * 32 + i) * kDim] = __float2bfloat16(__uint_as_float(r[i]));
-        }
 #pragma unroll
         for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * gL);
         tmem_st32(tmem_addr(tm, lane_base, kDhColS + cb * 32), r);
@@ -329,11 +310,19 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.ds_ready);
+      asm volatile("bar.sync 2, 128;" ::: "memory");  // all four warps have written (and fenced) their rows
+      if (store_dh && tid == 256) {
+        const int hr = static_cast<int>((static_cast<long long>(chunk_off + n) * p.H + h) * kDim);
+        tma_store_3d(&map_dh, s.dsbf, 0, 0, hr);
+        tma_store_3d(&map_dh, s.dsbf + 16384, 64, 0, hr);
+        tma_store_commit();
+      }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) { mbar_arrive(&s.ds_scaled); mbar_arrive(&s.gate_empty[gs]); }
     }
+    if (tid == 256) tma_store_wait_all<0>();
     if (alive && total > 0) {
       alive = mbar_wait(wc, &s.ds_done, (total - 1) & 1, 17);
       tc_fence_after();
@@ -403,21 +392,21 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
 extern "C" FQ_API int fq_gdr_bwd_dh(const void* q, const void* k, const void* Ag, const void* Pg, const void* dout,
                                     const float* g_cumsum, const float* beta, const float* dht, float* dh0,
-                                    void* dh_out, void* dvp_out, void* dv_out, int B, int T, int H, int Hg,
+                                    void* dh_out, int B, int T, int H, int Hg,
                                     const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
                                     int total_chunks, float scale, int32_t* status_dev, void* stream) {
-  return fq_gdr_bwd_dh_cp(q, k, Ag, Pg, dout, g_cumsum, beta, dht, dh0, dh_out, dvp_out, dv_out, nullptr, nullptr, nullptr,
+  return fq_gdr_bwd_dh_cp(q, k, Ag, Pg, dout, g_cumsum, beta, dht, dh0, dh_out, nullptr, nullptr, nullptr,
                           nullptr, B, T, H, Hg, cu_seqlens, chunk_offsets, n_seq, total_chunks, scale, status_dev, stream);
 }
 
 extern "C" FQ_API int fq_gdr_bwd_dh_cp(const void* q, const void* k, const void* Ag, const void* Pg, const void* dout,
                                        const float* g_cumsum, const float* beta, const float* dht, float* dh0,
-                                       void* dh_out, void* dvp_out, void* dv_out, const int32_t* dht_index,
+                                       void* dh_out, const int32_t* dht_index,
                                        const int32_t* dh0_index, const int32_t* seq_end, const int32_t* warmup, int B,
                                        int T, int H, int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets,
                                        int n_seq, int total_chunks, float scale, int32_t* status_dev, void* stream) {
   using namespace fq;
-  FQ_CHECK_ARG(q && k && Ag && Pg && dout && g_cumsum && beta && dh_out && dvp_out && dv_out, "fq_gdr_bwd_dh: null tensor");
+  FQ_CHECK_ARG(q && k && Ag && Pg && dout && g_cumsum && beta && dh_out, "fq_gdr_bwd_dh: null tensor");
   FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0,
                "fq_gdr_bwd_dh: bad sizes");
   FQ_CHECK_ARG((cu_seqlens == nullptr) == (chunk_offsets == nullptr),
@@ -426,18 +415,21 @@ extern "C" FQ_API int fq_gdr_bwd_dh_cp(const void* q, const void* k, const void*
   FQ_CHECK_ARG(cu_seqlens != nullptr || n_seq == B, "fq_gdr_bwd_dh: dense batches need n_seq == B");
   const uint64_t rows = static_cast<uint64_t>(B) * static_cast<uint64_t>(T);
   FQ_CHECK_ARG(rows > 0 && rows < (1ull << 31), "fq_gdr_bwd_dh: token count out of range");
-  CUtensorMap mq, mk, mdo, ma, mpg;
+  CUtensorMap mq, mk, mdo, ma, mpg, mdh;
   int rc;
   if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdo, dout, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&ma, Ag, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mpg, Pg, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
+  {
+    const uint64_t hrows = static_cast<uint64_t>(total_chunks) * H * kDim;
+    FQ_CHECK_ARG(hrows > 0 && hrows < (1ull << 31), "fq_gdr_bwd_dh: chunk count out of range");
+    if ((rc = make_tmap_rows_heads_dim(&mdh, dh_out, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
+  }
   BwdDhParams p;
   p.g_cum = g_cumsum; p.beta = beta; p.dht = dht; p.dh0 = dh0;
   p.dh_out = static_cast<__nv_bfloat16*>(dh_out);
-  p.dvp_out = static_cast<__nv_bfloat16*>(dvp_out);
-  p.dv_out = static_cast<__nv_bfloat16*>(dv_out);
   p.dht_index = dht_index; p.dh0_index = dh0_index; p.seq_end = seq_end; p.warmup = warmup;
   p.dht_index = dht_index; p.dh0_index = dh0_index; p.seq_end = seq_end; p.warmup = warmup;
   p.H = H; p.Hg = Hg; p.scale = scale;
@@ -453,7 +445,7 @@ extern "C" FQ_API int fq_gdr_bwd_dh_cp(const void* q, const void* k, const void*
   }
   const long long ctas = static_cast<long long>(n_seq) * H;
   FQ_CHECK_ARG(ctas < (1ll << 31), "fq_gdr_bwd_dh: too many (sequence, head) pairs");
-  gdr_bwd_dh_kernel<<<static_cast<unsigned>(ctas), kDhThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mdo, ma, mpg, p);
+  gdr_bwd_dh_kernel<<<static_cast<unsigned>(ctas), kDhThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mdo, ma, mpg, mdh, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }

@@ -72,7 +72,8 @@ struct FwdParams {
   const int* warmup;    // [n_seq, H] chunks to replay before the piece; bit 30 set = the replay starts at the
                         //            sequence start (use h0), else start from zero.  nullptr = {0 | bit 30}
   __nv_bfloat16* o;     // [rows, H, 128] or nullptr
-  __nv_bfloat16* h_out; // [total_chunks, H, 128, 128] state before each chunk, or nullptr
+  __nv_bfloat16* h_out; // [total_chunks, H, 128(v), 128(k)] TRANSPOSED state before each chunk, or nullptr
+                        // (written by TMA straight from the bf16 operand buffer)
   int H, Hg;
   float scale;
   SeqArgs sa;
@@ -86,7 +87,8 @@ __device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t bytes) { retur
 __global__ void __launch_bounds__(kFwdThreads, 1)
 gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_a,
-               const __grid_constant__ CUtensorMap map_pg, const FwdParams p) {
+               const __grid_constant__ CUtensorMap map_pg, const __grid_constant__ CUtensorMap map_h,
+               const FwdParams p) {
   extern __shared__ unsigned char smem_dyn[];
   FwdSmem& s = *reinterpret_cast<FwdSmem*>(
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
@@ -119,7 +121,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     mbar_init(&s.o_free, 4);
     fence_mbar_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); tma_prefetch_desc(&map_a);
-    tma_prefetch_desc(&map_pg);
+    tma_prefetch_desc(&map_pg); tma_prefetch_desc(&map_h);
   }
   if (warp == 1) {
     tmem_alloc(&s.tmem_base, 512);
@@ -274,9 +276,11 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 16)) { alive = false; break; }
       {
         const float gL = s.gate[gs][1][kChunk - 1];
-        __nv_bfloat16* hdst = (p.h_out && n >= 0)
-                                  ? p.h_out + (static_cast<size_t>(chunk_off + n) * p.H + h) * kDim * kDim + v
-                                  : nullptr;
+        const bool store_h = (p.h_out != nullptr) && (n >= 0);
+        if (p.h_out != nullptr) {  // the previous chunk's TMA store must have read the operand buffer
+          if (tid == 128) tma_store_wait_read<0>();
+          asm volatile("bar.sync 2, 256;" ::: "memory");
+        }
         // both 32-column pieces are loaded before anything is stored, so only one TMEM round trip is exposed
         uint32_t r0[32], r1[32];
         tmem_ld32(tmem_addr(tm, lane_base, kColS + 64 * hf), r0);
@@ -300,11 +304,13 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&s.s_ready);
         if (tid == 128) FQ_TS(it, 15);
-        if (hdst) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            hdst[static_cast<size_t>(64 * hf + i) * kDim] = __float2bfloat16(__uint_as_float(r0[i]));
-            hdst[static_cast<size_t>(64 * hf + 32 + i) * kDim] = __float2bfloat16(__uint_as_float(r1[i]));
+        if (p.h_out != nullptr) {
+          asm volatile("bar.sync 2, 256;" ::: "memory");  // all 8 warps have written (and fenced) their part
+          if (store_h && tid == 128) {
+            const int hr = static_cast<int>((static_cast<long long>(chunk_off + n) * p.H + h) * kDim);
+            tma_store_3d(&map_h, s.sbf, 0, 0, hr);
+            tma_store_3d(&map_h, s.sbf + 16384, 64, 0, hr);
+            tma_store_commit();
           }
         }
 #pragma unroll
@@ -370,6 +376,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       if (lane == 0) { mbar_arrive(&s.vp_ready); mbar_arrive(&s.gate_empty[gs]); }
       if (tid == 128) FQ_TS(it, 13);
     }
+    if (p.h_out != nullptr && tid == 128) tma_store_wait_all<0>();
     // ---- final state
     if (alive && total > 0) {
       alive = mbar_wait(wc, &s.s_done, (total - 1) & 1, 17);
@@ -467,7 +474,7 @@ extern "C" FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v,
   FQ_CHECK_ARG(warmup == nullptr || cu_seqlens != nullptr, "fq_gdr_fwd: warm-up tables need piece boundaries (cu_seqlens)");
   const uint64_t rows = static_cast<uint64_t>(B) * static_cast<uint64_t>(T);
   FQ_CHECK_ARG(rows > 0 && rows < (1ull << 31), "fq_gdr_fwd: token count out of range");
-  CUtensorMap mq, mk, mv, ma, mpg;
+  CUtensorMap mq, mk, mv, ma, mpg, mh;
   int rc;
   if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
@@ -475,6 +482,14 @@ extern "C" FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v,
   if ((rc = make_tmap_rows_heads_dim(&ma, Ag, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
   // in state-only mode (o == NULL) the P_g tile is loaded but never used; A_g stands in for a missing P_g
   if ((rc = make_tmap_rows_heads_dim(&mpg, Pg ? Pg : Ag, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
+  {
+    const uint64_t hrows = static_cast<uint64_t>(total_chunks) * H * kDim;
+    FQ_CHECK_ARG(hrows < (1ull << 31), "fq_gdr_fwd: too many chunks for the state tensor");
+    // without h_out the map is never dereferenced; v stands in to keep the descriptor valid
+    if (h_out) rc = make_tmap_rows_heads_dim(&mh, h_out, hrows, 1, kDim, kDim, 64);
+    else rc = make_tmap_rows_heads_dim(&mh, v, rows, H, kDim, kChunk, 64);
+    if (rc != FQ_OK) return rc;
+  }
   FwdParams p;
   p.g_cum = g_cumsum; p.beta = beta; p.h0 = h0; p.ht = ht; p.ht_index = ht_index; p.h0_index = h0_index;
   p.warmup = warmup;
@@ -492,7 +507,7 @@ extern "C" FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v,
   }
   const long long ctas = static_cast<long long>(n_seq) * H;
   FQ_CHECK_ARG(ctas < (1ll << 31), "fq_gdr_fwd: too many (sequence, head) pairs");
-  gdr_fwd_kernel<<<static_cast<unsigned>(ctas), kFwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, ma, mpg, p);
+  gdr_fwd_kernel<<<static_cast<unsigned>(ctas), kFwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, ma, mpg, mh, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }

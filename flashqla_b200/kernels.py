@@ -140,7 +140,9 @@ def fused_gdr_fwd(q, k, v, ag, pg, g, b, scale, initial_state=None, output_final
     """Fused forward recurrence.  g is the chunk-local cumsum, ag / pg the gated tiles from kkt_solve_gated.
     With a CpPlan `cp` (and its `warmup` table) every piece of a sequence runs as its own CTA.
 
-    Returns (o or None, h or None, final_state or None)."""
+    Returns (o or None, hT or None, final_state or None).  hT holds the state before every chunk
+    TRANSPOSED ([..., H, V, K]): the kernel stores it by TMA straight from its bf16 operand buffer and the
+    backward kernels consume it in that layout; ``hT.transpose(-1, -2)`` is the [K, V] view."""
     _require_cuda(q, k, v, ag, g, b)
     if q.dtype != torch.bfloat16:
         raise _lib.FlashQLAError("fused_gdr_fwd: only bfloat16 q/k/v are supported")

@@ -48,6 +48,8 @@ def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None,
                                               plan=plan, cp=cp, warmup=warm, status=status)
     if status is not None:
         kernels.check_status(status, "fq_gdr_fwd")
+    if h is not None:
+        h = h.transpose(-1, -2)  # stored [.., V, K] by the kernel; the interface is [.., K, V]
     return g_cum, A, o, h, final_state
 
 

@@ -137,13 +137,13 @@ FQ_API int fq_cp_warmup(const float* g_cumsum, const int32_t* piece_edge, const 
  *   Ag, Pg [B,T,H,64] bf16 from fq_kkt_solve_gated;
  *   dout [B,T,H,128] bf16 (gradient of o); dht [n_seq,H,128,128] fp32 or NULL (gradient of the final state);
  *   dh0  [n_seq,H,128,128] fp32 or NULL (gradient of the initial state);
- *   dh_out [total_chunks,H,128,128] bf16: gradient w.r.t. the state AFTER each chunk (scratch for
- *   fq_gdr_bwd_chunk); dvp_out [B,T,H,128] bf16 scratch (dV'); dv_out [B,T,H,128] bf16 = gradient of v.
+ *   dh_out [total_chunks,H,128(v),128(k)] bf16: gradient w.r.t. the state AFTER each chunk, stored transposed
+ *   (scratch for fq_gdr_bwd_chunk).
  */
 FQ_API int fq_gdr_bwd_dh(const void* q, const void* k, const void* Ag, const void* Pg, const void* dout,
-                         const float* g_cumsum, const float* beta, const float* dht, float* dh0, void* dh_out, void* dvp_out, void* dv_out,
-                         int B, int T, int H, int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets,
-                         int n_seq, int total_chunks, float scale, int32_t* status_dev, void* stream);
+                         const float* g_cumsum, const float* beta, const float* dht, float* dh0, void* dh_out, int B,
+                         int T, int H, int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
+                         int total_chunks, float scale, int32_t* status_dev, void* stream);
 
 /*
  * fq_gdr_bwd_dh over context-parallel pieces (`cu_seqlens` = piece boundaries, see fq_gdr_fwd_cp):
@@ -154,21 +154,21 @@ FQ_API int fq_gdr_bwd_dh(const void* q, const void* k, const void* Ag, const voi
  */
 FQ_API int fq_gdr_bwd_dh_cp(const void* q, const void* k, const void* Ag, const void* Pg, const void* dout,
                             const float* g_cumsum, const float* beta, const float* dht, float* dh0, void* dh_out,
-                            void* dvp_out, void* dv_out, const int32_t* dht_index, const int32_t* dh0_index,
-                            const int32_t* seq_end, const int32_t* warmup, int B, int T, int H, int Hg,
-                            const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq, int total_chunks,
-                            float scale, int32_t* status_dev, void* stream);
+                            const int32_t* dht_index, const int32_t* dh0_index, const int32_t* seq_end,
+                            const int32_t* warmup, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
+                            const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
+                            int32_t* status_dev, void* stream);
 
 /*
- * Backward, chunk-parallel part: dq, dk (per V-head, bf16 [B,T,H,128]), dg w.r.t. the gate cumsum
- * and dbeta (fp32 [B,T,H]) from h (state before each chunk, from fq_gdr_fwd with h_out), dh, dvp and dv
- * (from fq_gdr_bwd_dh).  Second half of the replacement of hopper/fused_bwd.py:900-985.
+ * Backward, chunk-parallel part: dv (bf16 [B,T,H,128]), dq, dk (per V-head, bf16 [B,T,H,128]), dg w.r.t. the
+ * gate cumsum and dbeta (fp32 [B,T,H]) from h (state before each chunk, from fq_gdr_fwd with h_out; stored
+ * transposed [.., 128(v), 128(k)]) and dh (from fq_gdr_bwd_dh, same layout).
+ * Second half of the replacement of hopper/fused_bwd.py:900-985.
  */
 FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void* v, const void* A, const void* Ag,
-                            const void* Pg, const void* dout,
-                            const void* dvp, const void* dv, const void* h, const void* dh, const float* g_cumsum,
-                            const float* beta, void* dq, void* dk, float* dg, float* db, int B, int T, int H, int Hg,
-                            const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq, int total_chunks,
+                            const void* Pg, const void* dout, const void* h, const void* dh, const float* g_cumsum,
+                            const float* beta, void* dq, void* dk, void* dv, float* dg, float* db, int B, int T, int H,
+                            int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq, int total_chunks,
                             float scale, int32_t* status_dev, void* stream);
 
 /*
@@ -194,10 +194,9 @@ FQ_API int fq_group_reduce(const void* in, void* out, long long rows, int H, int
  *   - it calls no cudaMalloc / cudaFree and no allocating library routine.
  */
 FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k, const void* v, const void* A, const void* Ag,
-                                        const void* Pg, const void* dout,
-                                        const void* dvp, const void* dv, const void* h, const void* dh,
-                                        const float* g_cumsum, const float* beta, void* dq, void* dk, float* dg,
-                                        float* db, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
+                                        const void* Pg, const void* dout, const void* h, const void* dh,
+                                        const float* g_cumsum, const float* beta, void* dq, void* dk, void* dv,
+                                        float* dg, float* db, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
                                         const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
                                         int32_t* status_dev, void* stream);
 

@@ -4,7 +4,7 @@ fq_gdr_bwd_chunk_gva_noalloc serves callers that may not allocate device memory 
 runs (a pre-planned step with a frozen allocator, or a host that would otherwise pay a
 device-synchronising cudaMalloc per call): it keeps the per-V-head dq / dk partial results in an
 array inside the library instead of in two caller-allocated buffers.  The test drives both entry
-points through the C ABI on the same inputs and compares dq, dk, dg and dbeta, twice in a row
+points through the C ABI on the same inputs and compares dq, dk, dv, dg and dbeta, twice in a row
 (the second call reuses the array with the first call's contents still in it).
 
 This file is named so that pytest collects it last.
@@ -46,17 +46,17 @@ def test_noalloc_matches_regular_entry_point(B, T, Hq, Hv, cu):
     _, Ag, Pg = kernels.kkt_solve_gated(k, q, beta, gc, scale, plan, A=A)
     _, h, _ = kernels.fused_gdr_fwd(q, k, v, Ag, None, gc, beta, scale, initial_state=h0, output_final_state=False,
                                     output_h=True, output_o=False, plan=plan)
-    dh, dvp, dv = torch.empty_like(h), torch.empty_like(v), torch.empty_like(v)
+    dh = torch.empty_like(h)
     cu_p, off_p = plan.ptrs()
     st = kernels._stream()
     rc = lib.fq_gdr_bwd_dh(q.data_ptr(), k.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), do.data_ptr(), gc.data_ptr(), beta.data_ptr(),
-                           dht.data_ptr(), None, dh.data_ptr(), dvp.data_ptr(), dv.data_ptr(), B, T, Hv, Hq, cu_p, off_p,
+                           dht.data_ptr(), None, dh.data_ptr(), B, T, Hv, Hq, cu_p, off_p,
                            plan.n_seq, plan.total_chunks, scale, None, st)
     _lib.check(rc, "fq_gdr_bwd_dh")
 
-    def common_args(dq, dk, dg, db):
-        return (q.data_ptr(), k.data_ptr(), v.data_ptr(), A.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), do.data_ptr(), dvp.data_ptr(), dv.data_ptr(),
-                h.data_ptr(), dh.data_ptr(), gc.data_ptr(), beta.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+    def common_args(dq, dk, dv, dg, db):
+        return (q.data_ptr(), k.data_ptr(), v.data_ptr(), A.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), do.data_ptr(),
+                h.data_ptr(), dh.data_ptr(), gc.data_ptr(), beta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                 dg.data_ptr(), db.data_ptr(), B, T, Hv, Hq, cu_p, off_p, plan.n_seq, plan.total_chunks, scale, None, st)
 
     # regular path: caller-allocated per-V-head buffers + head sum
@@ -64,7 +64,8 @@ def test_noalloc_matches_regular_entry_point(B, T, Hq, Hv, cu):
     dk_h = torch.empty_like(dq_h)
     dg_ref = torch.empty(B, T, Hv, device="cuda")
     db_ref = torch.empty_like(dg_ref)
-    _lib.check(lib.fq_gdr_bwd_chunk(*common_args(dq_h, dk_h, dg_ref, db_ref)), "fq_gdr_bwd_chunk")
+    dv_ref = torch.empty_like(v)
+    _lib.check(lib.fq_gdr_bwd_chunk(*common_args(dq_h, dk_h, dv_ref, dg_ref, db_ref)), "fq_gdr_bwd_chunk")
     dq_ref = torch.empty(B, T, Hq, 128, dtype=torch.bfloat16, device="cuda")
     dk_ref = torch.empty_like(dq_ref)
     _lib.check(lib.fq_group_reduce(dq_h.data_ptr(), dq_ref.data_ptr(), B * T, Hv, Hq, st), "fq_group_reduce")
@@ -75,9 +76,11 @@ def test_noalloc_matches_regular_entry_point(B, T, Hq, Hv, cu):
         dk = torch.full_like(dq, float("nan"))
         dg = torch.full((B, T, Hv), float("nan"), device="cuda")
         db = torch.full_like(dg, float("nan"))
-        _lib.check(lib.fq_gdr_bwd_chunk_gva_noalloc(*common_args(dq, dk, dg, db)), "fq_gdr_bwd_chunk_gva_noalloc")
+        dv = torch.full_like(v, float("nan"))
+        _lib.check(lib.fq_gdr_bwd_chunk_gva_noalloc(*common_args(dq, dk, dv, dg, db)), "fq_gdr_bwd_chunk_gva_noalloc")
         torch.cuda.synchronize()
-        for name, got, ref in (("dq", dq, dq_ref), ("dk", dk, dk_ref), ("dg", dg, dg_ref), ("db", db, db_ref)):
+        for name, got, ref in (("dq", dq, dq_ref), ("dk", dk, dk_ref), ("dv", dv, dv_ref), ("dg", dg, dg_ref),
+                               ("db", db, db_ref)):
             assert torch.isfinite(got.float()).all(), f"{name} (call {call})"
             assert orc.rel_to_max(got.float().cpu(), ref.float().cpu()) < TOL, f"{name} (call {call})"
 
@@ -87,6 +90,6 @@ def test_noalloc_rejects_oversized_problem():
     lib = _lib.load()
     x = torch.zeros(16, device="cuda")
     p = x.data_ptr()
-    rc = lib.fq_gdr_bwd_chunk_gva_noalloc(p, p, p, p, p, p, p, p, p, p, p, p, p, p, p, p, p, 1, 65536, 2, 1, None, None, 1, 1024,
+    rc = lib.fq_gdr_bwd_chunk_gva_noalloc(p, p, p, p, p, p, p, p, p, p, p, p, p, p, p, p, 1, 65536, 2, 1, None, None, 1, 1024,
                                           0.1, None, None)
     assert rc == -4 and b"exceeds the built-in scratch" in lib.fq_last_error()
