@@ -135,6 +135,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   const long long n_units = static_cast<long long>(p.total_chunks) * p.H;
   bool alive = true;
 
+#pragma unroll 1
   for (long long unit = blockIdx.x; unit < n_units && alive; unit += gridDim.x) {
     const int chunk = static_cast<int>(unit / p.H), h = static_cast<int>(unit - static_cast<long long>(chunk) * p.H);
     const int hg = h / (p.H / p.Hg);

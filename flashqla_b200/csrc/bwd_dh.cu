@@ -119,6 +119,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      #pragma unroll 1
       for (int it = 0; it < total; ++it) {
         const int n = total - 1 - it, st = it & 1;
         if (it >= 2 && !mbar_wait(wc, &s.empty[st], ((it >> 1) + 1) & 1, 1)) break;
@@ -142,6 +143,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       constexpr uint32_t id64_abmn = umma_idesc(128, 64, true, true, true);
       constexpr uint32_t id128_bmn = umma_idesc(128, 128, false, true, true);
       const uint32_t sds = smem_u32(s.dsbf), sdvp = smem_u32(s.dvp), sdvg = smem_u32(s.dvg), sdos = smem_u32(s.dos);
+      #pragma unroll 1
       for (int it = 0; it < total; ++it) {
         const int st = it & 1;
         const uint32_t ph = it & 1;
@@ -188,6 +190,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   } else if (warp < 4) {
     // ------------------------------------------------------------------ gate loader
     const int t = tid - 64;
+    #pragma unroll 1
     for (int it = 0; it < total; ++it) {
       const int n = total - 1 - it, gs = it & (kDhGateStages - 1);
       if (it >= kDhGateStages && !mbar_wait(wc, &s.gate_empty[gs], ((it >> 2) + 1) & 1, 10)) break;
@@ -209,6 +212,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // ------------------------------------------------------------------ dV', dv, dVg (critical chain)
     const int v = tid - 128;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32;
+    #pragma unroll 1
     for (int it = 0; it < total; ++it) {
       const int n = total - 1 - it, gs = it & (kDhGateStages - 1);
       const uint32_t ph = it & 1;
@@ -278,6 +282,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       tmem_wait_st();
     }
     bool alive = true;
+    #pragma unroll 1
     for (int it = 0; it < total && alive; ++it) {
       const int n = total - 1 - it, gs = it & (kDhGateStages - 1);
       if (it > 0) {
@@ -343,6 +348,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // ------------------------------------------------------------------ tail fix of P_g, scaled dO^T
     const int v = tid - 384;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32;
+    #pragma unroll 1
     for (int it = 0; it < total; ++it) {
       const int n = total - 1 - it, st = it & 1, gs = it & (kDhGateStages - 1);
       const uint32_t ph = it & 1;

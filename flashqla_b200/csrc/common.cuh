@@ -47,6 +47,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of a phase (never suspends the thread).
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Per-CTA abort cell + global status word.  A wait that runs out of time records where it gave
 // up and raises the abort flag; every later wait in the CTA then returns at once, so the CTA
 // drains, frees its TMEM and exits instead of spinning on a barrier nobody will complete.
@@ -56,18 +69,33 @@ struct WaitCtx {
   int kernel_id;             // reported in bits 12.. of the status code
 };
 
-__device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint64_t* bar, uint32_t parity, int where) {
-  if (mbar_try_wait(bar, parity)) return true;
+// Bounded wait on a phase: one inline probe, then the polling loop, which lives out of line (one copy per
+// kernel) - the kernels wait in dozens of places, and the loop bodies of their warp roles have to stay
+// resident in the instruction cache together.
+static __device__ __noinline__ bool mbar_wait_slow(volatile int* abort_flag, int* status_dev, int code, uint64_t* bar,
+                                                   uint32_t parity) {
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*w.abort_flag) return false;
+    if (*abort_flag) return false;
     if (clock64() - t0 > kWaitLimitCycles) {
-      *w.abort_flag = 1;
-      if (w.status_dev) atomicCAS(w.status_dev, 0, (w.kernel_id << 12) + where);
+      *abort_flag = 1;
+      if (status_dev) atomicCAS(status_dev, 0, code);
       return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint64_t* bar, uint32_t parity, int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(w.abort_flag, w.status_dev, (w.kernel_id << 12) + where, bar, parity);
+}
+// For the one or two waits per kernel whose wake-up latency sits on the serial chain and whose waiter is a single
+// thread: probes without suspending for a bounded number of rounds, then falls back to the suspending wait.
+__device__ __forceinline__ bool mbar_wait_spin(const WaitCtx& w, uint64_t* bar, uint32_t parity, int where) {
+#pragma unroll 1
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_test(bar, parity)) return true;
+  return mbar_wait_slow(w.abort_flag, w.status_dev, (w.kernel_id << 12) + where, bar, parity);
 }
 
 // ---- proxy fences ------------------------------------------------------------------------------

@@ -180,7 +180,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // V_d^T = V^T A_g^T (A operand = the V tile as loaded, MN-major)
           umma_ss(tm + kColVD, desc_add(d_vmn, kk * 2048), desc_add(d_a, kk * 32), id64_amn, kk > 0);
-        if (!mbar_wait(wc, &s.s_ready, ph, 3)) break;
+        if (!mbar_wait_spin(wc, &s.s_ready, ph, 3)) break;
         FQ_TS(it, 1);
         tc_fence_after();
 #pragma unroll
@@ -196,7 +196,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           for (int kk = 0; kk < 8; ++kk)
             umma_ss(tm + kColOI, desc_add(d_kq, 8192 + kq_off(kk)), desc_add(d_sbf, kq_off(kk)), id_o, kk > 0);
         }
-        if (!mbar_wait(wc, &s.w_ready, ph, 5)) break;
+        if (!mbar_wait_spin(wc, &s.w_ready, ph, 5)) break;
         FQ_TS(it, 4);
         tc_fence_after();
 #pragma unroll
@@ -204,9 +204,9 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           umma_ss(tm + kColVD, desc_add(d_w, kk * 32), desc_add(d_a, kk * 32), id64, 1);
         umma_commit(&s.vd_done);
         FQ_TS(it, 6);
-        if (!mbar_wait(wc, &s.vp_ready, ph, 7)) break;
+        if (!mbar_wait_spin(wc, &s.vp_ready, ph, 7)) break;
         FQ_TS(it, 7);
-        if (!mbar_wait(wc, &s.s_scaled, ph, 9)) break;
+        if (!mbar_wait_spin(wc, &s.s_scaled, ph, 9)) break;
         FQ_TS(it, 8);
         tc_fence_after();
 #pragma unroll
