@@ -13,8 +13,8 @@
 //   round 4  accQ += dP K | accK += dP^T Q | X1 = A^T dA | column sums T^T 1, T3^T 1 (ones-vector MMAs)
 //            -> dq, dg -= colsum(T), dbeta += colsum(T3)
 //   round 5  X2 = X1 A^T | KK = K K^T
-//            -> dL = -strict_lower(X2); dbeta += rowsum(dL o KK); dAs = beta_row dL + (beta_row dL)^T
-//   round 6  accK += dAs K                                        -> dk, dg, dbeta
+//            -> dL = -strict_lower(X2); dbeta += rowsum(dL o KK); T5 = beta_row dL
+//   round 6  accK += T5 K + T5^T K  (dAs = T5 + T5^T, T5 = beta_row dL)  -> dk, dg, dbeta
 //
 // A_g and P_g come from kkt_solve.cu; S0 and dS arrive transposed ([v][k]) as the recurrences store them.
 // dg is the gradient w.r.t. the chunk-local cumsum of the gate; the caller applies the reverse
@@ -25,8 +25,17 @@
 
 namespace fq {
 
+#ifdef FQ_TRACE
+// Debug builds only: clock64 stamps of one CTA for its third unit, read back with fq_trace_read_bc.
+__device__ long long g_trace_bc[32];
+#define BC_TS(id) do { if (blockIdx.x == 0 && tid == 0 && unit == 2LL * gridDim.x) g_trace_bc[id] = clock64(); } while (0)
+#else
+#define BC_TS(id) do { } while (0)
+#endif
+
 constexpr int kBcThreads = 256;
-constexpr uint32_t kBcLoadBytes = 4 * 16384 + 3 * 8192 + 2 * 32768;
+constexpr uint32_t kBcLoadBytesA = 2 * 32768 + 2 * 16384;  // S0, dS, V, dO: requested a unit ahead
+constexpr uint32_t kBcLoadBytesB = 2 * 16384 + 3 * 8192;  // K, Q, A, A_g, P_g: requested at the start of the unit
 
 constexpr uint32_t kBcColU = 0;    // 128: U, then V', then K1, then X1 (0-63) / X2 (64-127)
 constexpr uint32_t kBcColD1 = 128; // 128: D1 = K dS, then dW; later split into the two 64-column slots below
@@ -36,6 +45,9 @@ constexpr uint32_t kBcColK = 256;  // 128: D2 = P_g^T dO, then accK
 constexpr uint32_t kBcColQ = 384;  // 128: accQ
 
 struct BwdChunkSmem {
+  // The tiles that a unit needs from its start (K, Q, A, A_g, P_g) and tiles that it only produces later (V', dVg,
+  // dV', T) form pairs that swap roles from one unit to the next: the tiles of the CTA's next unit are loaded into
+  // the partner buffers while the current unit finishes.  Pairs: kt/vp, qt/dvg, (at, ag)/dvp, pg/t12.
   unsigned char kt[16384];   // K  [64 c][128 k]  (two 64-row regions: k 0-63 | 64-127)
   unsigned char qt[16384];   // Q
   unsigned char wt[16384];   // V, rewritten as W
@@ -54,7 +66,7 @@ struct BwdChunkSmem {
   float g[kChunk], gam[kChunk], rho[kChunk], beta[kChunk];
   float dg_s[kChunk], db_s[kChunk];
   float dgl_s;
-  uint64_t bar_tma, bar_mma;
+  uint64_t bar_tma_a, bar_tma_b, bar_mma;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -103,8 +115,9 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
   if (tid == 0) {
     s.abort_flag = 0;
-    mbar_init(&s.bar_tma, 1);
-    mbar_init(&s.bar_mma, 1);
+    mbar_init(&s.bar_tma_a, 1);
+    mbar_init(&s.bar_tma_b, 1);
+    mbar_init(&s.bar_mma, 4);  // four issuing threads per round, one commit each
     fence_mbar_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); tma_prefetch_desc(&map_do);
     tma_prefetch_desc(&map_a); tma_prefetch_desc(&map_h);
@@ -120,10 +133,11 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = s.tmem_base;
-  const uint32_t skt = smem_u32(s.kt), sqt = smem_u32(s.qt), swt = smem_u32(s.wt), sdot = smem_u32(s.dot),
-                 sdvp = smem_u32(s.dvp), sdvg = smem_u32(s.dvg), svp = smem_u32(s.vp), ss0 = smem_u32(s.s0),
-                 sds = smem_u32(s.ds), sat = smem_u32(s.at), sag = smem_u32(s.ag), spg = smem_u32(s.pg),
-                 st12 = smem_u32(s.t12), st3 = smem_u32(s.t3), sones = smem_u32(s.ones);
+  const uint32_t swt = smem_u32(s.wt), sdot = smem_u32(s.dot), ss0 = smem_u32(s.s0), sds = smem_u32(s.ds),
+                 st3 = smem_u32(s.t3), sones = smem_u32(s.ones);
+  // buffers that swap roles between units (see BwdChunkSmem)
+  unsigned char *b_kt = s.kt, *b_vp = s.vp, *b_qt = s.qt, *b_dvg = s.dvg, *b_at = s.at, *b_dvp = s.dvp, *b_pg = s.pg,
+                *b_t12 = s.t12;
   constexpr uint32_t id64_128_kk = umma_idesc(64, 128, false, false, true);
   constexpr uint32_t id64_128_kmn = umma_idesc(64, 128, false, true, true);
   constexpr uint32_t id64_128_mnmn = umma_idesc(64, 128, true, true, true);
@@ -132,7 +146,39 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   constexpr uint32_t id64_16_mnk = umma_idesc(64, 16, true, false, true);
 
   uint32_t tma_phase = 0, mma_phase = 0;
+  // S0, dS, V and dO are dead after the third round of products, so the tiles of the CTA's next unit are requested
+  // there and land while rounds four to six run
+  auto load_a = [&](long long unit) {
+    const int chunk = static_cast<int>(unit / p.H), h = static_cast<int>(unit - static_cast<long long>(chunk) * p.H);
+    const ChunkPos cp = chunk_lookup(p.sa, chunk);
+    mbar_arrive_expect_tx(&s.bar_tma_a, kBcLoadBytesA);
+    const int r0 = cp.tok0;
+    tma_load_3d(s.wt, &map_v, &s.bar_tma_a, 0, h, r0);
+    tma_load_3d(s.wt + 8192, &map_v, &s.bar_tma_a, 64, h, r0);
+    tma_load_3d(s.dot, &map_do, &s.bar_tma_a, 0, h, r0);
+    tma_load_3d(s.dot + 8192, &map_do, &s.bar_tma_a, 64, h, r0);
+    const int hr = static_cast<int>((static_cast<long long>(chunk) * p.H + h) * kDim);
+    tma_load_3d(s.s0, &map_h, &s.bar_tma_a, 0, 0, hr);
+    tma_load_3d(s.s0 + 16384, &map_h, &s.bar_tma_a, 64, 0, hr);
+    tma_load_3d(s.ds, &map_dh, &s.bar_tma_a, 0, 0, hr);
+    tma_load_3d(s.ds + 16384, &map_dh, &s.bar_tma_a, 64, 0, hr);
+  };
+  auto load_b = [&](long long unit, unsigned char* dk, unsigned char* dq, unsigned char* da, unsigned char* dpg) {
+    const int chunk = static_cast<int>(unit / p.H), h = static_cast<int>(unit - static_cast<long long>(chunk) * p.H);
+    const int hg = h / (p.H / p.Hg);
+    const ChunkPos cp = chunk_lookup(p.sa, chunk);
+    mbar_arrive_expect_tx(&s.bar_tma_b, kBcLoadBytesB);
+    const int r0 = cp.tok0;
+    tma_load_3d(dk, &map_k, &s.bar_tma_b, 0, hg, r0);
+    tma_load_3d(dk + 8192, &map_k, &s.bar_tma_b, 64, hg, r0);
+    tma_load_3d(dq, &map_q, &s.bar_tma_b, 0, hg, r0);
+    tma_load_3d(dq + 8192, &map_q, &s.bar_tma_b, 64, hg, r0);
+    tma_load_3d(da, &map_a, &s.bar_tma_b, 0, h, r0);
+    tma_load_3d(da + 8192, &map_ag, &s.bar_tma_b, 0, h, r0);
+    tma_load_3d(dpg, &map_pg, &s.bar_tma_b, 0, h, r0);
+  };
   const long long n_units = static_cast<long long>(p.total_chunks) * p.H;
+  if (tid == 0 && blockIdx.x < n_units) load_a(blockIdx.x);
   bool alive = true;
 
 #pragma unroll 1
@@ -141,28 +187,14 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int hg = h / (p.H / p.Hg);
     const ChunkPos cp = chunk_lookup(p.sa, chunk);
     const int len = cp.len;
+    unsigned char* b_ag = b_at + 8192;
+    const uint32_t skt = smem_u32(b_kt), sqt = smem_u32(b_qt), sdvp = smem_u32(b_dvp), sdvg = smem_u32(b_dvg),
+                   svp = smem_u32(b_vp), sat = smem_u32(b_at), sag = smem_u32(b_ag), spg = smem_u32(b_pg),
+                   st12 = smem_u32(b_t12);
     __syncthreads();  // the previous unit's shared-memory reads are complete
+    BC_TS(0);
 
-    if (tid == 0) {
-      mbar_arrive_expect_tx(&s.bar_tma, kBcLoadBytes);
-      const int r0 = cp.tok0;
-      tma_load_3d(s.kt, &map_k, &s.bar_tma, 0, hg, r0);
-      tma_load_3d(s.kt + 8192, &map_k, &s.bar_tma, 64, hg, r0);
-      tma_load_3d(s.qt, &map_q, &s.bar_tma, 0, hg, r0);
-      tma_load_3d(s.qt + 8192, &map_q, &s.bar_tma, 64, hg, r0);
-      tma_load_3d(s.wt, &map_v, &s.bar_tma, 0, h, r0);
-      tma_load_3d(s.wt + 8192, &map_v, &s.bar_tma, 64, h, r0);
-      tma_load_3d(s.dot, &map_do, &s.bar_tma, 0, h, r0);
-      tma_load_3d(s.dot + 8192, &map_do, &s.bar_tma, 64, h, r0);
-      tma_load_3d(s.at, &map_a, &s.bar_tma, 0, h, r0);
-      tma_load_3d(s.ag, &map_ag, &s.bar_tma, 0, h, r0);
-      tma_load_3d(s.pg, &map_pg, &s.bar_tma, 0, h, r0);
-      const int hr = static_cast<int>((static_cast<long long>(chunk) * p.H + h) * kDim);
-      tma_load_3d(s.s0, &map_h, &s.bar_tma, 0, 0, hr);
-      tma_load_3d(s.s0 + 16384, &map_h, &s.bar_tma, 64, 0, hr);
-      tma_load_3d(s.ds, &map_dh, &s.bar_tma, 0, 0, hr);
-      tma_load_3d(s.ds + 16384, &map_dh, &s.bar_tma, 64, 0, hr);
-    }
+    if (tid == 0 && unit == blockIdx.x) load_b(unit, b_kt, b_qt, b_at, b_pg);  // later units: requested a unit ahead
     if (tid < kChunk) {
       const size_t base = static_cast<size_t>(cp.tok0) * p.H + h;
       const float gl = __ldg(p.g_cum + base + static_cast<size_t>(len - 1) * p.H);
@@ -180,13 +212,15 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (tid == 0) s.dgl_s = 0.f;
     }
     __syncthreads();
-    if (!mbar_wait(wc, &s.bar_tma, tma_phase, 1)) { alive = false; break; }
+    if (!mbar_wait(wc, &s.bar_tma_a, tma_phase, 1)) { alive = false; break; }
+    if (!mbar_wait(wc, &s.bar_tma_b, tma_phase, 8)) { alive = false; break; }
     tma_phase ^= 1;
+    BC_TS(1);
 
     // ---- pre-pass on shared memory: zero the rows past the sequence end
     //      and the scalar gamma_last * sum(dS o S0)
     if (len < kChunk) {
-      unsigned char* tiles[4] = {s.kt, s.qt, s.wt, s.dot};
+      unsigned char* tiles[4] = {b_kt, b_qt, s.wt, s.dot};
       const int nrows = kChunk - len;
       for (int idx = tid; idx < nrows * 16; idx += kBcThreads) {
         const int r = len + (idx >> 4), pc = idx & 15;
@@ -194,9 +228,9 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
         for (int t6 = 0; t6 < 4; ++t6) *reinterpret_cast<uint4*>(tiles[t6] + off) = make_uint4(0, 0, 0, 0);
         if (pc < 8) {
-          *reinterpret_cast<uint4*>(s.at + r * 128 + pc * 16) = make_uint4(0, 0, 0, 0);
-          *reinterpret_cast<uint4*>(s.ag + r * 128 + pc * 16) = make_uint4(0, 0, 0, 0);
-          *reinterpret_cast<uint4*>(s.pg + r * 128 + pc * 16) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(b_at + r * 128 + pc * 16) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(b_ag + r * 128 + pc * 16) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(b_pg + r * 128 + pc * 16) = make_uint4(0, 0, 0, 0);
         }
       }
       __syncthreads();
@@ -220,36 +254,43 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     fence_async_smem();
     __syncthreads();
 
+    BC_TS(2);
     const float gam_r = s.gam[row], rho_r = s.rho[row];
 
     // ================================================================== round 1
-    if (tid == 0) {
+    if (lane == 0 && warp < 4) {  // the products of a round are issued by four threads in parallel
       tc_fence_after();
+      if (warp == 0) {
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)  // U = K S0
-        umma_ss(tm + kBcColU, umma_desc_sw128(skt + off64(kk), 16, 1024), umma_desc_sw128(ss0 + off128(kk), 16, 1024),
-                id64_128_kk, kk > 0);
+        for (int kk = 0; kk < 8; ++kk)  // U = K S0
+          umma_ss(tm + kBcColU, umma_desc_sw128(skt + off64(kk), 16, 1024), umma_desc_sw128(ss0 + off128(kk), 16, 1024),
+                  id64_128_kk, kk > 0);
+      } else if (warp == 1) {
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)  // D1 = K dS
-        umma_ss(tm + kBcColD1, umma_desc_sw128(skt + off64(kk), 16, 1024), umma_desc_sw128(sds + off128(kk), 16, 1024),
-                id64_128_kk, kk > 0);
+        for (int kk = 0; kk < 8; ++kk)  // D1 = K dS
+          umma_ss(tm + kBcColD1, umma_desc_sw128(skt + off64(kk), 16, 1024), umma_desc_sw128(sds + off128(kk), 16, 1024),
+                  id64_128_kk, kk > 0);
+      } else if (warp == 2) {
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk)  // D2 = P_g^T dO
-        umma_ss(tm + kBcColK, umma_desc_sw128(spg + kk * 2048, 8192, 1024), umma_desc_sw128(sdot + kk * 2048, 8192, 1024),
-                id64_128_mnmn, kk > 0);
+        for (int kk = 0; kk < 4; ++kk)  // D2 = P_g^T dO
+          umma_ss(tm + kBcColK, umma_desc_sw128(spg + kk * 2048, 8192, 1024), umma_desc_sw128(sdot + kk * 2048, 8192, 1024),
+                  id64_128_mnmn, kk > 0);
+      } else if (warp == 3) {
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)  // accQ = dO S0^T
-        umma_ss(tm + kBcColQ, umma_desc_sw128(sdot + off64(kk), 16, 1024), umma_desc_sw128(ss0 + kk * 2048, 16384, 1024),
-                id64_128_kmn, kk > 0);
+        for (int kk = 0; kk < 8; ++kk)  // accQ = dO S0^T
+          umma_ss(tm + kBcColQ, umma_desc_sw128(sdot + off64(kk), 16, 1024), umma_desc_sw128(ss0 + kk * 2048, 16384, 1024),
+                  id64_128_kmn, kk > 0);
+      }
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
     if (!mbar_wait(wc, &s.bar_mma, mma_phase, 2)) { alive = false; break; }
     mma_phase ^= 1;
+    BC_TS(3);
     tc_fence_after();
     {
       // W = V - gamma o U (in place over V);  dV' = rho o D1 + D2
-#pragma unroll
+#pragma unroll 1
       for (int pc = 0; pc < 2; ++pc) {
         uint32_t u[32];
         tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 64 * hf + 32 * pc), u);
@@ -280,13 +321,13 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             for (int e = 0; e < 4; ++e)
               xw[e] = pack_bf16(rho_r * __uint_as_float(u[8 * ch + 2 * e]) + __uint_as_float(d2[8 * ch + 2 * e]),
                                 rho_r * __uint_as_float(u[8 * ch + 2 * e + 1]) + __uint_as_float(d2[8 * ch + 2 * e + 1]));
-            *reinterpret_cast<uint4*>(s.dvp + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = x;
+            *reinterpret_cast<uint4*>(b_dvp + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = x;
           }
         }
       }
       // accQ *= scale * gamma (written back); dg += rowsum(Q o accQ)
       float part = 0.f;
-#pragma unroll
+#pragma unroll 1
       for (int pc = 0; pc < 2; ++pc) {
         uint32_t r[32];
         tmem_ld32(tmem_addr(tm, lane_base, kBcColQ + 64 * hf + 32 * pc), r);
@@ -294,7 +335,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const float f = p.scale * gam_r;
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
-          const uint4 qv = *reinterpret_cast<const uint4*>(s.qt + hf * 8192 + sw128(row, (4 * pc + ch) * 16));
+          const uint4 qv = *reinterpret_cast<const uint4*>(b_qt + hf * 8192 + sw128(row, (4 * pc + ch) * 16));
           const uint32_t* qw = reinterpret_cast<const uint32_t*>(&qv);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -313,26 +354,31 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     fence_async_smem();
     __syncthreads();
 
+    BC_TS(4);
     // ================================================================== round 2: V' = A_g W, dW = A_g^T dV'
-    if (tid == 0) {
+    if (lane == 0 && warp < 4) {  // the products of a round are issued by four threads in parallel
       tc_fence_after();
+      if (warp == 0) {
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-        umma_ss(tm + kBcColU, umma_desc_sw128(sag + kk * 32, 16, 1024), umma_desc_sw128(swt + kk * 2048, 8192, 1024),
-                id64_128_kmn, kk > 0);
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss(tm + kBcColU, umma_desc_sw128(sag + kk * 32, 16, 1024), umma_desc_sw128(swt + kk * 2048, 8192, 1024),
+                  id64_128_kmn, kk > 0);
+      } else if (warp == 1) {
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-        umma_ss(tm + kBcColD1, umma_desc_sw128(sag + kk * 2048, 8192, 1024), umma_desc_sw128(sdvp + kk * 2048, 8192, 1024),
-                id64_128_mnmn, kk > 0);
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss(tm + kBcColD1, umma_desc_sw128(sag + kk * 2048, 8192, 1024), umma_desc_sw128(sdvp + kk * 2048, 8192, 1024),
+                  id64_128_mnmn, kk > 0);
+      }
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
     if (!mbar_wait(wc, &s.bar_mma, mma_phase, 3)) { alive = false; break; }
     mma_phase ^= 1;
+    BC_TS(5);
     tc_fence_after();
     {
       __nv_bfloat16* dvdst = p.dv + (static_cast<size_t>(cp.tok0 + row) * p.H + h) * kDim + 64 * hf;
-#pragma unroll
+#pragma unroll 1
       for (int pc = 0; pc < 2; ++pc) {
         uint32_t r[32], w2[32];
         tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 64 * hf + 32 * pc), r);
@@ -346,7 +392,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             x.y = pack_bf16(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
             x.z = pack_bf16(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
             x.w = pack_bf16(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
-            *reinterpret_cast<uint4*>(s.vp + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = x;
+            *reinterpret_cast<uint4*>(b_vp + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = x;
             uint32_t* yw = reinterpret_cast<uint32_t*>(&y);
             uint32_t* zw = reinterpret_cast<uint32_t*>(&z);
 #pragma unroll
@@ -355,7 +401,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
               yw[e] = pack_bf16(d0, d1);                      // dv
               zw[e] = pack_bf16(-gam_r * d0, -gam_r * d1);    // dVg
             }
-            *reinterpret_cast<uint4*>(s.dvg + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = z;
+            *reinterpret_cast<uint4*>(b_dvg + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = z;
             if (row < len) *reinterpret_cast<uint4*>(dvdst + 32 * pc + 8 * ch) = y;
           }
         }
@@ -365,35 +411,42 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     fence_async_smem();
     __syncthreads();
 
+    BC_TS(6);
     // ================================================================== round 3
-    if (tid == 0) {
+    if (lane == 0 && warp < 4) {  // the products of a round are issued by four threads in parallel
       tc_fence_after();
+      if (warp == 0) {
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        umma_ss(tm + kBcColU, umma_desc_sw128(svp + off64(kk), 16, 1024), umma_desc_sw128(sds + kk * 2048, 16384, 1024),
-                id64_128_kmn, kk > 0);
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(tm + kBcColU, umma_desc_sw128(svp + off64(kk), 16, 1024), umma_desc_sw128(sds + kk * 2048, 16384, 1024),
+                  id64_128_kmn, kk > 0);
+      } else if (warp == 1) {
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        umma_ss(tm + kBcColQK, umma_desc_sw128(sdot + off64(kk), 16, 1024), umma_desc_sw128(svp + off64(kk), 16, 1024),
-                id64_64_kk, kk > 0);
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(tm + kBcColQK, umma_desc_sw128(sdot + off64(kk), 16, 1024), umma_desc_sw128(svp + off64(kk), 16, 1024),
+                  id64_64_kk, kk > 0);
+      } else if (warp == 2) {
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        umma_ss(tm + kBcColX, umma_desc_sw128(sdvp + off64(kk), 16, 1024), umma_desc_sw128(swt + off64(kk), 16, 1024),
-                id64_64_kk, kk > 0);
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(tm + kBcColX, umma_desc_sw128(sdvp + off64(kk), 16, 1024), umma_desc_sw128(swt + off64(kk), 16, 1024),
+                  id64_64_kk, kk > 0);
+      } else if (warp == 3) {
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)  // accK = dVg S0^T
-        umma_ss(tm + kBcColK, umma_desc_sw128(sdvg + off64(kk), 16, 1024), umma_desc_sw128(ss0 + kk * 2048, 16384, 1024),
-                id64_128_kmn, kk > 0);
+        for (int kk = 0; kk < 8; ++kk)  // accK = dVg S0^T
+          umma_ss(tm + kBcColK, umma_desc_sw128(sdvg + off64(kk), 16, 1024), umma_desc_sw128(ss0 + kk * 2048, 16384, 1024),
+                  id64_128_kmn, kk > 0);
+      }
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
     if (!mbar_wait(wc, &s.bar_mma, mma_phase, 4)) { alive = false; break; }
     mma_phase ^= 1;
+    BC_TS(7);
     tc_fence_after();
     {
       // dg += rowsum(K o accK); then accK += rho o K1 ; kk = rowsum(K o rho K1)
       float kkp = 0.f, kap = 0.f;
-#pragma unroll
+#pragma unroll 1
       for (int pc = 0; pc < 2; ++pc) {
         uint32_t r[32], a2[32];
         tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 64 * hf + 32 * pc), r);
@@ -401,7 +454,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         tmem_wait_ld();
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
-          const uint4 kv = *reinterpret_cast<const uint4*>(s.kt + hf * 8192 + sw128(row, (4 * pc + ch) * 16));
+          const uint4 kv = *reinterpret_cast<const uint4*>(b_kt + hf * 8192 + sw128(row, (4 * pc + ch) * 16));
           const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kv);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -440,8 +493,8 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       for (int c2 = 0; c2 < 2; ++c2) {
         const int ch = 2 * up + c2;  // 16-byte piece of the row's 64-byte half
         const uint32_t so = sw128(row2, (4 * hf + ch) * 16);
-        const uint4 pgv = *reinterpret_cast<const uint4*>(s.pg + so);
-        const uint4 av = *reinterpret_cast<const uint4*>(s.at + so);
+        const uint4 pgv = *reinterpret_cast<const uint4*>(b_pg + so);
+        const uint4 av = *reinterpret_cast<const uint4*>(b_at + so);
         const uint32_t* pw = reinterpret_cast<const uint32_t*>(&pgv);
         const uint32_t* aw = reinterpret_cast<const uint32_t*>(&av);
         uint4 dpv, dav, t12v, t3v;
@@ -481,9 +534,9 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           rows += bf16_lo(t12w[e]) + bf16_hi(t12w[e]);
           t3w[e] = pack_bf16(t3o[0], t3o[1]);
         }
-        *reinterpret_cast<uint4*>(s.pg + so) = dpv;
-        *reinterpret_cast<uint4*>(s.ag + so) = dav;
-        *reinterpret_cast<uint4*>(s.t12 + so) = t12v;
+        *reinterpret_cast<uint4*>(b_pg + so) = dpv;
+        *reinterpret_cast<uint4*>(b_ag + so) = dav;
+        *reinterpret_cast<uint4*>(b_t12 + so) = t12v;
         *reinterpret_cast<uint4*>(s.t3 + so) = t3v;
       }
       rows += __shfl_xor_sync(0xffffffffu, rows, 16);
@@ -494,34 +547,44 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     fence_async_smem();
     __syncthreads();
 
+    BC_TS(8);
     // ================================================================== round 4
-    if (tid == 0) {
+    if (lane == 0 && warp < 4) {  // the products of a round are issued by four threads in parallel
       tc_fence_after();
+      if (warp == 0) {
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-        umma_ss(tm + kBcColQ, umma_desc_sw128(spg + kk * 32, 16, 1024), umma_desc_sw128(skt + kk * 2048, 8192, 1024),
-                id64_128_kmn, 1);
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss(tm + kBcColQ, umma_desc_sw128(spg + kk * 32, 16, 1024), umma_desc_sw128(skt + kk * 2048, 8192, 1024),
+                  id64_128_kmn, 1);
+      } else if (warp == 1) {
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-        umma_ss(tm + kBcColK, umma_desc_sw128(spg + kk * 2048, 8192, 1024), umma_desc_sw128(sqt + kk * 2048, 8192, 1024),
-                id64_128_mnmn, 1);
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss(tm + kBcColK, umma_desc_sw128(spg + kk * 2048, 8192, 1024), umma_desc_sw128(sqt + kk * 2048, 8192, 1024),
+                  id64_128_mnmn, 1);
+      } else if (warp == 2) {
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-        umma_ss(tm + kBcColU, umma_desc_sw128(sat + kk * 2048, 8192, 1024), umma_desc_sw128(sag + kk * 2048, 8192, 1024),
-                id64_64_mnmn, kk > 0);
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss(tm + kBcColU, umma_desc_sw128(sat + kk * 2048, 8192, 1024), umma_desc_sw128(sag + kk * 2048, 8192, 1024),
+                  id64_64_mnmn, kk > 0);
+      } else if (warp == 3) {
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk)  // column sums: D[j][:] = sum_i T[i][j]
-        umma_ss(tm + kBcColX, umma_desc_sw128(st12 + kk * 2048, 8192, 1024), umma_desc_sw128(sones + kk * 32, 16, 1024),
-                id64_16_mnk, kk > 0);
+        for (int kk = 0; kk < 4; ++kk)  // column sums: D[j][:] = sum_i T[i][j]
+          umma_ss(tm + kBcColX, umma_desc_sw128(st12 + kk * 2048, 8192, 1024), umma_desc_sw128(sones + kk * 32, 16, 1024),
+                  id64_16_mnk, kk > 0);
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-        umma_ss(tm + kBcColX + 16, umma_desc_sw128(st3 + kk * 2048, 8192, 1024), umma_desc_sw128(sones + kk * 32, 16, 1024),
-                id64_16_mnk, kk > 0);
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss(tm + kBcColX + 16, umma_desc_sw128(st3 + kk * 2048, 8192, 1024), umma_desc_sw128(sones + kk * 32, 16, 1024),
+                  id64_16_mnk, kk > 0);
+      }
       umma_commit(&s.bar_mma);
+      // the tiles that only rounds one to three read are dead: request them for this CTA's next unit (the issue
+      // overlaps the products just queued)
+      if (warp == 0 && unit + gridDim.x < n_units) load_a(unit + gridDim.x);
     }
     __syncwarp();
     if (!mbar_wait(wc, &s.bar_mma, mma_phase, 5)) { alive = false; break; }
     mma_phase ^= 1;
+    BC_TS(9);
     tc_fence_after();
     {
       uint32_t r[32];
@@ -535,7 +598,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           x.y = pack_bf16(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
           x.z = pack_bf16(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
           x.w = pack_bf16(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
-          *reinterpret_cast<uint4*>(s.pg + sw128(row, (4 * hf + ch) * 16)) = x;
+          *reinterpret_cast<uint4*>(b_pg + sw128(row, (4 * hf + ch) * 16)) = x;
         }
       }
       // column sums of T and T3 (every column of the small accumulators holds the same sum)
@@ -551,7 +614,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
       // dq
       __nv_bfloat16* dst = p.dq + (static_cast<size_t>(cp.tok0 + row) * p.H + h) * kDim + 64 * hf;
-#pragma unroll
+#pragma unroll 1
       for (int pc = 0; pc < 2; ++pc) {
         tmem_ld32(tmem_addr(tm, lane_base, kBcColQ + 64 * hf + 32 * pc), r);
         tmem_wait_ld();
@@ -572,22 +635,30 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     fence_async_smem();
     __syncthreads();
 
+    BC_TS(10);
     // ================================================================== round 5
-    if (tid == 0) {
+    if (lane == 0 && warp < 4) {  // the products of a round are issued by four threads in parallel
       tc_fence_after();
+      if (warp == 0) {
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-        umma_ss(tm + kBcColU + 64, umma_desc_sw128(spg + kk * 32, 16, 1024), umma_desc_sw128(sat + kk * 32, 16, 1024),
-                id64_64_kk, kk > 0);
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss(tm + kBcColU + 64, umma_desc_sw128(spg + kk * 32, 16, 1024), umma_desc_sw128(sat + kk * 32, 16, 1024),
+                  id64_64_kk, kk > 0);
+      } else if (warp == 1) {
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        umma_ss(tm + kBcColQK, umma_desc_sw128(skt + off64(kk), 16, 1024), umma_desc_sw128(skt + off64(kk), 16, 1024),
-                id64_64_kk, kk > 0);
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(tm + kBcColQK, umma_desc_sw128(skt + off64(kk), 16, 1024), umma_desc_sw128(skt + off64(kk), 16, 1024),
+                  id64_64_kk, kk > 0);
+      }
       umma_commit(&s.bar_mma);
+      // V', dVg, dV' and T are dead (their last readers were rounds three and four): the K, Q, A, A_g and P_g tiles
+      // of this CTA's next unit go there
+      if (warp == 0 && unit + gridDim.x < n_units) load_b(unit + gridDim.x, b_vp, b_dvg, b_dvp, b_t12);
     }
     __syncwarp();
     if (!mbar_wait(wc, &s.bar_mma, mma_phase, 6)) { alive = false; break; }
     mma_phase ^= 1;
+    BC_TS(11);
     tc_fence_after();
     {
       uint32_t x2[32], kk2[32];
@@ -599,23 +670,27 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       const int row2 = 16 * q4 + (lane & 15);
       const float beta_r2 = s.beta[row2];
       float dbr = 0.f;
+      // Only the lower triangle T5 = beta_row o dL is stored (16 columns per lane, row-contiguous); round 6 applies
+      // it and its transpose, which together are dAs = T5 + T5^T.
+      uint32_t tw[8];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const uint32_t hx = __shfl_sync(0xffffffffu, x2[16 + i], lane & 15);
-        const uint32_t hk = __shfl_sync(0xffffffffu, kk2[16 + i], lane & 15);
-        const float xv = __uint_as_float(up ? hx : x2[i]);
-        const float kv = __uint_as_float(up ? hk : kk2[i]);
-        const int j = 32 * hf + 16 * up + i;
-        if (j < row2) {
-          const float dL = -xv;
+      for (int i = 0; i < 16; i += 2) {
+        float o2[2];
+#pragma unroll
+        for (int z = 0; z < 2; ++z) {
+          const uint32_t hx = __shfl_sync(0xffffffffu, x2[16 + i + z], lane & 15);
+          const uint32_t hk = __shfl_sync(0xffffffffu, kk2[16 + i + z], lane & 15);
+          const float xv = __uint_as_float(up ? hx : x2[i + z]);
+          const float kv = __uint_as_float(up ? hk : kk2[i + z]);
+          const int j = 32 * hf + 16 * up + i + z;
+          const float dL = (j < row2) ? -xv : 0.f;
           dbr += dL * kv;
-          const unsigned short bits = __bfloat16_as_ushort(__float2bfloat16(beta_r2 * dL));
-          *reinterpret_cast<unsigned short*>(s.ag + sw128(row2, j * 2)) = bits;
-          *reinterpret_cast<unsigned short*>(s.ag + sw128(j, row2 * 2)) = bits;
-        } else if (j == row2) {
-          *reinterpret_cast<unsigned short*>(s.ag + sw128(row2, j * 2)) = 0;
+          o2[z] = beta_r2 * dL;
         }
+        tw[i >> 1] = pack_bf16(o2[0], o2[1]);
       }
+      *reinterpret_cast<uint4*>(b_ag + sw128(row2, (4 * hf + 2 * up) * 16)) = make_uint4(tw[0], tw[1], tw[2], tw[3]);
+      *reinterpret_cast<uint4*>(b_ag + sw128(row2, (4 * hf + 2 * up + 1) * 16)) = make_uint4(tw[4], tw[5], tw[6], tw[7]);
       dbr += __shfl_xor_sync(0xffffffffu, dbr, 16);
       if (active) atomicAdd(&s.db_s[row], dbr);
     }
@@ -623,22 +698,31 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     fence_async_smem();
     __syncthreads();
 
+    BC_TS(12);
     // ================================================================== round 6
-    if (tid == 0) {
+    if (lane == 0 && warp < 4) {  // the products of a round are issued by four threads in parallel
       tc_fence_after();
+      if (warp == 0) {
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-        umma_ss(tm + kBcColK, umma_desc_sw128(sag + kk * 32, 16, 1024), umma_desc_sw128(skt + kk * 2048, 8192, 1024),
-                id64_128_kmn, 1);
+        for (int kk = 0; kk < 4; ++kk)  // accK += T5 K
+          umma_ss(tm + kBcColK, umma_desc_sw128(sag + kk * 32, 16, 1024), umma_desc_sw128(skt + kk * 2048, 8192, 1024),
+                  id64_128_kmn, 1);
+      } else if (warp == 1) {
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)  // accK += T5^T K
+          umma_ss(tm + kBcColK, umma_desc_sw128(sag + kk * 2048, 8192, 1024), umma_desc_sw128(skt + kk * 2048, 8192, 1024),
+                  id64_128_mnmn, 1);
+      }
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
     if (!mbar_wait(wc, &s.bar_mma, mma_phase, 7)) { alive = false; break; }
     mma_phase ^= 1;
+    BC_TS(13);
     tc_fence_after();
     {
       __nv_bfloat16* dst = p.dk + (static_cast<size_t>(cp.tok0 + row) * p.H + h) * kDim + 64 * hf;
-#pragma unroll
+#pragma unroll 1
       for (int pc = 0; pc < 2; ++pc) {
         uint32_t r[32];
         tmem_ld32(tmem_addr(tm, lane_base, kBcColK + 64 * hf + 32 * pc), r);
@@ -658,6 +742,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
     tc_fence_before();
     __syncthreads();
+    BC_TS(14);
     if (tid < kChunk) {
       // the padded rows of a tail chunk share the gate of the last valid token
       float dgv = s.dg_s[tid];
@@ -671,8 +756,21 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         p.db[o] = s.db_s[tid];
       }
     }
+    {  // the paired buffers swap roles
+      unsigned char* t;
+      t = b_kt; b_kt = b_vp; b_vp = t;
+      t = b_qt; b_qt = b_dvg; b_dvg = t;
+      t = b_at; b_at = b_dvp; b_dvp = t;
+      t = b_pg; b_pg = b_t12; b_t12 = t;
+    }
   }
 
+  if (!alive && tid == 0) {
+    // a bounded wait gave up: let the tile loads that are still in flight land before the CTA's shared memory is released
+#pragma unroll 1
+    for (int i = 0; i < (1 << 20) && !(mbar_test(&s.bar_tma_a, tma_phase) && mbar_test(&s.bar_tma_b, tma_phase)); ++i) {
+    }
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 512);
@@ -868,3 +966,9 @@ extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k,
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }
+
+#ifdef FQ_TRACE
+extern "C" FQ_API int fq_trace_read_bc(long long* out_host) {
+  return cudaMemcpyFromSymbol(out_host, fq::g_trace_bc, sizeof(long long) * 32) == cudaSuccess ? 0 : -2;
+}
+#endif
