@@ -11,7 +11,10 @@ from .kernels import make_plan
 from .planner import plan_cp
 
 
-def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, initial_state=None, cu_seqlens=None):
+def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, initial_state=None, cu_seqlens=None,
+                               gated_tiles=None):
+    """``gated_tiles`` = (A_g, P_g) as produced by the forward for the same inputs; when given, the pass that
+    rebuilds them from ``A`` is skipped (the autograd function keeps them unless FLASHQLA_RECOMPUTE_TILES=1)."""
     kernels._require_cuda(q, k, v, g, beta, A, do)
     if q.dtype != torch.bfloat16:
         raise _lib.FlashQLAError("chunk_gated_delta_rule_bwd: only bfloat16 q/k/v are supported")
@@ -38,7 +41,10 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
 
     # 1. gated tiles from the given A, then the state before every chunk (bf16) with the forward
     #    recurrence kernel in state-only mode (context parallel like the forward)
-    _, Ag, Pg = kernels.kkt_solve_gated(k, q, bt, g, scale, plan, A=A)
+    if gated_tiles is not None:
+        Ag, Pg = gated_tiles
+    else:
+        _, Ag, Pg = kernels.kkt_solve_gated(k, q, bt, g, scale, plan, A=A)
     from . import ops as _ops
     cp = plan_cp(plan, B, T, H, kernels.sm_count(dev), dev, piece_chunks=_ops._FORCE_PIECE_CHUNKS)
     warm = kernels.cp_warmup(g, cp, H) if cp is not None else None

@@ -163,24 +163,43 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     tma_load_3d(s.ds, &map_dh, &s.bar_tma_a, 0, 0, hr);
     tma_load_3d(s.ds + 16384, &map_dh, &s.bar_tma_a, 64, 0, hr);
   };
-  auto load_b = [&](long long unit, unsigned char* dk, unsigned char* dq, unsigned char* da, unsigned char* dpg) {
+  // part 0: K, Q, A, A_g (and the byte count of the whole group); part 1: P_g
+  auto load_b = [&](long long unit, int part, unsigned char* dk, unsigned char* dq, unsigned char* da,
+                    unsigned char* dpg) {
     const int chunk = static_cast<int>(unit / p.H), h = static_cast<int>(unit - static_cast<long long>(chunk) * p.H);
     const int hg = h / (p.H / p.Hg);
     const ChunkPos cp = chunk_lookup(p.sa, chunk);
-    mbar_arrive_expect_tx(&s.bar_tma_b, kBcLoadBytesB);
     const int r0 = cp.tok0;
-    tma_load_3d(dk, &map_k, &s.bar_tma_b, 0, hg, r0);
-    tma_load_3d(dk + 8192, &map_k, &s.bar_tma_b, 64, hg, r0);
-    tma_load_3d(dq, &map_q, &s.bar_tma_b, 0, hg, r0);
-    tma_load_3d(dq + 8192, &map_q, &s.bar_tma_b, 64, hg, r0);
-    tma_load_3d(da, &map_a, &s.bar_tma_b, 0, h, r0);
-    tma_load_3d(da + 8192, &map_ag, &s.bar_tma_b, 0, h, r0);
-    tma_load_3d(dpg, &map_pg, &s.bar_tma_b, 0, h, r0);
+    if (part != 1) {
+      mbar_arrive_expect_tx(&s.bar_tma_b, kBcLoadBytesB);
+      tma_load_3d(dk, &map_k, &s.bar_tma_b, 0, hg, r0);
+      tma_load_3d(dk + 8192, &map_k, &s.bar_tma_b, 64, hg, r0);
+      tma_load_3d(dq, &map_q, &s.bar_tma_b, 0, hg, r0);
+      tma_load_3d(dq + 8192, &map_q, &s.bar_tma_b, 64, hg, r0);
+      tma_load_3d(da, &map_a, &s.bar_tma_b, 0, h, r0);
+      tma_load_3d(da + 8192, &map_ag, &s.bar_tma_b, 0, h, r0);
+    }
+    if (part != 0) tma_load_3d(dpg, &map_pg, &s.bar_tma_b, 0, h, r0);
   };
   const long long n_units = static_cast<long long>(p.total_chunks) * p.H;
   if (tid == 0 && blockIdx.x < n_units) load_a(blockIdx.x);
   bool alive = true;
 
+  // raw gate values of a unit: threads 0-63 fetch them one unit ahead, so that the loads are not waited for
+  float gl_n = 0.f, gi_n = 0.f, bi_n = 0.f;
+  auto fetch_gates = [&](long long unit) {
+    const int chunk = static_cast<int>(unit / p.H), h = static_cast<int>(unit - static_cast<long long>(chunk) * p.H);
+    const ChunkPos cp = chunk_lookup(p.sa, chunk);
+    const size_t base = static_cast<size_t>(cp.tok0) * p.H + h;
+    gl_n = __ldg(p.g_cum + base + static_cast<size_t>(cp.len - 1) * p.H);
+    gi_n = gl_n;
+    bi_n = 0.f;
+    if (tid < cp.len) {
+      gi_n = __ldg(p.g_cum + base + static_cast<size_t>(tid) * p.H);
+      bi_n = __ldg(p.beta + base + static_cast<size_t>(tid) * p.H);
+    }
+  };
+  if (tid < kChunk && blockIdx.x < n_units) fetch_gates(blockIdx.x);
 #pragma unroll 1
   for (long long unit = blockIdx.x; unit < n_units && alive; unit += gridDim.x) {
     const int chunk = static_cast<int>(unit / p.H), h = static_cast<int>(unit - static_cast<long long>(chunk) * p.H);
@@ -194,15 +213,9 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     __syncthreads();  // the previous unit's shared-memory reads are complete
     BC_TS(0);
 
-    if (tid == 0 && unit == blockIdx.x) load_b(unit, b_kt, b_qt, b_at, b_pg);  // later units: requested a unit ahead
+    if (tid == 0 && unit == blockIdx.x) load_b(unit, 2, b_kt, b_qt, b_at, b_pg);  // later units: requested a unit ahead
     if (tid < kChunk) {
-      const size_t base = static_cast<size_t>(cp.tok0) * p.H + h;
-      const float gl = __ldg(p.g_cum + base + static_cast<size_t>(len - 1) * p.H);
-      float gi = gl, bi = 0.f;
-      if (tid < len) {
-        gi = __ldg(p.g_cum + base + static_cast<size_t>(tid) * p.H);
-        bi = __ldg(p.beta + base + static_cast<size_t>(tid) * p.H);
-      }
+      const float gl = gl_n, gi = gi_n, bi = bi_n;
       s.g[tid] = gi;
       s.gam[tid] = fast_exp(gi);
       s.rho[tid] = (tid < len) ? fast_exp(gl - gi) : 0.f;
@@ -218,7 +231,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     BC_TS(1);
 
     // ---- pre-pass on shared memory: zero the rows past the sequence end
-    //      and the scalar gamma_last * sum(dS o S0)
     if (len < kChunk) {
       unsigned char* tiles[4] = {b_kt, b_qt, s.wt, s.dot};
       const int nrows = kChunk - len;
@@ -234,22 +246,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
       }
       __syncthreads();
-    }
-    {
-      float acc = 0.f;
-#pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const uint32_t off = (it * kBcThreads + tid) * 16;
-        const uint4 a = *reinterpret_cast<const uint4*>(s.s0 + off);
-        const uint4 b = *reinterpret_cast<const uint4*>(s.ds + off);
-        const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
-        const uint32_t* bw = reinterpret_cast<const uint32_t*>(&b);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc += bf16_lo(aw[e]) * bf16_lo(bw[e]) + bf16_hi(aw[e]) * bf16_hi(bw[e]);
-      }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 16);
-      acc = half_warp_sum(acc);
-      if (lane == 0) atomicAdd(&s.dgl_s, acc * s.gam[kChunk - 1]);
     }
     fence_async_smem();
     __syncthreads();
@@ -284,6 +280,24 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
+    // while the first round runs: the scalar gamma_last * sum(dS o S0), and the next unit's gate values
+    {
+      float acc = 0.f;
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const uint32_t off = (it * kBcThreads + tid) * 16;
+        const uint4 a = *reinterpret_cast<const uint4*>(s.s0 + off);
+        const uint4 b = *reinterpret_cast<const uint4*>(s.ds + off);
+        const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
+        const uint32_t* bw = reinterpret_cast<const uint32_t*>(&b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc += bf16_lo(aw[e]) * bf16_lo(bw[e]) + bf16_hi(aw[e]) * bf16_hi(bw[e]);
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+      acc = half_warp_sum(acc);
+      if (lane == 0) atomicAdd(&s.dgl_s, acc * s.gam[kChunk - 1]);
+    }
+    if (tid < kChunk && unit + gridDim.x < n_units) fetch_gates(unit + gridDim.x);
     if (!mbar_wait(wc, &s.bar_mma, mma_phase, 2)) { alive = false; break; }
     mma_phase ^= 1;
     BC_TS(3);
@@ -577,9 +591,12 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                   id64_16_mnk, kk > 0);
       }
       umma_commit(&s.bar_mma);
-      // the tiles that only rounds one to three read are dead: request them for this CTA's next unit (the issue
-      // overlaps the products just queued)
-      if (warp == 0 && unit + gridDim.x < n_units) load_a(unit + gridDim.x);
+      // Tiles that were last read in round three are dead; two of the issuing threads request this CTA's next unit
+      // there: S0, dS, V, dO in place, and K, Q, A, A_g into V', dVg and dV'.
+      if (unit + gridDim.x < n_units) {
+        if (warp == 2) load_a(unit + gridDim.x);
+        if (warp == 3) load_b(unit + gridDim.x, 0, b_vp, b_dvg, b_dvp, b_t12);
+      }
     }
     __syncwarp();
     if (!mbar_wait(wc, &s.bar_mma, mma_phase, 5)) { alive = false; break; }
@@ -651,9 +668,8 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                   id64_64_kk, kk > 0);
       }
       umma_commit(&s.bar_mma);
-      // V', dVg, dV' and T are dead (their last readers were rounds three and four): the K, Q, A, A_g and P_g tiles
-      // of this CTA's next unit go there
-      if (warp == 0 && unit + gridDim.x < n_units) load_b(unit + gridDim.x, b_vp, b_dvg, b_dvp, b_t12);
+      // T was last read in round four: the next unit's P_g goes there
+      if (warp == 3 && unit + gridDim.x < n_units) load_b(unit + gridDim.x, 1, b_vp, b_dvg, b_dvp, b_t12);
     }
     __syncwarp();
     if (!mbar_wait(wc, &s.bar_mma, mma_phase, 6)) { alive = false; break; }

@@ -47,6 +47,17 @@ int make_tmap_rows_heads_dim(CUtensorMap* out, const void* base, uint64_t rows, 
     set_error("tensor base address must be 16-byte aligned for TMA");
     return FQ_ERR_INVALID;
   }
+  // The encoder is a driver call and needs a current context.  A host thread that has only selected a device
+  // (e.g. an autograd worker thread whose first CUDA work is this call) has none yet: a runtime call binds the
+  // device's primary context to the thread.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    if (cudaFree(nullptr) != cudaSuccess) {
+      set_error("no usable CUDA context on this thread: %s", cudaGetErrorString(cudaGetLastError()));
+      return FQ_ERR_CUDA;
+    }
+    ctx_bound = true;
+  }
   cuuint64_t gdim[3] = {dim, heads, rows};
   cuuint64_t gstride[2] = {dim * 2, heads * dim * 2};  // bytes, for dims 1 and 2
   cuuint32_t box[3] = {box_dim, 1, box_rows};

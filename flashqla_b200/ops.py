@@ -14,6 +14,9 @@ from .planner import plan_cp
 _DEBUG_STATUS = os.environ.get("FLASHQLA_CHECK_STATUS", "0") == "1"
 # testing hook: force a piece length (in chunks) for the context-parallel split
 _FORCE_PIECE_CHUNKS = int(os.environ["FLASHQLA_PIECE_CHUNKS"]) if "FLASHQLA_PIECE_CHUNKS" in os.environ else None
+# The autograd function keeps the gated operand tiles A_g and P_g (2 x [B,T,H,64] bf16) for the backward, which then
+# skips the pass that rebuilds them; set FLASHQLA_RECOMPUTE_TILES=1 to keep only A, like the reference does.
+_RECOMPUTE_TILES = os.environ.get("FLASHQLA_RECOMPUTE_TILES", "0") == "1"
 
 
 def l2norm(x: torch.Tensor, dim: int = -1, eps: float = 1e-6) -> torch.Tensor:
@@ -24,7 +27,7 @@ def l2norm(x: torch.Tensor, dim: int = -1, eps: float = 1e-6) -> torch.Tensor:
 
 
 def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None, cu_seqlens=None,
-                               output_final_state=True, output_h=False, auto_cp=True):
+                               output_final_state=True, output_h=False, auto_cp=True, _return_tiles=False):
     """Forward pipeline (chunk/__init__.py:17-67): cumsum -> K K^T + solve (+ gated tiles) -> fused recurrence.
 
     Returns ``(g_cumsum, A, o, h, final_state)``; ``A`` is the gate-free inverse (opaque, only
@@ -50,27 +53,35 @@ def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None,
         kernels.check_status(status, "fq_gdr_fwd")
     if h is not None:
         h = h.transpose(-1, -2)  # stored [.., V, K] by the kernel; the interface is [.., K, V]
+    if _return_tiles:
+        return g_cum, A, o, h, final_state, (Ag, Pg)
     return g_cum, A, o, h, final_state
 
 
-def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, initial_state=None, cu_seqlens=None):
+def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, initial_state=None, cu_seqlens=None,
+                               _gated_tiles=None):
     """Backward pipeline (chunk/__init__.py:70-113).  ``g`` is the cumsum returned by the forward,
     ``A`` the tensor returned by the forward.  Returns ``(dq, dk, dv, db, dg, dh0)``."""
     from . import bwd  # the backward kernels live in their own module
-    return bwd.chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht, scale, initial_state, cu_seqlens)
+    return bwd.chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht, scale, initial_state, cu_seqlens,
+                                          gated_tiles=_gated_tiles)
 
 
 class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
-    """Autograd glue (chunk/__init__.py:116-180): saves (q, k, v, g_cumsum, beta, A, h0, cu_seqlens);
-    neither o nor the per-chunk states are kept."""
+    """Autograd glue (chunk/__init__.py:116-180): saves (q, k, v, g_cumsum, beta, A, h0, cu_seqlens) and, unless
+    FLASHQLA_RECOMPUTE_TILES=1, the gated tiles A_g and P_g; neither o nor the per-chunk states are kept."""
 
     @staticmethod
     @torch.amp.custom_fwd(device_type="cuda")
     def forward(ctx, q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None):
-        g_cum, A, o, _, final_state = chunk_gated_delta_rule_fwd(
+        g_cum, A, o, _, final_state, tiles = chunk_gated_delta_rule_fwd(
             q=q, k=k, v=v, g=g, beta=beta, scale=scale, initial_state=initial_state,
-            output_final_state=output_final_state, output_h=False, cu_seqlens=cu_seqlens)
-        ctx.save_for_backward(q, k, v, g_cum, beta, A, initial_state, cu_seqlens)
+            output_final_state=output_final_state, output_h=False, cu_seqlens=cu_seqlens, _return_tiles=True)
+        ctx.keep_tiles = not _RECOMPUTE_TILES
+        if ctx.keep_tiles:
+            ctx.save_for_backward(q, k, v, g_cum, beta, A, initial_state, cu_seqlens, *tiles)
+        else:
+            ctx.save_for_backward(q, k, v, g_cum, beta, A, initial_state, cu_seqlens)
         ctx.scale = scale
         ctx.g_dtype = g.dtype
         ctx.beta_dtype = beta.dtype
@@ -79,10 +90,11 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     @staticmethod
     @torch.amp.custom_bwd(device_type="cuda")
     def backward(ctx, do, dht):
-        q, k, v, g_cum, beta, A, initial_state, cu_seqlens = ctx.saved_tensors
+        q, k, v, g_cum, beta, A, initial_state, cu_seqlens = ctx.saved_tensors[:8]
+        tiles = tuple(ctx.saved_tensors[8:10]) if ctx.keep_tiles else None
         dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(
             q=q, k=k, v=v, g=g_cum, beta=beta, A=A, do=do, dht=dht, scale=ctx.scale,
-            initial_state=initial_state, cu_seqlens=cu_seqlens)
+            initial_state=initial_state, cu_seqlens=cu_seqlens, _gated_tiles=tiles)
         return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dg.to(ctx.g_dtype), db.to(ctx.beta_dtype),
                 None, dh0, None, None)
 

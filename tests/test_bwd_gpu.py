@@ -83,8 +83,12 @@ def test_backward_vs_reference_fixture(name):
     assert all(e < TOL for e in errs.values()), str({k_: f'{v_:.2e}' for k_, v_ in errs.items()})
 
 
-def test_autograd_entry():
+@pytest.mark.parametrize("recompute_tiles", [False, True])
+def test_autograd_entry(recompute_tiles, monkeypatch):
+    """Public differentiable entry; with and without keeping the gated tiles A_g / P_g for the backward."""
     import flash_qla
+    from flashqla_b200 import ops
+    monkeypatch.setattr(ops, "_RECOMPUTE_TILES", recompute_tiles)
     q, k, v, g, beta, h0, do, dht = make_inputs(5, 2, 192, 2, 4)
     dev = "cuda"
     leaves = [x.to(dev).requires_grad_() for x in (q, k, v, g, beta, h0)]
