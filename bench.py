@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the chunked gated-delta-rule (GDN) hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c5|c2s|c3s]
 
 One "step" = one pass of the hot path over one synthetic batch.  The default workload is the
 configuration the headline metric is quoted on: single-GPU forward prefill,
@@ -41,10 +41,16 @@ WORKLOADS = {
                desc="fwd+bwd B=1 T=1048576 Hq=Hv=8 K=V=128 bf16, ONE sequence split contiguously over the GPUs"),
     "c3": dict(B=4, T=8192, Hq=16, Hv=32, bwd=True,
                desc="fwd+bwd B=4 T=8192 Hq=16 Hv=32 K=V=128 bf16, h0=0.1 randn, dht=0.01 randn"),
+    "c3s": dict(B=2, T=8192, Hq=8, Hv=16, bwd=True,
+                desc="(profiling case) fwd+bwd B=2 T=8192 Hq=8 Hv=16 K=V=128 bf16"),
 }
 # algorithmic HBM bytes per (chunk, V-head) of the fused forward kernel at Hq == Hv:
 # q, k, v read + o write (4 x 16 KiB) + g, beta (2 x 256 B)
 FWD_BYTES_PER_UNIT = 4 * 16384 + 512
+# DRAM traffic of gdr_fwd_kernel per (chunk, V-head) from one ncu capture of the smaller case c2s (Hq == Hv):
+# dram__bytes_read.sum + dram__bytes_write.sum = 665,837,312 B over 8192 units (profiles/forward_kernels_*.md);
+# traffic grows in proportion to the units, so a full launch is reported as units x this figure
+FWD_TRAFFIC_PER_UNIT_NCU = 665837312 / 8192
 
 
 def l2norm(x):
@@ -319,26 +325,59 @@ def main():
             kernel_ms[name] = kernel_ms.get(name, 0.0) + e0.elapsed_time(e1) / len(stamps)
     fwd_ms = kernel_ms["gdr_fwd"]
 
-    # ---- end to end through the public operator with host buffers (pinned), copies inside the timed region
-    def e2e_step():
-        dd = {k_: host[k_].to(dev, non_blocking=True) for k_ in host}
-        if not w["bwd"]:
-            _, _, o, _, fs = fq.chunk_gated_delta_rule_fwd(dd["q"], dd["k"], dd["v"], dd["g"], dd["beta"], scale,
-                                                           dd["h0"], None, True, False, True)
-            return [o.to("cpu", non_blocking=True), fs.to("cpu", non_blocking=True)]
-        leaves = [dd[k_].requires_grad_() for k_ in ("q", "k", "v", "g", "beta", "h0")]
-        o, fs = fq.chunk_gated_delta_rule(leaves[0], leaves[1], leaves[2], leaves[3], leaves[4], scale=scale,
-                                          initial_state=leaves[5], output_final_state=True)
-        torch.autograd.backward([o, fs], [dd["do"], dd["dht"]])
-        return [x.grad.to("cpu", non_blocking=True) for x in leaves] + [o.detach().to("cpu", non_blocking=True)]
+    # ---- end to end through the public operator with host buffers (pinned), copies inside the timed region.
+    # Steady-state pipeline, as a serving / training loop would run it: the inputs of a step go host -> device on
+    # one copy stream into one of two device buffer sets, the operator runs on the compute stream, and the results
+    # go device -> pinned host memory on a second copy stream, so the upload of step i+1 overlaps the download of
+    # step i (PCIe is full duplex).  Every step's copies are inside the timed region; one synchronise at the end.
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    main = torch.cuda.current_stream(dev)
+    dev_in = [{k_: torch.empty(host[k_].shape, dtype=host[k_].dtype, device=dev) for k_ in host} for _ in range(2)]
+    in_free = [None, None]
+    out_done = [None, None]
+    host_out = [None, None]
 
-    for _ in range(2):
-        e2e_step()
+    def e2e_step(i):
+        slot = i & 1
+        buf = dev_in[slot]
+        with torch.cuda.stream(s_in):
+            if in_free[slot] is not None:
+                s_in.wait_event(in_free[slot])  # the step that last used this buffer set has finished computing
+            for k_ in host:
+                buf[k_].copy_(host[k_], non_blocking=True)
+            ev_in = s_in.record_event()
+        main.wait_event(ev_in)
+        if not w["bwd"]:
+            _, _, o, _, fs = fq.chunk_gated_delta_rule_fwd(buf["q"], buf["k"], buf["v"], buf["g"], buf["beta"], scale,
+                                                           buf["h0"], None, True, False, True)
+            outs = [o, fs]
+        else:
+            leaves = [buf[k_].detach().requires_grad_() for k_ in ("q", "k", "v", "g", "beta", "h0")]
+            o, fs = fq.chunk_gated_delta_rule(leaves[0], leaves[1], leaves[2], leaves[3], leaves[4], scale=scale,
+                                              initial_state=leaves[5], output_final_state=True)
+            torch.autograd.backward([o, fs], [buf["do"], buf["dht"]])
+            outs = [x.grad for x in leaves] + [o.detach()]
+        in_free[slot] = main.record_event()
+        if host_out[slot] is None:
+            host_out[slot] = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in outs]
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(in_free[slot])
+            if out_done[slot] is not None:
+                out_done[slot].synchronize()  # the pinned result buffers of this slot were consumed two steps ago
+            for dst, src in zip(host_out[slot], outs):
+                dst.copy_(src, non_blocking=True)
+                src.record_stream(s_out)
+            out_done[slot] = s_out.record_event()
+
+    for i in range(2):
+        e2e_step(i)
+    torch.cuda.synchronize()
     barrier()
-    n_e2e = max(3, min(args.steps, 5))
+    n_e2e = max(4, min(args.steps, 10))
     w0 = time.perf_counter()
-    for _ in range(n_e2e):
-        e2e_step()
+    for i in range(n_e2e):
+        e2e_step(i)
+    torch.cuda.synchronize()
     barrier()
     e2e_ms = 1e3 * (time.perf_counter() - w0) / n_e2e
     h2d = sum(host[k_].numel() * host[k_].element_size() for k_ in host)
@@ -369,7 +408,8 @@ def main():
             "roofline": {"kernel": "gdr_fwd_kernel", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                          "peak_source": "measured copy bandwidth (MEASURED_PEAKS.json)" if how == "measured" else "fallback",
-                         "kernel_ms": fwd_ms, "algorithmic_bytes": alg_bytes, "traffic": None},
+                         "kernel_ms": fwd_ms, "algorithmic_bytes": alg_bytes,
+                         "traffic": (units * FWD_TRAFFIC_PER_UNIT_NCU if Hq == Hv else None)},
             "clocks": clocks,
             "e2e": {"value": world * tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
