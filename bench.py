@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the chunked gated-delta-rule (GDN) hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c5|c2s|c3s]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c5|decode|c2s|c3s]
 
 One "step" = one pass of the hot path over one synthetic batch.  The default workload is the
 configuration the headline metric is quoted on: single-GPU forward prefill,
@@ -43,6 +43,10 @@ WORKLOADS = {
                desc="fwd+bwd B=4 T=8192 Hq=16 Hv=32 K=V=128 bf16, h0=0.1 randn, dht=0.01 randn"),
     "c3s": dict(B=2, T=8192, Hq=8, Hv=16, bwd=True,
                 desc="(profiling case) fwd+bwd B=2 T=8192 Hq=8 Hv=16 K=V=128 bf16"),
+    # decode side of the path: one new token for each of N sequences, state resident on the device
+    "decode": dict(B=256, T=1, Hq=64, Hv=64, bwd=False, decode=True, tokens_per_step=64,
+                   desc="decode: 64 consecutive tokens for each of 256 sequences (one kernel call per token), Hq=Hv=64 "
+                        "K=V=128, fp32 state 1 GiB resident in HBM"),
 }
 # algorithmic HBM bytes per (chunk, V-head) of the fused forward kernel at Hq == Hv:
 # q, k, v read + o write (4 x 16 KiB) + g, beta (2 x 256 B)
@@ -67,7 +71,7 @@ def make_inputs(w, device, seed=0, pin=False):
     host = dict(
         q=l2norm(rn(B, T, Hq, 128)).bfloat16(), k=l2norm(rn(B, T, Hq, 128)).bfloat16(), v=rn(B, T, Hv, 128).bfloat16(),
         g=torch.nn.functional.logsigmoid(rn(B, T, Hv)), beta=rn(B, T, Hv).sigmoid(),
-        h0=(0.1 * rn(B, Hv, 128, 128)) if w["bwd"] else torch.zeros(B, Hv, 128, 128))
+        h0=(0.1 * rn(B, Hv, 128, 128)) if (w["bwd"] or w.get("decode")) else torch.zeros(B, Hv, 128, 128))
     if w["bwd"]:
         host["do"] = rn(B, T, Hv, 128).bfloat16()
         host["dht"] = 0.01 * rn(B, Hv, 128, 128)
@@ -228,6 +232,110 @@ def metric_name(w):
     return "GDN fwd+bwd tokens/s per B200" if w["bwd"] else "GDN fwd tokens/s per B200"
 
 
+def run_decode(args, w, rank, world, local):
+    """One recurrent step for N sequences per GPU (weak scaling: every rank has its own N sequences)."""
+    import torch.distributed as dist
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    import flashqla_b200 as fq
+    host, d = make_inputs(w, dev, seed=rank, pin=True)
+    N, Hq, Hv = w["B"], w["Hq"], w["Hv"]
+    scale = 128 ** -0.5
+    state = d["h0"].clone()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    n_tok = w["tokens_per_step"]
+
+    def step():
+        for _ in range(n_tok):
+            fq.fused_recurrent_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["beta"], scale=scale,
+                                                initial_state=state, inplace_state=True)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for _ in range(args.steps):
+        step()
+    t1.record()
+    barrier()
+    ms_step = t0.elapsed_time(t1) / args.steps
+
+    # end to end: the new token's q, k, v, g, beta come from pinned host memory, o goes back; the state stays on the GPU
+    small = {k_: host[k_] for k_ in ("q", "k", "v", "g", "beta")}
+    o_host = torch.empty(N, 1, Hv, 128, dtype=torch.bfloat16, pin_memory=True)
+
+    def e2e_step():
+        for _ in range(n_tok):
+            dd = {k_: small[k_].to(dev, non_blocking=True) for k_ in small}
+            o, _ = fq.fused_recurrent_gated_delta_rule(dd["q"], dd["k"], dd["v"], dd["g"], dd["beta"], scale=scale,
+                                                       initial_state=state, inplace_state=True)
+            o_host.copy_(o, non_blocking=True)
+            torch.cuda.synchronize()  # a decode loop needs the token's output before it can form the next input
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    n_e2e = max(3, min(args.steps, 10))
+    w0 = time.perf_counter()
+    for _ in range(n_e2e):
+        e2e_step()
+    barrier()
+    e2e_ms = 1e3 * (time.perf_counter() - w0) / n_e2e
+    clocks = sampler.stop() if sampler else None
+    ms = torch.tensor([ms_step, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_step, e2e_ms = (float(x) for x in ms.tolist())
+    if rank == 0:
+        peaks, how = measured_peaks()
+        # state read + write (2 x 64 KiB per head) + q, k, v, o, g, beta of the token
+        alg_bytes = N * Hv * (2 * 128 * 128 * 4 + 2 * 256 + 8) + N * Hq * 2 * 256  # per kernel launch (one token)
+        kernel_ms = ms_step / n_tok
+        achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
+        h2d = sum(small[k_].numel() * small[k_].element_size() for k_ in small)
+        line = {
+            "metric": "GDN decode tokens/s per B200", "value": world * N * n_tok / (ms_step * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": w["desc"], "l2": "the 1 GiB state exceeds the 126 MB L2; no flush needed"},
+            "gpu_launches": n_tok,
+            "roofline": {"kernel": "gdr_recurrent_kernel", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                         "peak_source": "measured copy bandwidth (MEASURED_PEAKS.json)" if how == "measured" else "fallback",
+                         "kernel_ms": kernel_ms, "algorithmic_bytes": alg_bytes, "traffic": None},
+            "clocks": clocks,
+            "e2e": {"value": world * N * n_tok / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": h2d * n_tok, "d2h_bytes_per_step": o_host.numel() * 2 * n_tok},
+        }
+        if not args.no_cpu_baseline:
+            sys.path.insert(0, ROOT)
+            from oracle import gdr_oracle as orc
+            threads = os.cpu_count() or 1
+            torch.set_num_threads(threads)
+            ns = 16
+            t_0 = time.perf_counter()
+            orc.gdr_recurrent(host["q"][:ns].float(), host["k"][:ns].float(), host["v"][:ns].float(), host["g"][:ns],
+                              host["beta"][:ns], scale, host["h0"][:ns], dtype=torch.float32)
+            dt = time.perf_counter() - t_0
+            line["cpu_baseline"] = {"value": ns / dt, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                    "sample": f"token-level oracle, {ns} of the {N} sequences, fp32", "seconds": dt}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -253,6 +361,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
     if w.get("seq_parallel"):
         run_sequence_parallel(args, w, rank, world, local)
+        return
+    if w.get("decode"):
+        run_decode(args, w, rank, world, local)
         return
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)

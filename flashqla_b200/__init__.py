@@ -11,4 +11,7 @@ from .ops import (  # noqa: E402
     chunk_gated_delta_rule_fwd,
 )
 
-__all__ = ["chunk_gated_delta_rule_fwd", "chunk_gated_delta_rule_bwd", "chunk_gated_delta_rule"]
+from .decode import fused_recurrent_gated_delta_rule  # noqa: E402
+
+__all__ = ["chunk_gated_delta_rule_fwd", "chunk_gated_delta_rule_bwd", "chunk_gated_delta_rule",
+           "fused_recurrent_gated_delta_rule"]

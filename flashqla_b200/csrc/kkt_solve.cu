@@ -52,6 +52,13 @@ __device__ __forceinline__ void mma_tf32_1688(float (&c)[4], const uint32_t (&a)
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
+// Four 8x8 bf16 matrices from shared memory in MMA fragment layout; lane l supplies the address of row (l & 7) of
+// matrix (l >> 3).
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(smem_row)));
+}
 // c += a * b with a, b given in fp32 and rounded to TF32.
 __device__ __forceinline__ void mma_tf32(float (&c)[4], const float (&a)[4], const float (&b)[2]) {
   uint32_t ah[4], bh[2];
@@ -115,29 +122,23 @@ __global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* 
       qk[j][0] = qk[j][1] = qk[j][2] = qk[j][3] = 0.f;
       acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     }
+    // fragment loads with ldmatrix: lane l addresses row (l & 7) + 8 * ((l >> 3) & 1) of a 16-row block and the
+    // 8-column half (l >> 4) for the A operand; for the B operand one x4 load covers two 8-row tiles of K
+    const int a_row = m0 + (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
+    const int b_row = (lane & 7) + 8 * (lane >> 4), b_col = 8 * ((lane >> 3) & 1);
 #pragma unroll
     for (int k0 = 0; k0 < kDim; k0 += 16) {
       uint32_t aq[4] = {0, 0, 0, 0}, ak[4] = {0, 0, 0, 0};
-      if (do_qk) {
-        aq[0] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g) * kKLd + k0 + 2 * t]);
-        aq[1] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g + 8) * kKLd + k0 + 2 * t]);
-        aq[2] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g) * kKLd + k0 + 8 + 2 * t]);
-        aq[3] = *reinterpret_cast<const uint32_t*>(&s.q[(m0 + g + 8) * kKLd + k0 + 8 + 2 * t]);
-      }
-      if (do_kk) {
-        ak[0] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g) * kKLd + k0 + 2 * t]);
-        ak[1] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g + 8) * kKLd + k0 + 2 * t]);
-        ak[2] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g) * kKLd + k0 + 8 + 2 * t]);
-        ak[3] = *reinterpret_cast<const uint32_t*>(&s.k[(m0 + g + 8) * kKLd + k0 + 8 + 2 * t]);
-      }
+      if (do_qk) ldmatrix_x4(aq, &s.q[a_row * kKLd + k0 + a_col]);
+      if (do_kk) ldmatrix_x4(ak, &s.k[a_row * kKLd + k0 + a_col]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (j < ntiles) {
-          uint32_t bfr[2];
-          bfr[0] = *reinterpret_cast<const uint32_t*>(&s.k[(j * 8 + g) * kKLd + k0 + 2 * t]);
-          bfr[1] = *reinterpret_cast<const uint32_t*>(&s.k[(j * 8 + g) * kKLd + k0 + 8 + 2 * t]);
-          if (do_qk) mma_bf16_16816(qk[j], aq, bfr);
-          if (do_kk) mma_bf16_16816(acc[j], ak, bfr);
+      for (int j = 0; j < 8; j += 2) {
+        if (j < ntiles) {  // ntiles is even
+          uint32_t b4[4];
+          ldmatrix_x4(b4, &s.k[(j * 8 + b_row) * kKLd + k0 + b_col]);
+          const uint32_t b0[2] = {b4[0], b4[1]}, b1[2] = {b4[2], b4[3]};
+          if (do_qk) { mma_bf16_16816(qk[j], aq, b0); mma_bf16_16816(qk[j + 1], aq, b1); }
+          if (do_kk) { mma_bf16_16816(acc[j], ak, b0); mma_bf16_16816(acc[j + 1], ak, b1); }
         }
       }
     }

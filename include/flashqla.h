@@ -178,6 +178,19 @@ FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void* v, const v
 FQ_API int fq_group_reduce(const void* in, void* out, long long rows, int H, int Hg, void* stream);
 
 /*
+ * Token-by-token recurrence (decode / short continuations): consumes the final state written by fq_gdr_fwd
+ * (flash_qla/ops/gated_delta_rule/chunk/hopper/fused_fwd.py:214-221 writes it, :173-179 reads it back as
+ * initial_state) and advances it by T tokens per sequence.  The reference has no such operator (prefill and
+ * training only); the arithmetic is the token-level form of the same recurrence:
+ *   S <- e^g S;  v' = beta (v - S^T k);  S <- S + k v'^T;  o = scale S^T q.
+ *   q, k [N,T,Hg,128] bf16; v, o [N,T,H,128] bf16; g (log gate, NOT cumulated), beta [N,T,H] fp32;
+ *   state_in [N,H,128,128] fp32 or NULL (zero); state_out [N,H,128,128] fp32 or NULL; may alias state_in.
+ */
+FQ_API int fq_gdr_recurrent(const void* q, const void* k, const void* v, const float* g, const float* beta,
+                            const float* state_in, float* state_out, void* o, int N, int T, int H, int Hg, float scale,
+                            void* stream);
+
+/*
  * Allocation-free variant of fq_gdr_bwd_chunk + fq_group_reduce for grouped heads; it has no
  * counterpart in the reference.  Same inputs as fq_gdr_bwd_chunk, but dq and dk are the final
  * [B,T,Hg,128] gradients: the per-V-head partial results that the regular path keeps in two

@@ -108,3 +108,14 @@ def test_context_parallel_planner():
     cp2 = planner.plan_cp(planner.plan_dense(2, 1024), 2, 1024, 1, 148, "cpu", piece_chunks=4)
     assert cp2.cu_seqlens.tolist() == [0, 256, 512, 768, 1024, 1280, 1536, 1792, 2048]
     assert cp2.seq_index.tolist() == [0, 0, 0, 0, 1, 1, 1, 1]
+
+
+def test_recurrent_operator_refuses_cpu_tensors():
+    """The decode-step operator has no CPU path either."""
+    import flashqla_b200 as fq
+    from flashqla_b200 import _lib
+    q = torch.zeros(1, 1, 1, 128, dtype=torch.bfloat16)
+    g = torch.zeros(1, 1, 1)
+    with pytest.raises(_lib.FlashQLAError):
+        fq.fused_recurrent_gated_delta_rule(q, q, q, g, g)
+
