@@ -1,5 +1,5 @@
 // Shared device helpers for the sm_100a kernels: mbarrier with bounded waits, TMA tile
-// copies (never multicast), tcgen05 (TMEM allocation, UMMA issue, TMEM load/store) and the
+// copies, tcgen05 (TMEM allocation, UMMA issue, TMEM load/store) and the
 // shared-memory operand descriptors.
 #pragma once
 #include <cuda.h>
