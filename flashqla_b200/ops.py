@@ -19,11 +19,38 @@ _FORCE_PIECE_CHUNKS = int(os.environ["FLASHQLA_PIECE_CHUNKS"]) if "FLASHQLA_PIEC
 _RECOMPUTE_TILES = os.environ.get("FLASHQLA_RECOMPUTE_TILES", "0") == "1"
 
 
+class _L2NormFunction(torch.autograd.Function):
+    """x * rsqrt(sum(x^2) + eps) over the last dim (128) with the fused kernels of csrc/l2norm.cu."""
+
+    @staticmethod
+    def forward(ctx, x, eps):
+        x = x.contiguous()
+        y = torch.empty_like(x)
+        rc = _lib.load().fq_l2norm_fwd(x.data_ptr(), y.data_ptr(), x.numel() // x.shape[-1], float(eps), kernels._stream())
+        _lib.check(rc, "fq_l2norm_fwd")
+        ctx.save_for_backward(x)
+        ctx.eps = eps
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        dy = dy.contiguous().to(x.dtype)
+        dx = torch.empty_like(x)
+        rc = _lib.load().fq_l2norm_bwd(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), x.numel() // x.shape[-1],
+                                       float(ctx.eps), kernels._stream())
+        _lib.check(rc, "fq_l2norm_bwd")
+        return dx, None
+
+
 def l2norm(x: torch.Tensor, dim: int = -1, eps: float = 1e-6) -> torch.Tensor:
-    """x * rsqrt(sum(x^2) + eps) over the last dim (flash_qla/utils/math.py:7-21)."""
+    """x * rsqrt(sum(x^2) + eps) over the last dim (flash_qla/utils/math.py:7-21), differentiable.
+    One fused pass over HBM per direction; bf16 CUDA tensors with a last dim of 128 only."""
     assert dim == -1
-    xf = x.float()
-    return (xf * torch.rsqrt((xf * xf).sum(-1, keepdim=True) + eps)).to(x.dtype)
+    kernels._require_cuda(x)
+    if x.dtype != torch.bfloat16 or x.shape[-1] != 128:
+        raise _lib.FlashQLAError("l2norm: bfloat16 tensors with a last dimension of 128 only")
+    return _L2NormFunction.apply(x, eps)
 
 
 def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None, cu_seqlens=None,

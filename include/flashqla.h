@@ -178,6 +178,14 @@ FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void* v, const v
 FQ_API int fq_group_reduce(const void* in, void* out, long long rows, int H, int Hg, void* stream);
 
 /*
+ * y = x * rsqrt(sum(x^2 over the last dim) + eps) for rows of 128 bf16 values, and its backward
+ * dx = r dy - x r^3 (x . dy).  Replaces l2norm, flash_qla/utils/math.py:7-21 (a torch.compile'd elementwise
+ * function there, applied to q and k when use_qk_l2norm_in_kernel is set, chunk/__init__.py:221-223).
+ */
+FQ_API int fq_l2norm_fwd(const void* x, void* y, long long rows, float eps, void* stream);
+FQ_API int fq_l2norm_bwd(const void* x, const void* dy, void* dx, long long rows, float eps, void* stream);
+
+/*
  * Token-by-token recurrence (decode / short continuations): consumes the final state written by fq_gdr_fwd
  * (flash_qla/ops/gated_delta_rule/chunk/hopper/fused_fwd.py:214-221 writes it, :173-179 reads it back as
  * initial_state) and advances it by T tokens per sequence.  The reference has no such operator (prefill and
