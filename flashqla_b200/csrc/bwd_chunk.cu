@@ -33,7 +33,7 @@ __device__ long long g_trace_bc[32];
 #define BC_TS(id) do { } while (0)
 #endif
 
-constexpr int kBcThreads = 256;
+constexpr int kBcThreads = 512;
 constexpr uint32_t kBcLoadBytesA = 2 * 32768 + 2 * 16384;  // S0, dS, V, dO: requested a unit ahead
 constexpr uint32_t kBcLoadBytesB = 2 * 16384 + 3 * 8192;  // K, Q, A, A_g, P_g: requested at the start of the unit
 
@@ -107,7 +107,9 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   BwdChunkSmem& s = *reinterpret_cast<BwdChunkSmem*>(
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int q4 = warp & 3, hf = warp >> 2;
+  // warp w: TMEM lane quarter q4 = w & 3 (token rows 16 q4 .. +15 in lanes 0-15), column quarter cq = w >> 2:
+  // 32 columns of a 128-column accumulator (half hf, piece pc), 16 columns of a 64-column one
+  const int q4 = warp & 3, cq = warp >> 2, hf = cq >> 1, pc = cq & 1;
   const bool active = lane < 16;
   const int row = active ? (16 * q4 + lane) : 0;
   const uint32_t lane_base = static_cast<uint32_t>(q4) * 32;
@@ -284,7 +286,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     {
       float acc = 0.f;
 #pragma unroll
-      for (int it = 0; it < 8; ++it) {
+      for (int it = 0; it < 32768 / (16 * kBcThreads); ++it) {
         const uint32_t off = (it * kBcThreads + tid) * 16;
         const uint4 a = *reinterpret_cast<const uint4*>(s.s0 + off);
         const uint4 b = *reinterpret_cast<const uint4*>(s.ds + off);
@@ -304,8 +306,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     tc_fence_after();
     {
       // W = V - gamma o U (in place over V);  dV' = rho o D1 + D2
-#pragma unroll 1
-      for (int pc = 0; pc < 2; ++pc) {
+      {
         uint32_t u[32];
         tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 64 * hf + 32 * pc), u);
         tmem_wait_ld();
@@ -341,8 +342,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
       // accQ *= scale * gamma (written back); dg += rowsum(Q o accQ)
       float part = 0.f;
-#pragma unroll 1
-      for (int pc = 0; pc < 2; ++pc) {
+      {
         uint32_t r[32];
         tmem_ld32(tmem_addr(tm, lane_base, kBcColQ + 64 * hf + 32 * pc), r);
         tmem_wait_ld();
@@ -392,8 +392,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     tc_fence_after();
     {
       __nv_bfloat16* dvdst = p.dv + (static_cast<size_t>(cp.tok0 + row) * p.H + h) * kDim + 64 * hf;
-#pragma unroll 1
-      for (int pc = 0; pc < 2; ++pc) {
+      {
         uint32_t r[32], w2[32];
         tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 64 * hf + 32 * pc), r);
         tmem_ld32(tmem_addr(tm, lane_base, kBcColD1 + 64 * hf + 32 * pc), w2);
@@ -460,8 +459,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     {
       // dg += rowsum(K o accK); then accK += rho o K1 ; kk = rowsum(K o rho K1)
       float kkp = 0.f, kap = 0.f;
-#pragma unroll 1
-      for (int pc = 0; pc < 2; ++pc) {
+      {
         uint32_t r[32], a2[32];
         tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 64 * hf + 32 * pc), r);
         tmem_ld32(tmem_addr(tm, lane_base, kBcColK + 64 * hf + 32 * pc), a2);
@@ -485,28 +483,27 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (active) atomicAdd(&s.dg_s[row], kap - kkp);
       const float kks = half_warp_sum(kkp);
       if (lane == 0) atomicAdd(&s.dgl_s, kks);
-      // dPg and dAg -> dP, dA, T, T3 tiles and the row sums of T.  Only lanes 0-15 hold accumulator rows
-      // (M = 64), so each of them hands half of its 32 columns to lane + 16: all 32 lanes work on 16 columns.
-      uint32_t r1[32], r2[32];
-      tmem_ld32(tmem_addr(tm, lane_base, kBcColQK + 32 * hf), r1);
-      tmem_ld32(tmem_addr(tm, lane_base, kBcColX + 32 * hf), r2);
+      // dPg and dAg -> dP, dA, T, T3 tiles and the row sums of T: this warp's 16 columns.  Only lanes 0-15 hold
+      // accumulator rows (M = 64), so each of them hands half of its columns to lane + 16: all 32 lanes work on
+      // 8 columns (one 16-byte piece of the tile row).
+      uint32_t r1[16], r2[16];
+      tmem_ld16(tmem_addr(tm, lane_base, kBcColQK + 16 * cq), r1);
+      tmem_ld16(tmem_addr(tm, lane_base, kBcColX + 16 * cq), r2);
       tmem_wait_ld();
-      const int up = lane >> 4;                 // 0: columns 0-15 of the piece, 1: columns 16-31
+      const int up = lane >> 4;                 // 0: columns 0-7 of the piece, 1: columns 8-15
       const int row2 = 16 * q4 + (lane & 15);   // row served by this lane
       const float g_r2 = s.g[row2];
-      float a1[16], a2[16];
+      float a1[8], a2[8];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const uint32_t h1 = __shfl_sync(0xffffffffu, r1[16 + i], lane & 15);
-        const uint32_t h2 = __shfl_sync(0xffffffffu, r2[16 + i], lane & 15);
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t h1 = __shfl_sync(0xffffffffu, r1[8 + i], lane & 15);
+        const uint32_t h2 = __shfl_sync(0xffffffffu, r2[8 + i], lane & 15);
         a1[i] = __uint_as_float(up ? h1 : r1[i]);
         a2[i] = __uint_as_float(up ? h2 : r2[i]);
       }
       float rows = 0.f;
-#pragma unroll
-      for (int c2 = 0; c2 < 2; ++c2) {
-        const int ch = 2 * up + c2;  // 16-byte piece of the row's 64-byte half
-        const uint32_t so = sw128(row2, (4 * hf + ch) * 16);
+      {
+        const uint32_t so = sw128(row2, (2 * cq + up) * 16);
         const uint4 pgv = *reinterpret_cast<const uint4*>(b_pg + so);
         const uint4 av = *reinterpret_cast<const uint4*>(b_at + so);
         const uint32_t* pw = reinterpret_cast<const uint32_t*>(&pgv);
@@ -516,7 +513,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         uint32_t* daw = reinterpret_cast<uint32_t*>(&dav);
         uint32_t* t12w = reinterpret_cast<uint32_t*>(&t12v);
         uint32_t* t3w = reinterpret_cast<uint32_t*>(&t3v);
-        const int jb = 32 * hf + 8 * ch;
+        const int jb = 16 * cq + 8 * up;
         const float4 gj0 = *reinterpret_cast<const float4*>(&s.g[jb]);
         const float4 gj1 = *reinterpret_cast<const float4*>(&s.g[jb + 4]);
         const float4 bj0 = *reinterpret_cast<const float4*>(&s.beta[jb]);
@@ -533,8 +530,8 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             const float G = keep ? fast_exp(g_r2 - gj[2 * e + z]) : 0.f;
             const float pgx = z ? bf16_hi(pw[e]) : bf16_lo(pw[e]);
             const float ax = z ? bf16_hi(aw[e]) : bf16_lo(aw[e]);
-            const float dpg = a1[8 * c2 + 2 * e + z];
-            const float dab = G * a2[8 * c2 + 2 * e + z];
+            const float dpg = a1[2 * e + z];
+            const float dab = G * a2[2 * e + z];
             const float bj = bjv[2 * e + z];
             t12o[z] = keep ? (dpg * pgx + dab * ax * bj) : 0.f;
             t3o[z] = dab * ax;
@@ -605,21 +602,24 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     tc_fence_after();
     {
       uint32_t r[32];
-      tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 32 * hf), r);
-      tmem_wait_ld();
-      if (active) {
+      {
+        uint32_t x1[16];
+        tmem_ld16(tmem_addr(tm, lane_base, kBcColU + 16 * cq), x1);
+        tmem_wait_ld();
+        if (active) {
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint4 x;
-          x.x = pack_bf16(__uint_as_float(r[8 * ch]), __uint_as_float(r[8 * ch + 1]));
-          x.y = pack_bf16(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
-          x.z = pack_bf16(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
-          x.w = pack_bf16(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
-          *reinterpret_cast<uint4*>(b_pg + sw128(row, (4 * hf + ch) * 16)) = x;
+          for (int ch = 0; ch < 2; ++ch) {
+            uint4 x;
+            x.x = pack_bf16(__uint_as_float(x1[8 * ch]), __uint_as_float(x1[8 * ch + 1]));
+            x.y = pack_bf16(__uint_as_float(x1[8 * ch + 2]), __uint_as_float(x1[8 * ch + 3]));
+            x.z = pack_bf16(__uint_as_float(x1[8 * ch + 4]), __uint_as_float(x1[8 * ch + 5]));
+            x.w = pack_bf16(__uint_as_float(x1[8 * ch + 6]), __uint_as_float(x1[8 * ch + 7]));
+            *reinterpret_cast<uint4*>(b_pg + sw128(row, (2 * cq + ch) * 16)) = x;
+          }
         }
       }
       // column sums of T and T3 (every column of the small accumulators holds the same sum)
-      if (hf == 0) {
+      if (cq == 0) {
         uint32_t c12[16], c3[16];
         tmem_ld16(tmem_addr(tm, lane_base, kBcColX), c12);
         tmem_ld16(tmem_addr(tm, lane_base, kBcColX + 16), c3);
@@ -631,8 +631,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
       // dq
       __nv_bfloat16* dst = p.dq + (static_cast<size_t>(cp.tok0 + row) * p.H + h) * kDim + 64 * hf;
-#pragma unroll 1
-      for (int pc = 0; pc < 2; ++pc) {
+      {
         tmem_ld32(tmem_addr(tm, lane_base, kBcColQ + 64 * hf + 32 * pc), r);
         tmem_wait_ld();
         if (active && row < len) {
@@ -677,36 +676,35 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     BC_TS(11);
     tc_fence_after();
     {
-      uint32_t x2[32], kk2[32];
-      tmem_ld32(tmem_addr(tm, lane_base, kBcColU + 64 + 32 * hf), x2);
-      tmem_ld32(tmem_addr(tm, lane_base, kBcColQK + 32 * hf), kk2);
+      uint32_t x2[16], kk2[16];
+      tmem_ld16(tmem_addr(tm, lane_base, kBcColU + 64 + 16 * cq), x2);
+      tmem_ld16(tmem_addr(tm, lane_base, kBcColQK + 16 * cq), kk2);
       tmem_wait_ld();
-      // as in round 3, lane + 16 takes over columns 16-31 of the row held by lane
+      // as in round 3, lane + 16 takes over columns 8-15 of the row held by lane
       const int up = lane >> 4;
       const int row2 = 16 * q4 + (lane & 15);
       const float beta_r2 = s.beta[row2];
       float dbr = 0.f;
-      // Only the lower triangle T5 = beta_row o dL is stored (16 columns per lane, row-contiguous); round 6 applies
+      // Only the lower triangle T5 = beta_row o dL is stored (8 columns per lane, row-contiguous); round 6 applies
       // it and its transpose, which together are dAs = T5 + T5^T.
-      uint32_t tw[8];
+      uint32_t tw[4];
 #pragma unroll
-      for (int i = 0; i < 16; i += 2) {
+      for (int i = 0; i < 8; i += 2) {
         float o2[2];
 #pragma unroll
         for (int z = 0; z < 2; ++z) {
-          const uint32_t hx = __shfl_sync(0xffffffffu, x2[16 + i + z], lane & 15);
-          const uint32_t hk = __shfl_sync(0xffffffffu, kk2[16 + i + z], lane & 15);
+          const uint32_t hx = __shfl_sync(0xffffffffu, x2[8 + i + z], lane & 15);
+          const uint32_t hk = __shfl_sync(0xffffffffu, kk2[8 + i + z], lane & 15);
           const float xv = __uint_as_float(up ? hx : x2[i + z]);
           const float kv = __uint_as_float(up ? hk : kk2[i + z]);
-          const int j = 32 * hf + 16 * up + i + z;
+          const int j = 16 * cq + 8 * up + i + z;
           const float dL = (j < row2) ? -xv : 0.f;
           dbr += dL * kv;
           o2[z] = beta_r2 * dL;
         }
         tw[i >> 1] = pack_bf16(o2[0], o2[1]);
       }
-      *reinterpret_cast<uint4*>(b_ag + sw128(row2, (4 * hf + 2 * up) * 16)) = make_uint4(tw[0], tw[1], tw[2], tw[3]);
-      *reinterpret_cast<uint4*>(b_ag + sw128(row2, (4 * hf + 2 * up + 1) * 16)) = make_uint4(tw[4], tw[5], tw[6], tw[7]);
+      *reinterpret_cast<uint4*>(b_ag + sw128(row2, (2 * cq + up) * 16)) = make_uint4(tw[0], tw[1], tw[2], tw[3]);
       dbr += __shfl_xor_sync(0xffffffffu, dbr, 16);
       if (active) atomicAdd(&s.db_s[row], dbr);
     }
@@ -738,8 +736,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     tc_fence_after();
     {
       __nv_bfloat16* dst = p.dk + (static_cast<size_t>(cp.tok0 + row) * p.H + h) * kDim + 64 * hf;
-#pragma unroll 1
-      for (int pc = 0; pc < 2; ++pc) {
+      {
         uint32_t r[32];
         tmem_ld32(tmem_addr(tm, lane_base, kBcColK + 64 * hf + 32 * pc), r);
         tmem_wait_ld();
