@@ -5,7 +5,7 @@
 //
 //   round 1  U = K S0 | D1 = K dS | D2 = P_g^T dO | accQ = dO S0^T
 //            -> W = V - gamma o U, dV' = rho o D1 + D2, accQ *= scale*gamma, dg += rowsum(Q o accQ)
-//   round 2  V' = A_g W | dW = A_g^T dV'
+//   round 2  V' = A_g W | dW = A_g^T dV' | Z = S0^T dS (M = 128; only its trace = sum(dS o S0) is used, for dg_last)
 //            -> dv = dW (output), dVg = -gamma o dW
 //   round 3  K1 = V' dS^T | dPg = dO V'^T | dAg = dV' W^T | accK = dVg S0^T
 //            -> dg += rowsum(K o accK); accK += rho o K1, dg -= rowsum(K o rho K1); dP = scale G o dPg;
@@ -146,6 +146,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   constexpr uint32_t id64_64_kk = umma_idesc(64, 64, false, false, true);
   constexpr uint32_t id64_64_mnmn = umma_idesc(64, 64, true, true, true);
   constexpr uint32_t id64_16_mnk = umma_idesc(64, 16, true, false, true);
+  constexpr uint32_t id128_128_kk = umma_idesc(128, 128, false, false, true);
 
   uint32_t tma_phase = 0, mma_phase = 0;
   // S0, dS, V and dO are dead after the third round of products, so the tiles of the CTA's next unit are requested
@@ -282,23 +283,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
-    // while the first round runs: the scalar gamma_last * sum(dS o S0), and the next unit's gate values
-    {
-      float acc = 0.f;
-#pragma unroll
-      for (int it = 0; it < 32768 / (16 * kBcThreads); ++it) {
-        const uint32_t off = (it * kBcThreads + tid) * 16;
-        const uint4 a = *reinterpret_cast<const uint4*>(s.s0 + off);
-        const uint4 b = *reinterpret_cast<const uint4*>(s.ds + off);
-        const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
-        const uint32_t* bw = reinterpret_cast<const uint32_t*>(&b);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc += bf16_lo(aw[e]) * bf16_lo(bw[e]) + bf16_hi(aw[e]) * bf16_hi(bw[e]);
-      }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 16);
-      acc = half_warp_sum(acc);
-      if (lane == 0) atomicAdd(&s.dgl_s, acc * s.gam[kChunk - 1]);
-    }
+    // while the first round runs: the next unit's gate values
     if (tid < kChunk && unit + gridDim.x < n_units) fetch_gates(unit + gridDim.x);
     if (!mbar_wait(wc, &s.bar_mma, mma_phase, 2)) { alive = false; break; }
     mma_phase ^= 1;
@@ -382,6 +367,11 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         for (int kk = 0; kk < 4; ++kk)
           umma_ss(tm + kBcColD1, umma_desc_sw128(sag + kk * 2048, 8192, 1024), umma_desc_sw128(sdvp + kk * 2048, 8192, 1024),
                   id64_128_mnmn, kk > 0);
+      } else if (warp == 2) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)  // Z = S0^T-tile (dS^T-tile)^T [128 v x 128 v']: its trace is sum(dS o S0)
+          umma_ss(tm + kBcColK, umma_desc_sw128(ss0 + off128(kk), 16, 1024), umma_desc_sw128(sds + off128(kk), 16, 1024),
+                  id128_128_kk, kk > 0);
       }
       umma_commit(&s.bar_mma);
     }
@@ -391,6 +381,18 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     BC_TS(5);
     tc_fence_after();
     {
+      if (cq == 0) {
+        // gamma_last * sum(dS o S0) = gamma_last * trace(Z): lane v of this warp's quarter picks column v
+        uint32_t z[32];
+        tmem_ld32(tmem_addr(tm, lane_base, kBcColK + 32 * q4), z);
+        tmem_wait_ld();
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) d = (lane == i) ? __uint_as_float(z[i]) : d;
+        d += __shfl_xor_sync(0xffffffffu, d, 16);
+        d = half_warp_sum(d);
+        if (lane == 0) atomicAdd(&s.dgl_s, d * s.gam[kChunk - 1]);
+      }
       __nv_bfloat16* dvdst = p.dv + (static_cast<size_t>(cp.tok0 + row) * p.H + h) * kDim + 64 * hf;
       {
         uint32_t r[32], w2[32];
