@@ -228,7 +228,9 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (tid == 0) s.dgl_s = 0.f;
     }
     __syncthreads();
+    BC_TS(15);
     if (!mbar_wait(wc, &s.bar_tma_a, tma_phase, 1)) { alive = false; break; }
+    BC_TS(16);
     if (!mbar_wait(wc, &s.bar_tma_b, tma_phase, 8)) { alive = false; break; }
     tma_phase ^= 1;
     BC_TS(1);
@@ -262,27 +264,28 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (warp == 0) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)  // U = K S0
-          umma_ss(tm + kBcColU, umma_desc_sw128(skt + off64(kk), 16, 1024), umma_desc_sw128(ss0 + off128(kk), 16, 1024),
+          umma_ss(tm + kBcColU, desc_add(umma_desc_sw128(skt, 16, 1024), off64(kk)), desc_add(umma_desc_sw128(ss0, 16, 1024), off128(kk)),
                   id64_128_kk, kk > 0);
       } else if (warp == 1) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)  // D1 = K dS
-          umma_ss(tm + kBcColD1, umma_desc_sw128(skt + off64(kk), 16, 1024), umma_desc_sw128(sds + off128(kk), 16, 1024),
+          umma_ss(tm + kBcColD1, desc_add(umma_desc_sw128(skt, 16, 1024), off64(kk)), desc_add(umma_desc_sw128(sds, 16, 1024), off128(kk)),
                   id64_128_kk, kk > 0);
       } else if (warp == 2) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // D2 = P_g^T dO
-          umma_ss(tm + kBcColK, umma_desc_sw128(spg + kk * 2048, 8192, 1024), umma_desc_sw128(sdot + kk * 2048, 8192, 1024),
+          umma_ss(tm + kBcColK, desc_add(umma_desc_sw128(spg, 8192, 1024), kk * 2048), desc_add(umma_desc_sw128(sdot, 8192, 1024), kk * 2048),
                   id64_128_mnmn, kk > 0);
       } else if (warp == 3) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)  // accQ = dO S0^T
-          umma_ss(tm + kBcColQ, umma_desc_sw128(sdot + off64(kk), 16, 1024), umma_desc_sw128(ss0 + kk * 2048, 16384, 1024),
+          umma_ss(tm + kBcColQ, desc_add(umma_desc_sw128(sdot, 16, 1024), off64(kk)), desc_add(umma_desc_sw128(ss0, 16384, 1024), kk * 2048),
                   id64_128_kmn, kk > 0);
       }
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
+    BC_TS(17);
     // while the first round runs: the next unit's gate values
     if (tid < kChunk && unit + gridDim.x < n_units) fetch_gates(unit + gridDim.x);
     if (!mbar_wait(wc, &s.bar_mma, mma_phase, 2)) { alive = false; break; }
@@ -360,17 +363,17 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (warp == 0) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tm + kBcColU, umma_desc_sw128(sag + kk * 32, 16, 1024), umma_desc_sw128(swt + kk * 2048, 8192, 1024),
+          umma_ss(tm + kBcColU, desc_add(umma_desc_sw128(sag, 16, 1024), kk * 32), desc_add(umma_desc_sw128(swt, 8192, 1024), kk * 2048),
                   id64_128_kmn, kk > 0);
       } else if (warp == 1) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tm + kBcColD1, umma_desc_sw128(sag + kk * 2048, 8192, 1024), umma_desc_sw128(sdvp + kk * 2048, 8192, 1024),
+          umma_ss(tm + kBcColD1, desc_add(umma_desc_sw128(sag, 8192, 1024), kk * 2048), desc_add(umma_desc_sw128(sdvp, 8192, 1024), kk * 2048),
                   id64_128_mnmn, kk > 0);
       } else if (warp == 2) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)  // Z = S0^T-tile (dS^T-tile)^T [128 v x 128 v']: its trace is sum(dS o S0)
-          umma_ss(tm + kBcColK, umma_desc_sw128(ss0 + off128(kk), 16, 1024), umma_desc_sw128(sds + off128(kk), 16, 1024),
+          umma_ss(tm + kBcColK, desc_add(umma_desc_sw128(ss0, 16, 1024), off128(kk)), desc_add(umma_desc_sw128(sds, 16, 1024), off128(kk)),
                   id128_128_kk, kk > 0);
       }
       umma_commit(&s.bar_mma);
@@ -433,22 +436,22 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (warp == 0) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tm + kBcColU, umma_desc_sw128(svp + off64(kk), 16, 1024), umma_desc_sw128(sds + kk * 2048, 16384, 1024),
+          umma_ss(tm + kBcColU, desc_add(umma_desc_sw128(svp, 16, 1024), off64(kk)), desc_add(umma_desc_sw128(sds, 16384, 1024), kk * 2048),
                   id64_128_kmn, kk > 0);
       } else if (warp == 1) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tm + kBcColQK, umma_desc_sw128(sdot + off64(kk), 16, 1024), umma_desc_sw128(svp + off64(kk), 16, 1024),
+          umma_ss(tm + kBcColQK, desc_add(umma_desc_sw128(sdot, 16, 1024), off64(kk)), desc_add(umma_desc_sw128(svp, 16, 1024), off64(kk)),
                   id64_64_kk, kk > 0);
       } else if (warp == 2) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tm + kBcColX, umma_desc_sw128(sdvp + off64(kk), 16, 1024), umma_desc_sw128(swt + off64(kk), 16, 1024),
+          umma_ss(tm + kBcColX, desc_add(umma_desc_sw128(sdvp, 16, 1024), off64(kk)), desc_add(umma_desc_sw128(swt, 16, 1024), off64(kk)),
                   id64_64_kk, kk > 0);
       } else if (warp == 3) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)  // accK = dVg S0^T
-          umma_ss(tm + kBcColK, umma_desc_sw128(sdvg + off64(kk), 16, 1024), umma_desc_sw128(ss0 + kk * 2048, 16384, 1024),
+          umma_ss(tm + kBcColK, desc_add(umma_desc_sw128(sdvg, 16, 1024), off64(kk)), desc_add(umma_desc_sw128(ss0, 16384, 1024), kk * 2048),
                   id64_128_kmn, kk > 0);
       }
       umma_commit(&s.bar_mma);
@@ -567,26 +570,26 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (warp == 0) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tm + kBcColQ, umma_desc_sw128(spg + kk * 32, 16, 1024), umma_desc_sw128(skt + kk * 2048, 8192, 1024),
+          umma_ss(tm + kBcColQ, desc_add(umma_desc_sw128(spg, 16, 1024), kk * 32), desc_add(umma_desc_sw128(skt, 8192, 1024), kk * 2048),
                   id64_128_kmn, 1);
       } else if (warp == 1) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tm + kBcColK, umma_desc_sw128(spg + kk * 2048, 8192, 1024), umma_desc_sw128(sqt + kk * 2048, 8192, 1024),
+          umma_ss(tm + kBcColK, desc_add(umma_desc_sw128(spg, 8192, 1024), kk * 2048), desc_add(umma_desc_sw128(sqt, 8192, 1024), kk * 2048),
                   id64_128_mnmn, 1);
       } else if (warp == 2) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tm + kBcColU, umma_desc_sw128(sat + kk * 2048, 8192, 1024), umma_desc_sw128(sag + kk * 2048, 8192, 1024),
+          umma_ss(tm + kBcColU, desc_add(umma_desc_sw128(sat, 8192, 1024), kk * 2048), desc_add(umma_desc_sw128(sag, 8192, 1024), kk * 2048),
                   id64_64_mnmn, kk > 0);
       } else if (warp == 3) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // column sums: D[j][:] = sum_i T[i][j]
-          umma_ss(tm + kBcColX, umma_desc_sw128(st12 + kk * 2048, 8192, 1024), umma_desc_sw128(sones + kk * 32, 16, 1024),
+          umma_ss(tm + kBcColX, desc_add(umma_desc_sw128(st12, 8192, 1024), kk * 2048), desc_add(umma_desc_sw128(sones, 16, 1024), kk * 32),
                   id64_16_mnk, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tm + kBcColX + 16, umma_desc_sw128(st3 + kk * 2048, 8192, 1024), umma_desc_sw128(sones + kk * 32, 16, 1024),
+          umma_ss(tm + kBcColX + 16, desc_add(umma_desc_sw128(st3, 8192, 1024), kk * 2048), desc_add(umma_desc_sw128(sones, 16, 1024), kk * 32),
                   id64_16_mnk, kk > 0);
       }
       umma_commit(&s.bar_mma);
@@ -660,12 +663,12 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (warp == 0) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tm + kBcColU + 64, umma_desc_sw128(spg + kk * 32, 16, 1024), umma_desc_sw128(sat + kk * 32, 16, 1024),
+          umma_ss(tm + kBcColU + 64, desc_add(umma_desc_sw128(spg, 16, 1024), kk * 32), desc_add(umma_desc_sw128(sat, 16, 1024), kk * 32),
                   id64_64_kk, kk > 0);
       } else if (warp == 1) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tm + kBcColQK, umma_desc_sw128(skt + off64(kk), 16, 1024), umma_desc_sw128(skt + off64(kk), 16, 1024),
+          umma_ss(tm + kBcColQK, desc_add(umma_desc_sw128(skt, 16, 1024), off64(kk)), desc_add(umma_desc_sw128(skt, 16, 1024), off64(kk)),
                   id64_64_kk, kk > 0);
       }
       umma_commit(&s.bar_mma);
@@ -721,12 +724,12 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (warp == 0) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // accK += T5 K
-          umma_ss(tm + kBcColK, umma_desc_sw128(sag + kk * 32, 16, 1024), umma_desc_sw128(skt + kk * 2048, 8192, 1024),
+          umma_ss(tm + kBcColK, desc_add(umma_desc_sw128(sag, 16, 1024), kk * 32), desc_add(umma_desc_sw128(skt, 8192, 1024), kk * 2048),
                   id64_128_kmn, 1);
       } else if (warp == 1) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // accK += T5^T K
-          umma_ss(tm + kBcColK, umma_desc_sw128(sag + kk * 2048, 8192, 1024), umma_desc_sw128(skt + kk * 2048, 8192, 1024),
+          umma_ss(tm + kBcColK, desc_add(umma_desc_sw128(sag, 8192, 1024), kk * 2048), desc_add(umma_desc_sw128(skt, 8192, 1024), kk * 2048),
                   id64_128_mnmn, 1);
       }
       umma_commit(&s.bar_mma);

@@ -176,6 +176,11 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr, uint32_t lbo
   return d;
 }
 
+// Descriptor with the start address advanced by `bytes` (the address field holds addr >> 4; shared-memory
+// addresses stay below 256 KB, so the 14-bit field cannot overflow).  Building the descriptor of a tile once and
+// stepping it with this costs one 64-bit add per product instead of a dozen instructions.
+__device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t bytes) { return d + (bytes >> 4); }
+
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                         uint32_t accumulate) {

@@ -81,8 +81,6 @@ struct FwdParams {
 };
 
 __device__ __forceinline__ uint32_t kq_off(int kk) { return (kk >> 2) * 16384 + (kk & 3) * 32; }
-// Descriptor with the start address advanced by `bytes` (the address field holds addr >> 4).
-__device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t bytes) { return d + (bytes >> 4); }
 
 __global__ void __launch_bounds__(kFwdThreads, 1)
 gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
