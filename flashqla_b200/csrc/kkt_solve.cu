@@ -24,7 +24,6 @@ namespace fq {
 
 constexpr int kKLd = 136;  // bf16 elements per K-tile row in shared memory (pad: conflict-free fragments)
 constexpr int kFLd = 68;   // fp32 elements per row of the 64x64 work matrices
-constexpr int kTLd = 36;   // fp32 elements per row of the 32x32 scratch
 
 struct KktSmem {
   union {  // the Q tile is only read while Q K^T is formed; K K^T (fp32) then takes its place
@@ -35,10 +34,19 @@ struct KktSmem {
     __nv_bfloat16 k[kChunk * kKLd];
     float x[kChunk * kFLd];
   };
-  float t[32 * kTLd];
   float beta[kChunk];
   float g[kChunk];
 };
+// Only the lower block triangle of K K^T is formed, so rows 0-31 x columns 32-63 of `kk` are free: the 32x32
+// scratch of the block products lives there (row stride kFLd).
+constexpr int kTLd = kFLd;
+constexpr int kTOff = 32;
+
+// 16-byte asynchronous copy global -> shared; `bytes` = 0 writes zeros instead (rows past the sequence end).
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
   asm volatile(
@@ -69,7 +77,61 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const float (&a)[4], con
   mma_tf32_1688(c, ah, bh);
 }
 
-__global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* __restrict__ k,
+// acc[j] (16 rows m0.. of `a_tile` times the 8 rows 8j.. of `b_tile`, both [64][kKLd] bf16) for the lower block
+// triangle j < ntiles.  Fragment loads with ldmatrix: lane l addresses row (l & 7) + 8 * ((l >> 3) & 1) of a 16-row
+// block and the 8-column half (l >> 4) for the A operand; for the B operand one x4 load covers two 8-row tiles.
+__device__ __forceinline__ void gram_pass(float (&acc)[8][4], const __nv_bfloat16* a_tile, const __nv_bfloat16* b_tile,
+                                          int m0, int ntiles, int lane) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  const int a_row = m0 + (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
+  const int b_row = (lane & 7) + 8 * (lane >> 4), b_col = 8 * ((lane >> 3) & 1);
+#pragma unroll
+  for (int k0 = 0; k0 < kDim; k0 += 16) {
+    uint32_t a[4];
+    ldmatrix_x4(a, &a_tile[a_row * kKLd + k0 + a_col]);
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      if (j < ntiles) {  // ntiles is even
+        uint32_t b4[4];
+        ldmatrix_x4(b4, &b_tile[(j * 8 + b_row) * kKLd + k0 + b_col]);
+        const uint32_t b0[2] = {b4[0], b4[1]}, b1[2] = {b4[2], b4[3]};
+        mma_bf16_16816(acc[j], a, b0);
+        mma_bf16_16816(acc[j + 1], a, b1);
+      }
+    }
+  }
+}
+
+// P_g straight from the Q K^T fragments (rows m0+g and m0+g+8, column pairs 8j+2t); g2 = gate cumsum * log2(e).
+__device__ __forceinline__ void store_pg(const float (&qk)[8][4], const float* g2, __nv_bfloat16* dstp, size_t row_stride,
+                                         int warp, int lane, int len, float scale) {
+  const int m0 = warp * 16, g = lane >> 2, t = lane & 3;
+  const float log2_scale = log2f(scale);
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int row = m0 + g + 8 * half;
+    if (row < len) {
+      const float gi = g2[row] + log2_scale;  // scale * 2^(g_i - g_j) = 2^(g_i + log2(scale) - g_j)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c0 = j * 8 + 2 * t;
+        float y0 = 0.f, y1 = 0.f;
+        if (j < 2 * warp + 2) {
+          const float2 gj = *reinterpret_cast<const float2*>(&g2[c0]);
+          if (c0 <= row) y0 = exp2f(gi - gj.x) * qk[j][2 * half];
+          if (c0 + 1 <= row) y1 = exp2f(gi - gj.y) * qk[j][2 * half + 1];
+        }
+        *reinterpret_cast<uint32_t*>(dstp + static_cast<size_t>(row) * row_stride + c0) = pack_bf16(y0, y1);
+      }
+    }
+  }
+}
+
+// kSingle: every QK head has one V head (G == 1); the gates are then loaded with the tiles and P_g leaves before
+// the solve, so that the Q K^T fragments are dead while K K^T is formed and inverted.
+template <bool kSingle>
+__global__ void __launch_bounds__(128, 6) kkt_solve_kernel(const __nv_bfloat16* __restrict__ k,
                                                        const float* __restrict__ beta,
                                                        __nv_bfloat16* __restrict__ A, int H, int Hg, SeqArgs sa,
                                                        const __nv_bfloat16* __restrict__ q,
@@ -84,67 +146,48 @@ __global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* 
   const int G = H / Hg;
   const ChunkPos p = chunk_lookup(sa, blockIdx.x);
 
-  // ---- K tile -> shared (rows past the sequence end are zero) and clear the X work matrix
+  // ---- K and Q tiles -> shared by asynchronous 16-byte copies (rows past the sequence end are zero-filled)
   {
     const __nv_bfloat16* src = k + (static_cast<size_t>(p.tok0) * Hg + hg) * kDim;
+    const __nv_bfloat16* qsrc = Pg ? q + (static_cast<size_t>(p.tok0) * Hg + hg) * kDim : nullptr;
 #pragma unroll
     for (int it = 0; it < 8; ++it) {
       const int idx = it * 128 + tid;  // 16-byte piece index: 16 per row
       const int row = idx >> 4, piece = idx & 15;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (row < p.len) v = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(row) * Hg * kDim) + piece);
-      *reinterpret_cast<uint4*>(&s.k[row * kKLd + piece * 8]) = v;
+      const int ok = row < p.len;
+      const size_t off = static_cast<size_t>(ok ? row : 0) * Hg * kDim + piece * 8;
+      cp_async16(&s.k[row * kKLd + piece * 8], src + off, ok ? 16 : 0);
+      if (Pg) cp_async16(&s.q[row * kKLd + piece * 8], qsrc + off, ok ? 16 : 0);
     }
-    if (Pg) {
-      const __nv_bfloat16* qsrc = q + (static_cast<size_t>(p.tok0) * Hg + hg) * kDim;
-#pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int idx = it * 128 + tid;
-        const int row = idx >> 4, piece = idx & 15;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < p.len) v = __ldg(reinterpret_cast<const uint4*>(qsrc + static_cast<size_t>(row) * Hg * kDim) + piece);
-        *reinterpret_cast<uint4*>(&s.q[row * kKLd + piece * 8]) = v;
-      }
+    if (kSingle && tid < kChunk) {
+      s.beta[tid] = (tid < p.len) ? __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hg) : 0.f;
+      // log-gate cumsum times log2(e): exp(g_i - g_j) = exp2(g2_i - g2_j)
+      if (Ag || Pg) s.g[tid] = 1.4426950408889634f * __ldg(g_cum + static_cast<size_t>(p.tok0 + min(tid, p.len - 1)) * H + hg);
     }
+    cp_async_wait_all();
   }
   __syncthreads();
 
-  // ---- Q K^T (kept in registers for all V-heads of the group) and K K^T (fp32, to shared), lower
-  //      block-triangle only; one pass over the K tile feeds both products (shared B fragments)
+  // ---- Q K^T (registers) and K K^T (fp32, to shared), lower block triangle only, one pass each
   float qk[8][4];
   {
     const int m0 = warp * 16;
     const int ntiles = 2 * warp + 2;
-    const bool do_qk = Pg != nullptr, do_kk = A_in == nullptr;
-    float acc[8][4];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      qk[j][0] = qk[j][1] = qk[j][2] = qk[j][3] = 0.f;
-      acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    if (Pg) {
+      gram_pass(qk, s.q, s.k, m0, ntiles, lane);
+      if (kSingle)
+        store_pg(qk, s.g, Pg + (static_cast<size_t>(p.tok0) * H + hg) * kChunk, static_cast<size_t>(H) * kChunk, warp, lane,
+                 p.len, scale);
     }
-    // fragment loads with ldmatrix: lane l addresses row (l & 7) + 8 * ((l >> 3) & 1) of a 16-row block and the
-    // 8-column half (l >> 4) for the A operand; for the B operand one x4 load covers two 8-row tiles of K
-    const int a_row = m0 + (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
-    const int b_row = (lane & 7) + 8 * (lane >> 4), b_col = 8 * ((lane >> 3) & 1);
-#pragma unroll
-    for (int k0 = 0; k0 < kDim; k0 += 16) {
-      uint32_t aq[4] = {0, 0, 0, 0}, ak[4] = {0, 0, 0, 0};
-      if (do_qk) ldmatrix_x4(aq, &s.q[a_row * kKLd + k0 + a_col]);
-      if (do_kk) ldmatrix_x4(ak, &s.k[a_row * kKLd + k0 + a_col]);
-#pragma unroll
-      for (int j = 0; j < 8; j += 2) {
-        if (j < ntiles) {  // ntiles is even
-          uint32_t b4[4];
-          ldmatrix_x4(b4, &s.k[(j * 8 + b_row) * kKLd + k0 + b_col]);
-          const uint32_t b0[2] = {b4[0], b4[1]}, b1[2] = {b4[2], b4[3]};
-          if (do_qk) { mma_bf16_16816(qk[j], aq, b0); mma_bf16_16816(qk[j + 1], aq, b1); }
-          if (do_kk) { mma_bf16_16816(acc[j], ak, b0); mma_bf16_16816(acc[j + 1], ak, b1); }
-        }
-      }
-    }
-    if (do_kk) {
+    if (A_in == nullptr) {
+      float acc[8][4];
+      gram_pass(acc, s.k, s.k, m0, ntiles, lane);
       __syncthreads();  // every warp is done reading the Q and K tiles, whose storage kk and x reuse
-      for (int i = tid; i < kChunk * kFLd; i += 128) s.x[i] = 0.f;
+      {  // the two 16x16 blocks above the diagonal that the 32x32 block products read must be zero
+        const int blk = tid >> 6, idx = tid & 63;
+        *reinterpret_cast<float4*>(&s.x[(32 * blk + (idx >> 2)) * kFLd + 32 * blk + 16 + 4 * (idx & 3)]) =
+            make_float4(0.f, 0.f, 0.f, 0.f);
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         if (j < ntiles) {
@@ -157,13 +200,14 @@ __global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* 
 
   for (int hi = 0; hi < G; ++hi) {
     const int hv = hg * G + hi;
-    __syncthreads();  // kk complete (first pass) / previous head's stores done
-    if (tid < kChunk) {
-      s.beta[tid] = (tid < p.len) ? __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hv) : 0.f;
-      // log-gate cumsum times log2(e): exp(g_i - g_j) = exp2(g2_i - g2_j)
-      if (Ag || Pg) s.g[tid] = 1.4426950408889634f * __ldg(g_cum + static_cast<size_t>(p.tok0 + min(tid, p.len - 1)) * H + hv);
+    __syncthreads();  // kk complete, tiles read (first pass) / previous head's stores done
+    if (!kSingle) {
+      if (tid < kChunk) {
+        s.beta[tid] = (tid < p.len) ? __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hv) : 0.f;
+        if (Ag || Pg) s.g[tid] = 1.4426950408889634f * __ldg(g_cum + static_cast<size_t>(p.tok0 + min(tid, p.len - 1)) * H + hv);
+      }
+      __syncthreads();
     }
-    __syncthreads();
 
     if (A_in != nullptr) {
       // A was computed earlier (backward pass): fetch it instead of solving again
@@ -203,7 +247,7 @@ __global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* 
     {
       const int blk = warp >> 1, nt = warp & 1;
       const int r0 = 16 * (2 * blk + 1), c0 = 16 * (2 * blk);
-      float* ts = &s.t[warp * 16 * 9];  // private 16 x 8 scratch (row stride 9)
+      float* ts = &s.kk[(16 * (warp >> 1)) * kTLd + kTOff + 16 * (warp & 1)];  // private 16 x 8 scratch
       float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int k0 = 0; k0 < 16; k0 += 8) {
@@ -217,10 +261,10 @@ __global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* 
         b[1] = s.x[(c0 + k0 + t + 4) * kFLd + c0 + 8 * nt + g];
         mma_tf32(c, a, b);
       }
-      ts[g * 9 + 2 * t] = c[0];
-      ts[g * 9 + 2 * t + 1] = c[1];
-      ts[(g + 8) * 9 + 2 * t] = c[2];
-      ts[(g + 8) * 9 + 2 * t + 1] = c[3];
+      ts[g * kTLd + 2 * t] = c[0];
+      ts[g * kTLd + 2 * t + 1] = c[1];
+      ts[(g + 8) * kTLd + 2 * t] = c[2];
+      ts[(g + 8) * kTLd + 2 * t + 1] = c[3];
       __syncwarp();
       float d[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -230,8 +274,8 @@ __global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* 
         a[1] = s.x[(r0 + g + 8) * kFLd + r0 + k0 + t];
         a[2] = s.x[(r0 + g) * kFLd + r0 + k0 + t + 4];
         a[3] = s.x[(r0 + g + 8) * kFLd + r0 + k0 + t + 4];
-        b[0] = ts[(k0 + t) * 9 + g];
-        b[1] = ts[(k0 + t + 4) * 9 + g];
+        b[0] = ts[(k0 + t) * kTLd + g];
+        b[1] = ts[(k0 + t + 4) * kTLd + g];
         mma_tf32(d, a, b);
       }
       __syncthreads();  // every warp has read its diagonal blocks; the scratch is free again
@@ -264,8 +308,8 @@ __global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* 
       }
 #pragma unroll
       for (int n = 0; n < 2; ++n) {
-        *reinterpret_cast<float2*>(&s.t[(16 * wr + g) * kTLd + 16 * wc + 8 * n + 2 * t]) = make_float2(c[n][0], c[n][1]);
-        *reinterpret_cast<float2*>(&s.t[(16 * wr + g + 8) * kTLd + 16 * wc + 8 * n + 2 * t]) =
+        *reinterpret_cast<float2*>(&s.kk[kTOff + (16 * wr + g) * kTLd + 16 * wc + 8 * n + 2 * t]) = make_float2(c[n][0], c[n][1]);
+        *reinterpret_cast<float2*>(&s.kk[kTOff + (16 * wr + g + 8) * kTLd + 16 * wc + 8 * n + 2 * t]) =
             make_float2(c[n][2], c[n][3]);
       }
       __syncthreads();
@@ -282,8 +326,8 @@ __global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* 
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
           float b[2];
-          b[0] = s.t[(k0 + t) * kTLd + 16 * wc + 8 * n + g];
-          b[1] = s.t[(k0 + t + 4) * kTLd + 16 * wc + 8 * n + g];
+          b[0] = s.kk[kTOff + (k0 + t) * kTLd + 16 * wc + 8 * n + g];
+          b[1] = s.kk[kTOff + (k0 + t + 4) * kTLd + 16 * wc + 8 * n + g];
           mma_tf32(d[n], a, b);
         }
       }
@@ -298,71 +342,69 @@ __global__ void __launch_bounds__(128, 5) kkt_solve_kernel(const __nv_bfloat16* 
     __syncthreads();
 
     }
-    // ---- store A (bf16) and, if asked, A_g; 128 contiguous bytes per token row
+    // ---- store A (bf16) and, if asked, A_g, in 16-byte pieces (8 columns of one token row).  Only the 320 pieces of
+    //      the lower block triangle carry values; they are spread evenly over the threads (2.5 per thread), the 192
+    //      pieces above it are written as zeros without touching the work matrix.
     {
-      __nv_bfloat16* dst = A + (static_cast<size_t>(p.tok0) * H + hv) * kChunk;
+      __nv_bfloat16* dst = A_in == nullptr ? A + (static_cast<size_t>(p.tok0) * H + hv) * kChunk : nullptr;
       __nv_bfloat16* dstg = Ag ? Ag + (static_cast<size_t>(p.tok0) * H + hv) * kChunk : nullptr;
-#pragma unroll
-      for (int it = 0; it < 4; ++it) {
-        const int row = it * 16 + (tid >> 3), piece = tid & 7;
-        if (row < p.len) {
-          const float4 x0 = *reinterpret_cast<const float4*>(&s.x[row * kFLd + piece * 8]);
-          const float4 x1 = *reinterpret_cast<const float4*>(&s.x[row * kFLd + piece * 8 + 4]);
-          const float xr[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-          uint4 v;
-          if (A_in == nullptr) {
-            v.x = pack_bf16(xr[0], xr[1]);
-            v.y = pack_bf16(xr[2], xr[3]);
-            v.z = pack_bf16(xr[4], xr[5]);
-            v.w = pack_bf16(xr[6], xr[7]);
-            *(reinterpret_cast<uint4*>(dst + static_cast<size_t>(row) * H * kChunk) + piece) = v;
-          }
-          if (dstg) {
-            float y[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            if (piece * 8 <= row) {  // pieces entirely above the diagonal stay zero
-              const float gi = s.g[row];
-              const float4 g0 = *reinterpret_cast<const float4*>(&s.g[piece * 8]);
-              const float4 g1 = *reinterpret_cast<const float4*>(&s.g[piece * 8 + 4]);
-              const float4 b0 = *reinterpret_cast<const float4*>(&s.beta[piece * 8]);
-              const float4 b1 = *reinterpret_cast<const float4*>(&s.beta[piece * 8 + 4]);
-              const float gj[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-              const float bj[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-              for (int e = 0; e < 8; ++e)
-                y[e] = (piece * 8 + e <= row) ? xr[e] * exp2f(gi - gj[e]) * bj[e] : 0.f;
-            }
-            v.x = pack_bf16(y[0], y[1]);
-            v.y = pack_bf16(y[2], y[3]);
-            v.z = pack_bf16(y[4], y[5]);
-            v.w = pack_bf16(y[6], y[7]);
-            *(reinterpret_cast<uint4*>(dstg + static_cast<size_t>(row) * H * kChunk) + piece) = v;
-          }
+      const size_t rs = static_cast<size_t>(H) * kChunk;
+      auto emit = [&](int row, int piece) {
+        if (row >= p.len) return;
+        const float4 x0 = *reinterpret_cast<const float4*>(&s.x[row * kFLd + piece * 8]);
+        const float4 x1 = *reinterpret_cast<const float4*>(&s.x[row * kFLd + piece * 8 + 4]);
+        const float xr[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        uint4 v;
+        if (dst) {
+          v.x = pack_bf16(xr[0], xr[1]);
+          v.y = pack_bf16(xr[2], xr[3]);
+          v.z = pack_bf16(xr[4], xr[5]);
+          v.w = pack_bf16(xr[6], xr[7]);
+          *(reinterpret_cast<uint4*>(dst + row * rs) + piece) = v;
         }
-      }
-    }
-    // ---- P_g straight from the Q K^T fragments (rows m0+g and m0+g+8, column pairs 8j+2t)
-    if (Pg) {
-      const int m0 = warp * 16;
-      __nv_bfloat16* dstp = Pg + (static_cast<size_t>(p.tok0) * H + hv) * kChunk;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int row = m0 + g + 8 * half;
-        if (row < p.len) {
+        if (dstg) {
           const float gi = s.g[row];
+          const float4 g0 = *reinterpret_cast<const float4*>(&s.g[piece * 8]);
+          const float4 g1 = *reinterpret_cast<const float4*>(&s.g[piece * 8 + 4]);
+          const float4 b0 = *reinterpret_cast<const float4*>(&s.beta[piece * 8]);
+          const float4 b1 = *reinterpret_cast<const float4*>(&s.beta[piece * 8 + 4]);
+          const float gj[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+          const float bj[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+          float y[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int c0 = j * 8 + 2 * t;
-            float y0 = 0.f, y1 = 0.f;
-            if (j < 2 * warp + 2) {
-              const float2 gj = *reinterpret_cast<const float2*>(&s.g[c0]);
-              if (c0 <= row) y0 = scale * exp2f(gi - gj.x) * qk[j][2 * half];
-              if (c0 + 1 <= row) y1 = scale * exp2f(gi - gj.y) * qk[j][2 * half + 1];
-            }
-            *reinterpret_cast<uint32_t*>(dstp + static_cast<size_t>(row) * H * kChunk + c0) = pack_bf16(y0, y1);
-          }
+          for (int e = 0; e < 8; ++e) y[e] = (piece * 8 + e <= row) ? xr[e] * exp2f(gi - gj[e]) * bj[e] : 0.f;
+          v.x = pack_bf16(y[0], y[1]);
+          v.y = pack_bf16(y[2], y[3]);
+          v.z = pack_bf16(y[4], y[5]);
+          v.w = pack_bf16(y[6], y[7]);
+          *(reinterpret_cast<uint4*>(dstg + row * rs) + piece) = v;
         }
+      };
+      auto emit_zero = [&](int row, int piece) {
+        if (row >= p.len) return;
+        if (dst) *(reinterpret_cast<uint4*>(dst + row * rs) + piece) = make_uint4(0, 0, 0, 0);
+        if (dstg) *(reinterpret_cast<uint4*>(dstg + row * rs) + piece) = make_uint4(0, 0, 0, 0);
+      };
+      emit(48 + (tid >> 3), tid & 7);  // rows 48-63: all 8 pieces
+      if (warp < 3) {                  // rows 32-47: pieces 0-5
+        const int r = tid / 6;
+        emit(32 + r, tid - 6 * r);
+      } else {                         // rows 0-15: pieces 0-1
+        emit((tid - 96) >> 1, tid & 1);
+      }
+      if (warp < 2) {                  // rows 16-31: pieces 0-3
+        emit(16 + (tid >> 2), tid & 3);
+      } else {                         // the 192 zero pieces
+        const int i = tid - 64;
+        emit_zero(i >> 2, 4 + (i & 3));
+        emit_zero(16 + (i >> 2), 4 + (i & 3));
+        if (i < 32) emit_zero(i >> 1, 2 + (i & 1));
+        else emit_zero(32 + ((i - 32) >> 1), 6 + (i & 1));
       }
     }
+    if (!kSingle && Pg)
+      store_pg(qk, s.g, Pg + (static_cast<size_t>(p.tok0) * H + hv) * kChunk, static_cast<size_t>(H) * kChunk, warp, lane,
+               p.len, scale);
   }
 }
 
@@ -389,12 +431,15 @@ extern "C" FQ_API int fq_kkt_solve_gated(const void* k, const void* q, const flo
   int dev = 0;
   FQ_CHECK_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    FQ_CHECK_CUDA(cudaFuncSetAttribute(kkt_solve_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    FQ_CHECK_CUDA(cudaFuncSetAttribute(kkt_solve_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(sizeof(KktSmem))));
+    FQ_CHECK_CUDA(cudaFuncSetAttribute(kkt_solve_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(KktSmem))));
     attr_set[dev] = true;
   }
   dim3 grid(total_chunks, Hg);
-  kkt_solve_kernel<<<grid, 128, sizeof(KktSmem), static_cast<cudaStream_t>(stream)>>>(
+  auto kern = (H == Hg) ? kkt_solve_kernel<true> : kkt_solve_kernel<false>;
+  kern<<<grid, 128, sizeof(KktSmem), static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(k), beta, static_cast<__nv_bfloat16*>(A), H, Hg, sa,
       static_cast<const __nv_bfloat16*>(q), g_cumsum, static_cast<__nv_bfloat16*>(Ag), static_cast<__nv_bfloat16*>(Pg),
       scale, a_is_input ? static_cast<const __nv_bfloat16*>(A) : nullptr);
