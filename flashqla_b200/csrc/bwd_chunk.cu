@@ -28,7 +28,7 @@ namespace fq {
 #ifdef FQ_TRACE
 // Debug builds only: clock64 stamps of one CTA for its third unit, read back with fq_trace_read_bc.
 __device__ long long g_trace_bc[32];
-#define BC_TS(id) do { if (blockIdx.x == 0 && tid == 0 && unit == 2LL * gridDim.x) g_trace_bc[id] = clock64(); } while (0)
+#define BC_TS(id) do { if (blockIdx.x == 0 && tid == 0 && iter == 2) g_trace_bc[id] = clock64(); } while (0)
 #else
 #define BC_TS(id) do { } while (0)
 #endif
@@ -114,6 +114,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   const int row = active ? (16 * q4 + lane) : 0;
   const uint32_t lane_base = static_cast<uint32_t>(q4) * 32;
   WaitCtx wc{&s.abort_flag, p.status_dev, 3};
+  const int heads_per_group = p.H / p.Hg;
 
   if (tid == 0) {
     s.abort_flag = 0;
@@ -149,10 +150,9 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   constexpr uint32_t id128_128_kk = umma_idesc(128, 128, false, false, true);
 
   uint32_t tma_phase = 0, mma_phase = 0;
-  // S0, dS, V and dO are dead after the third round of products, so the tiles of the CTA's next unit are requested
-  // there and land while rounds four to six run
-  auto load_a = [&](long long unit) {
-    const int chunk = static_cast<int>(unit / p.H), h = static_cast<int>(unit - static_cast<long long>(chunk) * p.H);
+  // S0, dS, V and dO are dead once the third round of products has completed, so the tiles of the CTA's next unit
+  // are requested there and land while the rest of the unit runs
+  auto load_a = [&](int chunk, int h) {
     const ChunkPos cp = chunk_lookup(p.sa, chunk);
     mbar_arrive_expect_tx(&s.bar_tma_a, kBcLoadBytesA);
     const int r0 = cp.tok0;
@@ -167,10 +167,9 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     tma_load_3d(s.ds + 16384, &map_dh, &s.bar_tma_a, 64, 0, hr);
   };
   // part 0: K, Q, A, A_g (and the byte count of the whole group); part 1: P_g
-  auto load_b = [&](long long unit, int part, unsigned char* dk, unsigned char* dq, unsigned char* da,
+  auto load_b = [&](int chunk, int h, int part, unsigned char* dk, unsigned char* dq, unsigned char* da,
                     unsigned char* dpg) {
-    const int chunk = static_cast<int>(unit / p.H), h = static_cast<int>(unit - static_cast<long long>(chunk) * p.H);
-    const int hg = h / (p.H / p.Hg);
+    const int hg = h / heads_per_group;
     const ChunkPos cp = chunk_lookup(p.sa, chunk);
     const int r0 = cp.tok0;
     if (part != 1) {
@@ -184,14 +183,15 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
     if (part != 0) tma_load_3d(dpg, &map_pg, &s.bar_tma_b, 0, h, r0);
   };
-  const long long n_units = static_cast<long long>(p.total_chunks) * p.H;
-  if (tid == 0 && blockIdx.x < n_units) load_a(blockIdx.x);
+  // Units (chunk, head) are walked with a stride of one grid; the index pair is stepped without divisions.
+  int chunk = static_cast<int>(blockIdx.x) / p.H, h = static_cast<int>(blockIdx.x) - chunk * p.H;
+  const int step_c = static_cast<int>(gridDim.x) / p.H, step_h = static_cast<int>(gridDim.x) - step_c * p.H;
+  if (tid == 0 && chunk < p.total_chunks) load_a(chunk, h);
   bool alive = true;
 
   // raw gate values of a unit: threads 0-63 fetch them one unit ahead, so that the loads are not waited for
   float gl_n = 0.f, gi_n = 0.f, bi_n = 0.f;
-  auto fetch_gates = [&](long long unit) {
-    const int chunk = static_cast<int>(unit / p.H), h = static_cast<int>(unit - static_cast<long long>(chunk) * p.H);
+  auto fetch_gates = [&](int chunk, int h) {
     const ChunkPos cp = chunk_lookup(p.sa, chunk);
     const size_t base = static_cast<size_t>(cp.tok0) * p.H + h;
     gl_n = __ldg(p.g_cum + base + static_cast<size_t>(cp.len - 1) * p.H);
@@ -202,11 +202,13 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       bi_n = __ldg(p.beta + base + static_cast<size_t>(tid) * p.H);
     }
   };
-  if (tid < kChunk && blockIdx.x < n_units) fetch_gates(blockIdx.x);
+  if (tid < kChunk && chunk < p.total_chunks) fetch_gates(chunk, h);
 #pragma unroll 1
-  for (long long unit = blockIdx.x; unit < n_units && alive; unit += gridDim.x) {
-    const int chunk = static_cast<int>(unit / p.H), h = static_cast<int>(unit - static_cast<long long>(chunk) * p.H);
-    const int hg = h / (p.H / p.Hg);
+  for (int iter = 0; chunk < p.total_chunks && alive; ++iter) {
+    int nchunk = chunk + step_c, nh = h + step_h;  // this CTA's next unit
+    if (nh >= p.H) { nh -= p.H; ++nchunk; }
+    const bool has_next = nchunk < p.total_chunks;
+    const int hg = h / heads_per_group;
     const ChunkPos cp = chunk_lookup(p.sa, chunk);
     const int len = cp.len;
     unsigned char* b_ag = b_at + 8192;
@@ -216,7 +218,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     __syncthreads();  // the previous unit's shared-memory reads are complete
     BC_TS(0);
 
-    if (tid == 0 && unit == blockIdx.x) load_b(unit, 2, b_kt, b_qt, b_at, b_pg);  // later units: requested a unit ahead
+    if (tid == 0 && iter == 0) load_b(chunk, h, 2, b_kt, b_qt, b_at, b_pg);  // later units: requested a unit ahead
     if (tid < kChunk) {
       const float gl = gl_n, gi = gi_n, bi = bi_n;
       s.g[tid] = gi;
@@ -287,7 +289,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     __syncwarp();
     BC_TS(17);
     // while the first round runs: the next unit's gate values
-    if (tid < kChunk && unit + gridDim.x < n_units) fetch_gates(unit + gridDim.x);
+    if (tid < kChunk && has_next) fetch_gates(nchunk, nh);
     if (!mbar_wait(wc, &s.bar_mma, mma_phase, 2)) { alive = false; break; }
     mma_phase ^= 1;
     BC_TS(3);
@@ -461,6 +463,12 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     mma_phase ^= 1;
     BC_TS(7);
     tc_fence_after();
+    // The tiles that round three read last are dead from here on; two threads request this CTA's next unit there:
+    // S0, dS, V, dO in place, and K, Q, A, A_g into V', dVg and dV'.  They land while rounds three to six finish.
+    if (lane == 0 && has_next) {
+      if (warp == 2) load_a(nchunk, nh);
+      if (warp == 3) load_b(nchunk, nh, 0, b_vp, b_dvg, b_dvp, b_t12);
+    }
     {
       // dg += rowsum(K o accK); then accK += rho o K1 ; kk = rowsum(K o rho K1)
       float kkp = 0.f, kap = 0.f;
@@ -593,12 +601,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                   id64_16_mnk, kk > 0);
       }
       umma_commit(&s.bar_mma);
-      // Tiles that were last read in round three are dead; two of the issuing threads request this CTA's next unit
-      // there: S0, dS, V, dO in place, and K, Q, A, A_g into V', dVg and dV'.
-      if (unit + gridDim.x < n_units) {
-        if (warp == 2) load_a(unit + gridDim.x);
-        if (warp == 3) load_b(unit + gridDim.x, 0, b_vp, b_dvg, b_dvp, b_t12);
-      }
     }
     __syncwarp();
     if (!mbar_wait(wc, &s.bar_mma, mma_phase, 5)) { alive = false; break; }
@@ -673,7 +675,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
       umma_commit(&s.bar_mma);
       // T was last read in round four: the next unit's P_g goes there
-      if (warp == 3 && unit + gridDim.x < n_units) load_b(unit + gridDim.x, 1, b_vp, b_dvg, b_dvp, b_t12);
+      if (warp == 3 && has_next) load_b(nchunk, nh, 1, b_vp, b_dvg, b_dvp, b_t12);
     }
     __syncwarp();
     if (!mbar_wait(wc, &s.bar_mma, mma_phase, 6)) { alive = false; break; }
@@ -781,6 +783,8 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       t = b_at; b_at = b_dvp; b_dvp = t;
       t = b_pg; b_pg = b_t12; b_t12 = t;
     }
+    chunk = nchunk;
+    h = nh;
   }
 
   if (!alive && tid == 0) {
