@@ -12,7 +12,7 @@ from .planner import plan_cp
 
 
 def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, initial_state=None, cu_seqlens=None,
-                               gated_tiles=None):
+                               gated_tiles=None, plan=None):
     """``gated_tiles`` = (A_g, P_g) as produced by the forward for the same inputs; when given, the pass that
     rebuilds them from ``A`` is skipped (the autograd function keeps them unless FLASHQLA_RECOMPUTE_TILES=1)."""
     kernels._require_cuda(q, k, v, g, beta, A, do)
@@ -23,7 +23,7 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
     if scale is None:
         scale = K ** -0.5
     dev = q.device
-    plan = make_plan(B, T, cu_seqlens, dev)
+    plan = plan if plan is not None else make_plan(B, T, cu_seqlens, dev)
     check = os.environ.get("FLASHQLA_CHECK_STATUS", "0") == "1"
     status = kernels._status_tensor(dev) if check else None
     st_p = None if status is None else status.data_ptr()

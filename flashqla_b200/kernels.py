@@ -22,14 +22,14 @@ def _require_cuda(*ts):
             raise _lib.FlashQLAError("flashqla_b200 kernels need CUDA tensors (there is no CPU path)")
 
 
-def make_plan(B: int, T: int, cu_seqlens, device) -> SeqPlan:
+def make_plan(B: int, T: int, cu_seqlens, device, host=None) -> SeqPlan:
     if cu_seqlens is None:
         return plan_dense(B, T)
     if B != 1:
         raise ValueError(
             f"The batch size is expected to be 1 rather than {B} when using `cu_seqlens`."
             f"Please flatten variable-length inputs before processing.")
-    return plan_packed(cu_seqlens, device)
+    return plan_packed(cu_seqlens, device, host=host)
 
 
 def chunk_local_cumsum(g: torch.Tensor, chunk_size: int = CHUNK, reverse: bool = False, cu_seqlens=None,

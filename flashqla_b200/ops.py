@@ -54,7 +54,7 @@ def l2norm(x: torch.Tensor, dim: int = -1, eps: float = 1e-6) -> torch.Tensor:
 
 
 def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None, cu_seqlens=None,
-                               output_final_state=True, output_h=False, auto_cp=True, _return_tiles=False):
+                               output_final_state=True, output_h=False, auto_cp=True, _return_tiles=False, _plan=None):
     """Forward pipeline (chunk/__init__.py:17-67): cumsum -> K K^T + solve (+ gated tiles) -> fused recurrence.
 
     Returns ``(g_cumsum, A, o, h, final_state)``; ``A`` is the gate-free inverse (opaque, only
@@ -64,7 +64,7 @@ def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None,
     H = v.shape[2]
     if scale is None:
         scale = K ** -0.5
-    plan = make_plan(B, T, cu_seqlens, q.device)
+    plan = _plan if _plan is not None else make_plan(B, T, cu_seqlens, q.device)
     g_cum = kernels.chunk_local_cumsum(g, cu_seqlens=cu_seqlens, plan=plan)
     A, Ag, Pg = kernels.kkt_solve_gated(k, q, beta, g_cum, scale, plan)
     status = kernels._status_tensor(q.device) if _DEBUG_STATUS else None
@@ -86,12 +86,12 @@ def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None,
 
 
 def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, initial_state=None, cu_seqlens=None,
-                               _gated_tiles=None):
+                               _gated_tiles=None, _plan=None):
     """Backward pipeline (chunk/__init__.py:70-113).  ``g`` is the cumsum returned by the forward,
     ``A`` the tensor returned by the forward.  Returns ``(dq, dk, dv, db, dg, dh0)``."""
     from . import bwd  # the backward kernels live in their own module
     return bwd.chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht, scale, initial_state, cu_seqlens,
-                                          gated_tiles=_gated_tiles)
+                                          gated_tiles=_gated_tiles, plan=_plan)
 
 
 class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
@@ -100,10 +100,13 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
 
     @staticmethod
     @torch.amp.custom_fwd(device_type="cuda")
-    def forward(ctx, q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None):
+    def forward(ctx, q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None,
+                plan=None):
         g_cum, A, o, _, final_state, tiles = chunk_gated_delta_rule_fwd(
             q=q, k=k, v=v, g=g, beta=beta, scale=scale, initial_state=initial_state,
-            output_final_state=output_final_state, output_h=False, cu_seqlens=cu_seqlens, _return_tiles=True)
+            output_final_state=output_final_state, output_h=False, cu_seqlens=cu_seqlens, _return_tiles=True,
+            _plan=plan)
+        ctx.plan = plan  # the backward reuses the forward's sequence plan (no second look at cu_seqlens)
         ctx.keep_tiles = not _RECOMPUTE_TILES
         if ctx.keep_tiles:
             ctx.save_for_backward(q, k, v, g_cum, beta, A, initial_state, cu_seqlens, *tiles)
@@ -121,22 +124,33 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
         tiles = tuple(ctx.saved_tensors[8:10]) if ctx.keep_tiles else None
         dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(
             q=q, k=k, v=v, g=g_cum, beta=beta, A=A, do=do, dht=dht, scale=ctx.scale,
-            initial_state=initial_state, cu_seqlens=cu_seqlens, _gated_tiles=tiles)
+            initial_state=initial_state, cu_seqlens=cu_seqlens, _gated_tiles=tiles, _plan=ctx.plan)
         return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dg.to(ctx.g_dtype), db.to(ctx.beta_dtype),
-                None, dh0, None, None)
+                None, dh0, None, None, None)
 
 
 @torch.compiler.disable
 def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
-                           use_qk_l2norm_in_kernel=False, cu_seqlens=None, head_first=False):
-    """Public, differentiable entry (chunk/__init__.py:183-237).  Returns ``(o, final_state)``."""
+                           use_qk_l2norm_in_kernel=False, cu_seqlens=None, head_first=False, cu_seqlens_cpu=None):
+    """Public, differentiable entry (chunk/__init__.py:183-237).  Returns ``(o, final_state)``.
+
+    ``cu_seqlens_cpu`` (not in the reference) is an optional host copy of ``cu_seqlens``; with it the variable-length
+    schedule is made without reading the device tensor back, so the call neither synchronises nor blocks capture into
+    a CUDA graph."""
     assert q.dtype == k.dtype == v.dtype
     assert q.dtype != torch.float32, (
         "ChunkGatedDeltaRuleFunction does not support float32. Please use bfloat16 or float16.")
     assert not head_first, "head_first=True is not supported."
     assert v.shape[2] % k.shape[2] == 0, "num_qk_heads must be divisible to num_v_heads."
+    if q.dtype == torch.float16:
+        # The kernels are built for bfloat16 operands only.  float16 inputs are cast in and the output cast back (one
+        # extra elementwise pass per tensor; autograd casts the gradients the same way), so the arithmetic is bfloat16.
+        o, final_state = chunk_gated_delta_rule(q.bfloat16(), k.bfloat16(), v.bfloat16(), g, beta, scale, initial_state,
+                                                output_final_state, use_qk_l2norm_in_kernel, cu_seqlens, head_first,
+                                                cu_seqlens_cpu)
+        return o.to(torch.float16), final_state
     if q.dtype != torch.bfloat16:
-        raise _lib.FlashQLAError("the sm_100a kernels take bfloat16 q/k/v; float16 is not built")
+        raise _lib.FlashQLAError("the sm_100a kernels take bfloat16 (or float16, computed as bfloat16) q/k/v")
     if cu_seqlens is not None:
         if q.shape[0] != 1:
             raise ValueError(
@@ -151,4 +165,6 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
     if use_qk_l2norm_in_kernel:
         q = l2norm(q)
         k = l2norm(k)
-    return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens)
+    plan = make_plan(q.shape[0], q.shape[1], cu_seqlens, q.device, host=cu_seqlens_cpu)
+    return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
+                                             plan)

@@ -68,8 +68,21 @@ def plan_dense(B: int, T: int) -> SeqPlan:
     return plan
 
 
-def plan_packed(cu_seqlens: torch.Tensor, device=None) -> SeqPlan:
-    """Plan for a packed batch.  ``cu_seqlens`` may live on the host or on the device."""
+def _to_device_i32(values, device) -> torch.Tensor:
+    """int32 device tensor from a host list / host tensor without a stream synchronisation (pinned staging buffer,
+    asynchronous copy on the current stream)."""
+    host = values if isinstance(values, torch.Tensor) else torch.tensor(values, dtype=torch.int32)
+    host = host.to(torch.int32).contiguous()
+    device = torch.device(device)
+    if device.type != "cuda":
+        return host.to(device)
+    return host.pin_memory().to(device, non_blocking=True)
+
+
+def plan_packed(cu_seqlens: torch.Tensor, device=None, host: torch.Tensor | None = None) -> SeqPlan:
+    """Plan for a packed batch.  ``cu_seqlens`` may live on the host or on the device; ``host`` is an optional host
+    copy of a device ``cu_seqlens``: with it the plan is made without reading the device tensor back, i.e. without a
+    synchronisation (the counterpart of the device-side TODO at flash_qla/utils/index.py:76 of the reference)."""
     if cu_seqlens.dim() != 1 or cu_seqlens.numel() < 2:
         raise ValueError("cu_seqlens must be a 1-D tensor with at least two entries")
     device = torch.device(device) if device is not None else cu_seqlens.device
@@ -78,12 +91,22 @@ def plan_packed(cu_seqlens: torch.Tensor, device=None) -> SeqPlan:
     if hit is not None and hit[0] is cu_seqlens:
         _CACHE.move_to_end(key)
         return hit[1]
-    cu = [int(x) for x in cu_seqlens.tolist()]
+    if host is not None:
+        if host.is_cuda or host.shape != cu_seqlens.shape:
+            raise ValueError("the host copy of cu_seqlens must be a CPU tensor of the same shape")
+        cu = [int(x) for x in host.tolist()]
+    else:
+        cu = [int(x) for x in cu_seqlens.tolist()]
     if cu[0] != 0 or any(cu[i + 1] < cu[i] for i in range(len(cu) - 1)):
         raise ValueError("cu_seqlens must start at 0 and be non-decreasing")
     off = chunk_offsets_from_lengths(cu)
-    cu_dev = cu_seqlens.to(device=device, dtype=torch.int32).contiguous()
-    off_dev = torch.tensor(off, dtype=torch.int32, device=device)
+    if cu_seqlens.device == device and cu_seqlens.dtype == torch.int32 and cu_seqlens.is_contiguous():
+        cu_dev = cu_seqlens
+    elif cu_seqlens.is_cuda:
+        cu_dev = cu_seqlens.to(device=device, dtype=torch.int32).contiguous()
+    else:
+        cu_dev = _to_device_i32(cu_seqlens, device)
+    off_dev = _to_device_i32(off, device)
     plan = SeqPlan(len(cu) - 1, off[-1], cu[-1], max((off[i + 1] - off[i]) for i in range(len(cu) - 1)),
                    cu_dev, off_dev, cu, off)
     _CACHE[key] = (cu_seqlens, plan)
@@ -224,7 +247,7 @@ def plan_cp(plan: SeqPlan, B: int, T: int, H: int, n_sm: int, device, piece_chun
             offs.append(offs[-1] + (b_ - a_ + CHUNK - 1) // CHUNK)
 
         def t(x):
-            return torch.tensor(x, dtype=torch.int32, device=device)
+            return _to_device_i32(x, device)
 
         result = CpPlan(len(starts), L, offs[-1], t(bounds), t(offs), t(seq_idx), t(out_f), t(out_b), t(starts), t(ends),
                         t(before), t(after), t(lastlen), t(send))

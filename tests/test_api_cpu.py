@@ -53,6 +53,18 @@ def test_planner_chunk_tables():
     assert (d.n_seq, d.total_chunks, d.max_chunks) == (3, 12, 4)
 
 
+def test_planner_takes_a_host_copy_of_cu_seqlens():
+    """A plan made from the host copy equals the plan made by reading the tensor itself."""
+    from flashqla_b200 import planner
+    cu = torch.tensor([0, 3, 64, 64, 200, 1000], dtype=torch.int32)
+    a = planner.plan_packed(cu.clone(), "cpu")
+    b = planner.plan_packed(cu.clone(), "cpu", host=cu.clone())
+    assert (a.n_seq, a.total_chunks, a.total_tokens, a.max_chunks) == (b.n_seq, b.total_chunks, b.total_tokens, b.max_chunks)
+    assert a.offsets_host == b.offsets_host and torch.equal(a.chunk_offsets, b.chunk_offsets)
+    with pytest.raises(ValueError):
+        planner.plan_packed(cu.clone(), "cpu", host=torch.tensor([0, 3], dtype=torch.int32))
+
+
 def test_public_operator_validation():
     import flash_qla
     q = torch.zeros(2, 64, 2, 128, dtype=torch.bfloat16)
