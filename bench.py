@@ -398,14 +398,18 @@ def main():
         g_cum = timed("chunk_cumsum", lambda: kernels.chunk_local_cumsum(d["g"], plan=plan), rec)
         A, Ag, Pg = timed("kkt_solve", lambda: kernels.kkt_solve_gated(d["k"], d["q"], d["beta"], g_cum, scale, plan), rec)
         warm = timed("cp_warmup", lambda: kernels.cp_warmup(g_cum, cp, Hv), rec) if cp is not None else None
+        # transition-matrix fallback for slowly decaying heads: state pass + chain (near-empty launches when no head needs it)
+        h0p = timed("cp_correct", lambda: kernels.cp_correct_states(d["q"], d["k"], d["v"], Ag, g_cum, d["beta"], scale,
+                                                                    d["h0"], cp, warm), rec) if cp is not None else None
         o, _, fs = timed("gdr_fwd", lambda: kernels.fused_gdr_fwd(d["q"], d["k"], d["v"], Ag, Pg, g_cum, d["beta"], scale,
-                                                                 initial_state=d["h0"], plan=plan, cp=cp, warmup=warm), rec)
-        n = 3 + (1 if cp is not None else 0)
+                                                                 initial_state=d["h0"], plan=plan, cp=cp, warmup=warm,
+                                                                 h0_piece=h0p), rec)
+        n = 3 + (5 if cp is not None else 0)  # scan, flag, resolve, state pass, chain
         if w["bwd"]:
             timed("backward", lambda: fq.chunk_gated_delta_rule_bwd(d["q"], d["k"], d["v"], g_cum, d["beta"], A, d["do"],
                                                                      d["dht"], scale, d["h0"], None), rec)
-            # kkt(gated) + fwd(h) + bwd_dh + bwd_chunk + reverse cumsum (+ 2 warm-up scans, + 2 head sums)
-            n += 5 + (2 if cp is not None else 0) + (2 if Hq < Hv else 0)
+            # fwd(h) + bwd_dh + bwd_chunk + reverse cumsum (+ 2 warm-up scans, 2 plan kernels, state pass, chain; + 2 head sums)
+            n += 4 + (6 if cp is not None else 0) + (2 if Hq < Hv else 0)
         if record:
             stamps.append(rec)
         launches[0] = n

@@ -69,8 +69,13 @@ struct FwdParams {
   float* ht;            // [n_out, H, 128, 128] or nullptr
   const int* ht_index;  // [n_seq] slot in ht per piece (negative: do not write) or nullptr (= piece index)
   const int* h0_index;  // [n_seq] slot in h0 per piece or nullptr (= piece index)
-  const int* warmup;    // [n_seq, H] chunks to replay before the piece; bit 30 set = the replay starts at the
-                        //            sequence start (use h0), else start from zero.  nullptr = {0 | bit 30}
+  const int* warmup;    // [n_entries, H] chunks to replay before the piece; bit 30 set = the replay starts at the
+                        //            sequence start (use h0), else start from zero.  nullptr = {0 | bit 30}.
+                        //            bit 29: start from h0_piece[piece] (no replay); bit 28: transition run (S = I and
+                        //            the V tile ignored: the final state is the piece's transition matrix);
+                        //            bit 27: nothing to do for this (entry, head)
+  const int* piece_map; // [n_entries] piece of each grid entry, or nullptr (= entry); warmup and ht_index are per entry
+  const float* h0_piece;  // [n_pieces, H, 128, 128] corrected start states (bit 29) or nullptr
   __nv_bfloat16* o;     // [rows, H, 128] or nullptr
   __nv_bfloat16* h_out; // [total_chunks, H, 128(v), 128(k)] TRANSPOSED state before each chunk, or nullptr
                         // (written by TMA straight from the bf16 operand buffer)
@@ -91,7 +96,8 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   FwdSmem& s = *reinterpret_cast<FwdSmem*>(
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int seq = blockIdx.x / p.H, h = blockIdx.x - seq * p.H;
+  const int entry = blockIdx.x / p.H, h = blockIdx.x - entry * p.H;
+  const int seq = p.piece_map ? __ldg(p.piece_map + entry) : entry;
   const int hg = h / (p.H / p.Hg);
   int tok_begin, seq_len, chunk_off;
   if (p.sa.cu_seqlens == nullptr) {
@@ -104,10 +110,11 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     chunk_off = __ldg(p.sa.chunk_offsets + seq);
   }
   const int nchunks = (seq_len + kChunk - 1) / kChunk;
-  const int warm_code = p.warmup ? __ldg(p.warmup + static_cast<size_t>(seq) * p.H + h) : (1 << 30);
+  const int warm_code = p.warmup ? __ldg(p.warmup + static_cast<size_t>(entry) * p.H + h) : (1 << 30);
   const int warm = warm_code & 0xFFFFFF;
-  const bool use_h0 = (warm_code >> 30) & 1;
-  const int total = nchunks > 0 ? warm + nchunks : 0;  // iterations; iteration `it` handles chunk n = it - warm
+  const bool use_h0 = (warm_code >> 30) & 1, use_piece_h0 = (warm_code >> 29) & 1, transition = (warm_code >> 28) & 1,
+             skip = (warm_code >> 27) & 1;
+  const int total = (nchunks > 0 && !skip) ? warm + nchunks : 0;  // iterations; iteration `it` handles chunk n = it - warm
   WaitCtx wc{&s.abort_flag, p.status_dev, 1};
 
   if (tid == 0) {
@@ -175,9 +182,11 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (!mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2)) break;
         FQ_TS(it, 0);
         tc_fence_after();
+        if (!transition) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)  // V_d^T = V^T A_g^T (A operand = the V tile as loaded, MN-major)
-          umma_ss(tm + kColVD, desc_add(d_vmn, kk * 2048), desc_add(d_a, kk * 32), id64_amn, kk > 0);
+          for (int kk = 0; kk < 4; ++kk)  // V_d^T = V^T A_g^T (A operand = the V tile as loaded, MN-major)
+            umma_ss(tm + kColVD, desc_add(d_vmn, kk * 2048), desc_add(d_a, kk * 32), id64_amn, kk > 0);
+        }
         if (!mbar_wait_spin(wc, &s.s_ready, ph, 3)) break;
         FQ_TS(it, 1);
         tc_fence_after();
@@ -199,7 +208,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // V_d^T -= (gamma o U)^T A_g^T
-          umma_ss(tm + kColVD, desc_add(d_w, kk * 32), desc_add(d_a, kk * 32), id64, 1);
+          umma_ss(tm + kColVD, desc_add(d_w, kk * 32), desc_add(d_a, kk * 32), id64, (transition && kk == 0) ? 0 : 1);
         umma_commit(&s.vd_done);
         FQ_TS(it, 6);
         if (!mbar_wait_spin(wc, &s.vp_ready, ph, 7)) break;
@@ -251,12 +260,16 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     {
       const int slot = p.h0_index ? __ldg(p.h0_index + seq) : seq;
       const float* src = (p.h0 && use_h0) ? p.h0 + (static_cast<size_t>(slot) * p.H + h) * kDim * kDim + v : nullptr;
+      if (use_piece_h0) src = p.h0_piece + (static_cast<size_t>(seq) * p.H + h) * kDim * kDim + v;
 #pragma unroll 1
       for (int pc = 0; pc < 2; ++pc) {
         uint32_t r[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          r[i] = src ? __float_as_uint(__ldg(src + static_cast<size_t>(64 * hf + 32 * pc + i) * kDim)) : 0u;
+        for (int i = 0; i < 32; ++i) {
+          const int kcol = 64 * hf + 32 * pc + i;
+          r[i] = src ? __float_as_uint(__ldg(src + static_cast<size_t>(kcol) * kDim))
+                     : ((transition && kcol == v) ? 0x3F800000u : 0u);
+        }
         tmem_st32(tmem_addr(tm, lane_base, kColS + 64 * hf + 32 * pc), r);
       }
       tmem_wait_st();
@@ -380,8 +393,8 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       alive = mbar_wait(wc, &s.s_done, (total - 1) & 1, 17);
       tc_fence_after();
     }
-    const int slot = p.ht_index ? __ldg(p.ht_index + seq) : seq;
-    if (alive && p.ht && slot >= 0) {
+    const int slot = p.ht_index ? __ldg(p.ht_index + entry) : entry;
+    if (alive && p.ht && slot >= 0 && !skip) {
       float* dst = p.ht + (static_cast<size_t>(slot) * p.H + h) * kDim * kDim + v;
 #pragma unroll 1
       for (int pc = 0; pc < 2; ++pc) {
@@ -461,7 +474,22 @@ extern "C" FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v,
                                     const int32_t* h0_index, const int32_t* warmup, void* o, void* h_out, int B, int T,
                                     int H, int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
                                     int total_chunks, float scale, int32_t* status_dev, void* stream) {
+  return fq_gdr_fwd_cp_ex(q, k, v, Ag, Pg, g_cumsum, beta, h0, ht, ht_index, h0_index, warmup, nullptr, n_seq, nullptr, o,
+                          h_out, B, T, H, Hg, cu_seqlens, chunk_offsets, n_seq, total_chunks, scale, status_dev, stream);
+}
+
+extern "C" FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void* v, const void* Ag, const void* Pg,
+                                       const float* g_cumsum, const float* beta, const float* h0, float* ht,
+                                       const int32_t* ht_index, const int32_t* h0_index, const int32_t* warmup,
+                                       const int32_t* piece_map, int n_entries, const float* h0_piece, void* o,
+                                       void* h_out, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
+                                       const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
+                                       int32_t* status_dev, void* stream) {
   using namespace fq;
+  FQ_CHECK_ARG(n_entries > 0 && (piece_map != nullptr || n_entries == n_seq),
+               "fq_gdr_fwd: a grid of entries other than the pieces needs piece_map");
+  FQ_CHECK_ARG(piece_map == nullptr || (o == nullptr && h_out == nullptr),
+               "fq_gdr_fwd: mapped entries are for state-only runs");
   FQ_CHECK_ARG(q && k && v && Ag && g_cumsum && beta, "fq_gdr_fwd: null input tensor");
   FQ_CHECK_ARG(o == nullptr || Pg != nullptr, "fq_gdr_fwd: P_g is needed when o is requested");
   FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0, "fq_gdr_fwd: bad sizes");
@@ -490,7 +518,7 @@ extern "C" FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v,
   }
   FwdParams p;
   p.g_cum = g_cumsum; p.beta = beta; p.h0 = h0; p.ht = ht; p.ht_index = ht_index; p.h0_index = h0_index;
-  p.warmup = warmup;
+  p.warmup = warmup; p.piece_map = piece_map; p.h0_piece = h0_piece;
   p.o = static_cast<__nv_bfloat16*>(o); p.h_out = static_cast<__nv_bfloat16*>(h_out);
   p.H = H; p.Hg = Hg; p.scale = scale;
   p.sa = SeqArgs{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
@@ -503,7 +531,7 @@ extern "C" FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v,
     FQ_CHECK_CUDA(cudaFuncSetAttribute(gdr_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     attr_set[dev] = true;
   }
-  const long long ctas = static_cast<long long>(n_seq) * H;
+  const long long ctas = static_cast<long long>(n_entries) * H;
   FQ_CHECK_ARG(ctas < (1ll << 31), "fq_gdr_fwd: too many (sequence, head) pairs");
   gdr_fwd_kernel<<<static_cast<unsigned>(ctas), kFwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, ma, mpg, mh, p);
   FQ_CHECK_CUDA(cudaGetLastError());

@@ -4,6 +4,8 @@ All tensors must live on the current CUDA device; work is enqueued on the curren
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
+
 import torch
 
 from . import _lib
@@ -121,22 +123,66 @@ def sm_count(device) -> int:
     return torch.cuda.get_device_properties(device).multi_processor_count
 
 
+@dataclass
+class CpWarm:
+    """Start-up codes of a context-parallel forward run (csrc/cp.cu): `codes` [P,H] for the final pass, `pass1`
+    [2P,H] for the state pass of the transition-matrix fallback, `flags` [n_seq,H] = which (sequence, head) pairs
+    use that fallback."""
+    codes: torch.Tensor
+    pass1: torch.Tensor
+    flags: torch.Tensor
+
+
 def cp_warmup(g_cum, cp, H, threshold=-16.0, reverse=False):
-    """Chunks to replay per (piece, head) for a context-parallel run (see csrc/cp.cu)."""
+    """Chunks to replay per (piece, head) for a context-parallel run (see csrc/cp.cu).  Forward direction: a CpWarm,
+    in which pairs whose replay would exceed one piece length are switched to corrected start states; reverse
+    direction: the plain [P,H] table."""
     out = torch.empty(cp.n_pieces, H, dtype=torch.int32, device=g_cum.device)
-    if not reverse:
-        rc = _lib.load().fq_cp_warmup(g_cum.data_ptr(), cp.piece_start.data_ptr(), cp.chunks_before.data_ptr(), None,
-                                      out.data_ptr(), cp.n_pieces, H, float(threshold), 0, _stream())
-    else:
-        rc = _lib.load().fq_cp_warmup(g_cum.data_ptr(), cp.piece_end.data_ptr(), cp.last_chunk_len.data_ptr(),
-                                      cp.chunks_after.data_ptr(), out.data_ptr(), cp.n_pieces, H, float(threshold), 1,
-                                      _stream())
+    lib = _lib.load()
+    if reverse:
+        rc = lib.fq_cp_warmup(g_cum.data_ptr(), cp.piece_end.data_ptr(), cp.last_chunk_len.data_ptr(),
+                              cp.chunks_after.data_ptr(), out.data_ptr(), cp.n_pieces, H, float(threshold), 1, _stream())
+        _lib.check(rc, "fq_cp_warmup")
+        return out
+    rc = lib.fq_cp_warmup(g_cum.data_ptr(), cp.piece_start.data_ptr(), cp.chunks_before.data_ptr(), None,
+                          out.data_ptr(), cp.n_pieces, H, float(threshold), 0, _stream())
     _lib.check(rc, "fq_cp_warmup")
-    return out
+    codes = torch.empty_like(out)
+    pass1 = torch.empty(2 * cp.n_pieces, H, dtype=torch.int32, device=g_cum.device)
+    flags = torch.empty(cp.n_seq, H, dtype=torch.int32, device=g_cum.device)
+    rc = lib.fq_cp_transition_plan(out.data_ptr(), cp.seq_index.data_ptr(), cp.chunks_before.data_ptr(),
+                                   cp.chunks_after.data_ptr(), flags.data_ptr(), codes.data_ptr(), pass1.data_ptr(),
+                                   cp.n_pieces, cp.n_seq, H, int(cp.piece_chunks), _stream())
+    _lib.check(rc, "fq_cp_transition_plan")
+    return CpWarm(codes, pass1, flags)
+
+
+def cp_correct_states(q, k, v, ag, g, b, scale, h0, cp, warm: CpWarm, status=None):
+    """Corrected start state of every piece for the (sequence, head) pairs flagged in `warm` (other slots are left
+    unwritten): one state-only launch over 2P entries (end state from zero, transition matrix) and the chain
+    h0[r+1] = T_r h0[r] + B_r.  All inputs contiguous, as prepared by fused_gdr_fwd."""
+    B, T, Hg, K = k.shape
+    H = v.shape[2]
+    dev = q.device
+    P = cp.n_pieces
+    bt = torch.empty(2 * P, H, K, K, dtype=torch.float32, device=dev)
+    h0_piece = torch.empty(P, H, K, K, dtype=torch.float32, device=dev)
+    p = lambda t: None if t is None else t.data_ptr()
+    lib = _lib.load()
+    rc = lib.fq_gdr_fwd_cp_ex(q.data_ptr(), k.data_ptr(), v.data_ptr(), ag.data_ptr(), None, g.data_ptr(), b.data_ptr(),
+                              p(h0), bt.data_ptr(), cp.entry_slot.data_ptr(), cp.seq_index.data_ptr(),
+                              warm.pass1.data_ptr(), cp.entry_piece.data_ptr(), 2 * P, None, None, None, 1, B * T, H, Hg,
+                              cp.cu_seqlens.data_ptr(), cp.chunk_offsets.data_ptr(), P, cp.total_chunks, float(scale),
+                              p(status), _stream())
+    _lib.check(rc, "fq_gdr_fwd_cp_ex")
+    rc = lib.fq_cp_chain(bt.data_ptr(), h0_piece.data_ptr(), warm.flags.data_ptr(), cp.seq_piece_offsets.data_ptr(), P,
+                         cp.n_seq, H, _stream())
+    _lib.check(rc, "fq_cp_chain")
+    return h0_piece
 
 
 def fused_gdr_fwd(q, k, v, ag, pg, g, b, scale, initial_state=None, output_final_state=True, output_h=False,
-                  output_o=True, plan: SeqPlan | None = None, cp=None, warmup=None, status=None):
+                  output_o=True, plan: SeqPlan | None = None, cp=None, warmup=None, status=None, h0_piece=None):
     """Fused forward recurrence.  g is the chunk-local cumsum, ag / pg the gated tiles from kkt_solve_gated.
     With a CpPlan `cp` (and its `warmup` table) every piece of a sequence runs as its own CTA.
 
@@ -169,10 +215,17 @@ def fused_gdr_fwd(q, k, v, ag, pg, g, b, scale, initial_state=None, output_final
                                     b.data_ptr(), p(h0), p(ht), None, p(o), p(h), B, T, H, Hg, cu_p, off_p, plan.n_seq,
                                     plan.total_chunks, float(scale), p(status), _stream())
     else:
-        rc = _lib.load().fq_gdr_fwd_cp(q.data_ptr(), k.data_ptr(), v.data_ptr(), ag.data_ptr(), p(pg), g.data_ptr(),
-                                       b.data_ptr(), p(h0), p(ht), cp.out_index_fwd.data_ptr(), cp.seq_index.data_ptr(),
-                                       warmup.data_ptr(), p(o), p(h), 1, B * T, H, Hg, cp.cu_seqlens.data_ptr(),
-                                       cp.chunk_offsets.data_ptr(), cp.n_pieces, cp.total_chunks, float(scale),
-                                       p(status), _stream())
+        if isinstance(warmup, CpWarm):
+            if h0_piece is None:
+                h0_piece = cp_correct_states(q, k, v, ag, g, b, scale, h0, cp, warmup, status)
+            codes = warmup.codes
+        else:
+            codes = warmup
+        rc = _lib.load().fq_gdr_fwd_cp_ex(q.data_ptr(), k.data_ptr(), v.data_ptr(), ag.data_ptr(), p(pg), g.data_ptr(),
+                                          b.data_ptr(), p(h0), p(ht), cp.out_index_fwd.data_ptr(),
+                                          cp.seq_index.data_ptr(), codes.data_ptr(), None, cp.n_pieces, p(h0_piece),
+                                          p(o), p(h), 1, B * T, H, Hg, cp.cu_seqlens.data_ptr(),
+                                          cp.chunk_offsets.data_ptr(), cp.n_pieces, cp.total_chunks, float(scale),
+                                          p(status), _stream())
     _lib.check(rc, "fq_gdr_fwd")
     return o, h, ht

@@ -154,6 +154,10 @@ class CpPlan:
     chunks_after: torch.Tensor      # [P] chunks of the sequence that follow the piece
     last_chunk_len: torch.Tensor    # [P] tokens in the last chunk of the piece's sequence
     seq_end: torch.Tensor           # [P] first token after the piece's sequence
+    seq_piece_offsets: torch.Tensor = None  # [n_seq+1] first piece of every sequence
+    entry_piece: torch.Tensor = None        # [2P] piece of every entry of the two-run state pass (0..P-1 twice)
+    entry_slot: torch.Tensor = None         # [2P] 0..2P-1: where each entry's end state goes
+    n_seq: int = 0
 
 
 def _makespan(pieces: list, H: int, n_sm: int, overhead: int) -> float:
@@ -249,8 +253,13 @@ def plan_cp(plan: SeqPlan, B: int, T: int, H: int, n_sm: int, device, piece_chun
         def t(x):
             return _to_device_i32(x, device)
 
-        result = CpPlan(len(starts), L, offs[-1], t(bounds), t(offs), t(seq_idx), t(out_f), t(out_b), t(starts), t(ends),
-                        t(before), t(after), t(lastlen), t(send))
+        P = len(starts)
+        seq_off = [0]
+        for i in range(len(n_chunks)):
+            seq_off.append(seq_off[-1] + sum(1 for s_ in seq_idx if s_ == i))
+        result = CpPlan(P, L, offs[-1], t(bounds), t(offs), t(seq_idx), t(out_f), t(out_b), t(starts), t(ends),
+                        t(before), t(after), t(lastlen), t(send), t(seq_off), t(list(range(P)) * 2), t(list(range(2 * P))),
+                        len(n_chunks))
     _CP_CACHE[key] = (plan, result)
     if len(_CP_CACHE) > _CACHE_SIZE:
         _CP_CACHE.popitem(last=False)

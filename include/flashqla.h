@@ -115,6 +115,42 @@ FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v, const void
                          float scale, int32_t* status_dev, void* stream);
 
 /*
+ * fq_gdr_fwd_cp over a grid of `n_entries` entries instead of one per piece: entry e runs piece piece_map[e]
+ * (NULL = e; mapped entries are state-only runs), `warmup` and `ht_index` are indexed by entry.  Further bits of
+ * warmup[e*H+h]: bit 29 = start from h0_piece[piece] ([n_pieces,H,128,128] fp32) without replay; bit 28 =
+ * transition run (state = identity, V ignored: the final state written to ht is the piece's K x K transition
+ * matrix); bit 27 = nothing to do.  Together with fq_cp_transition_plan and fq_cp_chain this is the counterpart
+ * of the (ht, mt) correction of flash_qla/ops/gated_delta_rule/chunk/hopper/cp_fwd.py:256-309, used for heads
+ * whose gate decays too slowly for a replay.
+ */
+FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void* v, const void* Ag, const void* Pg,
+                            const float* g_cumsum, const float* beta, const float* h0, float* ht,
+                            const int32_t* ht_index, const int32_t* h0_index, const int32_t* warmup,
+                            const int32_t* piece_map, int n_entries, const float* h0_piece, void* o, void* h_out, int B,
+                            int T, int H, int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
+                            int total_chunks, float scale, int32_t* status_dev, void* stream);
+
+/*
+ * Which (sequence, head) pairs fall back to transition matrices, and the codes of the two passes.
+ *   warmup_in [n_pieces,H] from fq_cp_warmup (reverse == 0); piece_seq / chunks_before / chunks_after [n_pieces].
+ *   flags [n_seq,H] (out): 1 where some piece would replay more than w_max chunks.
+ *   warmup_out [n_pieces,H]: codes of the final pass (bit 29 for every piece but the first of a flagged pair).
+ *   pass1_codes [2*n_pieces,H]: entry r = end state of piece r from zero (from h0 for a first piece), entry
+ *   n_pieces + r = transition matrix of piece r; bit 27 where not needed.
+ */
+FQ_API int fq_cp_transition_plan(const int32_t* warmup_in, const int32_t* piece_seq, const int32_t* chunks_before,
+                                 const int32_t* chunks_after, int32_t* flags, int32_t* warmup_out, int32_t* pass1_codes,
+                                 int n_pieces, int n_seq, int H, int w_max, void* stream);
+
+/*
+ * h0_piece[r+1] = T_r h0_piece[r] + B_r along the pieces of every flagged (sequence, head), in fp32.
+ *   bt [2*n_pieces,H,128,128]: B_r in slot r, T_r in slot n_pieces + r (the ht of the pass-1 run);
+ *   seq_piece_offsets [n_seq+1]: first piece of every sequence.
+ */
+FQ_API int fq_cp_chain(const float* bt, float* h0_piece, const int32_t* flags, const int32_t* seq_piece_offsets,
+                       int n_pieces, int n_seq, int H, void* stream);
+
+/*
  * Gate scan for context-parallel pieces (counterpart of get_warmup_chunks,
  * flash_qla/ops/gated_delta_rule/chunk/hopper/cp_fwd.py:69-101).  For every (piece, head) returns in
  * warmup[piece*H+h] the number of whole chunks adjacent to the piece that must be replayed so that

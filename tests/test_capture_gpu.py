@@ -12,6 +12,15 @@ from oracle import gdr_oracle as orc
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def _no_status_readback(monkeypatch):
+    """Other test modules switch on the debug read-back of the kernels' status word (a synchronisation by design);
+    these tests run the operator as a user does, without it."""
+    from flashqla_b200 import ops
+    monkeypatch.setenv("FLASHQLA_CHECK_STATUS", "0")
+    monkeypatch.setattr(ops, "_DEBUG_STATUS", False)
+
+
 def _inputs(seed, B, T, Hq, Hv, n_seq=None, dtype=torch.bfloat16):
     torch.manual_seed(seed)
     N = B if n_seq is None else n_seq
