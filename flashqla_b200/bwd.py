@@ -47,9 +47,14 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
         _, Ag, Pg = kernels.kkt_solve_gated(k, q, bt, g, scale, plan, A=A)
     from . import ops as _ops
     cp = plan_cp(plan, B, T, H, kernels.sm_count(dev), dev, piece_chunks=_ops._FORCE_PIECE_CHUNKS)
-    warm = kernels.cp_warmup(g, cp, H) if cp is not None else None
+    warm = h0_piece = tmats = None
+    if cp is not None:
+        # gate scans in both directions; pairs that would replay too far start from corrected states / gradients
+        warm = kernels.cp_warmup(g, cp, H, with_reverse=True)
+        h0_piece, tmats = kernels.cp_correct_states(q, k, v, Ag, g, bt, scale, h0, cp, warm, status, return_bt=True)
     _, h, _ = kernels.fused_gdr_fwd(q, k, v, Ag, None, g, bt, scale, initial_state=h0, output_final_state=False,
-                                    output_h=True, output_o=False, plan=plan, cp=cp, warmup=warm, status=status)
+                                    output_h=True, output_o=False, plan=plan, cp=cp, warmup=warm, status=status,
+                                    h0_piece=h0_piece)
     # 2. reverse recurrence of the state gradient
     dh = torch.empty_like(h)
     want_dh0 = (dht is not None) or (initial_state is not None)
@@ -62,13 +67,25 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
                                bt.data_ptr(), pp(dht_c), pp(dh0), dh.data_ptr(), B, T, H, Hg,
                                cu_p, off_p, plan.n_seq, plan.total_chunks, float(scale), st_p, kernels._stream())
     else:
-        warm_r = kernels.cp_warmup(g, cp, H, reverse=True)
-        rc = lib.fq_gdr_bwd_dh_cp(q.data_ptr(), k.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), do.data_ptr(), g.data_ptr(),
-                                  bt.data_ptr(), pp(dht_c), pp(dh0), dh.data_ptr(),
-                                  cp.seq_index.data_ptr(), cp.out_index_bwd.data_ptr(), cp.seq_end.data_ptr(),
-                                  warm_r.data_ptr(), 1, B * T, H, Hg, cp.cu_seqlens.data_ptr(),
-                                  cp.chunk_offsets.data_ptr(), cp.n_pieces, cp.total_chunks, float(scale), st_p,
-                                  kernels._stream())
+        P = cp.n_pieces
+        args = (q.data_ptr(), k.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), do.data_ptr(), g.data_ptr(), bt.data_ptr(),
+                pp(dht_c))
+        tail = (1, B * T, H, Hg, cp.cu_seqlens.data_ptr(), cp.chunk_offsets.data_ptr(), P, cp.total_chunks,
+                float(scale), st_p, kernels._stream())
+        # gradient pass of the flagged pairs: left-edge gradient C_r of every piece but the first (from zero; the last
+        # piece from dht), then e_{r-1} = T_r^T e_r + C_r down the pieces; dh is overwritten by the final pass
+        c_out = torch.empty(P, H, K, V, dtype=torch.float32, device=dev)
+        dht_piece = torch.empty(P, H, K, V, dtype=torch.float32, device=dev)
+        rc = lib.fq_gdr_bwd_dh_cp_ex(*args, c_out.data_ptr(), dh.data_ptr(), cp.seq_index.data_ptr(),
+                                     cp.entry_slot.data_ptr(), cp.seq_end.data_ptr(), warm.pass1_rev.data_ptr(), None,
+                                     *tail)
+        _lib.check(rc, "fq_gdr_bwd_dh")
+        rc = lib.fq_cp_chain_reverse(c_out.data_ptr(), tmats[P:].data_ptr(), dht_piece.data_ptr(), warm.flags.data_ptr(),
+                                     cp.seq_piece_offsets.data_ptr(), P, cp.n_seq, H, kernels._stream())
+        _lib.check(rc, "fq_cp_chain_reverse")
+        rc = lib.fq_gdr_bwd_dh_cp_ex(*args, pp(dh0), dh.data_ptr(), cp.seq_index.data_ptr(),
+                                     cp.out_index_bwd.data_ptr(), cp.seq_end.data_ptr(), warm.codes_rev.data_ptr(),
+                                     dht_piece.data_ptr(), *tail)
     _lib.check(rc, "fq_gdr_bwd_dh")
     # 3. chunk-parallel gradients
     dq_h = torch.empty(B, T, H, K, dtype=q.dtype, device=dev)

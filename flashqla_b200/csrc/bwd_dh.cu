@@ -57,6 +57,9 @@ struct BwdDhParams {
   const int* dh0_index;
   const int* seq_end;
   const int* warmup;
+  // further bits of warmup: bit 29 = start from dht_piece[piece] ([n_pieces, H, 128, 128] fp32, the corrected
+  // gradient at the piece's end) with no replay; bit 27 = nothing to do for this (piece, head)
+  const float* dht_piece;
   int H, Hg;
   float scale;
   SeqArgs sa;
@@ -89,7 +92,8 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const int nchunks = (seq_len + kChunk - 1) / kChunk;
   const int warm_code = p.warmup ? __ldg(p.warmup + static_cast<size_t>(seq) * p.H + h) : (1 << 30);
   const int warm = warm_code & 0xFFFFFF;
-  const bool use_dht = (warm_code >> 30) & 1;
+  const bool use_dht = (warm_code >> 30) & 1, use_piece_dht = (warm_code >> 29) & 1;
+  if ((warm_code >> 27) & 1) return;  // nothing to do: leave before any barrier or tensor memory is set up
   const int total = nchunks > 0 ? nchunks + warm : 0;  // iteration `it` handles chunk n = total - 1 - it of the piece
   // tokens available from the piece start to the end of its sequence (bounds the length of replayed chunks)
   const int avail = p.seq_end ? __ldg(p.seq_end + seq) - tok_begin : seq_len;
@@ -272,6 +276,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     {
       const int in_slot = p.dht_index ? __ldg(p.dht_index + seq) : seq;
       const float* src = (p.dht && use_dht) ? p.dht + (static_cast<size_t>(in_slot) * p.H + h) * kDim * kDim + v : nullptr;
+      if (use_piece_dht) src = p.dht_piece + (static_cast<size_t>(seq) * p.H + h) * kDim * kDim + v;
 #pragma unroll 1
       for (int cb = 0; cb < 4; ++cb) {
         uint32_t r[32];
@@ -411,6 +416,18 @@ extern "C" FQ_API int fq_gdr_bwd_dh_cp(const void* q, const void* k, const void*
                                        const int32_t* dh0_index, const int32_t* seq_end, const int32_t* warmup, int B,
                                        int T, int H, int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets,
                                        int n_seq, int total_chunks, float scale, int32_t* status_dev, void* stream) {
+  return fq_gdr_bwd_dh_cp_ex(q, k, Ag, Pg, dout, g_cumsum, beta, dht, dh0, dh_out, dht_index, dh0_index, seq_end, warmup,
+                             nullptr, B, T, H, Hg, cu_seqlens, chunk_offsets, n_seq, total_chunks, scale, status_dev,
+                             stream);
+}
+
+extern "C" FQ_API int fq_gdr_bwd_dh_cp_ex(const void* q, const void* k, const void* Ag, const void* Pg,
+                                          const void* dout, const float* g_cumsum, const float* beta, const float* dht,
+                                          float* dh0, void* dh_out, const int32_t* dht_index, const int32_t* dh0_index,
+                                          const int32_t* seq_end, const int32_t* warmup, const float* dht_piece, int B,
+                                          int T, int H, int Hg, const int32_t* cu_seqlens,
+                                          const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
+                                          int32_t* status_dev, void* stream) {
   using namespace fq;
   FQ_CHECK_ARG(q && k && Ag && Pg && dout && g_cumsum && beta && dh_out, "fq_gdr_bwd_dh: null tensor");
   FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0,
@@ -437,7 +454,7 @@ extern "C" FQ_API int fq_gdr_bwd_dh_cp(const void* q, const void* k, const void*
   p.g_cum = g_cumsum; p.beta = beta; p.dht = dht; p.dh0 = dh0;
   p.dh_out = static_cast<__nv_bfloat16*>(dh_out);
   p.dht_index = dht_index; p.dh0_index = dh0_index; p.seq_end = seq_end; p.warmup = warmup;
-  p.dht_index = dht_index; p.dh0_index = dh0_index; p.seq_end = seq_end; p.warmup = warmup;
+  p.dht_piece = dht_piece;
   p.H = H; p.Hg = Hg; p.scale = scale;
   p.sa = SeqArgs{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
   p.status_dev = status_dev;

@@ -11,48 +11,61 @@
 
 namespace fq {
 
+// One warp per (piece, head): lane l looks at the (32 i + l)-th chunk away from the piece, the running log-decay is an
+// inclusive warp scan, and the first chunk at which it drops below the threshold ends the replay.  `w_cap` bounds
+// the walk (0 = no bound): a replay that would be longer is reported as w_cap + 1 chunks without looking further,
+// which is all that the transition-matrix fallback needs to know.
 __global__ void __launch_bounds__(128) cp_warmup_kernel(const float* __restrict__ g_cum,
                                                        const int* __restrict__ piece_start,
                                                        const int* __restrict__ piece_first_chunk,
                                                        int* __restrict__ warmup, int n_pieces, int H, float threshold,
-                                                       int reverse, const int* __restrict__ piece_chunks_after) {
-  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+                                                       int reverse, const int* __restrict__ piece_chunks_after,
+                                                       int w_cap, const int* __restrict__ piece_seq,
+                                                       int* __restrict__ flags) {
+  const int idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (idx >= n_pieces * H) return;
   const int piece = idx / H, h = idx - piece * H;
-  if (!reverse) {
-    const int avail = __ldg(piece_first_chunk + piece);
-    const long long start = __ldg(piece_start + piece);
-    float acc = 0.f;
-    int w = 0;
-    bool decayed = false;
-    while (w < avail) {
-      acc += __ldg(g_cum + (start - static_cast<long long>(w) * kChunk - 1) * H + h);
-      ++w;
-      if (acc < threshold) { decayed = true; break; }
+  // forward: chunks before the piece, walking backwards from its first token; reverse (state gradient): chunks
+  // after the piece, walking forwards from the first token after it (piece_start holds that token,
+  // piece_chunks_after the number of chunks that follow and piece_first_chunk the length of the sequence's last chunk)
+  const int avail = reverse ? __ldg(piece_chunks_after + piece) : __ldg(piece_first_chunk + piece);
+  const long long edge = __ldg(piece_start + piece);
+  const int last_len = reverse ? __ldg(piece_first_chunk + piece) : kChunk;
+  const int limit = (w_cap > 0 && w_cap + 1 < avail) ? w_cap + 1 : avail;
+  float carry = 0.f;
+  int w = -1;
+  for (int base = 0; base < limit && w < 0; base += 32) {
+    const int c = base + lane;
+    float x = 0.f;
+    if (c < limit) {
+      long long tok;
+      if (!reverse) tok = edge - static_cast<long long>(c) * kChunk - 1;
+      else tok = edge + static_cast<long long>(c) * kChunk + ((c == avail - 1) ? last_len : kChunk) - 1;
+      x = __ldg(g_cum + tok * H + h);
     }
-    warmup[idx] = decayed ? w : (avail | (1 << 30));
-  } else {
-    // reverse direction (state gradient): replay the chunks AFTER the piece; piece_start holds the
-    // first token after the piece, piece_chunks_after the number of chunks that follow it in the
-    // sequence and piece_first_chunk the length in tokens of the sequence's last chunk.
-    const int avail = __ldg(piece_chunks_after + piece);
-    const long long end = __ldg(piece_start + piece);
-    const int last_len = __ldg(piece_first_chunk + piece);
-    float acc = 0.f;
-    int w = 0;
-    bool decayed = false;
-    while (w < avail) {
-      const int len = (w == avail - 1) ? last_len : kChunk;
-      acc += __ldg(g_cum + (end + static_cast<long long>(w) * kChunk + len - 1) * H + h);
-      ++w;
-      if (acc < threshold) { decayed = true; break; }
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const float y = __shfl_up_sync(0xffffffffu, x, d);
+      if (lane >= d) x += y;
     }
-    warmup[idx] = decayed ? w : (avail | (1 << 30));
+    x += carry;
+    const unsigned hit = __ballot_sync(0xffffffffu, c < limit && x < threshold);
+    if (hit) w = base + __ffs(hit);  // chunks replayed = index of the first hit + 1
+    carry = __shfl_sync(0xffffffffu, x, 31);
+  }
+  if (lane == 0) {
+    int code;
+    if (w > 0) code = w;                                   // decayed after w chunks
+    else if (limit == avail) code = avail | (1 << 30);     // reached the end of the sequence: exact
+    else code = limit;                                     // gave up at the cap
+    warmup[idx] = code;
+    // a replay of more than w_cap chunks: the (sequence, head) pair takes the transition-matrix route (see below)
+    if (flags != nullptr && (code & 0xFFFFFF) > w_cap) atomicOr(flags + __ldg(piece_seq + piece) * H + h, 1);
   }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Transition-matrix fallback.  A replay of more than `w_max` chunks costs more than it saves (a head whose gate
+// Transition-matrix fallback.  A replay of more than `w_cap` chunks costs more than it saves (a head whose gate
 // never decays would replay its whole prefix in every piece).  Such a (sequence, head) is flagged, and all of its
 // pieces then start from corrected states instead:
 //   pass 1  every piece r but the last runs state-only from zero (from h0 for the first piece): end state B_r; and,
@@ -63,14 +76,6 @@ __global__ void __launch_bounds__(128) cp_warmup_kernel(const float* __restrict_
 // Codes (per piece or pass-1 entry, and head), on top of the replay length in bits 0-23 and bit 30 (start from the
 // sequence's initial state): bit 29 = start from the piece's corrected state, bit 28 = transition run (S = I, V = 0),
 // bit 27 = nothing to do.
-
-__global__ void __launch_bounds__(128) cp_flag_kernel(const int* __restrict__ warmup, const int* __restrict__ piece_seq,
-                                                     int* __restrict__ flags, int n_pieces, int H, int w_max) {
-  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= n_pieces * H) return;
-  const int piece = idx / H, h = idx - piece * H;
-  if ((__ldg(warmup + idx) & 0xFFFFFF) > w_max) atomicOr(flags + __ldg(piece_seq + piece) * H + h, 1);
-}
 
 __global__ void __launch_bounds__(128) cp_resolve_kernel(const int* __restrict__ warmup_in,
                                                         const int* __restrict__ piece_seq,
@@ -90,47 +95,124 @@ __global__ void __launch_bounds__(128) cp_resolve_kernel(const int* __restrict__
   pass1[n_pieces * H + idx] = (flagged && !last && !first) ? (1 << 28) : kSkip;    // T_r
 }
 
-// h0_{r+1} = T_r h0_r + B_r for the pieces of one flagged (sequence, head); a CTA owns 16 of the 128 state columns.
-// bt: [2 * n_pieces, H, 128, 128] fp32 (B_r in slot r, T_r in slot n_pieces + r); h0_piece: [n_pieces, H, 128, 128].
-__global__ void __launch_bounds__(256) cp_chain_kernel(const float* __restrict__ bt, float* __restrict__ h0_piece,
-                                                      const int* __restrict__ flags,
-                                                      const int* __restrict__ seq_piece_offsets, int n_pieces, int H) {
-  constexpr int kCols = 16;
-  __shared__ float sx[kDim][kCols];       // current state slice
-  __shared__ float st[kDim][kDim / 4 + 1];  // a 128 x 32 tile of T_r
-  const int seq = blockIdx.x / H, h = blockIdx.x - seq * H, c0 = blockIdx.y * kCols;
+// Codes of the reverse direction (state gradient) for the pairs flagged by the forward plan: every piece but the last
+// of its sequence starts from the corrected gradient e_r (bit 29); the gradient pass runs every piece but the first from
+// zero (the last one from dht, bit 30) with no replay, its left-edge gradient is C_r.
+__global__ void __launch_bounds__(128) cp_resolve_reverse_kernel(const int* __restrict__ warmup_in,
+                                                                const int* __restrict__ piece_seq,
+                                                                const int* __restrict__ chunks_before,
+                                                                const int* __restrict__ chunks_after,
+                                                                const int* __restrict__ flags,
+                                                                int* __restrict__ warmup_out, int* __restrict__ pass1,
+                                                                int n_pieces, int H) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_pieces * H) return;
+  const int piece = idx / H, h = idx - piece * H;
+  const bool flagged = __ldg(flags + __ldg(piece_seq + piece) * H + h) != 0;
+  const bool first = __ldg(chunks_before + piece) == 0, last = __ldg(chunks_after + piece) == 0;
+  warmup_out[idx] = (flagged && !last) ? (1 << 29) : __ldg(warmup_in + idx);
+  pass1[idx] = (flagged && !first) ? (last ? (1 << 30) : 0) : (1 << 27);
+}
+
+__device__ __forceinline__ void mma_tf32_1688(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// x = hi + lo with both parts representable in TF32 (the split that makes three TF32 products as good as fp32)
+__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+  const float r = x - __uint_as_float(hi);
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
+}
+
+// h0_{r+1} = T_r h0_r + B_r for the pieces of one flagged (sequence, head); a CTA (8 warps) owns kChainCols of the 128
+// state columns, warp w the rows 16 w .. 16 w + 15.  The 128 x 128 x kChainCols product of a step runs on the warp-level
+// tensor path with split TF32 operands (hi*hi + lo*hi + hi*lo: fp32-grade); the step's T_r fragments come straight
+// from global memory (they were written by the state pass just before and sit in L2), the state slice goes through
+// shared memory.  bt: [2 * n_pieces, H, 128, 128] fp32 (B_r in slot r, T_r in slot n_pieces + r);
+// h0_piece: [n_pieces, H, 128, 128].
+constexpr int kChainCols = 16;
+constexpr int kChainLd = kChainCols + 8;  // row stride of the state slice: conflict-free B fragments
+
+// kReverse: the chain of the state gradient, e_{r-1} = T_r^T e_r + C_r from the last piece down (add = C, out = e).
+template <bool kReverse>
+__global__ void __launch_bounds__(256) cp_chain_kernel(const float* __restrict__ add, const float* __restrict__ tmat,
+                                                      float* __restrict__ out, const int* __restrict__ flags,
+                                                      const int* __restrict__ seq_piece_offsets, int H) {
+  __shared__ float sx[kDim * kChainLd];
+  const int seq = blockIdx.x / H, h = blockIdx.x - seq * H, c0 = blockIdx.y * kChainCols;
   if (__ldg(flags + seq * H + h) == 0) return;
   const int p0 = __ldg(seq_piece_offsets + seq), p1 = __ldg(seq_piece_offsets + seq + 1);
-  const int tid = threadIdx.x;
-  const int i = tid >> 1, cb = (tid & 1) * 8;  // this thread's output row and its 8 columns
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int m0 = warp * 16;
   const size_t mat = static_cast<size_t>(kDim) * kDim;
-  for (int r = p0; r + 1 < p1; ++r) {
-    const float* B = bt + (static_cast<size_t>(r) * H + h) * mat;
-    float acc[8];
+  const int steps = p1 - p0 - 1;
+  for (int st = 0; st < steps; ++st) {
+    const int r = kReverse ? p1 - 1 - st : p0 + st;  // piece whose (T, add) pair this step applies
+    // accumulators start from B_r (C_r): rows m0+g and m0+g+8, column pairs c0 + 8 n + 2 t
+    const float* B = add + (static_cast<size_t>(r) * H + h) * mat;
+    float acc[kChainCols / 8][4];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] = __ldg(B + static_cast<size_t>(i) * kDim + c0 + cb + e);
-    if (r > p0) {
-      const float* Tm = bt + (static_cast<size_t>(n_pieces + r) * H + h) * mat;
-      for (int k0 = 0; k0 < kDim; k0 += 32) {
-        __syncthreads();  // the previous tile (and, for k0 == 0, the previous state) has been consumed
-        for (int idx = tid; idx < kDim * 32; idx += 256) st[idx >> 5][idx & 31] = __ldg(Tm + static_cast<size_t>(idx >> 5) * kDim + k0 + (idx & 31));
-        __syncthreads();
-#pragma unroll 8
-        for (int kk = 0; kk < 32; ++kk) {
-          const float t = st[i][kk];
-          const float4 x0 = *reinterpret_cast<const float4*>(&sx[k0 + kk][cb]);
-          const float4 x1 = *reinterpret_cast<const float4*>(&sx[k0 + kk][cb + 4]);
-          acc[0] += t * x0.x; acc[1] += t * x0.y; acc[2] += t * x0.z; acc[3] += t * x0.w;
-          acc[4] += t * x1.x; acc[5] += t * x1.y; acc[6] += t * x1.z; acc[7] += t * x1.w;
+    for (int n = 0; n < kChainCols / 8; ++n) {
+      const float2 lo = __ldg(reinterpret_cast<const float2*>(B + static_cast<size_t>(m0 + g) * kDim + c0 + 8 * n + 2 * t));
+      const float2 hi = __ldg(reinterpret_cast<const float2*>(B + static_cast<size_t>(m0 + g + 8) * kDim + c0 + 8 * n + 2 * t));
+      acc[n][0] = lo.x; acc[n][1] = lo.y; acc[n][2] = hi.x; acc[n][3] = hi.y;
+    }
+    float acc1[kChainCols / 8][4], acc2[kChainCols / 8][4];
+#pragma unroll
+    for (int n = 0; n < kChainCols / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc1[n][e] = acc2[n][e] = 0.f;
+    if (st > 0) {
+      const float* Tm = tmat + (static_cast<size_t>(r) * H + h) * mat;
+      float ta[16][4];  // the A fragments of all sixteen k-steps: one round trip to L2 per step of the chain
+#pragma unroll
+      for (int ks = 0; ks < 16; ++ks) {
+        const int k0 = 8 * ks;
+        if (!kReverse) {
+          ta[ks][0] = __ldg(Tm + static_cast<size_t>(m0 + g) * kDim + k0 + t);
+          ta[ks][1] = __ldg(Tm + static_cast<size_t>(m0 + g + 8) * kDim + k0 + t);
+          ta[ks][2] = __ldg(Tm + static_cast<size_t>(m0 + g) * kDim + k0 + t + 4);
+          ta[ks][3] = __ldg(Tm + static_cast<size_t>(m0 + g + 8) * kDim + k0 + t + 4);
+        } else {  // A = T^T
+          ta[ks][0] = __ldg(Tm + static_cast<size_t>(k0 + t) * kDim + m0 + g);
+          ta[ks][1] = __ldg(Tm + static_cast<size_t>(k0 + t) * kDim + m0 + g + 8);
+          ta[ks][2] = __ldg(Tm + static_cast<size_t>(k0 + t + 4) * kDim + m0 + g);
+          ta[ks][3] = __ldg(Tm + static_cast<size_t>(k0 + t + 4) * kDim + m0 + g + 8);
+        }
+      }
+#pragma unroll
+      for (int ks = 0; ks < 16; ++ks) {
+        const int k0 = 8 * ks;
+        uint32_t ah[4], al[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) split_tf32(ta[ks][e], ah[e], al[e]);
+#pragma unroll
+        for (int n = 0; n < kChainCols / 8; ++n) {
+          uint32_t bh[2], bl[2];
+          split_tf32(sx[(k0 + t) * kChainLd + 8 * n + g], bh[0], bl[0]);
+          split_tf32(sx[(k0 + t + 4) * kChainLd + 8 * n + g], bh[1], bl[1]);
+          mma_tf32_1688(acc1[n], al, bh);  // three independent accumulation chains per tile
+          mma_tf32_1688(acc2[n], ah, bl);
+          mma_tf32_1688(acc[n], ah, bh);
         }
       }
     }
-    __syncthreads();  // every thread has read the old state
-    float* dst = h0_piece + (static_cast<size_t>(r + 1) * H + h) * mat + static_cast<size_t>(i) * kDim + c0 + cb;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      sx[i][cb + e] = acc[e];
-      dst[e] = acc[e];
+    for (int n = 0; n < kChainCols / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[n][e] += acc1[n][e] + acc2[n][e];
+    __syncthreads();  // every warp has read the old state slice
+    float* dst = out + (static_cast<size_t>(kReverse ? r - 1 : r + 1) * H + h) * mat;
+#pragma unroll
+    for (int n = 0; n < kChainCols / 8; ++n) {
+      const int col = 8 * n + 2 * t;
+      *reinterpret_cast<float2*>(&sx[(m0 + g) * kChainLd + col]) = make_float2(acc[n][0], acc[n][1]);
+      *reinterpret_cast<float2*>(&sx[(m0 + g + 8) * kChainLd + col]) = make_float2(acc[n][2], acc[n][3]);
+      *reinterpret_cast<float2*>(dst + static_cast<size_t>(m0 + g) * kDim + c0 + col) = make_float2(acc[n][0], acc[n][1]);
+      *reinterpret_cast<float2*>(dst + static_cast<size_t>(m0 + g + 8) * kDim + c0 + col) = make_float2(acc[n][2], acc[n][3]);
     }
     __syncthreads();
   }
@@ -140,32 +222,32 @@ __global__ void __launch_bounds__(256) cp_chain_kernel(const float* __restrict__
 
 extern "C" FQ_API int fq_cp_warmup(const float* g_cumsum, const int32_t* piece_edge, const int32_t* piece_aux,
                                    const int32_t* piece_chunks_after, int32_t* warmup, int n_pieces, int H,
-                                   float threshold, int reverse, void* stream) {
+                                   float threshold, int reverse, int w_cap, const int32_t* piece_seq, int32_t* flags,
+                                   void* stream) {
   using namespace fq;
   FQ_CHECK_ARG(g_cumsum && piece_edge && piece_aux && warmup, "fq_cp_warmup: null tensor");
   FQ_CHECK_ARG(!reverse || piece_chunks_after, "fq_cp_warmup: the reverse scan needs piece_chunks_after");
   FQ_CHECK_ARG(n_pieces > 0 && H > 0 && threshold < 0.f, "fq_cp_warmup: bad arguments");
-  const int total = n_pieces * H;
-  cp_warmup_kernel<<<(total + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      g_cumsum, piece_edge, piece_aux, warmup, n_pieces, H, threshold, reverse, piece_chunks_after);
+  FQ_CHECK_ARG(w_cap >= 0, "fq_cp_warmup: bad cap");
+  FQ_CHECK_ARG(flags == nullptr || (piece_seq != nullptr && w_cap > 0), "fq_cp_warmup: flags need piece_seq and a cap");
+  const long long total = static_cast<long long>(n_pieces) * H;  // one warp each, four warps per CTA
+  cp_warmup_kernel<<<static_cast<unsigned>((total + 3) / 4), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      g_cumsum, piece_edge, piece_aux, warmup, n_pieces, H, threshold, reverse, piece_chunks_after, w_cap, piece_seq, flags);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }
 
 extern "C" FQ_API int fq_cp_transition_plan(const int32_t* warmup_in, const int32_t* piece_seq,
-                                            const int32_t* chunks_before, const int32_t* chunks_after, int32_t* flags,
-                                            int32_t* warmup_out, int32_t* pass1_codes, int n_pieces, int n_seq, int H,
-                                            int w_max, void* stream) {
+                                            const int32_t* chunks_before, const int32_t* chunks_after,
+                                            const int32_t* flags, int32_t* warmup_out, int32_t* pass1_codes,
+                                            int n_pieces, int H, void* stream) {
   using namespace fq;
   FQ_CHECK_ARG(warmup_in && piece_seq && chunks_before && chunks_after && flags && warmup_out && pass1_codes,
                "fq_cp_transition_plan: null tensor");
-  FQ_CHECK_ARG(n_pieces > 0 && n_seq > 0 && H > 0 && w_max >= 0, "fq_cp_transition_plan: bad arguments");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  FQ_CHECK_CUDA(cudaMemsetAsync(flags, 0, sizeof(int32_t) * static_cast<size_t>(n_seq) * H, st));
+  FQ_CHECK_ARG(n_pieces > 0 && H > 0, "fq_cp_transition_plan: bad arguments");
   const int total = n_pieces * H;
-  cp_flag_kernel<<<(total + 127) / 128, 128, 0, st>>>(warmup_in, piece_seq, flags, n_pieces, H, w_max);
-  cp_resolve_kernel<<<(total + 127) / 128, 128, 0, st>>>(warmup_in, piece_seq, chunks_before, chunks_after, flags,
-                                                         warmup_out, pass1_codes, n_pieces, H);
+  cp_resolve_kernel<<<(total + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      warmup_in, piece_seq, chunks_before, chunks_after, flags, warmup_out, pass1_codes, n_pieces, H);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }
@@ -175,8 +257,36 @@ extern "C" FQ_API int fq_cp_chain(const float* bt, float* h0_piece, const int32_
   using namespace fq;
   FQ_CHECK_ARG(bt && h0_piece && flags && seq_piece_offsets, "fq_cp_chain: null tensor");
   FQ_CHECK_ARG(n_pieces > 0 && n_seq > 0 && H > 0, "fq_cp_chain: bad arguments");
-  dim3 grid(static_cast<unsigned>(n_seq) * H, kDim / 16);
-  cp_chain_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(bt, h0_piece, flags, seq_piece_offsets, n_pieces, H);
+  dim3 grid(static_cast<unsigned>(n_seq) * H, kDim / kChainCols);
+  const float* tmat = bt + static_cast<size_t>(n_pieces) * H * kDim * kDim;
+  cp_chain_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(bt, tmat, h0_piece, flags, seq_piece_offsets, H);
+  FQ_CHECK_CUDA(cudaGetLastError());
+  return FQ_OK;
+}
+
+extern "C" FQ_API int fq_cp_transition_plan_reverse(const int32_t* warmup_in, const int32_t* piece_seq,
+                                                    const int32_t* chunks_before, const int32_t* chunks_after,
+                                                    const int32_t* flags, int32_t* warmup_out, int32_t* pass1_codes,
+                                                    int n_pieces, int H, void* stream) {
+  using namespace fq;
+  FQ_CHECK_ARG(warmup_in && piece_seq && chunks_before && chunks_after && flags && warmup_out && pass1_codes,
+               "fq_cp_transition_plan_reverse: null tensor");
+  FQ_CHECK_ARG(n_pieces > 0 && H > 0, "fq_cp_transition_plan_reverse: bad arguments");
+  const int total = n_pieces * H;
+  cp_resolve_reverse_kernel<<<(total + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      warmup_in, piece_seq, chunks_before, chunks_after, flags, warmup_out, pass1_codes, n_pieces, H);
+  FQ_CHECK_CUDA(cudaGetLastError());
+  return FQ_OK;
+}
+
+extern "C" FQ_API int fq_cp_chain_reverse(const float* c, const float* tmat, float* dht_piece, const int32_t* flags,
+                                          const int32_t* seq_piece_offsets, int n_pieces, int n_seq, int H,
+                                          void* stream) {
+  using namespace fq;
+  FQ_CHECK_ARG(c && tmat && dht_piece && flags && seq_piece_offsets, "fq_cp_chain_reverse: null tensor");
+  FQ_CHECK_ARG(n_pieces > 0 && n_seq > 0 && H > 0, "fq_cp_chain_reverse: bad arguments");
+  dim3 grid(static_cast<unsigned>(n_seq) * H, kDim / kChainCols);
+  cp_chain_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(c, tmat, dht_piece, flags, seq_piece_offsets, H);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }

@@ -115,6 +115,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   const bool use_h0 = (warm_code >> 30) & 1, use_piece_h0 = (warm_code >> 29) & 1, transition = (warm_code >> 28) & 1,
              skip = (warm_code >> 27) & 1;
   const int total = (nchunks > 0 && !skip) ? warm + nchunks : 0;  // iterations; iteration `it` handles chunk n = it - warm
+  if (skip) return;  // nothing to do for this (entry, head): leave before any barrier or tensor memory is set up
   WaitCtx wc{&s.abort_flag, p.status_dev, 1};
 
   if (tid == 0) {

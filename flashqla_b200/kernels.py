@@ -125,42 +125,59 @@ def sm_count(device) -> int:
 
 @dataclass
 class CpWarm:
-    """Start-up codes of a context-parallel forward run (csrc/cp.cu): `codes` [P,H] for the final pass, `pass1`
+    """Start-up codes of a context-parallel run (csrc/cp.cu): `codes` [P,H] for the final forward pass, `pass1`
     [2P,H] for the state pass of the transition-matrix fallback, `flags` [n_seq,H] = which (sequence, head) pairs
-    use that fallback."""
+    use that fallback; with the reverse direction also `codes_rev` / `pass1_rev` [P,H] for the state-gradient
+    recurrence."""
     codes: torch.Tensor
     pass1: torch.Tensor
     flags: torch.Tensor
+    codes_rev: torch.Tensor | None = None
+    pass1_rev: torch.Tensor | None = None
 
 
-def cp_warmup(g_cum, cp, H, threshold=-16.0, reverse=False):
-    """Chunks to replay per (piece, head) for a context-parallel run (see csrc/cp.cu).  Forward direction: a CpWarm,
-    in which pairs whose replay would exceed one piece length are switched to corrected start states; reverse
-    direction: the plain [P,H] table."""
-    out = torch.empty(cp.n_pieces, H, dtype=torch.int32, device=g_cum.device)
+def cp_warmup(g_cum, cp, H, threshold=-16.0, with_reverse=False) -> CpWarm:
+    """Gate scans and start-up codes for a context-parallel run.  A pair whose replay would exceed one piece length
+    (in either direction when `with_reverse`) is switched to corrected start states."""
+    dev = g_cum.device
+    P = cp.n_pieces
     lib = _lib.load()
-    if reverse:
-        rc = lib.fq_cp_warmup(g_cum.data_ptr(), cp.piece_end.data_ptr(), cp.last_chunk_len.data_ptr(),
-                              cp.chunks_after.data_ptr(), out.data_ptr(), cp.n_pieces, H, float(threshold), 1, _stream())
-        _lib.check(rc, "fq_cp_warmup")
-        return out
+    cap = int(cp.piece_chunks)
+    raw = torch.empty(P, H, dtype=torch.int32, device=dev)
+    flags = torch.zeros(cp.n_seq, H, dtype=torch.int32, device=dev)
     rc = lib.fq_cp_warmup(g_cum.data_ptr(), cp.piece_start.data_ptr(), cp.chunks_before.data_ptr(), None,
-                          out.data_ptr(), cp.n_pieces, H, float(threshold), 0, _stream())
+                          raw.data_ptr(), P, H, float(threshold), 0, cap, cp.seq_index.data_ptr(), flags.data_ptr(),
+                          _stream())
     _lib.check(rc, "fq_cp_warmup")
-    codes = torch.empty_like(out)
-    pass1 = torch.empty(2 * cp.n_pieces, H, dtype=torch.int32, device=g_cum.device)
-    flags = torch.empty(cp.n_seq, H, dtype=torch.int32, device=g_cum.device)
-    rc = lib.fq_cp_transition_plan(out.data_ptr(), cp.seq_index.data_ptr(), cp.chunks_before.data_ptr(),
-                                   cp.chunks_after.data_ptr(), flags.data_ptr(), codes.data_ptr(), pass1.data_ptr(),
-                                   cp.n_pieces, cp.n_seq, H, int(cp.piece_chunks), _stream())
+    raw_r = None
+    if with_reverse:
+        raw_r = torch.empty(P, H, dtype=torch.int32, device=dev)
+        rc = lib.fq_cp_warmup(g_cum.data_ptr(), cp.piece_end.data_ptr(), cp.last_chunk_len.data_ptr(),
+                              cp.chunks_after.data_ptr(), raw_r.data_ptr(), P, H, float(threshold), 1, cap,
+                              cp.seq_index.data_ptr(), flags.data_ptr(), _stream())
+        _lib.check(rc, "fq_cp_warmup")
+    codes = torch.empty_like(raw)
+    pass1 = torch.empty(2 * P, H, dtype=torch.int32, device=dev)
+    rc = lib.fq_cp_transition_plan(raw.data_ptr(), cp.seq_index.data_ptr(), cp.chunks_before.data_ptr(),
+                                   cp.chunks_after.data_ptr(), flags.data_ptr(), codes.data_ptr(), pass1.data_ptr(), P, H,
+                                   _stream())
     _lib.check(rc, "fq_cp_transition_plan")
-    return CpWarm(codes, pass1, flags)
+    warm = CpWarm(codes, pass1, flags)
+    if with_reverse:
+        warm.codes_rev = torch.empty_like(raw)
+        warm.pass1_rev = torch.empty_like(raw)
+        rc = lib.fq_cp_transition_plan_reverse(raw_r.data_ptr(), cp.seq_index.data_ptr(), cp.chunks_before.data_ptr(),
+                                               cp.chunks_after.data_ptr(), flags.data_ptr(), warm.codes_rev.data_ptr(),
+                                               warm.pass1_rev.data_ptr(), P, H, _stream())
+        _lib.check(rc, "fq_cp_transition_plan_reverse")
+    return warm
 
 
-def cp_correct_states(q, k, v, ag, g, b, scale, h0, cp, warm: CpWarm, status=None):
+def cp_correct_states(q, k, v, ag, g, b, scale, h0, cp, warm: CpWarm, status=None, return_bt=False):
     """Corrected start state of every piece for the (sequence, head) pairs flagged in `warm` (other slots are left
     unwritten): one state-only launch over 2P entries (end state from zero, transition matrix) and the chain
-    h0[r+1] = T_r h0[r] + B_r.  All inputs contiguous, as prepared by fused_gdr_fwd."""
+    h0[r+1] = T_r h0[r] + B_r.  All inputs contiguous, as prepared by fused_gdr_fwd.  `return_bt` also returns the
+    [2P,H,128,128] scratch whose second half holds the transition matrices (the backward reuses them)."""
     B, T, Hg, K = k.shape
     H = v.shape[2]
     dev = q.device
@@ -178,7 +195,7 @@ def cp_correct_states(q, k, v, ag, g, b, scale, h0, cp, warm: CpWarm, status=Non
     rc = lib.fq_cp_chain(bt.data_ptr(), h0_piece.data_ptr(), warm.flags.data_ptr(), cp.seq_piece_offsets.data_ptr(), P,
                          cp.n_seq, H, _stream())
     _lib.check(rc, "fq_cp_chain")
-    return h0_piece
+    return (h0_piece, bt) if return_bt else h0_piece
 
 
 def fused_gdr_fwd(q, k, v, ag, pg, g, b, scale, initial_state=None, output_final_state=True, output_h=False,

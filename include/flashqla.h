@@ -131,16 +131,16 @@ FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void* v, const v
                             int total_chunks, float scale, int32_t* status_dev, void* stream);
 
 /*
- * Which (sequence, head) pairs fall back to transition matrices, and the codes of the two passes.
- *   warmup_in [n_pieces,H] from fq_cp_warmup (reverse == 0); piece_seq / chunks_before / chunks_after [n_pieces].
- *   flags [n_seq,H] (out): 1 where some piece would replay more than w_max chunks.
+ * Codes of the two forward passes for the (sequence, head) pairs flagged by fq_cp_warmup.
+ *   warmup_in [n_pieces,H] from fq_cp_warmup (reverse == 0); piece_seq / chunks_before / chunks_after [n_pieces];
+ *   flags [n_seq,H] as left by the scan(s): a backward pass runs both directions into the same flags.
  *   warmup_out [n_pieces,H]: codes of the final pass (bit 29 for every piece but the first of a flagged pair).
  *   pass1_codes [2*n_pieces,H]: entry r = end state of piece r from zero (from h0 for a first piece), entry
  *   n_pieces + r = transition matrix of piece r; bit 27 where not needed.
  */
 FQ_API int fq_cp_transition_plan(const int32_t* warmup_in, const int32_t* piece_seq, const int32_t* chunks_before,
-                                 const int32_t* chunks_after, int32_t* flags, int32_t* warmup_out, int32_t* pass1_codes,
-                                 int n_pieces, int n_seq, int H, int w_max, void* stream);
+                                 const int32_t* chunks_after, const int32_t* flags, int32_t* warmup_out,
+                                 int32_t* pass1_codes, int n_pieces, int H, void* stream);
 
 /*
  * h0_piece[r+1] = T_r h0_piece[r] + B_r along the pieces of every flagged (sequence, head), in fp32.
@@ -161,10 +161,14 @@ FQ_API int fq_cp_chain(const float* bt, float* h0_piece, const int32_t* flags, c
  *   reverse != 0 (state gradient): piece_edge = first token after the piece, piece_chunks_after =
  *                chunks that follow the piece in its sequence, piece_aux = token count of the
  *                sequence's last chunk.
+ *   w_cap > 0 bounds the walk: a replay longer than w_cap chunks is reported as w_cap + 1 (no bit 30) without
+ *                looking further; 0 = walk to the end.
+ *   flags [n_seq,H] (optional, zeroed by the caller; needs piece_seq [n_pieces] = sequence of each piece and a cap):
+ *                set to 1 for every (sequence, head) with a piece whose replay exceeds w_cap chunks.
  */
 FQ_API int fq_cp_warmup(const float* g_cumsum, const int32_t* piece_edge, const int32_t* piece_aux,
                         const int32_t* piece_chunks_after, int32_t* warmup, int n_pieces, int H, float threshold,
-                        int reverse, void* stream);
+                        int reverse, int w_cap, const int32_t* piece_seq, int32_t* flags, void* stream);
 
 /*
  * Backward, serial part: reverse recurrence of the state gradient per (sequence, V-head).
@@ -194,6 +198,26 @@ FQ_API int fq_gdr_bwd_dh_cp(const void* q, const void* k, const void* Ag, const 
                             const int32_t* warmup, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
                             const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
                             int32_t* status_dev, void* stream);
+
+/*
+ * fq_gdr_bwd_dh_cp with corrected start gradients: bit 29 of warmup[i*H+h] = start piece i from
+ * dht_piece[i] ([n_pieces,H,128,128] fp32: the gradient at the piece's end) with no replay; bit 27 = nothing to do.
+ * fq_cp_transition_plan_reverse makes the codes of the two launches for the pairs flagged by
+ * fq_cp_transition_plan: the gradient pass (every piece but the first of its sequence from zero, the last one from
+ * dht; its dh0 slots give C_r) and the final pass; fq_cp_chain_reverse forms e_{r-1} = T_r^T e_r + C_r from the last
+ * piece down, with the transition matrices T_r of the forward state pass (tmat = bt + n_pieces*H*128*128).
+ */
+FQ_API int fq_gdr_bwd_dh_cp_ex(const void* q, const void* k, const void* Ag, const void* Pg, const void* dout,
+                               const float* g_cumsum, const float* beta, const float* dht, float* dh0, void* dh_out,
+                               const int32_t* dht_index, const int32_t* dh0_index, const int32_t* seq_end,
+                               const int32_t* warmup, const float* dht_piece, int B, int T, int H, int Hg,
+                               const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq, int total_chunks,
+                               float scale, int32_t* status_dev, void* stream);
+FQ_API int fq_cp_transition_plan_reverse(const int32_t* warmup_in, const int32_t* piece_seq,
+                                         const int32_t* chunks_before, const int32_t* chunks_after, const int32_t* flags,
+                                         int32_t* warmup_out, int32_t* pass1_codes, int n_pieces, int H, void* stream);
+FQ_API int fq_cp_chain_reverse(const float* c, const float* tmat, float* dht_piece, const int32_t* flags,
+                               const int32_t* seq_piece_offsets, int n_pieces, int n_seq, int H, void* stream);
 
 /*
  * Backward, chunk-parallel part: dv (bf16 [B,T,H,128]), dq, dk (per V-head, bf16 [B,T,H,128]), dg w.r.t. the
