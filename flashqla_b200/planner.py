@@ -185,15 +185,23 @@ def choose_piece_chunks(n_chunks: list, H: int, n_sm: int, overhead: int = 8) ->
     standing for the replayed chunks and the CTA start-up; the kernels keep one CTA per SM, so the
     run time is the makespan of scheduling the CTAs, in launch order, on n_sm machines.  The
     reference's rule (cp_context.py:52-57, 86-87) was fitted to 132 SMs with up to two CTAs each;
-    this one follows from the one-CTA-per-SM kernels.
+    this one follows from the one-CTA-per-SM kernels and was checked against sweeps of the piece length on the
+    reference's benchmark grid.
     """
     longest = max(n_chunks) if n_chunks else 0
     if longest <= 8:
         return None
 
     def cost(L):
-        pieces = [min(L, c - i) for c in n_chunks for i in range(0, c, L)] if L < longest else list(n_chunks)
-        return _makespan(pieces, H, n_sm, overhead)
+        if L >= longest:
+            return _makespan(list(n_chunks), H, n_sm, overhead)
+        pieces = [min(L, c - i) for c in n_chunks for i in range(0, c, L)]
+        # Splitting has a price beyond the replayed chunks: a handful of extra launches (about twelve chunk steps),
+        # and - for heads whose gate decays too slowly, which only the device knows - a state pass (L chunk steps, or
+        # half the final pass once the SMs are saturated: two runs per piece for about a quarter of the heads) plus one
+        # chain step per piece of the longest sequence; that part is weighted three quarters.
+        span = _makespan(pieces, H, n_sm, overhead)
+        return span + 12 + 0.75 * max(L + -(-longest // L), 0.5 * span)
 
     base = cost(longest)
     best_L, best = None, base
