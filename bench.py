@@ -54,7 +54,7 @@ FWD_BYTES_PER_UNIT = 4 * 16384 + 512
 # DRAM traffic of gdr_fwd_kernel per (chunk, V-head) from one ncu capture of the smaller case c2s (Hq == Hv):
 # dram__bytes_read.sum + dram__bytes_write.sum = 665,837,312 B over 8192 units (profiles/forward_kernels_*.md);
 # traffic grows in proportion to the units, so a full launch is reported as units x this figure
-FWD_TRAFFIC_PER_UNIT_NCU = 665837312 / 8192
+FWD_TRAFFIC_PER_UNIT_NCU = 673319680 / 8192
 
 
 def l2norm(x):
@@ -404,12 +404,13 @@ def main():
         o, _, fs = timed("gdr_fwd", lambda: kernels.fused_gdr_fwd(d["q"], d["k"], d["v"], Ag, Pg, g_cum, d["beta"], scale,
                                                                  initial_state=d["h0"], plan=plan, cp=cp, warmup=warm,
                                                                  h0_piece=h0p), rec)
-        n = 3 + (5 if cp is not None else 0)  # scan, flag, resolve, state pass, chain
+        n = 3 + (4 if cp is not None else 0)  # gate scan, codes, state pass, chain
         if w["bwd"]:
             timed("backward", lambda: fq.chunk_gated_delta_rule_bwd(d["q"], d["k"], d["v"], g_cum, d["beta"], A, d["do"],
                                                                      d["dht"], scale, d["h0"], None), rec)
-            # fwd(h) + bwd_dh + bwd_chunk + reverse cumsum (+ 2 warm-up scans, 2 plan kernels, state pass, chain; + 2 head sums)
-            n += 4 + (6 if cp is not None else 0) + (2 if Hq < Hv else 0)
+            # fwd(h) + bwd_dh + bwd_chunk + reverse cumsum (+ 2 gate scans, 2 code kernels, state pass, chain, gradient
+            # pass, reverse chain; + 2 head sums)
+            n += 4 + (8 if cp is not None else 0) + (2 if Hq < Hv else 0)
         if record:
             stamps.append(rec)
         launches[0] = n
