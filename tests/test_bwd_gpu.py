@@ -107,6 +107,10 @@ CP_CASES = [
     (1, 1024, 2, 2, None, "reftest", 4),   # the g = 0 head replays to the sequence end / start: exact
     (2, 520, 1, 2, None, "baseline", 2),
     (1, 1500, 2, 4, [0, 1, 64, 65, 700, 700, 1500], "reftest", 3),
+    # piece length chosen by the planner; the g = 0 head and (with short pieces) the slowly decaying heads take the
+    # transition-matrix route: state pass, chain of piece states, final pass
+    (1, 4096, 2, 4, None, "reftest", None),
+    (1, 6000, 1, 2, [0, 3000, 3100, 6000], "reftest", 5),
 ]
 
 
