@@ -395,8 +395,8 @@ def main():
 
     def step(record=False):
         rec = [] if record else None
-        g_cum = timed("chunk_cumsum", lambda: kernels.chunk_local_cumsum(d["g"], plan=plan), rec)
-        A, Ag, Pg = timed("kkt_solve", lambda: kernels.kkt_solve_gated(d["k"], d["q"], d["beta"], g_cum, scale, plan), rec)
+        # chunk-local cumsum of g, A and the gated tiles in one launch
+        g_cum, A, Ag, Pg = timed("kkt_solve", lambda: kernels.kkt_solve_fused(d["k"], d["q"], d["beta"], d["g"], scale, plan), rec)
         warm = timed("cp_warmup", lambda: kernels.cp_warmup(g_cum, cp, Hv), rec) if cp is not None else None
         # transition-matrix fallback for slowly decaying heads: state pass + chain (near-empty launches when no head needs it)
         h0p = timed("cp_correct", lambda: kernels.cp_correct_states(d["q"], d["k"], d["v"], Ag, g_cum, d["beta"], scale,
@@ -404,7 +404,7 @@ def main():
         o, _, fs = timed("gdr_fwd", lambda: kernels.fused_gdr_fwd(d["q"], d["k"], d["v"], Ag, Pg, g_cum, d["beta"], scale,
                                                                  initial_state=d["h0"], plan=plan, cp=cp, warmup=warm,
                                                                  h0_piece=h0p), rec)
-        n = 3 + (4 if cp is not None else 0)  # gate scan, codes, state pass, chain
+        n = 2 + (4 if cp is not None else 0)  # kkt_solve, gdr_fwd (+ gate scan, codes, state pass, chain)
         if w["bwd"]:
             timed("backward", lambda: fq.chunk_gated_delta_rule_bwd(d["q"], d["k"], d["v"], g_cum, d["beta"], A, d["do"],
                                                                      d["dht"], scale, d["h0"], None), rec)

@@ -40,6 +40,7 @@ SIGNATURES = {
     "fq_l2norm_fwd": [_vp, _vp, ctypes.c_longlong, _f32, _vp],
     "fq_l2norm_bwd": [_vp, _vp, _vp, ctypes.c_longlong, _f32, _vp],
     "fq_kkt_solve_gated": [_vp] * 7 + [_i32] * 5 + [_vp, _vp, _i32, _i32, _f32, _vp],
+    "fq_kkt_solve_fused": [_vp] * 8 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp],
     "fq_selftest_umma": [_vp, _vp, _vp, _i32, _vp, _vp],
 }
 _RESTYPES = {"fq_last_error": _cp}

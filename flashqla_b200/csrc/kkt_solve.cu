@@ -128,6 +128,33 @@ __device__ __forceinline__ void store_pg(const float (&qk)[8][4], const float* g
   }
 }
 
+// Gate values of one (chunk, head) into shared memory, times log2(e): exp(g_i - g_j) = exp2(g2_i - g2_j).  Called by
+// warps 0 and 1.  With `g_cum_out` the input is the RAW log gate: warp 0 forms the chunk-local inclusive sum (two tokens
+// per lane, shuffle scan) and also stores it, so that no separate prefix-sum pass over g is needed
+// (chunk_local_cumsum, flash_qla/ops/utils/cumsum.py:131-165, folded into this kernel).  Rows past the sequence end
+// get the last valid sum.
+__device__ __forceinline__ void load_gates(float* sg, const float* __restrict__ g_in, float* __restrict__ g_cum_out,
+                                           size_t base, int H, int len, int tid) {
+  constexpr float kLog2e = 1.4426950408889634f;
+  if (g_cum_out == nullptr) {
+    sg[tid] = kLog2e * __ldg(g_in + base + static_cast<size_t>(min(tid, len - 1)) * H);
+    return;
+  }
+  if (tid >= 32) return;
+  float a = (tid < len) ? __ldg(g_in + base + static_cast<size_t>(tid) * H) : 0.f;
+  float b = (tid + 32 < len) ? __ldg(g_in + base + static_cast<size_t>(tid + 32) * H) : 0.f;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const float ya = __shfl_up_sync(0xffffffffu, a, d), yb = __shfl_up_sync(0xffffffffu, b, d);
+    if (tid >= d) { a += ya; b += yb; }
+  }
+  b += __shfl_sync(0xffffffffu, a, 31);
+  if (tid < len) g_cum_out[base + static_cast<size_t>(tid) * H] = a;
+  if (tid + 32 < len) g_cum_out[base + static_cast<size_t>(tid + 32) * H] = b;
+  sg[tid] = kLog2e * a;
+  sg[tid + 32] = kLog2e * b;
+}
+
 // kSingle: every QK head has one V head (G == 1); the gates are then loaded with the tiles and P_g leaves before
 // the solve, so that the Q K^T fragments are dead while K K^T is formed and inverted.
 template <bool kSingle>
@@ -137,7 +164,8 @@ __global__ void __launch_bounds__(128, 6) kkt_solve_kernel(const __nv_bfloat16* 
                                                        const __nv_bfloat16* __restrict__ q,
                                                        const float* __restrict__ g_cum,
                                                        __nv_bfloat16* __restrict__ Ag, __nv_bfloat16* __restrict__ Pg,
-                                                       float scale, const __nv_bfloat16* __restrict__ A_in) {
+                                                       float scale, const __nv_bfloat16* __restrict__ A_in,
+                                                       float* __restrict__ g_cum_out) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   KktSmem& s = *reinterpret_cast<KktSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -161,8 +189,7 @@ __global__ void __launch_bounds__(128, 6) kkt_solve_kernel(const __nv_bfloat16* 
     }
     if (kSingle && tid < kChunk) {
       s.beta[tid] = (tid < p.len) ? __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hg) : 0.f;
-      // log-gate cumsum times log2(e): exp(g_i - g_j) = exp2(g2_i - g2_j)
-      if (Ag || Pg) s.g[tid] = 1.4426950408889634f * __ldg(g_cum + static_cast<size_t>(p.tok0 + min(tid, p.len - 1)) * H + hg);
+      if (Ag || Pg) load_gates(s.g, g_cum, g_cum_out, static_cast<size_t>(p.tok0) * H + hg, H, p.len, tid);
     }
     cp_async_wait_all();
   }
@@ -204,7 +231,7 @@ __global__ void __launch_bounds__(128, 6) kkt_solve_kernel(const __nv_bfloat16* 
     if (!kSingle) {
       if (tid < kChunk) {
         s.beta[tid] = (tid < p.len) ? __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hv) : 0.f;
-        if (Ag || Pg) s.g[tid] = 1.4426950408889634f * __ldg(g_cum + static_cast<size_t>(p.tok0 + min(tid, p.len - 1)) * H + hv);
+        if (Ag || Pg) load_gates(s.g, g_cum, g_cum_out, static_cast<size_t>(p.tok0) * H + hv, H, p.len, tid);
       }
       __syncthreads();
     }
@@ -410,10 +437,9 @@ __global__ void __launch_bounds__(128, 6) kkt_solve_kernel(const __nv_bfloat16* 
 
 }  // namespace fq
 
-extern "C" FQ_API int fq_kkt_solve_gated(const void* k, const void* q, const float* beta, const float* g_cumsum, void* A,
-                                         void* Ag, void* Pg, int a_is_input, int B, int T, int H, int Hg,
-                                         const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
-                                         int total_chunks, float scale, void* stream) {
+static int kkt_launch(const void* k, const void* q, const float* beta, const float* g_cumsum, float* g_cum_out, void* A,
+                      void* Ag, void* Pg, int a_is_input, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
+                      const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale, void* stream) {
   using namespace fq;
   FQ_CHECK_ARG(k && beta && A, "fq_kkt_solve: null tensor");
   FQ_CHECK_ARG((Ag == nullptr && Pg == nullptr) || (g_cumsum != nullptr), "fq_kkt_solve: A_g / P_g need the gate cumsum");
@@ -442,9 +468,26 @@ extern "C" FQ_API int fq_kkt_solve_gated(const void* k, const void* q, const flo
   kern<<<grid, 128, sizeof(KktSmem), static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(k), beta, static_cast<__nv_bfloat16*>(A), H, Hg, sa,
       static_cast<const __nv_bfloat16*>(q), g_cumsum, static_cast<__nv_bfloat16*>(Ag), static_cast<__nv_bfloat16*>(Pg),
-      scale, a_is_input ? static_cast<const __nv_bfloat16*>(A) : nullptr);
+      scale, a_is_input ? static_cast<const __nv_bfloat16*>(A) : nullptr, g_cum_out);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
+}
+
+extern "C" FQ_API int fq_kkt_solve_gated(const void* k, const void* q, const float* beta, const float* g_cumsum, void* A,
+                                         void* Ag, void* Pg, int a_is_input, int B, int T, int H, int Hg,
+                                         const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
+                                         int total_chunks, float scale, void* stream) {
+  return kkt_launch(k, q, beta, g_cumsum, nullptr, A, Ag, Pg, a_is_input, B, T, H, Hg, cu_seqlens, chunk_offsets, n_seq,
+                    total_chunks, scale, stream);
+}
+
+extern "C" FQ_API int fq_kkt_solve_fused(const void* k, const void* q, const float* beta, const float* g, float* g_cumsum,
+                                         void* A, void* Ag, void* Pg, int B, int T, int H, int Hg,
+                                         const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
+                                         int total_chunks, float scale, void* stream) {
+  FQ_CHECK_ARG(g && g_cumsum && Ag && Pg, "fq_kkt_solve_fused: null tensor");
+  return kkt_launch(k, q, beta, g, g_cumsum, A, Ag, Pg, 0, B, T, H, Hg, cu_seqlens, chunk_offsets, n_seq, total_chunks,
+                    scale, stream);
 }
 
 extern "C" FQ_API int fq_kkt_solve(const void* k, const float* beta, void* A, int B, int T, int H, int Hg,

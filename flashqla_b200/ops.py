@@ -55,7 +55,7 @@ def l2norm(x: torch.Tensor, dim: int = -1, eps: float = 1e-6) -> torch.Tensor:
 
 def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None, cu_seqlens=None,
                                output_final_state=True, output_h=False, auto_cp=True, _return_tiles=False, _plan=None):
-    """Forward pipeline (chunk/__init__.py:17-67): cumsum -> K K^T + solve (+ gated tiles) -> fused recurrence.
+    """Forward pipeline (chunk/__init__.py:17-67): [cumsum + K K^T + solve + gated tiles] -> fused recurrence.
 
     Returns ``(g_cumsum, A, o, h, final_state)``; ``A`` is the gate-free inverse (opaque, only
     meant to be passed back to ``chunk_gated_delta_rule_bwd``).  With ``auto_cp`` long sequences are
@@ -65,8 +65,7 @@ def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None,
     if scale is None:
         scale = K ** -0.5
     plan = _plan if _plan is not None else make_plan(B, T, cu_seqlens, q.device)
-    g_cum = kernels.chunk_local_cumsum(g, cu_seqlens=cu_seqlens, plan=plan)
-    A, Ag, Pg = kernels.kkt_solve_gated(k, q, beta, g_cum, scale, plan)
+    g_cum, A, Ag, Pg = kernels.kkt_solve_fused(k, q, beta, g, scale, plan)  # the cumsum of g is formed in the same launch
     status = kernels._status_tensor(q.device) if _DEBUG_STATUS else None
     cp = warm = None
     if auto_cp:

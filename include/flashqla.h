@@ -79,6 +79,15 @@ FQ_API int fq_kkt_solve_gated(const void* k, const void* q, const float* beta, c
                               const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale, void* stream);
 
 /*
+ * fq_chunk_cumsum + fq_kkt_solve_gated in one launch: `g` is the RAW log gate [B,T,H] fp32, its chunk-local
+ * inclusive sum is formed per (chunk, V-head) inside the kernel (a warp scan), used for the gated tiles and written
+ * to g_cumsum [B,T,H] fp32.  Saves the separate pass of flash_qla/ops/utils/cumsum.py:131-165 over g.
+ */
+FQ_API int fq_kkt_solve_fused(const void* k, const void* q, const float* beta, const float* g, float* g_cumsum, void* A,
+                              void* Ag, void* Pg, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
+                              const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale, void* stream);
+
+/*
  * Fused forward recurrence: per (sequence, V-head) walks the chunks, carries the fp32 K x V state
  * and writes o = scale*exp(g) o (Q S) + P_g V_d per chunk.
  * Replaces fused_gdr_fwd, flash_qla/ops/gated_delta_rule/chunk/hopper/fused_fwd.py:535-658
