@@ -182,6 +182,19 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr, uint32_t lbo
 __device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t bytes) { return d + (bytes >> 4); }
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
+// One lane of a converged warp.  The issuing warp runs its loop with all 32 lanes (waits, descriptor arithmetic) and
+// only the tcgen05 instructions sit under this predicate: control flow then stays warp-uniform and the compiler can
+// keep the descriptors in uniform registers, which is where the tensor-core instructions take them from.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                         uint32_t accumulate) {
   asm volatile(

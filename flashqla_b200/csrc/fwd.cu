@@ -157,8 +157,9 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ UMMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ UMMA issuer: the whole warp runs the loop,
+    // one elected lane issues (see elect_one)
+    {
       constexpr uint32_t id64 = umma_idesc(128, 64, false, false, true);
       constexpr uint32_t id64_amn = umma_idesc(128, 64, true, false, true);
       constexpr uint32_t id128_bmn = umma_idesc(128, 128, false, true, true);
@@ -183,52 +184,65 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (!mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2)) break;
         FQ_TS(it, 0);
         tc_fence_after();
-        if (!transition) {
+        if (!transition && elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)  // V_d^T = V^T A_g^T (A operand = the V tile as loaded, MN-major)
             umma_ss(tm + kColVD, desc_add(d_vmn, kk * 2048), desc_add(d_a, kk * 32), id64_amn, kk > 0);
         }
+        __syncwarp();
         if (!mbar_wait_spin(wc, &s.s_ready, ph, 3)) break;
         FQ_TS(it, 1);
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)  // U^T = S^T K^T
-          umma_ss(tm + kColUQ, desc_add(d_sbf, kq_off(kk)), desc_add(d_kq, kq_off(kk)), id64, kk > 0);
-        umma_commit(&s.uq_done);
+          for (int kk = 0; kk < 8; ++kk)  // U^T = S^T K^T
+            umma_ss(tm + kColUQ, desc_add(d_sbf, kq_off(kk)), desc_add(d_kq, kq_off(kk)), id64, kk > 0);
+          umma_commit(&s.uq_done);
+        }
+        __syncwarp();
         FQ_TS(it, 3);
         if (do_o) {  // OI = Q S: the accumulators of the previous chunk must have been drained
           if (it > 0 && !mbar_wait(wc, &s.o_free, (it - 1) & 1, 4)) break;
           FQ_TS(it, 2);
           tc_fence_after();
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            umma_ss(tm + kColOI, desc_add(d_kq, 8192 + kq_off(kk)), desc_add(d_sbf, kq_off(kk)), id_o, kk > 0);
+            for (int kk = 0; kk < 8; ++kk)
+              umma_ss(tm + kColOI, desc_add(d_kq, 8192 + kq_off(kk)), desc_add(d_sbf, kq_off(kk)), id_o, kk > 0);
+          }
+          __syncwarp();
         }
         if (!mbar_wait_spin(wc, &s.w_ready, ph, 5)) break;
         FQ_TS(it, 4);
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)  // V_d^T -= (gamma o U)^T A_g^T
-          umma_ss(tm + kColVD, desc_add(d_w, kk * 32), desc_add(d_a, kk * 32), id64, (transition && kk == 0) ? 0 : 1);
-        umma_commit(&s.vd_done);
+          for (int kk = 0; kk < 4; ++kk)  // V_d^T -= (gamma o U)^T A_g^T
+            umma_ss(tm + kColVD, desc_add(d_w, kk * 32), desc_add(d_a, kk * 32), id64, (transition && kk == 0) ? 0 : 1);
+          umma_commit(&s.vd_done);
+        }
+        __syncwarp();
         FQ_TS(it, 6);
         if (!mbar_wait_spin(wc, &s.vp_ready, ph, 7)) break;
         FQ_TS(it, 7);
         if (!mbar_wait_spin(wc, &s.s_scaled, ph, 9)) break;
         FQ_TS(it, 8);
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)  // S^T += V'^T K
-          umma_ss(tm + kColS, desc_add(d_w, kk * 32), desc_add(d_kmn, kk * 2048), id128_bmn, 1);
-        umma_commit(&s.s_done);
-        FQ_TS(it, 9);
-        if (do_o) {
+          for (int kk = 0; kk < 4; ++kk)  // S^T += V'^T K
+            umma_ss(tm + kColS, desc_add(d_w, kk * 32), desc_add(d_kmn, kk * 2048), id128_bmn, 1);
+          umma_commit(&s.s_done);
+          if (do_o) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)  // OX = P_g V_d
-            umma_ss(tm + kColOX, desc_add(d_pg, kk * 32), desc_add(d_vd, kk * 32), id_o, kk > 0);
+            for (int kk = 0; kk < 4; ++kk)  // OX = P_g V_d
+              umma_ss(tm + kColOX, desc_add(d_pg, kk * 32), desc_add(d_vd, kk * 32), id_o, kk > 0);
+          }
+          umma_commit(&s.o_done);
+          umma_commit(&s.empty[st]);
         }
-        umma_commit(&s.o_done);
-        umma_commit(&s.empty[st]);
+        __syncwarp();
+        FQ_TS(it, 9);
       }
     }
   } else if (warp < 4) {
