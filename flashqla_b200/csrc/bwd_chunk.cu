@@ -261,7 +261,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const float gam_r = s.gam[row], rho_r = s.rho[row];
 
     // ================================================================== round 1
-    if (lane == 0 && warp < 4) {  // the products of a round are issued by four threads in parallel
+    if (warp < 4 && elect_one()) {  // the products of a round are issued by one elected lane of each of four warps
       tc_fence_after();
       if (warp == 0) {
 #pragma unroll
@@ -360,7 +360,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
     BC_TS(4);
     // ================================================================== round 2: V' = A_g W, dW = A_g^T dV'
-    if (lane == 0 && warp < 4) {  // the products of a round are issued by four threads in parallel
+    if (warp < 4 && elect_one()) {  // the products of a round are issued by one elected lane of each of four warps
       tc_fence_after();
       if (warp == 0) {
 #pragma unroll
@@ -433,7 +433,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
     BC_TS(6);
     // ================================================================== round 3
-    if (lane == 0 && warp < 4) {  // the products of a round are issued by four threads in parallel
+    if (warp < 4 && elect_one()) {  // the products of a round are issued by one elected lane of each of four warps
       tc_fence_after();
       if (warp == 0) {
 #pragma unroll
@@ -465,9 +465,12 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     tc_fence_after();
     // The tiles that round three read last are dead from here on; two threads request this CTA's next unit there:
     // S0, dS, V, dO in place, and K, Q, A, A_g into V', dVg and dV'.  They land while rounds three to six finish.
-    if (lane == 0 && has_next) {
-      if (warp == 2) load_a(nchunk, nh);
-      if (warp == 3) load_b(nchunk, nh, 0, b_vp, b_dvg, b_dvp, b_t12);
+    if (has_next && (warp == 2 || warp == 3)) {
+      if (elect_one()) {
+        if (warp == 2) load_a(nchunk, nh);
+        else load_b(nchunk, nh, 0, b_vp, b_dvg, b_dvp, b_t12);
+      }
+      __syncwarp();
     }
     {
       // dg += rowsum(K o accK); then accK += rho o K1 ; kk = rowsum(K o rho K1)
@@ -573,7 +576,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
     BC_TS(8);
     // ================================================================== round 4
-    if (lane == 0 && warp < 4) {  // the products of a round are issued by four threads in parallel
+    if (warp < 4 && elect_one()) {  // the products of a round are issued by one elected lane of each of four warps
       tc_fence_after();
       if (warp == 0) {
 #pragma unroll
@@ -660,7 +663,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
     BC_TS(10);
     // ================================================================== round 5
-    if (lane == 0 && warp < 4) {  // the products of a round are issued by four threads in parallel
+    if (warp < 4 && elect_one()) {  // the products of a round are issued by one elected lane of each of four warps
       tc_fence_after();
       if (warp == 0) {
 #pragma unroll
@@ -721,7 +724,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
     BC_TS(12);
     // ================================================================== round 6
-    if (lane == 0 && warp < 4) {  // the products of a round are issued by four threads in parallel
+    if (warp < 4 && elect_one()) {  // the products of a round are issued by one elected lane of each of four warps
       tc_fence_after();
       if (warp == 0) {
 #pragma unroll

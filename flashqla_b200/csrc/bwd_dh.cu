@@ -140,8 +140,9 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ UMMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ UMMA issuer: the whole warp runs the loop,
+    // one elected lane issues (see elect_one)
+    {
       constexpr uint32_t id64 = umma_idesc(128, 64, false, false, true);
       constexpr uint32_t id64_bmn = umma_idesc(128, 64, false, true, true);
       constexpr uint32_t id64_abmn = umma_idesc(128, 64, true, true, true);
@@ -156,39 +157,51 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         tc_fence_after();
         if (!mbar_wait(wc, &s.pg_ready[st], (it >> 1) & 1, 3)) break;
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tm + kDhColD2, umma_desc_sw128(sdo + kk * 2048, 8192, 1024), umma_desc_sw128(spg + kk * 2048, 8192, 1024),
-                  id64_abmn, kk > 0);
-        umma_commit(&s.d2_done);
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ss(tm + kDhColD2, umma_desc_sw128(sdo + kk * 2048, 8192, 1024), umma_desc_sw128(spg + kk * 2048, 8192, 1024),
+                    id64_abmn, kk > 0);
+          umma_commit(&s.d2_done);
+        }
+        __syncwarp();
         if (!mbar_wait(wc, &s.ds_ready, ph, 4)) break;
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tm + kDhColD1, umma_desc_sw128(sds + dh_koff(kk), 16, 1024), umma_desc_sw128(skq + dh_koff(kk), 16, 1024),
-                  id64, kk > 0);
-        umma_commit(&s.d1_done);
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(tm + kDhColD1, umma_desc_sw128(sds + dh_koff(kk), 16, 1024), umma_desc_sw128(skq + dh_koff(kk), 16, 1024),
+                    id64, kk > 0);
+          umma_commit(&s.d1_done);
+        }
+        __syncwarp();
         if (!mbar_wait(wc, &s.dvp_ready, ph, 5)) break;
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tm + kDhColD1, umma_desc_sw128(sdvp + kk * 32, 16, 1024), umma_desc_sw128(sa + kk * 2048, 8192, 1024),
-                  id64_bmn, kk > 0);
-        umma_commit(&s.dw_done);
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ss(tm + kDhColD1, umma_desc_sw128(sdvp + kk * 32, 16, 1024), umma_desc_sw128(sa + kk * 2048, 8192, 1024),
+                    id64_bmn, kk > 0);
+          umma_commit(&s.dw_done);
+        }
+        __syncwarp();
         if (!mbar_wait(wc, &s.dvg_ready, ph, 7)) break;
         if (!mbar_wait(wc, &s.dos_ready, ph, 8)) break;
         if (!mbar_wait(wc, &s.ds_scaled, ph, 9)) break;
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tm + kDhColS, umma_desc_sw128(sdvg + kk * 32, 16, 1024), umma_desc_sw128(skq + kk * 2048, 16384, 1024),
-                  id128_bmn, 1);
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ss(tm + kDhColS, umma_desc_sw128(sdvg + kk * 32, 16, 1024), umma_desc_sw128(skq + kk * 2048, 16384, 1024),
+                    id128_bmn, 1);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tm + kDhColS, umma_desc_sw128(sdos + kk * 32, 16, 1024),
-                  umma_desc_sw128(skq + 8192 + kk * 2048, 16384, 1024), id128_bmn, 1);
-        umma_commit(&s.ds_done);
-        umma_commit(&s.empty[st]);
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ss(tm + kDhColS, umma_desc_sw128(sdos + kk * 32, 16, 1024),
+                    umma_desc_sw128(skq + 8192 + kk * 2048, 16384, 1024), id128_bmn, 1);
+          umma_commit(&s.ds_done);
+          umma_commit(&s.empty[st]);
+        }
+        __syncwarp();
       }
     }
   } else if (warp < 4) {
