@@ -312,6 +312,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tmem_ld32(tmem_addr(tm, lane_base, kColS + 64 * hf), r0);
         tmem_ld32(tmem_addr(tm, lane_base, kColS + 64 * hf + 32), r1);
         tmem_wait_ld();
+        if (tid == 128) FQ_TS(it, 23);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           uint4 x0, x1;
@@ -347,6 +348,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tmem_st32(tmem_addr(tm, lane_base, kColS + 64 * hf), r0);
         tmem_st32(tmem_addr(tm, lane_base, kColS + 64 * hf + 32), r1);
         tmem_wait_st();
+        if (tid == 128) FQ_TS(it, 25);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s.s_scaled);
@@ -359,6 +361,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         uint32_t u[32];
         tmem_ld32(tmem_addr(tm, lane_base, kColUQ + 32 * hf), u);
         tmem_wait_ld();
+        if (tid == 128) FQ_TS(it, 20);
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -369,8 +372,10 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         for (int j = 0; j < 4; ++j)
           *reinterpret_cast<uint4*>(s.w + sw128(v, hf * 64 + j * 16)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
       }
+      if (tid == 128) FQ_TS(it, 21);
       tc_fence_before();
       fence_async_smem();
+      if (tid == 128) FQ_TS(it, 22);
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.w_ready);
       if (tid == 128) FQ_TS(it, 11);
