@@ -52,7 +52,6 @@ struct FwdSmem {
   unsigned char a[2][8192];    // per stage, A_g tile [64 i][64 j]
   unsigned char pg[2][8192];   // per stage, P_g tile [64 i][64 j]
   unsigned char sbf[32768];    // bf16 S^T [128 v][128 k] as two 128-row regions
-  unsigned char w[16384];      // -(gamma o U)^T, later V'^T   [128 v][64 c]
   unsigned char vd[16384];     // V_d^T             [128 v][64 i]
   float gate[kGateStages][4][kChunk];  // g, exp(g), exp(g_last - g), beta
   uint64_t full[2], empty[2], gate_full[kGateStages], gate_empty[kGateStages];
@@ -86,6 +85,10 @@ struct FwdParams {
 };
 
 __device__ __forceinline__ uint32_t kq_off(int kk) { return (kk >> 2) * 16384 + (kk & 3) * 32; }
+// The chain group hands W^T = -(gamma o U)^T and V'^T to the tensor core as A operands in TENSOR memory, written over
+// the accumulator they were computed from: the warp that owns the fp32 columns [32 hf, 32 hf + 32) of U^T (V_d^T)
+// stores its 32 values as 16 bf16 pairs into columns [32 hf, 32 hf + 16).  K step kk (16 tokens = 8 pair columns):
+__device__ __forceinline__ uint32_t a_col(int kk) { return 32 * (kk >> 1) + 8 * (kk & 1); }
 
 __global__ void __launch_bounds__(kFwdThreads, 1)
 gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -166,7 +169,6 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       constexpr uint32_t id_o = umma_idesc(64, 128, false, false, true);
       const bool want_o = p.o != nullptr;
       const uint64_t d_sbf = umma_desc_sw128(smem_u32(s.sbf), 16, 1024);
-      const uint64_t d_w = umma_desc_sw128(smem_u32(s.w), 16, 1024);
       const uint64_t d_vd = umma_desc_sw128(smem_u32(s.vd), 16, 1024);
       // stage-0 descriptors; stage 1 adds the stage stride to the address field (kept in registers)
       const uint64_t d_vmn0 = umma_desc_sw128(smem_u32(s.v[0]), 8192, 1024);
@@ -217,8 +219,8 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)  // V_d^T -= (gamma o U)^T A_g^T
-            umma_ss(tm + kColVD, desc_add(d_w, kk * 32), desc_add(d_a, kk * 32), id64, (transition && kk == 0) ? 0 : 1);
+          for (int kk = 0; kk < 4; ++kk)  // V_d^T -= (gamma o U)^T A_g^T; A operand: bf16 pairs in the U columns
+            umma_ts(tm + kColVD, tm + kColUQ + a_col(kk), desc_add(d_a, kk * 32), id64, (transition && kk == 0) ? 0 : 1);
           umma_commit(&s.vd_done);
         }
         __syncwarp();
@@ -230,8 +232,8 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)  // S^T += V'^T K
-            umma_ss(tm + kColS, desc_add(d_w, kk * 32), desc_add(d_kmn, kk * 2048), id128_bmn, 1);
+          for (int kk = 0; kk < 4; ++kk)  // S^T += V'^T K; A operand: bf16 pairs in the V_d columns
+            umma_ts(tm + kColS, tm + kColVD + a_col(kk), desc_add(d_kmn, kk * 2048), id128_bmn, 1);
           umma_commit(&s.s_done);
           if (do_o) {
 #pragma unroll
@@ -368,13 +370,11 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           const int c = 32 * hf + i;
           pk[i >> 1] = pack_bf16(-s.gate[gs][1][c] * __uint_as_float(u[i]), -s.gate[gs][1][c + 1] * __uint_as_float(u[i + 1]));
         }
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(s.w + sw128(v, hf * 64 + j * 16)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+        tmem_st16(tmem_addr(tm, lane_base, kColUQ + 32 * hf), pk);
+        tmem_wait_st();
       }
       if (tid == 128) FQ_TS(it, 21);
       tc_fence_before();
-      fence_async_smem();
       if (tid == 128) FQ_TS(it, 22);
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.w_ready);
@@ -395,11 +395,11 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           pd[i >> 1] = pack_bf16(d0, d1);
           pp[i >> 1] = pack_bf16(s.gate[gs][2][c] * d0, s.gate[gs][2][c + 1] * d1);
         }
+        tmem_st16(tmem_addr(tm, lane_base, kColVD + 32 * hf), pp);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 4; ++j)
           *reinterpret_cast<uint4*>(s.vd + sw128(v, hf * 64 + j * 16)) = make_uint4(pd[4 * j], pd[4 * j + 1], pd[4 * j + 2], pd[4 * j + 3]);
-          *reinterpret_cast<uint4*>(s.w + sw128(v, hf * 64 + j * 16)) = make_uint4(pp[4 * j], pp[4 * j + 1], pp[4 * j + 2], pp[4 * j + 3]);
-        }
+        tmem_wait_st();
       }
       tc_fence_before();
       fence_async_smem();
