@@ -32,8 +32,6 @@ struct BwdDhSmem {
   unsigned char a[2][8192];      // A_g tile [64 i][64 j]
   unsigned char pg[2][8192];     // P_g tile [64 i][64 j]
   unsigned char dsbf[32768];     // bf16 dS^T [128 v][128 k]
-  unsigned char dvp[16384];      // dV'^T [128 v][64 c]
-  unsigned char dvg[16384];      // dVg^T [128 v][64 c]
   unsigned char dos[16384];      // (scale*gamma o dO)^T [128 v][64 c]
   float gate[kDhGateStages][4][kChunk];
   uint64_t full[2], empty[2], gate_full[kDhGateStages], gate_empty[kDhGateStages];
@@ -147,7 +145,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       constexpr uint32_t id64_bmn = umma_idesc(128, 64, false, true, true);
       constexpr uint32_t id64_abmn = umma_idesc(128, 64, true, true, true);
       constexpr uint32_t id128_bmn = umma_idesc(128, 128, false, true, true);
-      const uint32_t sds = smem_u32(s.dsbf), sdvp = smem_u32(s.dvp), sdvg = smem_u32(s.dvg), sdos = smem_u32(s.dos);
+      const uint32_t sds = smem_u32(s.dsbf), sdos = smem_u32(s.dos);
       #pragma unroll 1
       for (int it = 0; it < total; ++it) {
         const int st = it & 1;
@@ -180,7 +178,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ss(tm + kDhColD1, umma_desc_sw128(sdvp + kk * 32, 16, 1024), umma_desc_sw128(sa + kk * 2048, 8192, 1024),
+            umma_ts(tm + kDhColD1, tm + kDhColD2 + 8 * kk, umma_desc_sw128(sa + kk * 2048, 8192, 1024),
                     id64_bmn, kk > 0);
           umma_commit(&s.dw_done);
         }
@@ -192,7 +190,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ss(tm + kDhColS, umma_desc_sw128(sdvg + kk * 32, 16, 1024), umma_desc_sw128(skq + kk * 2048, 16384, 1024),
+            umma_ts(tm + kDhColS, tm + kDhColD1 + 8 * kk, umma_desc_sw128(skq + kk * 2048, 16384, 1024),
                     id128_bmn, 1);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
@@ -227,7 +225,6 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ dV', dv, dVg (critical chain)
-    const int v = tid - 128;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32;
     #pragma unroll 1
     for (int it = 0; it < total; ++it) {
@@ -252,11 +249,11 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           packed[c >> 1] = pack_bf16(x0, x1);
         }
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        *reinterpret_cast<uint4*>(s.dvp + sw128(v, j * 16)) = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+      // dV'^T goes to the tensor core as an A operand in tensor memory (bf16 pairs: 32 columns), written over the
+      // D2 accumulator that this thread has just read; likewise dVg^T below over the dW accumulator
+      tmem_st32(tmem_addr(tm, lane_base, kDhColD2), packed);
+      tmem_wait_st();
       tc_fence_before();
-      fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.dvp_ready);
       if (!mbar_wait(wc, &s.dw_done, ph, 14)) break;
@@ -274,11 +271,9 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           pg2[c >> 1] = pack_bf16(-s.gate[gs][1][c] * w0, -s.gate[gs][1][c + 1] * w1);
         }
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        *reinterpret_cast<uint4*>(s.dvg + sw128(v, j * 16)) = make_uint4(pg2[4 * j], pg2[4 * j + 1], pg2[4 * j + 2], pg2[4 * j + 3]);
+      tmem_st32(tmem_addr(tm, lane_base, kDhColD1), pg2);
+      tmem_wait_st();
       tc_fence_before();
-      fence_async_smem();
       __syncwarp();
       if (lane == 0) { mbar_arrive(&s.dvg_ready); mbar_arrive(&s.gate_empty[gs]); }
     }
