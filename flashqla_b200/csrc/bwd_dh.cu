@@ -25,6 +25,7 @@ constexpr uint32_t kDhStageBytes = 32768 + 16384 + 8192 + 8192;
 constexpr uint32_t kDhColS = 0;     // fp32 dS^T
 constexpr uint32_t kDhColD1 = 128;  // D1, later DW
 constexpr uint32_t kDhColD2 = 192;
+constexpr uint32_t kDhColSB = 256;  // bf16 pairs of dS^T (64 columns): the A operand of D1 = dS^T K^T
 
 struct BwdDhSmem {
   unsigned char kq[2][32768];    // k rows 0-63 | q rows 64-127, two 128-row regions (d 0-63 | 64-127)
@@ -145,7 +146,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       constexpr uint32_t id64_bmn = umma_idesc(128, 64, false, true, true);
       constexpr uint32_t id64_abmn = umma_idesc(128, 64, true, true, true);
       constexpr uint32_t id128_bmn = umma_idesc(128, 128, false, true, true);
-      const uint32_t sds = smem_u32(s.dsbf), sdos = smem_u32(s.dos);
+      const uint32_t sdos = smem_u32(s.dos);
       #pragma unroll 1
       for (int it = 0; it < total; ++it) {
         const int st = it & 1;
@@ -168,7 +169,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            umma_ss(tm + kDhColD1, umma_desc_sw128(sds + dh_koff(kk), 16, 1024), umma_desc_sw128(skq + dh_koff(kk), 16, 1024),
+            umma_ts(tm + kDhColD1, tm + kDhColSB + 8 * kk, umma_desc_sw128(skq + dh_koff(kk), 16, 1024),
                     id64, kk > 0);
           umma_commit(&s.d1_done);
         }
@@ -305,29 +306,50 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 16)) { alive = false; break; }
       const float gL = s.gate[gs][1][kChunk - 1];
       const bool store_dh = n < nchunks;
-      if (tid == 256) tma_store_wait_read<0>();  // the previous chunk's TMA store has read the operand buffer
+      // chain part: a bf16 copy of dS^T in tensor memory, the A operand of D1 = dS^T K^T (two column blocks per
+      // round trip)
+#pragma unroll 1
+      for (int cb = 0; cb < 4; cb += 2) {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tmem_addr(tm, lane_base, kDhColS + cb * 32), r0);
+        tmem_ld32(tmem_addr(tm, lane_base, kDhColS + cb * 32 + 32), r1);
+        tmem_wait_ld();
+        uint32_t pk[32];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          pk[j] = pack_bf16(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+          pk[16 + j] = pack_bf16(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+        }
+        tmem_st32(tmem_addr(tm, lane_base, kDhColSB + cb * 16), pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.ds_ready);
+      // trailing part: the same values as a shared-memory tile for the TMA store of dh, and the decay in place
+      if (tid == 256) tma_store_wait_read<0>();  // the previous chunk's TMA store has read the tile
       asm volatile("bar.sync 2, 128;" ::: "memory");
 #pragma unroll 1
       for (int cb = 0; cb < 4; ++cb) {
         uint32_t r[32];
         tmem_ld32(tmem_addr(tm, lane_base, kDhColS + cb * 32), r);
         tmem_wait_ld();
+        if (p.dh_out != nullptr) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 q4;
-          q4.x = pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
-          q4.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-          q4.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-          q4.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-          *reinterpret_cast<uint4*>(s.dsbf + (cb >> 1) * 16384 + sw128(v, (cb & 1) * 64 + j * 16)) = q4;
+          for (int j = 0; j < 4; ++j) {
+            uint4 q4;
+            q4.x = pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+            q4.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+            q4.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+            q4.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            *reinterpret_cast<uint4*>(s.dsbf + (cb >> 1) * 16384 + sw128(v, (cb & 1) * 64 + j * 16)) = q4;
+          }
         }
 #pragma unroll
         for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * gL);
         tmem_st32(tmem_addr(tm, lane_base, kDhColS + cb * 32), r);
       }
       fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s.ds_ready);
       asm volatile("bar.sync 2, 128;" ::: "memory");  // all four warps have written (and fenced) their rows
       if (store_dh && tid == 256) {
         const int hr = static_cast<int>((static_cast<long long>(chunk_off + n) * p.H + h) * kDim);
