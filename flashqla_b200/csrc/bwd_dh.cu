@@ -10,8 +10,13 @@
 //   dS  <- gamma_last dS + dVg^T K + (scale*gamma o dO)^T Q
 //
 // The state BEFORE each update (the gradient w.r.t. the state after the chunk) is written as bf16
-// (transposed, by TMA from the operand buffer) to dh [chunks, H, 128, 128]; the chunk-parallel kernel
+// (transposed, by TMA from a shared-memory tile) to dh [chunks, H, 128, 128]; the chunk-parallel kernel
 // (bwd_chunk.cu) consumes it and forms dv, dq, dk, dg, dbeta.  Nothing else is stored here.
+//
+// The operands that the CUDA cores produce on the chain (dS^T, dV'^T, dVg^T as bf16) reach the tensor core as A
+// operands in TENSOR memory (bf16 pairs, written over / beside the accumulators they come from): no shared-memory
+// round trip and no operand fetch from shared memory for them.  The issuing warp runs its loop with all lanes and
+// issues through one elected lane (see elect_one in common.cuh).
 #include "flashqla.h"
 #include "host.cuh"
 #include "seq.cuh"

@@ -11,6 +11,9 @@
 //   OI   [64 x 128]  = Q S,   OX [64 x 128] = P_g V_d              natural orientation (row = token)
 //
 // Per chunk:  o = scale*gamma o OI + OX,   S <- gamma_last S + K^T V'.
+// W^T = -(gamma o U)^T and V'^T are handed to the tensor core as A operands in TENSOR memory (bf16 pairs written over
+// the accumulators they come from); the bf16 state and V_d^T stay in shared memory (they are B operands, and the
+// state leaves by TMA).  The issuing warp runs its loop with all lanes and issues through one elected lane.
 // Warp roles (16 warps): 0 TMA producer, 1 UMMA issuer, 2-3 gate loader, 4-11 chain group
 // (TMEM state -> bf16 operand + decay, then -gamma o U, then V_d / V'), 12-15 output tile
 // (row-contiguous stores straight from the accumulators).
