@@ -199,9 +199,15 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         FQ_TS(it, 1);
         tc_fence_after();
         if (elect_one()) {
+          if (want_o) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)  // U^T = S^T K^T
-            umma_ss(tm + kColUQ, desc_add(d_sbf, kq_off(kk)), desc_add(d_kq, kq_off(kk)), id64, kk > 0);
+            for (int kk = 0; kk < 8; ++kk)  // U^T = S^T K^T
+              umma_ss(tm + kColUQ, desc_add(d_sbf, kq_off(kk)), desc_add(d_kq, kq_off(kk)), id64, kk > 0);
+          } else {  // state-only runs: the bf16 state is an A operand in tensor memory (the output columns are free)
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)
+              umma_ts(tm + kColUQ, tm + kColOI + 8 * kk, desc_add(d_kq, kq_off(kk)), id64, kk > 0);
+          }
           umma_commit(&s.uq_done);
         }
         __syncwarp();
@@ -308,7 +314,8 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       {
         const float gL = s.gate[gs][1][kChunk - 1];
         const bool store_h = (p.h_out != nullptr) && (n >= 0);
-        if (p.h_out != nullptr) {  // the previous chunk's TMA store must have read the operand buffer
+        const bool state_only = p.o == nullptr;  // then the chain takes the bf16 state from tensor memory
+        if (p.h_out != nullptr && !state_only) {  // the previous chunk's TMA store must have read the operand buffer
           if (tid == 128) tma_store_wait_read<0>();
           asm volatile("bar.sync 2, 256;" ::: "memory");
         }
@@ -318,24 +325,40 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tmem_ld32(tmem_addr(tm, lane_base, kColS + 64 * hf + 32), r1);
         tmem_wait_ld();
         if (tid == 128) FQ_TS(it, 23);
+        uint32_t pk[32];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 x0, x1;
-          x0.x = pack_bf16(__uint_as_float(r0[8 * j]), __uint_as_float(r0[8 * j + 1]));
-          x0.y = pack_bf16(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
-          x0.z = pack_bf16(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
-          x0.w = pack_bf16(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
-          x1.x = pack_bf16(__uint_as_float(r1[8 * j]), __uint_as_float(r1[8 * j + 1]));
-          x1.y = pack_bf16(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
-          x1.z = pack_bf16(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
-          x1.w = pack_bf16(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
-          *reinterpret_cast<uint4*>(s.sbf + hf * 16384 + sw128(v, j * 16)) = x0;
-          *reinterpret_cast<uint4*>(s.sbf + hf * 16384 + sw128(v, 64 + j * 16)) = x1;
+        for (int j = 0; j < 16; ++j) {
+          pk[j] = pack_bf16(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+          pk[16 + j] = pack_bf16(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
         }
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s.s_ready);
-        if (tid == 128) FQ_TS(it, 15);
+        if (state_only) {
+          // chain part: bf16 pairs into the (unused) output columns, the A operand of U^T = S^T K^T
+          tmem_st32(tmem_addr(tm, lane_base, kColOI + 32 * hf), pk);
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s.s_ready);
+          if (tid == 128) FQ_TS(it, 15);
+          if (p.h_out != nullptr) {  // trailing part: the same values as the tile that the TMA store of h reads
+            if (tid == 128) tma_store_wait_read<0>();
+            asm volatile("bar.sync 2, 256;" ::: "memory");
+          }
+        }
+        if (!state_only || p.h_out != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            *reinterpret_cast<uint4*>(s.sbf + hf * 16384 + sw128(v, j * 16)) =
+                make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+            *reinterpret_cast<uint4*>(s.sbf + hf * 16384 + sw128(v, 64 + j * 16)) =
+                make_uint4(pk[16 + 4 * j], pk[16 + 4 * j + 1], pk[16 + 4 * j + 2], pk[16 + 4 * j + 3]);
+          }
+          fence_async_smem();
+        }
+        if (!state_only) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s.s_ready);
+          if (tid == 128) FQ_TS(it, 15);
+        }
         if (p.h_out != nullptr) {
           asm volatile("bar.sync 2, 256;" ::: "memory");  // all 8 warps have written (and fenced) their part
           if (store_h && tid == 128) {
