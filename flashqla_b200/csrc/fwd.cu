@@ -93,6 +93,10 @@ __device__ __forceinline__ uint32_t kq_off(int kk) { return (kk >> 2) * 16384 + 
 // stores its 32 values as 16 bf16 pairs into columns [32 hf, 32 hf + 16).  K step kk (16 tokens = 8 pair columns):
 __device__ __forceinline__ uint32_t a_col(int kk) { return 32 * (kk >> 1) + 8 * (kk & 1); }
 
+// kStateOnly: no output is asked for (state recompute for the backward, state pass of the context-parallel fallback).
+// The two instantiations keep each other's code out of the instruction cache; the state-only one also takes the bf16
+// state from tensor memory (the output accumulators' columns are free there).
+template <bool kStateOnly>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_a,
@@ -170,7 +174,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       constexpr uint32_t id64_amn = umma_idesc(128, 64, true, false, true);
       constexpr uint32_t id128_bmn = umma_idesc(128, 128, false, true, true);
       constexpr uint32_t id_o = umma_idesc(64, 128, false, false, true);
-      const bool want_o = p.o != nullptr;
+      constexpr bool want_o = !kStateOnly;
       const uint64_t d_sbf = umma_desc_sw128(smem_u32(s.sbf), 16, 1024);
       const uint64_t d_vd = umma_desc_sw128(smem_u32(s.vd), 16, 1024);
       // stage-0 descriptors; stage 1 adds the stage stride to the address field (kept in registers)
@@ -314,7 +318,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       {
         const float gL = s.gate[gs][1][kChunk - 1];
         const bool store_h = (p.h_out != nullptr) && (n >= 0);
-        const bool state_only = p.o == nullptr;  // then the chain takes the bf16 state from tensor memory
+        constexpr bool state_only = kStateOnly;  // then the chain takes the bf16 state from tensor memory
         if (p.h_out != nullptr && !state_only) {  // the previous chunk's TMA store must have read the operand buffer
           if (tid == 128) tma_store_wait_read<0>();
           asm volatile("bar.sync 2, 256;" ::: "memory");
@@ -463,7 +467,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       if (!mbar_wait(wc, &s.o_done, ph, 21)) break;
       if (tid == 384) FQ_TS(it, 18);
       tc_fence_after();
-      if (p.o != nullptr && n >= 0) {
+      if (!kStateOnly && n >= 0) {
         const int len = min(kChunk, seq_len - n * kChunk);
         const bool wr = (lane < 16) && (c < len);
         const float f = p.scale * s.gate[gs][1][c];
@@ -574,12 +578,14 @@ extern "C" FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void*
   int dev = 0;
   FQ_CHECK_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    FQ_CHECK_CUDA(cudaFuncSetAttribute(gdr_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    FQ_CHECK_CUDA(cudaFuncSetAttribute(gdr_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    FQ_CHECK_CUDA(cudaFuncSetAttribute(gdr_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     attr_set[dev] = true;
   }
   const long long ctas = static_cast<long long>(n_entries) * H;
   FQ_CHECK_ARG(ctas < (1ll << 31), "fq_gdr_fwd: too many (sequence, head) pairs");
-  gdr_fwd_kernel<<<static_cast<unsigned>(ctas), kFwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, ma, mpg, mh, p);
+  auto kern = (o != nullptr) ? gdr_fwd_kernel<false> : gdr_fwd_kernel<true>;
+  kern<<<static_cast<unsigned>(ctas), kFwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, ma, mpg, mh, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }
