@@ -396,7 +396,9 @@ def main():
     def step(record=False):
         rec = [] if record else None
         # chunk-local cumsum of g, A and the gated tiles in one launch
-        g_cum, A, Ag, Pg = timed("kkt_solve", lambda: kernels.kkt_solve_fused(d["k"], d["q"], d["beta"], d["g"], scale, plan), rec)
+        # (A, which only the backward reads, is stored in the fwd+bwd workloads only)
+        g_cum, A, Ag, Pg = timed("kkt_solve", lambda: kernels.kkt_solve_fused(d["k"], d["q"], d["beta"], d["g"], scale, plan,
+                                                                              want_A=w["bwd"]), rec)
         warm = timed("cp_warmup", lambda: kernels.cp_warmup(g_cum, cp, Hv), rec) if cp is not None else None
         # transition-matrix fallback for slowly decaying heads: state pass + chain (near-empty launches when no head needs it)
         h0p = timed("cp_correct", lambda: kernels.cp_correct_states(d["q"], d["k"], d["v"], Ag, g_cum, d["beta"], scale,

@@ -373,7 +373,8 @@ __global__ void __launch_bounds__(128, 6) kkt_solve_kernel(const __nv_bfloat16* 
     //      the lower block triangle carry values; they are spread evenly over the threads (2.5 per thread), the 192
     //      pieces above it are written as zeros without touching the work matrix.
     {
-      __nv_bfloat16* dst = A_in == nullptr ? A + (static_cast<size_t>(p.tok0) * H + hv) * kChunk : nullptr;
+      // A itself is only read by the backward: a forward that will not be differentiated passes A == nullptr
+      __nv_bfloat16* dst = (A_in == nullptr && A != nullptr) ? A + (static_cast<size_t>(p.tok0) * H + hv) * kChunk : nullptr;
       __nv_bfloat16* dstg = Ag ? Ag + (static_cast<size_t>(p.tok0) * H + hv) * kChunk : nullptr;
       const size_t rs = static_cast<size_t>(H) * kChunk;
       auto emit = [&](int row, int piece) {
@@ -441,7 +442,7 @@ static int kkt_launch(const void* k, const void* q, const float* beta, const flo
                       void* Ag, void* Pg, int a_is_input, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
                       const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale, void* stream) {
   using namespace fq;
-  FQ_CHECK_ARG(k && beta && A, "fq_kkt_solve: null tensor");
+  FQ_CHECK_ARG(k && beta && (A || (Ag && !a_is_input)), "fq_kkt_solve: null tensor");
   FQ_CHECK_ARG((Ag == nullptr && Pg == nullptr) || (g_cumsum != nullptr), "fq_kkt_solve: A_g / P_g need the gate cumsum");
   FQ_CHECK_ARG(Pg == nullptr || q != nullptr, "fq_kkt_solve: P_g needs q");
   FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0,

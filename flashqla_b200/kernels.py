@@ -119,8 +119,9 @@ def kkt_solve_gated(k, q, b, g_cum, scale, plan: SeqPlan, A=None, want_pg=True):
     return A, Ag, Pg
 
 
-def kkt_solve_fused(k, q, b, g, scale, plan: SeqPlan):
-    """Chunk-local cumsum of the raw log gate `g`, A, A_g and P_g in one launch.  Returns (g_cumsum, A, A_g, P_g)."""
+def kkt_solve_fused(k, q, b, g, scale, plan: SeqPlan, want_A=True):
+    """Chunk-local cumsum of the raw log gate `g`, A, A_g and P_g in one launch.  Returns (g_cumsum, A, A_g, P_g).
+    `want_A=False` (A is None then) skips the store of the gate-free inverse, which only the backward reads."""
     _require_cuda(k, q, b, g)
     if k.dtype != torch.bfloat16:
         raise _lib.FlashQLAError("kkt_solve_fused: only bfloat16 keys are supported")
@@ -132,12 +133,13 @@ def kkt_solve_fused(k, q, b, g, scale, plan: SeqPlan):
     bf = b.contiguous() if b.dtype == torch.float32 else b.float().contiguous()
     gf = g.contiguous() if g.dtype == torch.float32 else g.float().contiguous()
     g_cum = torch.empty_like(gf)
-    A = torch.empty(B, T, H, CHUNK, dtype=k.dtype, device=k.device)
-    Ag = torch.empty_like(A)
-    Pg = torch.empty_like(A)
+    Ag = torch.empty(B, T, H, CHUNK, dtype=k.dtype, device=k.device)
+    Pg = torch.empty_like(Ag)
+    A = torch.empty_like(Ag) if want_A else None
     cu_p, off_p = plan.ptrs()
     rc = _lib.load().fq_kkt_solve_fused(k.data_ptr(), q.data_ptr(), bf.data_ptr(), gf.data_ptr(), g_cum.data_ptr(),
-                                        A.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), B, T, H, Hg, cu_p, off_p, plan.n_seq,
+                                        None if A is None else A.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), B, T, H, Hg,
+                                        cu_p, off_p, plan.n_seq,
                                         plan.total_chunks, float(scale), _stream())
     _lib.check(rc, "fq_kkt_solve_fused")
     return g_cum, A, Ag, Pg

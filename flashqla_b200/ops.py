@@ -54,7 +54,8 @@ def l2norm(x: torch.Tensor, dim: int = -1, eps: float = 1e-6) -> torch.Tensor:
 
 
 def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None, cu_seqlens=None,
-                               output_final_state=True, output_h=False, auto_cp=True, _return_tiles=False, _plan=None):
+                               output_final_state=True, output_h=False, auto_cp=True, _return_tiles=False, _plan=None,
+                               _want_A=True):
     """Forward pipeline (chunk/__init__.py:17-67): [cumsum + K K^T + solve + gated tiles] -> fused recurrence.
 
     Returns ``(g_cumsum, A, o, h, final_state)``; ``A`` is the gate-free inverse (opaque, only
@@ -65,7 +66,8 @@ def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None,
     if scale is None:
         scale = K ** -0.5
     plan = _plan if _plan is not None else make_plan(B, T, cu_seqlens, q.device)
-    g_cum, A, Ag, Pg = kernels.kkt_solve_fused(k, q, beta, g, scale, plan)  # the cumsum of g is formed in the same launch
+    # the cumsum of g is formed in the same launch; A is only stored if a backward may follow
+    g_cum, A, Ag, Pg = kernels.kkt_solve_fused(k, q, beta, g, scale, plan, want_A=_want_A)
     status = kernels._status_tensor(q.device) if _DEBUG_STATUS else None
     cp = warm = None
     if auto_cp:
@@ -101,10 +103,14 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     @torch.amp.custom_fwd(device_type="cuda")
     def forward(ctx, q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None,
                 plan=None):
+        # without a gradient to come (inference / prefill) neither A nor anything else is kept
+        needs_bwd = any(ctx.needs_input_grad)
         g_cum, A, o, _, final_state, tiles = chunk_gated_delta_rule_fwd(
             q=q, k=k, v=v, g=g, beta=beta, scale=scale, initial_state=initial_state,
             output_final_state=output_final_state, output_h=False, cu_seqlens=cu_seqlens, _return_tiles=True,
-            _plan=plan)
+            _plan=plan, _want_A=needs_bwd)
+        if not needs_bwd:
+            return o.to(q.dtype), final_state
         ctx.plan = plan  # the backward reuses the forward's sequence plan (no second look at cu_seqlens)
         ctx.keep_tiles = not _RECOMPUTE_TILES
         if ctx.keep_tiles:

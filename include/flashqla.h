@@ -82,6 +82,8 @@ FQ_API int fq_kkt_solve_gated(const void* k, const void* q, const float* beta, c
  * fq_chunk_cumsum + fq_kkt_solve_gated in one launch: `g` is the RAW log gate [B,T,H] fp32, its chunk-local
  * inclusive sum is formed per (chunk, V-head) inside the kernel (a warp scan), used for the gated tiles and written
  * to g_cumsum [B,T,H] fp32.  Saves the separate pass of flash_qla/ops/utils/cumsum.py:131-165 over g.
+ * A may be NULL: the recurrence kernels read only A_g and P_g, A is an input of the backward alone, so a forward that
+ * will not be differentiated (prefill) need not write it.
  */
 FQ_API int fq_kkt_solve_fused(const void* k, const void* q, const float* beta, const float* g, float* g_cumsum, void* A,
                               void* Ag, void* Pg, int B, int T, int H, int Hg, const int32_t* cu_seqlens,

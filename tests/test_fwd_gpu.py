@@ -132,3 +132,16 @@ def test_forward_context_parallel(B, T, Hq, Hv, cu, dist, pc, monkeypatch):
     assert orc.rel_to_max(o.float().cpu(), o_r) < TOL_BF16, "o"
     assert orc.rel_to_max(fs.cpu(), fs_r) < TOL_FP32, "final_state"
     assert orc.rel_to_max(h.float().cpu().reshape(h_r.shape), h_r) < TOL_BF16, "h"
+
+
+def test_inference_call_skips_nothing_visible():
+    """Without a gradient to come the operator does not store the inverse A (only the backward reads it): o and the
+    final state must be bitwise those of the differentiable call."""
+    from flashqla_b200 import chunk_gated_delta_rule
+    q, k, v, g, beta, h0 = (t.to("cuda") for t in make_inputs(21, 2, 700, 2, 4))
+    with torch.no_grad():
+        o_a, fs_a = chunk_gated_delta_rule(q, k, v, g, beta, initial_state=h0, output_final_state=True)
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    o_b, fs_b = chunk_gated_delta_rule(*leaves, g, beta, initial_state=h0, output_final_state=True)
+    torch.cuda.synchronize()
+    assert torch.equal(o_a, o_b.detach()) and torch.equal(fs_a, fs_b.detach())
