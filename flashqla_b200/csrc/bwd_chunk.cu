@@ -231,9 +231,9 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
     __syncthreads();
     BC_TS(15);
-    if (!mbar_wait(wc, &s.bar_tma_a, tma_phase, 1)) { alive = false; break; }
+    if (!warp_all(mbar_wait(wc, &s.bar_tma_a, tma_phase, 1))) { alive = false; break; }
     BC_TS(16);
-    if (!mbar_wait(wc, &s.bar_tma_b, tma_phase, 8)) { alive = false; break; }
+    if (!warp_all(mbar_wait(wc, &s.bar_tma_b, tma_phase, 8))) { alive = false; break; }
     tma_phase ^= 1;
     BC_TS(1);
 
@@ -290,7 +290,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     BC_TS(17);
     // while the first round runs: the next unit's gate values
     if (tid < kChunk && has_next) fetch_gates(nchunk, nh);
-    if (!mbar_wait(wc, &s.bar_mma, mma_phase, 2)) { alive = false; break; }
+    if (!warp_all(mbar_wait(wc, &s.bar_mma, mma_phase, 2))) { alive = false; break; }
     mma_phase ^= 1;
     BC_TS(3);
     tc_fence_after();
@@ -381,7 +381,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
-    if (!mbar_wait(wc, &s.bar_mma, mma_phase, 3)) { alive = false; break; }
+    if (!warp_all(mbar_wait(wc, &s.bar_mma, mma_phase, 3))) { alive = false; break; }
     mma_phase ^= 1;
     BC_TS(5);
     tc_fence_after();
@@ -459,7 +459,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
-    if (!mbar_wait(wc, &s.bar_mma, mma_phase, 4)) { alive = false; break; }
+    if (!warp_all(mbar_wait(wc, &s.bar_mma, mma_phase, 4))) { alive = false; break; }
     mma_phase ^= 1;
     BC_TS(7);
     tc_fence_after();
@@ -606,7 +606,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
-    if (!mbar_wait(wc, &s.bar_mma, mma_phase, 5)) { alive = false; break; }
+    if (!warp_all(mbar_wait(wc, &s.bar_mma, mma_phase, 5))) { alive = false; break; }
     mma_phase ^= 1;
     BC_TS(9);
     tc_fence_after();
@@ -681,7 +681,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (warp == 3 && has_next) load_b(nchunk, nh, 1, b_vp, b_dvg, b_dvp, b_t12);
     }
     __syncwarp();
-    if (!mbar_wait(wc, &s.bar_mma, mma_phase, 6)) { alive = false; break; }
+    if (!warp_all(mbar_wait(wc, &s.bar_mma, mma_phase, 6))) { alive = false; break; }
     mma_phase ^= 1;
     BC_TS(11);
     tc_fence_after();
@@ -740,7 +740,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
-    if (!mbar_wait(wc, &s.bar_mma, mma_phase, 7)) { alive = false; break; }
+    if (!warp_all(mbar_wait(wc, &s.bar_mma, mma_phase, 7))) { alive = false; break; }
     mma_phase ^= 1;
     BC_TS(13);
     tc_fence_after();

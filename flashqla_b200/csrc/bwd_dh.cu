@@ -157,9 +157,9 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const int st = it & 1;
         const uint32_t ph = it & 1;
         const uint32_t skq = smem_u32(s.kq[st]), sa = smem_u32(s.a[st]), sdo = smem_u32(s.dout[st]), spg = smem_u32(s.pg[st]);
-        if (!mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2)) break;
+        if (!warp_all(mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2))) break;
         tc_fence_after();
-        if (!mbar_wait(wc, &s.pg_ready[st], (it >> 1) & 1, 3)) break;
+        if (!warp_all(mbar_wait(wc, &s.pg_ready[st], (it >> 1) & 1, 3))) break;
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
@@ -169,7 +169,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           umma_commit(&s.d2_done);
         }
         __syncwarp();
-        if (!mbar_wait(wc, &s.ds_ready, ph, 4)) break;
+        if (!warp_all(mbar_wait(wc, &s.ds_ready, ph, 4))) break;
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
@@ -179,7 +179,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           umma_commit(&s.d1_done);
         }
         __syncwarp();
-        if (!mbar_wait(wc, &s.dvp_ready, ph, 5)) break;
+        if (!warp_all(mbar_wait(wc, &s.dvp_ready, ph, 5))) break;
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
@@ -189,9 +189,9 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           umma_commit(&s.dw_done);
         }
         __syncwarp();
-        if (!mbar_wait(wc, &s.dvg_ready, ph, 7)) break;
-        if (!mbar_wait(wc, &s.dos_ready, ph, 8)) break;
-        if (!mbar_wait(wc, &s.ds_scaled, ph, 9)) break;
+        if (!warp_all(mbar_wait(wc, &s.dvg_ready, ph, 7))) break;
+        if (!warp_all(mbar_wait(wc, &s.dos_ready, ph, 8))) break;
+        if (!warp_all(mbar_wait(wc, &s.ds_scaled, ph, 9))) break;
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll

@@ -195,6 +195,10 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// The outcome of a bounded wait, made the same for every lane of the (converged) warp: a warp that issues through
+// elect_one must leave its loop as a whole when a wait gives up.
+__device__ __forceinline__ bool warp_all(bool ok) { return __all_sync(0xffffffffu, ok); }
+
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                         uint32_t accumulate) {
   asm volatile(

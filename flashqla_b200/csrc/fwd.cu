@@ -190,7 +190,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const uint64_t d_vmn = desc_add(d_vmn0, st * 16384), d_kq = desc_add(d_kq0, st * 32768),
                        d_kmn = desc_add(d_kmn0, st * 32768), d_a = desc_add(d_a0, st * 8192),
                        d_pg = desc_add(d_pg0, st * 8192);
-        if (!mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2)) break;
+        if (!warp_all(mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2))) break;
         FQ_TS(it, 0);
         tc_fence_after();
         if (!transition && elect_one()) {
@@ -199,7 +199,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             umma_ss(tm + kColVD, desc_add(d_vmn, kk * 2048), desc_add(d_a, kk * 32), id64_amn, kk > 0);
         }
         __syncwarp();
-        if (!mbar_wait_spin(wc, &s.s_ready, ph, 3)) break;
+        if (!warp_all(mbar_wait_spin(wc, &s.s_ready, ph, 3))) break;
         FQ_TS(it, 1);
         tc_fence_after();
         if (elect_one()) {
@@ -217,7 +217,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         __syncwarp();
         FQ_TS(it, 3);
         if (do_o) {  // OI = Q S: the accumulators of the previous chunk must have been drained
-          if (it > 0 && !mbar_wait(wc, &s.o_free, (it - 1) & 1, 4)) break;
+          if (it > 0 && !warp_all(mbar_wait(wc, &s.o_free, (it - 1) & 1, 4))) break;
           FQ_TS(it, 2);
           tc_fence_after();
           if (elect_one()) {
@@ -227,7 +227,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           }
           __syncwarp();
         }
-        if (!mbar_wait_spin(wc, &s.w_ready, ph, 5)) break;
+        if (!warp_all(mbar_wait_spin(wc, &s.w_ready, ph, 5))) break;
         FQ_TS(it, 4);
         tc_fence_after();
         if (elect_one()) {
@@ -238,9 +238,9 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         __syncwarp();
         FQ_TS(it, 6);
-        if (!mbar_wait_spin(wc, &s.vp_ready, ph, 7)) break;
+        if (!warp_all(mbar_wait_spin(wc, &s.vp_ready, ph, 7))) break;
         FQ_TS(it, 7);
-        if (!mbar_wait_spin(wc, &s.s_scaled, ph, 9)) break;
+        if (!warp_all(mbar_wait_spin(wc, &s.s_scaled, ph, 9))) break;
         FQ_TS(it, 8);
         tc_fence_after();
         if (elect_one()) {
