@@ -56,6 +56,7 @@ struct FwdSmem {
   unsigned char pg[2][8192];   // per stage, P_g tile [64 i][64 j]
   unsigned char sbf[32768];    // bf16 S^T [128 v][128 k] as two 128-row regions
   unsigned char vd[16384];     // V_d^T             [128 v][64 i]
+  unsigned char ostage[16384]; // o tile of a whole chunk [64 c][128 v] as two 64-row regions (v 0-63 | 64-127): TMA store
   float gate[kGateStages][4][kChunk];  // g, exp(g), exp(g_last - g), beta
   uint64_t full[2], empty[2], gate_full[kGateStages], gate_empty[kGateStages];
   uint64_t uq_done, vd_done, s_done, o_done;
@@ -101,7 +102,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_a,
                const __grid_constant__ CUtensorMap map_pg, const __grid_constant__ CUtensorMap map_h,
-               const FwdParams p) {
+               const __grid_constant__ CUtensorMap map_o, const FwdParams p) {
   extern __shared__ unsigned char smem_dyn[];
   FwdSmem& s = *reinterpret_cast<FwdSmem*>(
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
@@ -137,7 +138,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     mbar_init(&s.o_free, 4);
     fence_mbar_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); tma_prefetch_desc(&map_a);
-    tma_prefetch_desc(&map_pg); tma_prefetch_desc(&map_h);
+    tma_prefetch_desc(&map_pg); tma_prefetch_desc(&map_h); tma_prefetch_desc(&map_o);
   }
   if (warp == 1) {
     tmem_alloc(&s.tmem_base, 512);
@@ -467,11 +468,20 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       if (!mbar_wait(wc, &s.o_done, ph, 21)) break;
       if (tid == 384) FQ_TS(it, 18);
       tc_fence_after();
+      bool staged = false;
       if (!kStateOnly && n >= 0) {
         const int len = min(kChunk, seq_len - n * kChunk);
+        // A whole chunk leaves through a shared-memory tile and two TMA stores (coalesced, and off the load/store
+        // pipe that the chain group needs); a tail chunk is written row by row so that nothing past the sequence end
+        // is touched.
+        staged = len == kChunk;
         const bool wr = (lane < 16) && (c < len);
         const float f = p.scale * s.gate[gs][1][c];
         __nv_bfloat16* dst = p.o + (static_cast<size_t>(tok_begin + n * kChunk + (wr ? c : 0)) * p.H + h) * kDim;
+        if (staged) {  // the previous chunk's TMA store has read the tile
+          if (tid == 384) tma_store_wait_read<0>();
+          asm volatile("bar.sync 3, 128;" ::: "memory");
+        }
 #pragma unroll
         for (int pc = 0; pc < 4; ++pc) {
           uint32_t oi[32], ox[32];
@@ -490,16 +500,29 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                               f * __uint_as_float(oi[8 * j + 5]) + __uint_as_float(ox[8 * j + 5]));
               x.w = pack_bf16(f * __uint_as_float(oi[8 * j + 6]) + __uint_as_float(ox[8 * j + 6]),
                               f * __uint_as_float(oi[8 * j + 7]) + __uint_as_float(ox[8 * j + 7]));
-              *reinterpret_cast<uint4*>(dst + 32 * pc + 8 * j) = x;
+              if (staged) *reinterpret_cast<uint4*>(s.ostage + (pc >> 1) * 8192 + sw128(c, (pc & 1) * 64 + j * 16)) = x;
+              else *reinterpret_cast<uint4*>(dst + 32 * pc + 8 * j) = x;
             }
           }
         }
       }
+      // the accumulators have been read: the next chunk's output products may start
       tc_fence_before();
       __syncwarp();
       if (lane == 0) { mbar_arrive(&s.o_free); mbar_arrive(&s.gate_empty[gs]); }
+      if (staged) {
+        fence_async_smem();
+        asm volatile("bar.sync 3, 128;" ::: "memory");  // all four warps have written (and fenced) their rows
+        if (tid == 384) {
+          const int row0 = tok_begin + n * kChunk;
+          tma_store_3d(&map_o, s.ostage, 0, h, row0);
+          tma_store_3d(&map_o, s.ostage + 8192, 64, h, row0);
+          tma_store_commit();
+        }
+      }
       if (tid == 384) FQ_TS(it, 19);
     }
+    if (!kStateOnly && tid == 384) tma_store_wait_all<0>();
   }
 
   tc_fence_before();
@@ -550,7 +573,7 @@ extern "C" FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void*
   FQ_CHECK_ARG(warmup == nullptr || cu_seqlens != nullptr, "fq_gdr_fwd: warm-up tables need piece boundaries (cu_seqlens)");
   const uint64_t rows = static_cast<uint64_t>(B) * static_cast<uint64_t>(T);
   FQ_CHECK_ARG(rows > 0 && rows < (1ull << 31), "fq_gdr_fwd: token count out of range");
-  CUtensorMap mq, mk, mv, ma, mpg, mh;
+  CUtensorMap mq, mk, mv, ma, mpg, mh, mo;
   int rc;
   if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
@@ -566,6 +589,8 @@ extern "C" FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void*
     else rc = make_tmap_rows_heads_dim(&mh, v, rows, H, kDim, kChunk, 64);
     if (rc != FQ_OK) return rc;
   }
+  // without o the map is never dereferenced; v stands in to keep the descriptor valid
+  if ((rc = make_tmap_rows_heads_dim(&mo, o ? o : v, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   FwdParams p;
   p.g_cum = g_cumsum; p.beta = beta; p.h0 = h0; p.ht = ht; p.ht_index = ht_index; p.h0_index = h0_index;
   p.warmup = warmup; p.piece_map = piece_map; p.h0_piece = h0_piece;
@@ -585,7 +610,7 @@ extern "C" FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void*
   const long long ctas = static_cast<long long>(n_entries) * H;
   FQ_CHECK_ARG(ctas < (1ll << 31), "fq_gdr_fwd: too many (sequence, head) pairs");
   auto kern = (o != nullptr) ? gdr_fwd_kernel<false> : gdr_fwd_kernel<true>;
-  kern<<<static_cast<unsigned>(ctas), kFwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, ma, mpg, mh, p);
+  kern<<<static_cast<unsigned>(ctas), kFwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, ma, mpg, mh, mo, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }
