@@ -34,6 +34,7 @@ __device__ long long g_trace_bc[32];
 #endif
 
 constexpr int kBcThreads = 512;
+constexpr int kStoreTid = 480;  // warp 15, lane 0: issues the TMA stores of dq and dk (not one of the issuing warps)
 constexpr uint32_t kBcLoadBytesA = 2 * 32768 + 2 * 16384;  // S0, dS, V, dO: requested a unit ahead
 constexpr uint32_t kBcLoadBytesB = 2 * 16384 + 3 * 8192;  // K, Q, A, A_g, P_g: requested at the start of the unit
 
@@ -102,7 +103,8 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                      const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_ag,
                      const __grid_constant__ CUtensorMap map_pg, const __grid_constant__ CUtensorMap map_h,
-                     const __grid_constant__ CUtensorMap map_dh, const BwdChunkParams p) {
+                     const __grid_constant__ CUtensorMap map_dh, const __grid_constant__ CUtensorMap map_dq,
+                     const __grid_constant__ CUtensorMap map_dk, const BwdChunkParams p) {
   extern __shared__ unsigned char smem_dyn[];
   BwdChunkSmem& s = *reinterpret_cast<BwdChunkSmem*>(
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
@@ -211,10 +213,14 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int hg = h / heads_per_group;
     const ChunkPos cp = chunk_lookup(p.sa, chunk);
     const int len = cp.len;
+    const bool whole = len == kChunk;  // then dq and dk leave by TMA; a tail chunk is written row by row
     unsigned char* b_ag = b_at + 8192;
     const uint32_t skt = smem_u32(b_kt), sqt = smem_u32(b_qt), sdvp = smem_u32(b_dvp), sdvg = smem_u32(b_dvg),
                    svp = smem_u32(b_vp), sat = smem_u32(b_at), sag = smem_u32(b_ag), spg = smem_u32(b_pg),
                    st12 = smem_u32(b_t12);
+    // dq and dk of a whole chunk leave through the (dead) Q and K tiles and TMA stores issued by thread kStoreTid; those
+    // tiles are written again in this unit's second round, after the syncs below
+    if (tid == kStoreTid) tma_store_wait_read<0>();
     __syncthreads();  // the previous unit's shared-memory reads are complete
     BC_TS(0);
 
@@ -644,7 +650,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       {
         tmem_ld32(tmem_addr(tm, lane_base, kBcColQ + 64 * hf + 32 * pc), r);
         tmem_wait_ld();
-        if (active && row < len) {
+        if (active && (row < len || whole)) {
 #pragma unroll
           for (int ch = 0; ch < 4; ++ch) {
             uint4 x;
@@ -652,7 +658,9 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             x.y = pack_bf16(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
             x.z = pack_bf16(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
             x.w = pack_bf16(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
-            *reinterpret_cast<uint4*>(dst + 32 * pc + 8 * ch) = x;
+            // whole chunk: into the Q tile (dead since this round's products completed), stored by TMA below
+            if (whole) *reinterpret_cast<uint4*>(b_qt + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = x;
+            else *reinterpret_cast<uint4*>(dst + 32 * pc + 8 * ch) = x;
           }
         }
       }
@@ -660,6 +668,11 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     tc_fence_before();
     fence_async_smem();
     __syncthreads();
+    if (whole && tid == kStoreTid) {
+      tma_store_3d(&map_dq, b_qt, 0, h, cp.tok0);
+      tma_store_3d(&map_dq, b_qt + 8192, 64, h, cp.tok0);
+      tma_store_commit();
+    }
 
     BC_TS(10);
     // ================================================================== round 5
@@ -727,11 +740,12 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     if (warp < 4 && elect_one()) {  // the products of a round are issued by one elected lane of each of four warps
       tc_fence_after();
       if (warp == 0) {
+        // both groups add to the same accumulator: one thread issues them, so that the order of the fp32 additions
+        // (and with it every bit of dk) is the same from run to run
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // accK += T5 K
           umma_ss(tm + kBcColK, desc_add(umma_desc_sw128(sag, 16, 1024), kk * 32), desc_add(umma_desc_sw128(skt, 8192, 1024), kk * 2048),
                   id64_128_kmn, 1);
-      } else if (warp == 1) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // accK += T5^T K
           umma_ss(tm + kBcColK, desc_add(umma_desc_sw128(sag, 8192, 1024), kk * 2048), desc_add(umma_desc_sw128(skt, 8192, 1024), kk * 2048),
@@ -750,7 +764,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         uint32_t r[32];
         tmem_ld32(tmem_addr(tm, lane_base, kBcColK + 64 * hf + 32 * pc), r);
         tmem_wait_ld();
-        if (active && row < len) {
+        if (active && (row < len || whole)) {
 #pragma unroll
           for (int ch = 0; ch < 4; ++ch) {
             uint4 x;
@@ -758,13 +772,21 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             x.y = pack_bf16(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
             x.z = pack_bf16(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
             x.w = pack_bf16(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
-            *reinterpret_cast<uint4*>(dst + 32 * pc + 8 * ch) = x;
+            // whole chunk: into the K tile (dead since this round's products completed), stored by TMA below
+            if (whole) *reinterpret_cast<uint4*>(b_kt + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = x;
+            else *reinterpret_cast<uint4*>(dst + 32 * pc + 8 * ch) = x;
           }
         }
       }
     }
     tc_fence_before();
+    fence_async_smem();
     __syncthreads();
+    if (whole && tid == kStoreTid) {
+      tma_store_3d(&map_dk, b_kt, 0, h, cp.tok0);
+      tma_store_3d(&map_dk, b_kt + 8192, 64, h, cp.tok0);
+      tma_store_commit();
+    }
     BC_TS(14);
     if (tid < kChunk) {
       // the padded rows of a tail chunk share the gate of the last valid token
@@ -790,6 +812,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     h = nh;
   }
 
+  if (tid == kStoreTid) tma_store_wait_all<0>();
   if (!alive && tid == 0) {
     // a bounded wait gave up: let the tile loads that are still in flight land before the CTA's shared memory is released
 #pragma unroll 1
@@ -853,7 +876,7 @@ extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void*
   const uint64_t rows = static_cast<uint64_t>(B) * static_cast<uint64_t>(T);
   const uint64_t hrows = static_cast<uint64_t>(total_chunks) * H * kDim;
   FQ_CHECK_ARG(rows > 0 && rows < (1ull << 31) && hrows < (1ull << 31), "fq_gdr_bwd_chunk: sizes out of range");
-  CUtensorMap mq, mk, mv, mdo, ma, mag, mpg, mh, mdh;
+  CUtensorMap mq, mk, mv, mdo, ma, mag, mpg, mh, mdh, mdq, mdk;
   int rc;
   if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
@@ -864,6 +887,8 @@ extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void*
   if ((rc = make_tmap_rows_heads_dim(&mpg, Pg, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mh, h, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdh, dh, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdq, dq, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdk, dk, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   BwdChunkParams p;
   p.g_cum = g_cumsum; p.beta = beta;
   p.dq = static_cast<__nv_bfloat16*>(dq); p.dk = static_cast<__nv_bfloat16*>(dk); p.dg = dg; p.db = db;
@@ -882,7 +907,7 @@ extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void*
   const long long units = static_cast<long long>(total_chunks) * H;
   const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
   gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mdo, ma, mag, mpg, mh,
-                                                                                      mdh, p);
+                                                                                      mdh, mdq, mdk, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }
@@ -958,7 +983,7 @@ extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k,
   __nv_bfloat16* dq_h = reinterpret_cast<__nv_bfloat16*>(scratch_dev[dev]);
   __nv_bfloat16* dk_h = reinterpret_cast<__nv_bfloat16*>(scratch_dev[dev] + per_buffer);
 
-  CUtensorMap mq, mk, mv, mdo, ma, mag, mpg, mh, mdh;
+  CUtensorMap mq, mk, mv, mdo, ma, mag, mpg, mh, mdh, mdq, mdk;
   int rc;
   if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
@@ -969,6 +994,8 @@ extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k,
   if ((rc = make_tmap_rows_heads_dim(&mpg, Pg, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mh, h, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdh, dh, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdq, dq_h, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdk, dk_h, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   BwdChunkParams p;
   p.g_cum = g_cumsum; p.beta = beta;
   p.dq = dq_h; p.dk = dk_h; p.dg = dg; p.db = db;
@@ -979,7 +1006,7 @@ extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long units = static_cast<long long>(total_chunks) * H;
   const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
-  gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, st>>>(mq, mk, mv, mdo, ma, mag, mpg, mh, mdh, p);
+  gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, st>>>(mq, mk, mv, mdo, ma, mag, mpg, mh, mdh, mdq, mdk, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   // Every token row of both scratch buffers was just written (each row belongs to exactly one
   // chunk), so nothing has to be cleared before the sum reads them.

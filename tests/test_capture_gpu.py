@@ -35,13 +35,13 @@ def _inputs(seed, B, T, Hq, Hv, n_seq=None, dtype=torch.bfloat16):
 
 
 def _same(got, want):
-    """o and final_state bitwise (the forward is deterministic); gradients to 1e-4 of their maximum (the backward
-    sums dg and dbeta with shared-memory atomics, whose order varies from run to run)."""
+    """(o, final_state, dq, dk, dv, dg, dbeta, dh0): everything bitwise except dg and dbeta, which the backward sums
+    with shared-memory atomics whose order varies from run to run (those to 1e-4 of their maximum)."""
     for i, (a, b) in enumerate(zip(got, want)):
-        if i < 2:
-            assert torch.equal(a, b)
-        else:
+        if i in (5, 6):
             assert (a.float() - b.float()).abs().max() <= 1e-4 * b.float().abs().max()
+        else:
+            assert torch.equal(a, b), i
 
 
 def _fwd_bwd(q, k, v, g, beta, h0, do, dht, **kw):
