@@ -34,7 +34,7 @@ __device__ long long g_trace_bc[32];
 #endif
 
 constexpr int kBcThreads = 512;
-constexpr int kStoreTid = 480;  // warp 15, lane 0: issues the TMA stores of dq and dk (not one of the issuing warps)
+constexpr int kStoreTid = 480;  // warp 15, lane 0: issues the TMA stores of dq, dk and dv (not one of the issuing warps)
 constexpr uint32_t kBcLoadBytesA = 2 * 32768 + 2 * 16384;  // S0, dS, V, dO: requested a unit ahead
 constexpr uint32_t kBcLoadBytesB = 2 * 16384 + 3 * 8192;  // K, Q, A, A_g, P_g: requested at the start of the unit
 
@@ -104,7 +104,8 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                      const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_ag,
                      const __grid_constant__ CUtensorMap map_pg, const __grid_constant__ CUtensorMap map_h,
                      const __grid_constant__ CUtensorMap map_dh, const __grid_constant__ CUtensorMap map_dq,
-                     const __grid_constant__ CUtensorMap map_dk, const BwdChunkParams p) {
+                     const __grid_constant__ CUtensorMap map_dk, const __grid_constant__ CUtensorMap map_dv,
+                     const BwdChunkParams p) {
   extern __shared__ unsigned char smem_dyn[];
   BwdChunkSmem& s = *reinterpret_cast<BwdChunkSmem*>(
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
@@ -428,7 +429,10 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
               zw[e] = pack_bf16(-gam_r * d0, -gam_r * d1);    // dVg
             }
             *reinterpret_cast<uint4*>(b_dvg + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = z;
-            if (row < len) *reinterpret_cast<uint4*>(dvdst + 32 * pc + 8 * ch) = y;
+            // whole chunk: the two 64-column halves of dv go into the T and T3 tiles (free until the third round's
+            // epilogue) and leave by TMA below
+            if (whole) *reinterpret_cast<uint4*>((hf ? s.t3 : b_t12) + sw128(row, (4 * pc + ch) * 16)) = y;
+            else if (row < len) *reinterpret_cast<uint4*>(dvdst + 32 * pc + 8 * ch) = y;
           }
         }
       }
@@ -436,6 +440,11 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     tc_fence_before();
     fence_async_smem();
     __syncthreads();
+    if (whole && tid == kStoreTid) {
+      tma_store_3d(&map_dv, b_t12, 0, h, cp.tok0);
+      tma_store_3d(&map_dv, s.t3, 64, h, cp.tok0);
+      tma_store_commit();
+    }
 
     BC_TS(6);
     // ================================================================== round 3
@@ -469,6 +478,10 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     mma_phase ^= 1;
     BC_TS(7);
     tc_fence_after();
+    if (whole) {  // the TMA store of dv has read the T / T3 tiles, which this round's epilogue writes
+      if (tid == kStoreTid) tma_store_wait_read<0>();
+      __syncthreads();
+    }
     // The tiles that round three read last are dead from here on; two threads request this CTA's next unit there:
     // S0, dS, V, dO in place, and K, Q, A, A_g into V', dVg and dV'.  They land while rounds three to six finish.
     if (has_next && (warp == 2 || warp == 3)) {
@@ -876,7 +889,7 @@ extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void*
   const uint64_t rows = static_cast<uint64_t>(B) * static_cast<uint64_t>(T);
   const uint64_t hrows = static_cast<uint64_t>(total_chunks) * H * kDim;
   FQ_CHECK_ARG(rows > 0 && rows < (1ull << 31) && hrows < (1ull << 31), "fq_gdr_bwd_chunk: sizes out of range");
-  CUtensorMap mq, mk, mv, mdo, ma, mag, mpg, mh, mdh, mdq, mdk;
+  CUtensorMap mq, mk, mv, mdo, ma, mag, mpg, mh, mdh, mdq, mdk, mdv;
   int rc;
   if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
@@ -889,6 +902,7 @@ extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void*
   if ((rc = make_tmap_rows_heads_dim(&mdh, dh, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdq, dq, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdk, dk, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdv, dv, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   BwdChunkParams p;
   p.g_cum = g_cumsum; p.beta = beta;
   p.dq = static_cast<__nv_bfloat16*>(dq); p.dk = static_cast<__nv_bfloat16*>(dk); p.dg = dg; p.db = db;
@@ -907,7 +921,7 @@ extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void*
   const long long units = static_cast<long long>(total_chunks) * H;
   const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
   gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mdo, ma, mag, mpg, mh,
-                                                                                      mdh, mdq, mdk, p);
+                                                                                      mdh, mdq, mdk, mdv, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }
@@ -983,7 +997,7 @@ extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k,
   __nv_bfloat16* dq_h = reinterpret_cast<__nv_bfloat16*>(scratch_dev[dev]);
   __nv_bfloat16* dk_h = reinterpret_cast<__nv_bfloat16*>(scratch_dev[dev] + per_buffer);
 
-  CUtensorMap mq, mk, mv, mdo, ma, mag, mpg, mh, mdh, mdq, mdk;
+  CUtensorMap mq, mk, mv, mdo, ma, mag, mpg, mh, mdh, mdq, mdk, mdv;
   int rc;
   if ((rc = make_tmap_rows_heads_dim(&mq, q, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
@@ -996,6 +1010,7 @@ extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k,
   if ((rc = make_tmap_rows_heads_dim(&mdh, dh, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdq, dq_h, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdk, dk_h, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdv, dv, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   BwdChunkParams p;
   p.g_cum = g_cumsum; p.beta = beta;
   p.dq = dq_h; p.dk = dk_h; p.dg = dg; p.db = db;
@@ -1006,7 +1021,7 @@ extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long units = static_cast<long long>(total_chunks) * H;
   const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
-  gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, st>>>(mq, mk, mv, mdo, ma, mag, mpg, mh, mdh, mdq, mdk, p);
+  gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, st>>>(mq, mk, mv, mdo, ma, mag, mpg, mh, mdh, mdq, mdk, mdv, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   // Every token row of both scratch buffers was just written (each row belongs to exactly one
   // chunk), so nothing has to be cleared before the sum reads them.
