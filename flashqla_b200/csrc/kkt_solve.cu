@@ -104,8 +104,10 @@ __device__ __forceinline__ void gram_pass(float (&acc)[8][4], const __nv_bfloat1
 }
 
 // P_g straight from the Q K^T fragments (rows m0+g and m0+g+8, column pairs 8j+2t); g2 = gate cumsum * log2(e).
+// `stage`: this warp's own 16 rows of a dead [64][kKLd] bf16 tile, or nullptr.  With it the values are first laid down
+// in shared memory and leave as 16-byte pieces (eight lanes per 128-byte row) instead of 4-byte stores.
 __device__ __forceinline__ void store_pg(const float (&qk)[8][4], const float* g2, __nv_bfloat16* dstp, size_t row_stride,
-                                         int warp, int lane, int len, float scale) {
+                                         int warp, int lane, int len, float scale, __nv_bfloat16* stage = nullptr) {
   const int m0 = warp * 16, g = lane >> 2, t = lane & 3;
   const float log2_scale = log2f(scale);
 #pragma unroll
@@ -122,8 +124,19 @@ __device__ __forceinline__ void store_pg(const float (&qk)[8][4], const float* g
           if (c0 <= row) y0 = exp2f(gi - gj.x) * qk[j][2 * half];
           if (c0 + 1 <= row) y1 = exp2f(gi - gj.y) * qk[j][2 * half + 1];
         }
-        *reinterpret_cast<uint32_t*>(dstp + static_cast<size_t>(row) * row_stride + c0) = pack_bf16(y0, y1);
+        if (stage) *reinterpret_cast<uint32_t*>(stage + (g + 8 * half) * kKLd + c0) = pack_bf16(y0, y1);
+        else *reinterpret_cast<uint32_t*>(dstp + static_cast<size_t>(row) * row_stride + c0) = pack_bf16(y0, y1);
       }
+    }
+  }
+  if (stage) {
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int i = it * 32 + lane, r = i >> 3, piece = i & 7;
+      if (m0 + r < len)
+        *(reinterpret_cast<uint4*>(dstp + static_cast<size_t>(m0 + r) * row_stride) + piece) =
+            *reinterpret_cast<const uint4*>(stage + r * kKLd + piece * 8);
     }
   }
 }
@@ -203,8 +216,9 @@ __global__ void __launch_bounds__(128, 6) kkt_solve_kernel(const __nv_bfloat16* 
     if (Pg) {
       gram_pass(qk, s.q, s.k, m0, ntiles, lane);
       if (kSingle)
+        // the warp's own rows of the Q tile are dead once its Q K^T fragments are formed: staging for P_g
         store_pg(qk, s.g, Pg + (static_cast<size_t>(p.tok0) * H + hg) * kChunk, static_cast<size_t>(H) * kChunk, warp, lane,
-                 p.len, scale);
+                 p.len, scale, &s.q[m0 * kKLd]);
     }
     if (A_in == nullptr) {
       float acc[8][4];
