@@ -406,15 +406,15 @@ def main():
         o, _, fs = timed("gdr_fwd", lambda: kernels.fused_gdr_fwd(d["q"], d["k"], d["v"], Ag, Pg, g_cum, d["beta"], scale,
                                                                  initial_state=d["h0"], plan=plan, cp=cp, warmup=warm,
                                                                  h0_piece=h0p), rec)
-        n = 2 + (4 if cp is not None else 0)  # kkt_solve, gdr_fwd (+ gate scan, codes, state pass, chain)
+        n = 2 + (3 if cp is not None else 0)  # kkt_solve, gdr_fwd (+ plan kernel, state pass, chain)
         if w["bwd"]:
             # as in the autograd function, which keeps the forward's gated tiles for its backward
             timed("backward", lambda: fq.chunk_gated_delta_rule_bwd(d["q"], d["k"], d["v"], g_cum, d["beta"], A, d["do"],
                                                                      d["dht"], scale, d["h0"], None,
                                                                      _gated_tiles=(Ag, Pg)), rec)
-            # fwd(h) + bwd_dh + bwd_chunk + reverse cumsum (+ 2 gate scans, 2 code kernels, state pass, chain, gradient
-            # pass, reverse chain; + 2 head sums)
-            n += 4 + (8 if cp is not None else 0) + (2 if Hq < Hv else 0)
+            # fwd(h) + bwd_dh + bwd_chunk + reverse cumsum (+ plan kernel, state pass, chain, gradient pass, reverse chain;
+            # + 2 head sums)
+            n += 4 + (5 if cp is not None else 0) + (2 if Hq < Hv else 0)
         if record:
             stamps.append(rec)
         launches[0] = n

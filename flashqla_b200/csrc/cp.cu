@@ -15,22 +15,13 @@ namespace fq {
 // inclusive warp scan, and the first chunk at which it drops below the threshold ends the replay.  `w_cap` bounds
 // the walk (0 = no bound): a replay that would be longer is reported as w_cap + 1 chunks without looking further,
 // which is all that the transition-matrix fallback needs to know.
-__global__ void __launch_bounds__(128) cp_warmup_kernel(const float* __restrict__ g_cum,
-                                                       const int* __restrict__ piece_start,
-                                                       const int* __restrict__ piece_first_chunk,
-                                                       int* __restrict__ warmup, int n_pieces, int H, float threshold,
-                                                       int reverse, const int* __restrict__ piece_chunks_after,
-                                                       int w_cap, const int* __restrict__ piece_seq,
-                                                       int* __restrict__ flags) {
-  const int idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (idx >= n_pieces * H) return;
-  const int piece = idx / H, h = idx - piece * H;
-  // forward: chunks before the piece, walking backwards from its first token; reverse (state gradient): chunks
-  // after the piece, walking forwards from the first token after it (piece_start holds that token,
-  // piece_chunks_after the number of chunks that follow and piece_first_chunk the length of the sequence's last chunk)
-  const int avail = reverse ? __ldg(piece_chunks_after + piece) : __ldg(piece_first_chunk + piece);
-  const long long edge = __ldg(piece_start + piece);
-  const int last_len = reverse ? __ldg(piece_first_chunk + piece) : kChunk;
+// The walk of one warp: returns (in every lane) the code of the replay - w chunks, or avail | bit 30 when the end of
+// the sequence is reached first, or limit = w_cap + 1 when the walk gave up at the cap.
+__device__ __forceinline__ int scan_replay(const float* __restrict__ g_cum, long long edge, int avail, int last_len,
+                                           bool reverse, int H, int h, float threshold, int w_cap, int lane) {
+  // forward: chunks before the piece, walking backwards from its first token `edge`; reverse (state gradient): chunks
+  // after the piece, walking forwards from the first token after it (`edge`), `last_len` = tokens in the sequence's
+  // last chunk
   const int limit = (w_cap > 0 && w_cap + 1 < avail) ? w_cap + 1 : avail;
   float carry = 0.f;
   int w = -1;
@@ -53,11 +44,25 @@ __global__ void __launch_bounds__(128) cp_warmup_kernel(const float* __restrict_
     if (hit) w = base + __ffs(hit);  // chunks replayed = index of the first hit + 1
     carry = __shfl_sync(0xffffffffu, x, 31);
   }
+  if (w > 0) return w;                           // decayed after w chunks
+  if (limit == avail) return avail | (1 << 30);  // reached the end of the sequence: exact
+  return limit;                                  // gave up at the cap
+}
+
+__global__ void __launch_bounds__(128) cp_warmup_kernel(const float* __restrict__ g_cum,
+                                                       const int* __restrict__ piece_start,
+                                                       const int* __restrict__ piece_first_chunk,
+                                                       int* __restrict__ warmup, int n_pieces, int H, float threshold,
+                                                       int reverse, const int* __restrict__ piece_chunks_after,
+                                                       int w_cap, const int* __restrict__ piece_seq,
+                                                       int* __restrict__ flags) {
+  const int idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (idx >= n_pieces * H) return;
+  const int piece = idx / H, h = idx - piece * H;
+  const int avail = reverse ? __ldg(piece_chunks_after + piece) : __ldg(piece_first_chunk + piece);
+  const int last_len = reverse ? __ldg(piece_first_chunk + piece) : kChunk;
+  const int code = scan_replay(g_cum, __ldg(piece_start + piece), avail, last_len, reverse != 0, H, h, threshold, w_cap, lane);
   if (lane == 0) {
-    int code;
-    if (w > 0) code = w;                                   // decayed after w chunks
-    else if (limit == avail) code = avail | (1 << 30);     // reached the end of the sequence: exact
-    else code = limit;                                     // gave up at the cap
     warmup[idx] = code;
     // a replay of more than w_cap chunks: the (sequence, head) pair takes the transition-matrix route (see below)
     if (flags != nullptr && (code & 0xFFFFFF) > w_cap) atomicOr(flags + __ldg(piece_seq + piece) * H + h, 1);
@@ -112,6 +117,54 @@ __global__ void __launch_bounds__(128) cp_resolve_reverse_kernel(const int* __re
   const bool first = __ldg(chunks_before + piece) == 0, last = __ldg(chunks_after + piece) == 0;
   warmup_out[idx] = (flagged && !last) ? (1 << 29) : __ldg(warmup_in + idx);
   pass1[idx] = (flagged && !first) ? (last ? (1 << 30) : 0) : (1 << 27);
+}
+
+// Gate scans (both directions if codes_rev is given), flag and codes of one (sequence, head) in ONE launch: a CTA per
+// pair, a warp per piece for the scans, then - the flag being known inside the CTA - a thread per piece for the codes.
+// Same results as fq_cp_warmup (+ reverse) followed by fq_cp_transition_plan(_reverse).
+__global__ void __launch_bounds__(256) cp_plan_kernel(const float* __restrict__ g_cum, const int* __restrict__ piece_start,
+                                                     const int* __restrict__ piece_end,
+                                                     const int* __restrict__ chunks_before,
+                                                     const int* __restrict__ chunks_after,
+                                                     const int* __restrict__ last_chunk_len,
+                                                     const int* __restrict__ seq_piece_offsets, int* __restrict__ flags,
+                                                     int* __restrict__ codes, int* __restrict__ pass1,
+                                                     int* __restrict__ codes_rev, int* __restrict__ pass1_rev,
+                                                     int n_pieces, int H, float threshold, int w_cap) {
+  __shared__ int any_far;
+  const int seq = blockIdx.x / H, h = blockIdx.x - seq * H;
+  const int p0 = __ldg(seq_piece_offsets + seq), p1 = __ldg(seq_piece_offsets + seq + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) any_far = 0;
+  __syncthreads();
+  for (int piece = p0 + warp; piece < p1; piece += 8) {
+    const int cf = scan_replay(g_cum, __ldg(piece_start + piece), __ldg(chunks_before + piece), kChunk, false, H, h,
+                               threshold, w_cap, lane);
+    int cr = 0;
+    if (codes_rev != nullptr)
+      cr = scan_replay(g_cum, __ldg(piece_end + piece), __ldg(chunks_after + piece), __ldg(last_chunk_len + piece), true, H,
+                       h, threshold, w_cap, lane);
+    if (lane == 0) {
+      codes[piece * H + h] = cf;
+      if (codes_rev != nullptr) codes_rev[piece * H + h] = cr;
+      if ((cf & 0xFFFFFF) > w_cap || (cr & 0xFFFFFF) > w_cap) atomicOr(&any_far, 1);
+    }
+  }
+  __syncthreads();  // also makes this CTA's own global writes above visible to its threads below
+  const bool flagged = any_far != 0;
+  if (threadIdx.x == 0) flags[seq * H + h] = flagged ? 1 : 0;
+  constexpr int kSkip = 1 << 27;
+  for (int piece = p0 + threadIdx.x; piece < p1; piece += 256) {
+    const int idx = piece * H + h;
+    const bool first = __ldg(chunks_before + piece) == 0, last = __ldg(chunks_after + piece) == 0;
+    if (flagged && !first) codes[idx] = 1 << 29;
+    pass1[idx] = (flagged && !last) ? (first ? (1 << 30) : 0) : kSkip;               // B_r
+    pass1[n_pieces * H + idx] = (flagged && !last && !first) ? (1 << 28) : kSkip;    // T_r
+    if (codes_rev != nullptr) {
+      if (flagged && !last) codes_rev[idx] = 1 << 29;
+      pass1_rev[idx] = (flagged && !first) ? (last ? (1 << 30) : 0) : kSkip;
+    }
+  }
 }
 
 __device__ __forceinline__ void mma_tf32_1688(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
@@ -287,6 +340,24 @@ extern "C" FQ_API int fq_cp_chain_reverse(const float* c, const float* tmat, flo
   FQ_CHECK_ARG(n_pieces > 0 && n_seq > 0 && H > 0, "fq_cp_chain_reverse: bad arguments");
   dim3 grid(static_cast<unsigned>(n_seq) * H, kDim / kChainCols);
   cp_chain_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(c, tmat, dht_piece, flags, seq_piece_offsets, H);
+  FQ_CHECK_CUDA(cudaGetLastError());
+  return FQ_OK;
+}
+
+extern "C" FQ_API int fq_cp_plan(const float* g_cumsum, const int32_t* piece_start, const int32_t* piece_end,
+                                 const int32_t* chunks_before, const int32_t* chunks_after,
+                                 const int32_t* last_chunk_len, const int32_t* seq_piece_offsets, int32_t* flags,
+                                 int32_t* codes, int32_t* pass1_codes, int32_t* codes_rev, int32_t* pass1_rev,
+                                 int n_pieces, int n_seq, int H, float threshold, int w_cap, void* stream) {
+  using namespace fq;
+  FQ_CHECK_ARG(g_cumsum && piece_start && piece_end && chunks_before && chunks_after && last_chunk_len &&
+                   seq_piece_offsets && flags && codes && pass1_codes,
+               "fq_cp_plan: null tensor");
+  FQ_CHECK_ARG((codes_rev == nullptr) == (pass1_rev == nullptr), "fq_cp_plan: the reverse tables come together");
+  FQ_CHECK_ARG(n_pieces > 0 && n_seq > 0 && H > 0 && threshold < 0.f && w_cap > 0, "fq_cp_plan: bad arguments");
+  cp_plan_kernel<<<static_cast<unsigned>(n_seq) * H, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      g_cumsum, piece_start, piece_end, chunks_before, chunks_after, last_chunk_len, seq_piece_offsets, flags, codes,
+      pass1_codes, codes_rev, pass1_rev, n_pieces, H, threshold, w_cap);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }

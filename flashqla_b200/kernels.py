@@ -167,35 +167,22 @@ def cp_warmup(g_cum, cp, H, threshold=-16.0, with_reverse=False) -> CpWarm:
     (in either direction when `with_reverse`) is switched to corrected start states."""
     dev = g_cum.device
     P = cp.n_pieces
-    lib = _lib.load()
     cap = int(cp.piece_chunks)
-    raw = torch.empty(P, H, dtype=torch.int32, device=dev)
-    flags = torch.zeros(cp.n_seq, H, dtype=torch.int32, device=dev)
-    rc = lib.fq_cp_warmup(g_cum.data_ptr(), cp.piece_start.data_ptr(), cp.chunks_before.data_ptr(), None,
-                          raw.data_ptr(), P, H, float(threshold), 0, cap, cp.seq_index.data_ptr(), flags.data_ptr(),
-                          _stream())
-    _lib.check(rc, "fq_cp_warmup")
-    raw_r = None
-    if with_reverse:
-        raw_r = torch.empty(P, H, dtype=torch.int32, device=dev)
-        rc = lib.fq_cp_warmup(g_cum.data_ptr(), cp.piece_end.data_ptr(), cp.last_chunk_len.data_ptr(),
-                              cp.chunks_after.data_ptr(), raw_r.data_ptr(), P, H, float(threshold), 1, cap,
-                              cp.seq_index.data_ptr(), flags.data_ptr(), _stream())
-        _lib.check(rc, "fq_cp_warmup")
-    codes = torch.empty_like(raw)
+    codes = torch.empty(P, H, dtype=torch.int32, device=dev)
     pass1 = torch.empty(2 * P, H, dtype=torch.int32, device=dev)
-    rc = lib.fq_cp_transition_plan(raw.data_ptr(), cp.seq_index.data_ptr(), cp.chunks_before.data_ptr(),
-                                   cp.chunks_after.data_ptr(), flags.data_ptr(), codes.data_ptr(), pass1.data_ptr(), P, H,
-                                   _stream())
-    _lib.check(rc, "fq_cp_transition_plan")
+    flags = torch.empty(cp.n_seq, H, dtype=torch.int32, device=dev)
     warm = CpWarm(codes, pass1, flags)
     if with_reverse:
-        warm.codes_rev = torch.empty_like(raw)
-        warm.pass1_rev = torch.empty_like(raw)
-        rc = lib.fq_cp_transition_plan_reverse(raw_r.data_ptr(), cp.seq_index.data_ptr(), cp.chunks_before.data_ptr(),
-                                               cp.chunks_after.data_ptr(), flags.data_ptr(), warm.codes_rev.data_ptr(),
-                                               warm.pass1_rev.data_ptr(), P, H, _stream())
-        _lib.check(rc, "fq_cp_transition_plan_reverse")
+        warm.codes_rev = torch.empty_like(codes)
+        warm.pass1_rev = torch.empty_like(codes)
+    # scans, flag and codes of every (sequence, head) in one launch
+    rc = _lib.load().fq_cp_plan(g_cum.data_ptr(), cp.piece_start.data_ptr(), cp.piece_end.data_ptr(),
+                                cp.chunks_before.data_ptr(), cp.chunks_after.data_ptr(), cp.last_chunk_len.data_ptr(),
+                                cp.seq_piece_offsets.data_ptr(), flags.data_ptr(), codes.data_ptr(), pass1.data_ptr(),
+                                None if not with_reverse else warm.codes_rev.data_ptr(),
+                                None if not with_reverse else warm.pass1_rev.data_ptr(), P, cp.n_seq, H,
+                                float(threshold), cap, _stream())
+    _lib.check(rc, "fq_cp_plan")
     return warm
 
 

@@ -154,6 +154,21 @@ FQ_API int fq_cp_transition_plan(const int32_t* warmup_in, const int32_t* piece_
                                  int32_t* pass1_codes, int n_pieces, int H, void* stream);
 
 /*
+ * fq_cp_warmup (one or both directions) and fq_cp_transition_plan(_reverse) in ONE launch: a CTA per (sequence, head)
+ * scans the replay length of every piece of that pair, derives the flag and writes the codes.
+ *   piece_start / piece_end [n_pieces]: first token of / after the piece; chunks_before / chunks_after [n_pieces];
+ *   last_chunk_len [n_pieces]: tokens in the last chunk of the piece's sequence; seq_piece_offsets [n_seq+1].
+ *   flags [n_seq,H], codes [n_pieces,H], pass1_codes [2*n_pieces,H] as documented at fq_cp_transition_plan;
+ *   codes_rev / pass1_rev [n_pieces,H] (both or neither): the tables of the state-gradient recurrence, a pair being
+ *   flagged when the replay of either direction exceeds w_cap chunks.
+ */
+FQ_API int fq_cp_plan(const float* g_cumsum, const int32_t* piece_start, const int32_t* piece_end,
+                      const int32_t* chunks_before, const int32_t* chunks_after, const int32_t* last_chunk_len,
+                      const int32_t* seq_piece_offsets, int32_t* flags, int32_t* codes, int32_t* pass1_codes,
+                      int32_t* codes_rev, int32_t* pass1_rev, int n_pieces, int n_seq, int H, float threshold, int w_cap,
+                      void* stream);
+
+/*
  * h0_piece[r+1] = T_r h0_piece[r] + B_r along the pieces of every flagged (sequence, head), in fp32.
  *   bt [2*n_pieces,H,128,128]: B_r in slot r, T_r in slot n_pieces + r (the ht of the pass-1 run);
  *   seq_piece_offsets [n_seq+1]: first piece of every sequence.
