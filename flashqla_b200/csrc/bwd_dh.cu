@@ -31,6 +31,7 @@ constexpr uint32_t kDhColS = 0;     // fp32 dS^T
 constexpr uint32_t kDhColD1 = 128;  // D1, later DW
 constexpr uint32_t kDhColD2 = 192;
 constexpr uint32_t kDhColSB = 256;  // bf16 pairs of dS^T (64 columns): the A operand of D1 = dS^T K^T
+constexpr uint32_t kDhColDOS = 320; // bf16 pairs of (scale*gamma o dO)^T (32 columns): an A operand of the dS update
 
 struct BwdDhSmem {
   unsigned char kq[2][32768];    // k rows 0-63 | q rows 64-127, two 128-row regions (d 0-63 | 64-127)
@@ -38,7 +39,6 @@ struct BwdDhSmem {
   unsigned char a[2][8192];      // A_g tile [64 i][64 j]
   unsigned char pg[2][8192];     // P_g tile [64 i][64 j]
   unsigned char dsbf[32768];     // bf16 dS^T [128 v][128 k]
-  unsigned char dos[16384];      // (scale*gamma o dO)^T [128 v][64 c]
   float gate[kDhGateStages][4][kChunk];
   uint64_t full[2], empty[2], gate_full[kDhGateStages], gate_empty[kDhGateStages];
   uint64_t d2_done, d1_done, dw_done, ds_done;
@@ -151,7 +151,6 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       constexpr uint32_t id64_bmn = umma_idesc(128, 64, false, true, true);
       constexpr uint32_t id64_abmn = umma_idesc(128, 64, true, true, true);
       constexpr uint32_t id128_bmn = umma_idesc(128, 128, false, true, true);
-      const uint32_t sdos = smem_u32(s.dos);
       #pragma unroll 1
       for (int it = 0; it < total; ++it) {
         const int st = it & 1;
@@ -200,7 +199,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     id128_bmn, 1);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ss(tm + kDhColS, umma_desc_sw128(sdos + kk * 32, 16, 1024),
+            umma_ts(tm + kDhColS, tm + kDhColDOS + 8 * kk,
                     umma_desc_sw128(skq + 8192 + kk * 2048, 16384, 1024), id128_bmn, 1);
           umma_commit(&s.ds_done);
           umma_commit(&s.empty[st]);
@@ -405,12 +404,12 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.pg_ready[st]);
-      // (scale * gamma_c * dO[c][v])^T; the previous iteration's state update must have consumed the buffer
-      if (it > 0 && !mbar_wait(wc, &s.ds_done, (it - 1) & 1, 21)) break;
+      // (scale * gamma_c * dO[c][v])^T as bf16 pairs, formed before the wait below so that only the store remains
+      // once the previous iteration's state update has consumed the columns
+      uint32_t pk[32];
       {
         const unsigned char* dt = s.dout[st] + (v >> 6) * 8192;
         const uint32_t vb = (v & 63) * 2;
-        uint32_t pk[32];
 #pragma unroll
         for (int c = 0; c < kChunk; c += 2) {
           const float x0 = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(dt + sw128(c, vb))) << 16);
@@ -419,11 +418,12 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           const float s1 = (c + 1 < len) ? p.scale * s.gate[gs][1][c + 1] * x1 : 0.f;
           pk[c >> 1] = pack_bf16(s0, s1);
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<uint4*>(s.dos + sw128(v, j * 16)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
       }
-      fence_async_smem();
+      if (it > 0 && !mbar_wait(wc, &s.ds_done, (it - 1) & 1, 21)) break;
+      tc_fence_after();
+      tmem_st32(tmem_addr(tm, lane_base, kDhColDOS), pk);  // A operand in tensor memory, like dV' and dVg
+      tmem_wait_st();
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) { mbar_arrive(&s.dos_ready); mbar_arrive(&s.empty[st]); mbar_arrive(&s.gate_empty[gs]); }
     }
