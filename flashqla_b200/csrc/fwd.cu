@@ -194,12 +194,6 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (!warp_all(mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2))) break;
         FQ_TS(it, 0);
         tc_fence_after();
-        if (!transition && elect_one()) {
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)  // V_d^T = V^T A_g^T (A operand = the V tile as loaded, MN-major)
-            umma_ss(tm + kColVD, desc_add(d_vmn, kk * 2048), desc_add(d_a, kk * 32), id64_amn, kk > 0);
-        }
-        __syncwarp();
         if (!warp_all(mbar_wait_spin(wc, &s.s_ready, ph, 3))) break;
         FQ_TS(it, 1);
         tc_fence_after();
@@ -217,6 +211,14 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         __syncwarp();
         FQ_TS(it, 3);
+        // the state-independent half of V_d goes behind U^T: it then runs beside the short W epilogue instead of beside the
+        // conversion of the state, the longest stretch of the chain group
+        if (!transition && elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)  // V_d^T = V^T A_g^T (A operand = the V tile as loaded, MN-major)
+            umma_ss(tm + kColVD, desc_add(d_vmn, kk * 2048), desc_add(d_a, kk * 32), id64_amn, kk > 0);
+        }
+        __syncwarp();
         if (do_o) {  // OI = Q S: the accumulators of the previous chunk must have been drained
           if (it > 0 && !warp_all(mbar_wait(wc, &s.o_free, (it - 1) & 1, 4))) break;
           FQ_TS(it, 2);
