@@ -54,7 +54,7 @@ FWD_BYTES_PER_UNIT = 4 * 16384 + 512
 # DRAM traffic of gdr_fwd_kernel per (chunk, V-head) from one ncu capture of the smaller case c2s (Hq == Hv):
 # dram__bytes_read.sum + dram__bytes_write.sum = 665,837,312 B over 8192 units (profiles/forward_kernels_*.md);
 # traffic grows in proportion to the units, so a full launch is reported as units x this figure
-FWD_TRAFFIC_PER_UNIT_NCU = 674919936 / 8192
+FWD_TRAFFIC_PER_UNIT_NCU = 674940416 / 8192
 
 
 def l2norm(x):
