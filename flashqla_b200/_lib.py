@@ -21,6 +21,7 @@ SIGNATURES = {
     "fq_version": [],
     "fq_last_error": [],
     "fq_chunk_cumsum": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp],
+    "fq_dg_boundary_fix": [_vp] * 6 + [_i32] * 3 + [_vp, _vp, _i32, _i32, _vp],
     "fq_kkt_solve": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _vp],
     "fq_gdr_fwd": [_vp] * 12 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "fq_gdr_fwd_cp": [_vp] * 14 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
@@ -37,12 +38,14 @@ SIGNATURES = {
     "fq_gdr_bwd_chunk": [_vp] * 16 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "fq_gdr_bwd_chunk_gva_noalloc": [_vp] * 16 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "fq_group_reduce": [_vp, _vp, ctypes.c_longlong, _i32, _i32, _vp],
+    "fq_group_reduce_pair": [_vp, _vp, _vp, _vp, ctypes.c_longlong, _i32, _i32, _vp],
     "fq_gdr_recurrent": [_vp] * 8 + [_i32] * 4 + [_f32, _vp],
     "fq_l2norm_fwd": [_vp, _vp, ctypes.c_longlong, _f32, _vp],
     "fq_l2norm_bwd": [_vp, _vp, _vp, ctypes.c_longlong, _f32, _vp],
     "fq_kkt_solve_gated": [_vp] * 7 + [_i32] * 5 + [_vp, _vp, _i32, _i32, _f32, _vp],
     "fq_kkt_solve_fused": [_vp] * 8 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp],
     "fq_selftest_umma": [_vp, _vp, _vp, _i32, _vp, _vp],
+    "fq_selftest_wait_expiry": [_vp, _vp, ctypes.c_longlong, _vp],
 }
 _RESTYPES = {"fq_last_error": _cp}
 

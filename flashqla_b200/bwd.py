@@ -12,7 +12,7 @@ from .planner import plan_cp
 
 
 def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, initial_state=None, cu_seqlens=None,
-                               gated_tiles=None, plan=None):
+                               gated_tiles=None, plan=None, want_dh0=None):
     """``gated_tiles`` = (A_g, P_g) as produced by the forward for the same inputs; when given, the pass that
     rebuilds them from ``A`` is skipped (the autograd function keeps them unless FLASHQLA_RECOMPUTE_TILES=1)."""
     kernels._require_cuda(q, k, v, g, beta, A, do)
@@ -57,7 +57,8 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
                                     h0_piece=h0_piece)
     # 2. reverse recurrence of the state gradient
     dh = torch.empty_like(h)
-    want_dh0 = (dht is not None) or (initial_state is not None)
+    if want_dh0 is None:
+        want_dh0 = (dht is not None) or (initial_state is not None)
     dh0 = torch.empty(plan.n_seq, H, K, V, dtype=torch.float32, device=dev) if want_dh0 else None
     cu_p, off_p = plan.ptrs()
     lib = _lib.load()
@@ -98,13 +99,19 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
                               dk_h.data_ptr(), dv.data_ptr(), dg_c.data_ptr(), db.data_ptr(), B, T, H, Hg, cu_p, off_p, plan.n_seq,
                               plan.total_chunks, float(scale), st_p, kernels._stream())
     _lib.check(rc, "fq_gdr_bwd_chunk")
+    # 3b. the whole-state dot product in dg of a sequence's first / last chunk, corrected with the fp32 initial state /
+    #     final-state gradient (the chunk kernel used their bf16 copies)
+    if h0 is not None or dht_c is not None:
+        rc = lib.fq_dg_boundary_fix(pp(h0), pp(dht_c), h.data_ptr(), dh.data_ptr(), g.data_ptr(), dg_c.data_ptr(), B, T, H,
+                                    cu_p, off_p, plan.n_seq, plan.total_chunks, kernels._stream())
+        _lib.check(rc, "fq_dg_boundary_fix")
     # 4. sum the V-heads of every QK head
     if Hg < H:
         dq = torch.empty(B, T, Hg, K, dtype=q.dtype, device=dev)
         dk = torch.empty(B, T, Hg, K, dtype=q.dtype, device=dev)
-        for src, dst in ((dq_h, dq), (dk_h, dk)):
-            rc = lib.fq_group_reduce(src.data_ptr(), dst.data_ptr(), B * T, H, Hg, kernels._stream())
-            _lib.check(rc, "fq_group_reduce")
+        rc = lib.fq_group_reduce_pair(dq_h.data_ptr(), dq.data_ptr(), dk_h.data_ptr(), dk.data_ptr(), B * T, H, Hg,
+                                      kernels._stream())
+        _lib.check(rc, "fq_group_reduce_pair")
     else:
         dq, dk = dq_h, dk_h
     # 5. d/d(cumsum) -> d/d(raw gate)

@@ -23,15 +23,10 @@
 #include "host.cuh"
 #include "seq.cuh"
 
+#include <mutex>
+
 namespace fq {
 
-#ifdef FQ_TRACE
-// Debug builds only: clock64 stamps of one CTA for its third unit, read back with fq_trace_read_bc.
-__device__ long long g_trace_bc[32];
-#define BC_TS(id) do { if (blockIdx.x == 0 && tid == 0 && iter == 2) g_trace_bc[id] = clock64(); } while (0)
-#else
-#define BC_TS(id) do { } while (0)
-#endif
 
 constexpr int kBcThreads = 512;
 constexpr int kStoreTid = 480;  // warp 15, lane 0: issues the TMA stores of dq, dk and dv (not one of the issuing warps)
@@ -68,6 +63,7 @@ struct BwdChunkSmem {
   float dg_s[kChunk], db_s[kChunk];
   float dgl_s;
   uint64_t bar_tma_a, bar_tma_b, bar_mma;
+  uint64_t drain_bar;  // only used by drain_after_abort
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -116,7 +112,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   const bool active = lane < 16;
   const int row = active ? (16 * q4 + lane) : 0;
   const uint32_t lane_base = static_cast<uint32_t>(q4) * 32;
-  WaitCtx wc{&s.abort_flag, p.status_dev, 3};
+  WaitCtx wc{&s.abort_flag, p.status_dev, 3, kWaitLimitCycles};
   const int heads_per_group = p.H / p.Hg;
 
   if (tid == 0) {
@@ -124,6 +120,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     mbar_init(&s.bar_tma_a, 1);
     mbar_init(&s.bar_tma_b, 1);
     mbar_init(&s.bar_mma, 4);  // four issuing threads per round, one commit each
+    mbar_init(&s.drain_bar, 4);
     fence_mbar_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); tma_prefetch_desc(&map_do);
     tma_prefetch_desc(&map_a); tma_prefetch_desc(&map_h);
@@ -190,7 +187,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   int chunk = static_cast<int>(blockIdx.x) / p.H, h = static_cast<int>(blockIdx.x) - chunk * p.H;
   const int step_c = static_cast<int>(gridDim.x) / p.H, step_h = static_cast<int>(gridDim.x) - step_c * p.H;
   if (tid == 0 && chunk < p.total_chunks) load_a(chunk, h);
-  bool alive = true;
 
   // raw gate values of a unit: threads 0-63 fetch them one unit ahead, so that the loads are not waited for
   float gl_n = 0.f, gi_n = 0.f, bi_n = 0.f;
@@ -207,7 +203,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   };
   if (tid < kChunk && chunk < p.total_chunks) fetch_gates(chunk, h);
 #pragma unroll 1
-  for (int iter = 0; chunk < p.total_chunks && alive; ++iter) {
+  for (int iter = 0; chunk < p.total_chunks; ++iter) {
     int nchunk = chunk + step_c, nh = h + step_h;  // this CTA's next unit
     if (nh >= p.H) { nh -= p.H; ++nchunk; }
     const bool has_next = nchunk < p.total_chunks;
@@ -223,7 +219,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     // tiles are written again in this unit's second round, after the syncs below
     if (tid == kStoreTid) tma_store_wait_read<0>();
     __syncthreads();  // the previous unit's shared-memory reads are complete
-    BC_TS(0);
 
     if (tid == 0 && iter == 0) load_b(chunk, h, 2, b_kt, b_qt, b_at, b_pg);  // later units: requested a unit ahead
     if (tid < kChunk) {
@@ -237,12 +232,9 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (tid == 0) s.dgl_s = 0.f;
     }
     __syncthreads();
-    BC_TS(15);
-    if (!warp_all(mbar_wait(wc, &s.bar_tma_a, tma_phase, 1))) { alive = false; break; }
-    BC_TS(16);
-    if (!warp_all(mbar_wait(wc, &s.bar_tma_b, tma_phase, 8))) { alive = false; break; }
+    mbar_wait(wc, &s.bar_tma_a, tma_phase, 1);
+    mbar_wait(wc, &s.bar_tma_b, tma_phase, 8);
     tma_phase ^= 1;
-    BC_TS(1);
 
     // ---- pre-pass on shared memory: zero the rows past the sequence end
     if (len < kChunk) {
@@ -264,7 +256,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     fence_async_smem();
     __syncthreads();
 
-    BC_TS(2);
     const float gam_r = s.gam[row], rho_r = s.rho[row];
 
     // ================================================================== round 1
@@ -294,12 +285,10 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
-    BC_TS(17);
     // while the first round runs: the next unit's gate values
     if (tid < kChunk && has_next) fetch_gates(nchunk, nh);
-    if (!warp_all(mbar_wait(wc, &s.bar_mma, mma_phase, 2))) { alive = false; break; }
+    mbar_wait(wc, &s.bar_mma, mma_phase, 2);
     mma_phase ^= 1;
-    BC_TS(3);
     tc_fence_after();
     {
       // W = V - gamma o U (in place over V);  dV' = rho o D1 + D2
@@ -365,7 +354,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     fence_async_smem();
     __syncthreads();
 
-    BC_TS(4);
     // ================================================================== round 2: V' = A_g W, dW = A_g^T dV'
     if (warp < 4 && elect_one()) {  // the products of a round are issued by one elected lane of each of four warps
       tc_fence_after();
@@ -388,9 +376,8 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
-    if (!warp_all(mbar_wait(wc, &s.bar_mma, mma_phase, 3))) { alive = false; break; }
+    mbar_wait(wc, &s.bar_mma, mma_phase, 3);
     mma_phase ^= 1;
-    BC_TS(5);
     tc_fence_after();
     {
       if (cq == 0) {
@@ -446,7 +433,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       tma_store_commit();
     }
 
-    BC_TS(6);
     // ================================================================== round 3
     if (warp < 4 && elect_one()) {  // the products of a round are issued by one elected lane of each of four warps
       tc_fence_after();
@@ -474,9 +460,8 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
-    if (!warp_all(mbar_wait(wc, &s.bar_mma, mma_phase, 4))) { alive = false; break; }
+    mbar_wait(wc, &s.bar_mma, mma_phase, 4);
     mma_phase ^= 1;
-    BC_TS(7);
     tc_fence_after();
     if (whole) {  // the TMA store of dv has read the T / T3 tiles, which this round's epilogue writes
       if (tid == kStoreTid) tma_store_wait_read<0>();
@@ -593,7 +578,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     fence_async_smem();
     __syncthreads();
 
-    BC_TS(8);
     // ================================================================== round 4
     if (warp < 4 && elect_one()) {  // the products of a round are issued by one elected lane of each of four warps
       tc_fence_after();
@@ -625,9 +609,8 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
-    if (!warp_all(mbar_wait(wc, &s.bar_mma, mma_phase, 5))) { alive = false; break; }
+    mbar_wait(wc, &s.bar_mma, mma_phase, 5);
     mma_phase ^= 1;
-    BC_TS(9);
     tc_fence_after();
     {
       uint32_t r[32];
@@ -687,7 +670,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       tma_store_commit();
     }
 
-    BC_TS(10);
     // ================================================================== round 5
     if (warp < 4 && elect_one()) {  // the products of a round are issued by one elected lane of each of four warps
       tc_fence_after();
@@ -707,9 +689,8 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (warp == 3 && has_next) load_b(nchunk, nh, 1, b_vp, b_dvg, b_dvp, b_t12);
     }
     __syncwarp();
-    if (!warp_all(mbar_wait(wc, &s.bar_mma, mma_phase, 6))) { alive = false; break; }
+    mbar_wait(wc, &s.bar_mma, mma_phase, 6);
     mma_phase ^= 1;
-    BC_TS(11);
     tc_fence_after();
     {
       uint32_t x2[16], kk2[16];
@@ -748,7 +729,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     fence_async_smem();
     __syncthreads();
 
-    BC_TS(12);
     // ================================================================== round 6
     if (warp < 4 && elect_one()) {  // the products of a round are issued by one elected lane of each of four warps
       tc_fence_after();
@@ -767,9 +747,8 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       umma_commit(&s.bar_mma);
     }
     __syncwarp();
-    if (!warp_all(mbar_wait(wc, &s.bar_mma, mma_phase, 7))) { alive = false; break; }
+    mbar_wait(wc, &s.bar_mma, mma_phase, 7);
     mma_phase ^= 1;
-    BC_TS(13);
     tc_fence_after();
     {
       __nv_bfloat16* dst = p.dk + (static_cast<size_t>(cp.tok0 + row) * p.H + h) * kDim + 64 * hf;
@@ -800,7 +779,6 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       tma_store_3d(&map_dk, b_kt + 8192, 64, h, cp.tok0);
       tma_store_commit();
     }
-    BC_TS(14);
     if (tid < kChunk) {
       // the padded rows of a tail chunk share the gate of the last valid token
       float dgv = s.dg_s[tid];
@@ -826,20 +804,23 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   }
 
   if (tid == kStoreTid) tma_store_wait_all<0>();
-  if (!alive && tid == 0) {
-    // a bounded wait gave up: let the tile loads that are still in flight land before the CTA's shared memory is released
-#pragma unroll 1
-    for (int i = 0; i < (1 << 20) && !(mbar_test(&s.bar_tma_a, tma_phase) && mbar_test(&s.bar_tma_b, tma_phase)); ++i) {
-    }
-  }
   tc_fence_before();
   __syncthreads();
+  if (s.abort_flag) {  // a wait expired somewhere in the CTA (the same value for every thread: all loops are done)
+    drain_after_abort(warp < 4 && elect_one(), &s.drain_bar);
+    __syncthreads();
+  }
   if (warp == 0) tmem_dealloc(tm, 512);
 }
 
 // Sum of the G V-heads of every QK head: in [rows, H, 128] bf16 -> out [rows, Hg, 128] bf16 (fp32 accumulate).
-__global__ void __launch_bounds__(256) group_reduce_kernel(const __nv_bfloat16* __restrict__ in,
-                                                          __nv_bfloat16* __restrict__ out, long long rows, int H, int Hg) {
+// One launch serves up to two tensors (dq and dk of the backward): blockIdx.y picks the pair.
+__global__ void __launch_bounds__(256) group_reduce_kernel(const __nv_bfloat16* __restrict__ in0,
+                                                          __nv_bfloat16* __restrict__ out0,
+                                                          const __nv_bfloat16* __restrict__ in1,
+                                                          __nv_bfloat16* __restrict__ out1, long long rows, int H, int Hg) {
+  const __nv_bfloat16* __restrict__ in = blockIdx.y ? in1 : in0;
+  __nv_bfloat16* __restrict__ out = blockIdx.y ? out1 : out0;
   const int G = H / Hg;
   const long long total = rows * Hg * (kDim / 8);
   for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
@@ -865,6 +846,19 @@ __global__ void __launch_bounds__(256) group_reduce_kernel(const __nv_bfloat16* 
     y.w = pack_bf16(acc[6], acc[7]);
     *(reinterpret_cast<uint4*>(out + (r * Hg + hg) * kDim) + piece) = y;
   }
+}
+
+// Launch of group_reduce_kernel for one tensor (in1 == nullptr) or two; 16 CTAs of 256 threads per SM at most.
+static int launch_group_reduce(const void* in0, void* out0, const void* in1, void* out1, long long rows, int H, int Hg,
+                               cudaStream_t st) {
+  const long long total = rows * Hg * (kDim / 8);
+  const long long blocks = (total + 255) / 256;
+  const long long cap = 16LL * sm_count();
+  dim3 grid(static_cast<unsigned>(blocks < cap ? blocks : cap), in1 ? 2 : 1);
+  group_reduce_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in0), static_cast<__nv_bfloat16*>(out0),
+                                            static_cast<const __nv_bfloat16*>(in1), static_cast<__nv_bfloat16*>(out1), rows,
+                                            H, Hg);
+  return cudaGetLastError() == cudaSuccess ? FQ_OK : FQ_ERR_CUDA;
 }
 
 }  // namespace fq
@@ -911,12 +905,10 @@ extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void*
   p.sa = SeqArgs{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
   p.status_dev = status_dev;
   const size_t smem = sizeof(BwdChunkSmem) + 1024;
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  FQ_CHECK_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    FQ_CHECK_CUDA(cudaFuncSetAttribute(gdr_bwd_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    attr_set[dev] = true;
+  {
+    static std::atomic<unsigned long long> done0{0};
+    const int rc_attr = set_smem_limit_once(reinterpret_cast<const void*>(gdr_bwd_chunk_kernel), static_cast<int>(smem), &done0);
+    if (rc_attr != FQ_OK) return rc_attr;
   }
   const long long units = static_cast<long long>(total_chunks) * H;
   const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
@@ -930,12 +922,23 @@ extern "C" FQ_API int fq_group_reduce(const void* in, void* out, long long rows,
   using namespace fq;
   FQ_CHECK_ARG(in && out && rows >= 0 && H > 0 && Hg > 0 && H % Hg == 0, "fq_group_reduce: bad arguments");
   if (rows == 0) return FQ_OK;
-  const long long total = rows * Hg * (kDim / 8);
-  const long long blocks = (total + 255) / 256;
-  const int grid = static_cast<int>(blocks < 148LL * 16 ? blocks : 148LL * 16);
-  group_reduce_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(in),
-                                                                          static_cast<__nv_bfloat16*>(out), rows, H, Hg);
-  FQ_CHECK_CUDA(cudaGetLastError());
+  if (launch_group_reduce(in, out, nullptr, nullptr, rows, H, Hg, static_cast<cudaStream_t>(stream)) != FQ_OK) {
+    set_error("fq_group_reduce: launch failed");
+    return FQ_ERR_CUDA;
+  }
+  return FQ_OK;
+}
+
+extern "C" FQ_API int fq_group_reduce_pair(const void* in_a, void* out_a, const void* in_b, void* out_b, long long rows,
+                                           int H, int Hg, void* stream) {
+  using namespace fq;
+  FQ_CHECK_ARG(in_a && out_a && in_b && out_b && rows >= 0 && H > 0 && Hg > 0 && H % Hg == 0,
+               "fq_group_reduce_pair: bad arguments");
+  if (rows == 0) return FQ_OK;
+  if (launch_group_reduce(in_a, out_a, in_b, out_b, rows, H, Hg, static_cast<cudaStream_t>(stream)) != FQ_OK) {
+    set_error("fq_group_reduce_pair: launch failed");
+    return FQ_ERR_CUDA;
+  }
   return FQ_OK;
 }
 
@@ -982,17 +985,22 @@ extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k,
   FQ_CHECK_ARG(rows > 0 && rows < (1ull << 31) && hrows < (1ull << 31), "fq_gdr_bwd_chunk_gva_noalloc: sizes out of range");
 
   // One-time set-up per device, with that device current: resolve the device address of the scratch
-  // array (its name is only a host-side handle) and raise the kernel's shared-memory limit.
+  // array (its name is only a host-side handle) and raise the kernel's shared-memory limit.  The
+  // cache is filled under a mutex, so first calls from several host threads are safe.
   static unsigned char* scratch_dev[64] = {nullptr};
+  static std::mutex setup_mutex;
   int dev = 0;
   FQ_CHECK_CUDA(cudaGetDevice(&dev));
   FQ_CHECK_ARG(dev >= 0 && dev < 64, "fq_gdr_bwd_chunk_gva_noalloc: device index out of range");
   const size_t smem = sizeof(BwdChunkSmem) + 1024;
-  if (scratch_dev[dev] == nullptr) {
-    void* ptr = nullptr;
-    FQ_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
-    FQ_CHECK_CUDA(cudaFuncSetAttribute(gdr_bwd_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    scratch_dev[dev] = static_cast<unsigned char*>(ptr);
+  {
+    std::lock_guard<std::mutex> lock(setup_mutex);
+    if (scratch_dev[dev] == nullptr) {
+      void* ptr = nullptr;
+      FQ_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+      FQ_CHECK_CUDA(cudaFuncSetAttribute(gdr_bwd_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      scratch_dev[dev] = static_cast<unsigned char*>(ptr);
+    }
   }
   __nv_bfloat16* dq_h = reinterpret_cast<__nv_bfloat16*>(scratch_dev[dev]);
   __nv_bfloat16* dk_h = reinterpret_cast<__nv_bfloat16*>(scratch_dev[dev] + per_buffer);
@@ -1025,17 +1033,11 @@ extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k,
   FQ_CHECK_CUDA(cudaGetLastError());
   // Every token row of both scratch buffers was just written (each row belongs to exactly one
   // chunk), so nothing has to be cleared before the sum reads them.
-  const long long total = static_cast<long long>(rows) * Hg * (kDim / 8);
-  const long long blocks = (total + 255) / 256;
-  const int rgrid = static_cast<int>(blocks < 148LL * 16 ? blocks : 148LL * 16);
-  group_reduce_kernel<<<rgrid, 256, 0, st>>>(dq_h, static_cast<__nv_bfloat16*>(dq), static_cast<long long>(rows), H, Hg);
-  group_reduce_kernel<<<rgrid, 256, 0, st>>>(dk_h, static_cast<__nv_bfloat16*>(dk), static_cast<long long>(rows), H, Hg);
+  if (launch_group_reduce(dq_h, dq, dk_h, dk, static_cast<long long>(rows), H, Hg, st) != FQ_OK) {
+    set_error("fq_gdr_bwd_chunk_gva_noalloc: head-sum launch failed");
+    return FQ_ERR_CUDA;
+  }
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }
 
-#ifdef FQ_TRACE
-extern "C" FQ_API int fq_trace_read_bc(long long* out_host) {
-  return cudaMemcpyFromSymbol(out_host, fq::g_trace_bc, sizeof(long long) * 32) == cudaSuccess ? 0 : -2;
-}
-#endif

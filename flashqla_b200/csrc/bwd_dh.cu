@@ -43,6 +43,7 @@ struct BwdDhSmem {
   uint64_t full[2], empty[2], gate_full[kDhGateStages], gate_empty[kDhGateStages];
   uint64_t d2_done, d1_done, dw_done, ds_done;
   uint64_t ds_ready, ds_scaled, dvp_ready, dvg_ready, dos_ready;
+  uint64_t drain_bar;    // only used by drain_after_abort
   uint64_t pg_ready[2];  // per stage: the aux warps may run one iteration ahead of the UMMA issuer
   uint32_t tmem_base;
   int abort_flag;
@@ -101,7 +102,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const int total = nchunks > 0 ? nchunks + warm : 0;  // iteration `it` handles chunk n = total - 1 - it of the piece
   // tokens available from the piece start to the end of its sequence (bounds the length of replayed chunks)
   const int avail = p.seq_end ? __ldg(p.seq_end + seq) - tok_begin : seq_len;
-  WaitCtx wc{&s.abort_flag, p.status_dev, 2};
+  WaitCtx wc{&s.abort_flag, p.status_dev, 2, kWaitLimitCycles};
 
   if (tid == 0) {
     s.abort_flag = 0;
@@ -111,6 +112,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     mbar_init(&s.ds_done, 1);
     mbar_init(&s.ds_ready, 4); mbar_init(&s.ds_scaled, 4); mbar_init(&s.dvp_ready, 4); mbar_init(&s.dvg_ready, 4);
     mbar_init(&s.dos_ready, 4); mbar_init(&s.pg_ready[0], 4); mbar_init(&s.pg_ready[1], 4);
+    mbar_init(&s.drain_bar, 1);
     fence_mbar_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_pg); tma_prefetch_desc(&map_dh);
@@ -130,7 +132,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       #pragma unroll 1
       for (int it = 0; it < total; ++it) {
         const int n = total - 1 - it, st = it & 1;
-        if (it >= 2 && !mbar_wait(wc, &s.empty[st], ((it >> 1) + 1) & 1, 1)) break;
+        if (it >= 2) mbar_wait(wc, &s.empty[st], ((it >> 1) + 1) & 1, 1);
         mbar_arrive_expect_tx(&s.full[st], kDhStageBytes);
         const int row = tok_begin + n * kChunk;
         tma_load_3d(s.kq[st], &map_k, &s.full[st], 0, hg, row);
@@ -156,9 +158,9 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const int st = it & 1;
         const uint32_t ph = it & 1;
         const uint32_t skq = smem_u32(s.kq[st]), sa = smem_u32(s.a[st]), sdo = smem_u32(s.dout[st]), spg = smem_u32(s.pg[st]);
-        if (!warp_all(mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2))) break;
+        mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2);
         tc_fence_after();
-        if (!warp_all(mbar_wait(wc, &s.pg_ready[st], (it >> 1) & 1, 3))) break;
+        mbar_wait(wc, &s.pg_ready[st], (it >> 1) & 1, 3);
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
@@ -168,7 +170,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           umma_commit(&s.d2_done);
         }
         __syncwarp();
-        if (!warp_all(mbar_wait(wc, &s.ds_ready, ph, 4))) break;
+        mbar_wait(wc, &s.ds_ready, ph, 4);
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
@@ -178,7 +180,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           umma_commit(&s.d1_done);
         }
         __syncwarp();
-        if (!warp_all(mbar_wait(wc, &s.dvp_ready, ph, 5))) break;
+        mbar_wait(wc, &s.dvp_ready, ph, 5);
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
@@ -188,9 +190,9 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           umma_commit(&s.dw_done);
         }
         __syncwarp();
-        if (!warp_all(mbar_wait(wc, &s.dvg_ready, ph, 7))) break;
-        if (!warp_all(mbar_wait(wc, &s.dos_ready, ph, 8))) break;
-        if (!warp_all(mbar_wait(wc, &s.ds_scaled, ph, 9))) break;
+        mbar_wait(wc, &s.dvg_ready, ph, 7);
+        mbar_wait(wc, &s.dos_ready, ph, 8);
+        mbar_wait(wc, &s.ds_scaled, ph, 9);
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
@@ -213,7 +215,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     #pragma unroll 1
     for (int it = 0; it < total; ++it) {
       const int n = total - 1 - it, gs = it & (kDhGateStages - 1);
-      if (it >= kDhGateStages && !mbar_wait(wc, &s.gate_empty[gs], ((it >> 2) + 1) & 1, 10)) break;
+      if (it >= kDhGateStages) mbar_wait(wc, &s.gate_empty[gs], ((it >> 2) + 1) & 1, 10);
       const int len = min(kChunk, avail - n * kChunk);
       const size_t row = static_cast<size_t>(tok_begin) + n * kChunk;
       const float gl = __ldg(p.g_cum + (row + len - 1) * p.H + h);
@@ -235,9 +237,9 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     for (int it = 0; it < total; ++it) {
       const int n = total - 1 - it, gs = it & (kDhGateStages - 1);
       const uint32_t ph = it & 1;
-      if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 11)) break;
-      if (!mbar_wait(wc, &s.d2_done, ph, 12)) break;
-      if (!mbar_wait(wc, &s.d1_done, ph, 13)) break;
+      mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 11);
+      mbar_wait(wc, &s.d2_done, ph, 12);
+      mbar_wait(wc, &s.d1_done, ph, 13);
       tc_fence_after();
       uint32_t packed[32];
 #pragma unroll
@@ -261,7 +263,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.dvp_ready);
-      if (!mbar_wait(wc, &s.dw_done, ph, 14)) break;
+      mbar_wait(wc, &s.dw_done, ph, 14);
       tc_fence_after();
       uint32_t pg2[32];
 #pragma unroll
@@ -299,15 +301,14 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
       tmem_wait_st();
     }
-    bool alive = true;
     #pragma unroll 1
-    for (int it = 0; it < total && alive; ++it) {
+    for (int it = 0; it < total; ++it) {
       const int n = total - 1 - it, gs = it & (kDhGateStages - 1);
       if (it > 0) {
-        if (!mbar_wait(wc, &s.ds_done, (it - 1) & 1, 15)) { alive = false; break; }
+        mbar_wait(wc, &s.ds_done, (it - 1) & 1, 15);
         tc_fence_after();
       }
-      if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 16)) { alive = false; break; }
+      mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 16);
       const float gL = s.gate[gs][1][kChunk - 1];
       const bool store_dh = n < nchunks;
       // chain part: a bf16 copy of dS^T in tensor memory, the A operand of D1 = dS^T K^T (two column blocks per
@@ -367,12 +368,12 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       if (lane == 0) { mbar_arrive(&s.ds_scaled); mbar_arrive(&s.gate_empty[gs]); }
     }
     if (tid == 256) tma_store_wait_all<0>();
-    if (alive && total > 0) {
-      alive = mbar_wait(wc, &s.ds_done, (total - 1) & 1, 17);
+    if (total > 0) {
+      mbar_wait(wc, &s.ds_done, (total - 1) & 1, 17);
       tc_fence_after();
     }
     const int out_slot = p.dh0_index ? __ldg(p.dh0_index + seq) : seq;
-    if (alive && p.dh0 && out_slot >= 0) {
+    if (p.dh0 && out_slot >= 0) {
       float* dst = p.dh0 + (static_cast<size_t>(out_slot) * p.H + h) * kDim * kDim + v;
 #pragma unroll 1
       for (int cb = 0; cb < 4; ++cb) {
@@ -392,8 +393,8 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       const int n = total - 1 - it, st = it & 1, gs = it & (kDhGateStages - 1);
       const uint32_t ph = it & 1;
       const int len = min(kChunk, avail - n * kChunk);
-      if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 18)) break;
-      if (!mbar_wait(wc, &s.full[st], (it >> 1) & 1, 19)) break;
+      mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 18);
+      mbar_wait(wc, &s.full[st], (it >> 1) & 1, 19);
       // P_g rows past the sequence end were produced for the NEXT sequence's tokens: clear them
       if (len < kChunk) {
         for (int idx = v; idx < (kChunk - len) * 8; idx += 128) {
@@ -419,7 +420,7 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           pk[c >> 1] = pack_bf16(s0, s1);
         }
       }
-      if (it > 0 && !mbar_wait(wc, &s.ds_done, (it - 1) & 1, 21)) break;
+      if (it > 0) mbar_wait(wc, &s.ds_done, (it - 1) & 1, 21);
       tc_fence_after();
       tmem_st32(tmem_addr(tm, lane_base, kDhColDOS), pk);  // A operand in tensor memory, like dV' and dVg
       tmem_wait_st();
@@ -431,6 +432,10 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
+  if (s.abort_flag) {  // a wait expired somewhere in the CTA (the same value for every thread: all roles are done)
+    drain_after_abort(warp == 1 && elect_one(), &s.drain_bar);
+    __syncthreads();
+  }
   if (warp == 1) tmem_dealloc(tm, 512);
 }
 
@@ -494,12 +499,10 @@ extern "C" FQ_API int fq_gdr_bwd_dh_cp_ex(const void* q, const void* k, const vo
   p.sa = SeqArgs{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
   p.status_dev = status_dev;
   const size_t smem = sizeof(BwdDhSmem) + 1024;
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  FQ_CHECK_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    FQ_CHECK_CUDA(cudaFuncSetAttribute(gdr_bwd_dh_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    attr_set[dev] = true;
+  {
+    static std::atomic<unsigned long long> done0{0};
+    const int rc_attr = set_smem_limit_once(reinterpret_cast<const void*>(gdr_bwd_dh_kernel), static_cast<int>(smem), &done0);
+    if (rc_attr != FQ_OK) return rc_attr;
   }
   const long long ctas = static_cast<long long>(n_seq) * H;
   FQ_CHECK_ARG(ctas < (1ll << 31), "fq_gdr_bwd_dh: too many (sequence, head) pairs");

@@ -60,34 +60,40 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Per-CTA abort cell + global status word.  A wait that runs out of time records where it gave
-// up and raises the abort flag; every later wait in the CTA then returns at once, so the CTA
-// drains, frees its TMEM and exits instead of spinning on a barrier nobody will complete.
+// Per-CTA abort cell + global status word.  A wait that runs out of time records where it gave up (first expiry wins)
+// and raises the CTA's abort flag.  The waiting thread then goes on AS IF the wait had succeeded, and from that moment
+// no wait of the CTA blocks any more: every warp runs through its remaining iterations with the control flow of a
+// normal run - the named barriers, the warp-aligned tensor-memory instructions and the loop trip counts of all roles
+// stay matched, which a role that left its loop early could not guarantee - and the kernel ends through its ordinary
+// epilogue (drain_after_abort, then the release of tensor memory).  The results of such a launch are meaningless; the
+// host learns of it from the status word.
 struct WaitCtx {
   volatile int* abort_flag;  // shared memory
   int* status_dev;           // global memory, may be nullptr
   int kernel_id;             // reported in bits 12.. of the status code
+  long long limit;           // cycles a wait may take before it gives up
 };
 
 // Bounded wait on a phase: one inline probe, then the polling loop, which lives out of line (one copy per
 // kernel) - the kernels wait in dozens of places, and the loop bodies of their warp roles have to stay
-// resident in the instruction cache together.
+// resident in the instruction cache together.  Always returns true (see WaitCtx); the return value is kept so that
+// the call sites read like a wait that can fail.
 static __device__ __noinline__ bool mbar_wait_slow(volatile int* abort_flag, int* status_dev, int code, uint64_t* bar,
-                                                   uint32_t parity) {
+                                                   uint32_t parity, long long limit) {
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (*abort_flag) return true;
+    if (clock64() - t0 > limit) {
       *abort_flag = 1;
       if (status_dev) atomicCAS(status_dev, 0, code);
-      return false;
+      return true;
     }
   }
 }
 __device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint64_t* bar, uint32_t parity, int where) {
   if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(w.abort_flag, w.status_dev, (w.kernel_id << 12) + where, bar, parity);
+  return mbar_wait_slow(w.abort_flag, w.status_dev, (w.kernel_id << 12) + where, bar, parity, w.limit);
 }
 // For the one or two waits per kernel whose wake-up latency sits on the serial chain and whose waiter is a single
 // thread: probes without suspending for a bounded number of rounds, then falls back to the suspending wait.
@@ -95,7 +101,7 @@ __device__ __forceinline__ bool mbar_wait_spin(const WaitCtx& w, uint64_t* bar, 
 #pragma unroll 1
   for (int i = 0; i < 4096; ++i)
     if (mbar_test(bar, parity)) return true;
-  return mbar_wait_slow(w.abort_flag, w.status_dev, (w.kernel_id << 12) + where, bar, parity);
+  return mbar_wait_slow(w.abort_flag, w.status_dev, (w.kernel_id << 12) + where, bar, parity, w.limit);
 }
 
 // ---- proxy fences ------------------------------------------------------------------------------
@@ -289,5 +295,24 @@ __device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u 
 __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xFFFF0000u); }
 
 __device__ __forceinline__ float fast_exp(float x) { return exp2f(x * 1.4426950408889634f); }
+
+
+// Last step of a CTA whose abort flag is up, called by every thread before the closing __syncthreads: tile loads and
+// tensor-core products that were issued before (or during the run-through after) the expiry get a bounded time to
+// land, so that shared and tensor memory are not released under them.  `issuer` is true for the thread(s) that issue
+// the products; `bar` is an mbarrier of count 1 that nothing else uses (the commit below is its only arrival).
+static __device__ __noinline__ void drain_after_abort(bool issuer, uint64_t* bar) {
+  const long long t0 = clock64();
+  if (issuer) {
+    umma_commit(bar);  // arrives once every product issued so far by this thread has completed
+#pragma unroll 1
+    while (!mbar_test(bar, 0) && clock64() - t0 < 2000000) {
+    }
+  }
+  // tile copies in flight land within microseconds; 200k cycles is far beyond that and still a bound
+#pragma unroll 1
+  while (clock64() - t0 < 200000) {
+  }
+}
 
 }  // namespace fq

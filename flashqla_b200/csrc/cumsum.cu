@@ -36,7 +36,111 @@ __global__ void __launch_bounds__(256) chunk_cumsum_kernel(const float* __restri
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// fp32 correction of the gate gradient at the two ends of every sequence.
+//
+// dg of a chunk's last token contains gamma_last * sum(dS o S0) over the whole 128 x 128 state (S0: state before the
+// chunk, dS: gradient w.r.t. the state after it).  The chunk-parallel backward evaluates that sum from the bf16 copies
+// of both states that travel between the kernels.  The sum cancels heavily (16384 products of either sign), so for a
+// sequence's FIRST chunk (S0 = the caller's fp32 initial state, e.g. ~ randn) and LAST chunk (dS = the caller's fp32
+// final-state gradient) the rounding of those copies can show in dg of a short sequence.  Both fp32 tensors are at
+// hand, so the difference between the exact products and the rounded ones is added here:
+//   first chunk:  gamma_last * sum( bf16(dS) o (h0 - bf16(h0)) )
+//   last chunk:   gamma_last * sum( (dht - bf16(dht)) o S0x ),  S0x = h0 (fp32) if the sequence has one chunk, else
+//                 the bf16 state copy before the last chunk
+// Eight CTAs per (sequence, head): (first | last chunk) x four blocks of 32 state columns.  h, dh: [total_chunks, H, 128(v), 128(k)] bf16 (transposed, as the recurrences store
+// them); h0, dht: [n_seq, H, 128(k), 128(v)] fp32 or nullptr; dg_cum: [rows, H] gradient w.r.t. the gate cumsum, updated
+// in place at the last valid token of the chunk concerned.
+__global__ void __launch_bounds__(256) dg_boundary_fix_kernel(const float* __restrict__ h0, const float* __restrict__ dht,
+                                                             const __nv_bfloat16* __restrict__ h,
+                                                             const __nv_bfloat16* __restrict__ dh,
+                                                             const float* __restrict__ g_cum, float* __restrict__ dg_cum,
+                                                             int H, SeqArgs sa) {
+  __shared__ float tile[32][kDim + 1];
+  __shared__ float red[8];
+  const int seq = blockIdx.x / H, hd = blockIdx.x - seq * H;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int tok_begin, seq_len, chunk_off;
+  if (sa.cu_seqlens == nullptr) {
+    tok_begin = seq * sa.T; seq_len = sa.T; chunk_off = seq * sa.nc_dense;
+  } else {
+    tok_begin = __ldg(sa.cu_seqlens + seq);
+    seq_len = __ldg(sa.cu_seqlens + seq + 1) - tok_begin;
+    chunk_off = __ldg(sa.chunk_offsets + seq);
+  }
+  if (seq_len <= 0) return;
+  const int nchunks = (seq_len + kChunk - 1) / kChunk;
+  const size_t mat = static_cast<size_t>(kDim) * kDim;
+  const float* h0m = h0 ? h0 + (static_cast<size_t>(seq) * H + hd) * mat : nullptr;
+  const float* dhtm = dht ? dht + (static_cast<size_t>(seq) * H + hd) * mat : nullptr;
+  // blockIdx.y = 4 * part + (block of 32 v): part 0 = first chunk (needs h0), part 1 = last chunk (needs dht); the
+  // partial sums of a pair's CTAs meet in dg_cum by atomic adds
+  const int part = blockIdx.y >> 2, vb = (blockIdx.y & 3) * 32;
+  const float* fp = part == 0 ? h0m : dhtm;  // the fp32 tensor whose rounding is corrected, [k][v]
+  if (fp == nullptr) return;
+  const int c = part == 0 ? 0 : nchunks - 1;
+  // the other factor: part 0 -> bf16 dS of chunk 0; part 1 -> fp32 h0 for a one-chunk sequence, else bf16 S0 of chunk c
+  const bool other_fp32 = (part == 1 && nchunks == 1 && h0m != nullptr);
+  const __nv_bfloat16* ot = (part == 0 ? dh : h) + (static_cast<size_t>(chunk_off + c) * H + hd) * mat;  // [v][k]
+  if (!other_fp32) {
+    // rows vb .. vb+31 of the transposed tile: 32 x 128 bf16 = 512 pieces of 16 bytes, two per thread
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const int i = tid + 256 * it, r = i >> 4, piece = i & 15;
+      const uint4 x = __ldg(reinterpret_cast<const uint4*>(ot + static_cast<size_t>(vb + r) * kDim) + piece);
+      const uint32_t* xw = reinterpret_cast<const uint32_t*>(&x);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        tile[r][piece * 8 + 2 * e] = bf16_lo(xw[e]);
+        tile[r][piece * 8 + 2 * e + 1] = bf16_hi(xw[e]);
+      }
+    }
+    __syncthreads();
+  }
+  float x[16], o[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {  // sixteen independent loads in flight per thread
+    const int k = warp + 8 * i;
+    x[i] = __ldg(fp + static_cast<size_t>(k) * kDim + vb + lane);
+    o[i] = other_fp32 ? __ldg(h0m + static_cast<size_t>(k) * kDim + vb + lane) : tile[lane][k];
+  }
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc += (x[i] - __bfloat162float(__float2bfloat16_rn(x[i]))) * o[i];
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+  if (lane == 0) red[warp] = acc;
+  __syncthreads();
+  if (tid == 0) {
+    float sum = 0.f;
+    for (int w = 0; w < 8; ++w) sum += red[w];
+    const int len = min(kChunk, seq_len - c * kChunk);
+    const size_t off = (static_cast<size_t>(tok_begin) + c * kChunk + len - 1) * H + hd;
+    atomicAdd(dg_cum + off, sum * __expf(g_cum[off]));
+  }
+}
+
 }  // namespace fq
+
+extern "C" FQ_API int fq_dg_boundary_fix(const float* h0, const float* dht, const void* h, const void* dh,
+                                         const float* g_cumsum, float* dg_cum, int B, int T, int H,
+                                         const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
+                                         int total_chunks, void* stream) {
+  using namespace fq;
+  FQ_CHECK_ARG(h && dh && g_cumsum && dg_cum, "fq_dg_boundary_fix: null tensor");
+  FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && n_seq > 0 && total_chunks >= 0, "fq_dg_boundary_fix: bad sizes");
+  FQ_CHECK_ARG((cu_seqlens == nullptr) == (chunk_offsets == nullptr),
+               "fq_dg_boundary_fix: cu_seqlens and chunk_offsets must be given together");
+  FQ_CHECK_ARG(cu_seqlens != nullptr || n_seq == B, "fq_dg_boundary_fix: dense batches need n_seq == B");
+  if (total_chunks == 0 || (h0 == nullptr && dht == nullptr)) return FQ_OK;
+  SeqArgs sa{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
+  const long long ctas = static_cast<long long>(n_seq) * H;
+  FQ_CHECK_ARG(ctas < (1ll << 31), "fq_dg_boundary_fix: too many (sequence, head) pairs");
+  dg_boundary_fix_kernel<<<dim3(static_cast<unsigned>(ctas), 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      h0, dht, static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(dh), g_cumsum, dg_cum, H, sa);
+  FQ_CHECK_CUDA(cudaGetLastError());
+  return FQ_OK;
+}
 
 extern "C" FQ_API int fq_chunk_cumsum(const float* g, float* out, int B, int T, int H, const int32_t* cu_seqlens,
                                       const int32_t* chunk_offsets, int n_seq, int total_chunks, int reverse,

@@ -23,20 +23,14 @@
 // sequence's initial state when the replay reaches the sequence start.  `w` comes from the gate
 // scan (cp.cu): the decay accumulated over the replayed chunks makes older history negligible.
 //
-// Every wait on an mbarrier is bounded; on expiry the CTA drains and reports through status_dev.
+// Every wait on an mbarrier is bounded; on expiry the CTA reports through status_dev and runs through without
+// blocking again (WaitCtx in common.cuh).
 #include "flashqla.h"
 #include "host.cuh"
 #include "seq.cuh"
 
 namespace fq {
 
-#ifdef FQ_TRACE
-// Debug builds only: clock64 stamps of one CTA for a few chunks, read back with fq_trace_read.
-__device__ long long g_trace[8][32];
-#define FQ_TS(n, id) do { if (blockIdx.x == 0 && (n) >= 16 && (n) < 24) g_trace[(n) - 16][id] = clock64(); } while (0)
-#else
-#define FQ_TS(n, id) do { } while (0)
-#endif
 
 constexpr int kFwdThreads = 512;
 constexpr int kGateStages = 4;
@@ -61,6 +55,7 @@ struct FwdSmem {
   uint64_t full[2], empty[2], gate_full[kGateStages], gate_empty[kGateStages];
   uint64_t uq_done, vd_done, s_done, o_done;
   uint64_t s_ready, s_scaled, w_ready, vp_ready, o_free;
+  uint64_t drain_bar;  // only used by drain_after_abort
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -127,7 +122,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
              skip = (warm_code >> 27) & 1;
   const int total = (nchunks > 0 && !skip) ? warm + nchunks : 0;  // iterations; iteration `it` handles chunk n = it - warm
   if (skip) return;  // nothing to do for this (entry, head): leave before any barrier or tensor memory is set up
-  WaitCtx wc{&s.abort_flag, p.status_dev, 1};
+  WaitCtx wc{&s.abort_flag, p.status_dev, 1, kWaitLimitCycles};
 
   if (tid == 0) {
     s.abort_flag = 0;
@@ -136,6 +131,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     mbar_init(&s.uq_done, 1); mbar_init(&s.vd_done, 1); mbar_init(&s.s_done, 1); mbar_init(&s.o_done, 1);
     mbar_init(&s.s_ready, 8); mbar_init(&s.s_scaled, 8); mbar_init(&s.w_ready, 8); mbar_init(&s.vp_ready, 8);
     mbar_init(&s.o_free, 4);
+    mbar_init(&s.drain_bar, 1);
     fence_mbar_init();
     tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_pg); tma_prefetch_desc(&map_h); tma_prefetch_desc(&map_o);
@@ -154,7 +150,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     if (lane == 0) {
       for (int it = 0; it < total; ++it) {
         const int st = it & 1;
-        if (it >= 2 && !mbar_wait(wc, &s.empty[st], ((it >> 1) + 1) & 1, 1)) break;
+        if (it >= 2) mbar_wait(wc, &s.empty[st], ((it >> 1) + 1) & 1, 1);
         mbar_arrive_expect_tx(&s.full[st], kStageBytes);
         const int row = tok_begin + (it - warm) * kChunk;
         tma_load_3d(s.kq[st], &map_k, &s.full[st], 0, hg, row);
@@ -191,11 +187,9 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const uint64_t d_vmn = desc_add(d_vmn0, st * 16384), d_kq = desc_add(d_kq0, st * 32768),
                        d_kmn = desc_add(d_kmn0, st * 32768), d_a = desc_add(d_a0, st * 8192),
                        d_pg = desc_add(d_pg0, st * 8192);
-        if (!warp_all(mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2))) break;
-        FQ_TS(it, 0);
+        mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2);
         tc_fence_after();
-        if (!warp_all(mbar_wait_spin(wc, &s.s_ready, ph, 3))) break;
-        FQ_TS(it, 1);
+        mbar_wait_spin(wc, &s.s_ready, ph, 3);
         tc_fence_after();
         if (elect_one()) {
           if (want_o) {
@@ -210,7 +204,6 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           umma_commit(&s.uq_done);
         }
         __syncwarp();
-        FQ_TS(it, 3);
         // the state-independent half of V_d goes behind U^T: it then runs beside the short W epilogue instead of beside the
         // conversion of the state, the longest stretch of the chain group
         if (!transition && elect_one()) {
@@ -220,8 +213,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         __syncwarp();
         if (do_o) {  // OI = Q S: the accumulators of the previous chunk must have been drained
-          if (it > 0 && !warp_all(mbar_wait(wc, &s.o_free, (it - 1) & 1, 4))) break;
-          FQ_TS(it, 2);
+          if (it > 0) mbar_wait(wc, &s.o_free, (it - 1) & 1, 4);
           tc_fence_after();
           if (elect_one()) {
 #pragma unroll
@@ -230,8 +222,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           }
           __syncwarp();
         }
-        if (!warp_all(mbar_wait_spin(wc, &s.w_ready, ph, 5))) break;
-        FQ_TS(it, 4);
+        mbar_wait_spin(wc, &s.w_ready, ph, 5);
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
@@ -240,11 +231,8 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           umma_commit(&s.vd_done);
         }
         __syncwarp();
-        FQ_TS(it, 6);
-        if (!warp_all(mbar_wait_spin(wc, &s.vp_ready, ph, 7))) break;
-        FQ_TS(it, 7);
-        if (!warp_all(mbar_wait_spin(wc, &s.s_scaled, ph, 9))) break;
-        FQ_TS(it, 8);
+        mbar_wait_spin(wc, &s.vp_ready, ph, 7);
+        mbar_wait_spin(wc, &s.s_scaled, ph, 9);
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
@@ -260,7 +248,6 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           umma_commit(&s.empty[st]);
         }
         __syncwarp();
-        FQ_TS(it, 9);
       }
     }
   } else if (warp < 4) {
@@ -268,7 +255,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int t = tid - 64;
     for (int it = 0; it < total; ++it) {
       const int n = it - warm, gs = it & (kGateStages - 1);
-      if (it >= kGateStages && !mbar_wait(wc, &s.gate_empty[gs], ((it >> 2) + 1) & 1, 10)) break;
+      if (it >= kGateStages) mbar_wait(wc, &s.gate_empty[gs], ((it >> 2) + 1) & 1, 10);
       const int len = min(kChunk, seq_len - n * kChunk);  // replayed chunks (n < 0) are always whole
       const long long row = static_cast<long long>(tok_begin) + static_cast<long long>(n) * kChunk;
       const float gl = __ldg(p.g_cum + (row + len - 1) * p.H + h);
@@ -307,17 +294,15 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
       tmem_wait_st();
     }
-    bool alive = true;
     for (int it = 0; it < total; ++it) {
       const int n = it - warm, st = it & 1, gs = it & (kGateStages - 1);
       const uint32_t ph = it & 1;
       // ---- state -> bf16 operand, optional h, decay
       if (it > 0) {
-        if (!mbar_wait(wc, &s.s_done, (it - 1) & 1, 15)) { alive = false; break; }
+        mbar_wait(wc, &s.s_done, (it - 1) & 1, 15);
         tc_fence_after();
       }
-      if (tid == 128) FQ_TS(it, 14);
-      if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 16)) { alive = false; break; }
+      mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 16);
       {
         const float gL = s.gate[gs][1][kChunk - 1];
         const bool store_h = (p.h_out != nullptr) && (n >= 0);
@@ -331,7 +316,6 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tmem_ld32(tmem_addr(tm, lane_base, kColS + 64 * hf), r0);
         tmem_ld32(tmem_addr(tm, lane_base, kColS + 64 * hf + 32), r1);
         tmem_wait_ld();
-        if (tid == 128) FQ_TS(it, 23);
         uint32_t pk[32];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -345,7 +329,6 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&s.s_ready);
-          if (tid == 128) FQ_TS(it, 15);
           if (p.h_out != nullptr) {  // trailing part: the same values as the tile that the TMA store of h reads
             if (tid == 128) tma_store_wait_read<0>();
             asm volatile("bar.sync 2, 256;" ::: "memory");
@@ -364,7 +347,6 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (!state_only) {
           __syncwarp();
           if (lane == 0) mbar_arrive(&s.s_ready);
-          if (tid == 128) FQ_TS(it, 15);
         }
         if (p.h_out != nullptr) {
           asm volatile("bar.sync 2, 256;" ::: "memory");  // all 8 warps have written (and fenced) their part
@@ -383,20 +365,17 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tmem_st32(tmem_addr(tm, lane_base, kColS + 64 * hf), r0);
         tmem_st32(tmem_addr(tm, lane_base, kColS + 64 * hf + 32), r1);
         tmem_wait_st();
-        if (tid == 128) FQ_TS(it, 25);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s.s_scaled);
       }
       // ---- -(gamma_c U^T[v][c]) for c in [32 hf, 32 hf + 32): the state-dependent half of W = V - gamma o U
-      if (!mbar_wait(wc, &s.uq_done, ph, 13)) { alive = false; break; }
-      if (tid == 128) FQ_TS(it, 10);
+      mbar_wait(wc, &s.uq_done, ph, 13);
       tc_fence_after();
       {
         uint32_t u[32];
         tmem_ld32(tmem_addr(tm, lane_base, kColUQ + 32 * hf), u);
         tmem_wait_ld();
-        if (tid == 128) FQ_TS(it, 20);
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -406,15 +385,11 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tmem_st16(tmem_addr(tm, lane_base, kColUQ + 32 * hf), pk);
         tmem_wait_st();
       }
-      if (tid == 128) FQ_TS(it, 21);
       tc_fence_before();
-      if (tid == 128) FQ_TS(it, 22);
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.w_ready);
-      if (tid == 128) FQ_TS(it, 11);
       // ---- V_d^T and V'^T = rho o V_d^T
-      if (!mbar_wait(wc, &s.vd_done, ph, 14)) { alive = false; break; }
-      if (tid == 128) FQ_TS(it, 12);
+      mbar_wait(wc, &s.vd_done, ph, 14);
       tc_fence_after();
       {
         uint32_t d[32];
@@ -438,16 +413,15 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       fence_async_smem();
       __syncwarp();
       if (lane == 0) { mbar_arrive(&s.vp_ready); mbar_arrive(&s.gate_empty[gs]); }
-      if (tid == 128) FQ_TS(it, 13);
     }
     if (p.h_out != nullptr && tid == 128) tma_store_wait_all<0>();
     // ---- final state
-    if (alive && total > 0) {
-      alive = mbar_wait(wc, &s.s_done, (total - 1) & 1, 17);
+    if (total > 0) {
+      mbar_wait(wc, &s.s_done, (total - 1) & 1, 17);
       tc_fence_after();
     }
     const int slot = p.ht_index ? __ldg(p.ht_index + entry) : entry;
-    if (alive && p.ht && slot >= 0 && !skip) {
+    if (p.ht && slot >= 0) {
       float* dst = p.ht + (static_cast<size_t>(slot) * p.H + h) * kDim * kDim + v;
 #pragma unroll 1
       for (int pc = 0; pc < 2; ++pc) {
@@ -466,9 +440,8 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     for (int it = 0; it < total; ++it) {
       const int n = it - warm, gs = it & (kGateStages - 1);
       const uint32_t ph = it & 1;
-      if (!mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 18)) break;
-      if (!mbar_wait(wc, &s.o_done, ph, 21)) break;
-      if (tid == 384) FQ_TS(it, 18);
+      mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 18);
+      mbar_wait(wc, &s.o_done, ph, 21);
       tc_fence_after();
       bool staged = false;
       if (!kStateOnly && n >= 0) {
@@ -522,13 +495,16 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           tma_store_commit();
         }
       }
-      if (tid == 384) FQ_TS(it, 19);
     }
     if (!kStateOnly && tid == 384) tma_store_wait_all<0>();
   }
 
   tc_fence_before();
   __syncthreads();
+  if (s.abort_flag) {  // a wait expired somewhere in the CTA (the same value for every thread: all roles are done)
+    drain_after_abort(warp == 1 && elect_one(), &s.drain_bar);
+    __syncthreads();
+  }
   if (warp == 1) tmem_dealloc(tm, 512);
 }
 
@@ -601,13 +577,15 @@ extern "C" FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void*
   p.sa = SeqArgs{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
   p.status_dev = status_dev;
   const size_t smem = sizeof(FwdSmem) + 1024;
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  FQ_CHECK_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    FQ_CHECK_CUDA(cudaFuncSetAttribute(gdr_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    FQ_CHECK_CUDA(cudaFuncSetAttribute(gdr_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    attr_set[dev] = true;
+  {
+    static std::atomic<unsigned long long> done0{0};
+    const int rc_attr = set_smem_limit_once(reinterpret_cast<const void*>(gdr_fwd_kernel<false>), static_cast<int>(smem), &done0);
+    if (rc_attr != FQ_OK) return rc_attr;
+  }
+  {
+    static std::atomic<unsigned long long> done1{0};
+    const int rc_attr = set_smem_limit_once(reinterpret_cast<const void*>(gdr_fwd_kernel<true>), static_cast<int>(smem), &done1);
+    if (rc_attr != FQ_OK) return rc_attr;
   }
   const long long ctas = static_cast<long long>(n_entries) * H;
   FQ_CHECK_ARG(ctas < (1ll << 31), "fq_gdr_fwd: too many (sequence, head) pairs");
@@ -617,8 +595,3 @@ extern "C" FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void*
   return FQ_OK;
 }
 
-#ifdef FQ_TRACE
-extern "C" FQ_API int fq_trace_read(long long* out_host) {
-  return cudaMemcpyFromSymbol(out_host, fq::g_trace, sizeof(long long) * 8 * 32) == cudaSuccess ? 0 : -2;
-}
-#endif

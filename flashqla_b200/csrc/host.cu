@@ -2,6 +2,7 @@
 #include "host.cuh"
 
 #include <stdarg.h>
+#include <atomic>
 #include <string.h>
 
 #include "flashqla.h"
@@ -48,11 +49,12 @@ int make_tmap_rows_heads_dim(CUtensorMap* out, const void* base, uint64_t rows, 
     return FQ_ERR_INVALID;
   }
   // The encoder is a driver call and needs a current context.  A host thread that has only selected a device
-  // (e.g. an autograd worker thread whose first CUDA work is this call) has none yet: a runtime call binds the
-  // device's primary context to the thread.
+  // (e.g. an autograd worker thread whose first CUDA work is this call) has none yet: re-selecting the current
+  // device through the runtime initialises the device's primary context and binds it to the thread.
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) {
-    if (cudaFree(nullptr) != cudaSuccess) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) {
       set_error("no usable CUDA context on this thread: %s", cudaGetErrorString(cudaGetLastError()));
       return FQ_ERR_CUDA;
     }
@@ -70,6 +72,25 @@ int make_tmap_rows_heads_dim(CUtensorMap* out, const void* base, uint64_t rows, 
               (unsigned long long)rows, (unsigned long long)heads, (unsigned long long)dim);
     return FQ_ERR_CUDA;
   }
+  return FQ_OK;
+}
+
+int set_smem_limit_once(const void* func, int bytes, std::atomic<unsigned long long>* done_mask) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    set_error("cudaGetDevice failed: %s", cudaGetErrorString(e));
+    return FQ_ERR_CUDA;
+  }
+  const unsigned long long bit = (dev >= 0 && dev < 64) ? (1ull << dev) : 0ull;
+  if (bit && (done_mask->load(std::memory_order_acquire) & bit)) return FQ_OK;
+  // idempotent: two host threads that get here together both set the same value
+  e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(MaxDynamicSharedMemorySize=%d) failed: %s", bytes, cudaGetErrorString(e));
+    return FQ_ERR_CUDA;
+  }
+  if (bit) done_mask->fetch_or(bit, std::memory_order_release);
   return FQ_OK;
 }
 

@@ -6,6 +6,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace fq {
@@ -36,6 +38,11 @@ void set_error(const char* fmt, ...);
 // Returns FQ_OK or an error code.
 int make_tmap_rows_heads_dim(CUtensorMap* out, const void* base, uint64_t rows, uint64_t heads, uint64_t dim,
                              uint32_t box_rows, uint32_t box_dim);
+
+// Raises the dynamic shared-memory limit of kernel `func` to `bytes` on the current device, once per device
+// (`done_mask`: one bit per device index, owned by the caller as a function-local static).  Safe to call from
+// several host threads at once.  Returns FQ_OK or an error code.
+int set_smem_limit_once(const void* func, int bytes, std::atomic<unsigned long long>* done_mask);
 
 // Number of SMs of the current device (cached per device).
 int sm_count();

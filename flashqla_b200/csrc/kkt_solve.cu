@@ -468,15 +468,15 @@ static int kkt_launch(const void* k, const void* q, const float* beta, const flo
   FQ_CHECK_ARG(cu_seqlens != nullptr || n_seq == B, "fq_kkt_solve: dense batches need n_seq == B");
   if (total_chunks == 0) return FQ_OK;
   SeqArgs sa{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  FQ_CHECK_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    FQ_CHECK_CUDA(cudaFuncSetAttribute(kkt_solve_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(sizeof(KktSmem))));
-    FQ_CHECK_CUDA(cudaFuncSetAttribute(kkt_solve_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(sizeof(KktSmem))));
-    attr_set[dev] = true;
+  {
+    static std::atomic<unsigned long long> done0{0};
+    const int rc_attr = set_smem_limit_once(reinterpret_cast<const void*>(kkt_solve_kernel<true>), static_cast<int>(sizeof(KktSmem)), &done0);
+    if (rc_attr != FQ_OK) return rc_attr;
+  }
+  {
+    static std::atomic<unsigned long long> done1{0};
+    const int rc_attr = set_smem_limit_once(reinterpret_cast<const void*>(kkt_solve_kernel<false>), static_cast<int>(sizeof(KktSmem)), &done1);
+    if (rc_attr != FQ_OK) return rc_attr;
   }
   dim3 grid(total_chunks, Hg);
   auto kern = (H == Hg) ? kkt_solve_kernel<true> : kkt_solve_kernel<false>;

@@ -18,6 +18,7 @@ struct SelfTestSmem {
   unsigned char b[32768];
   uint64_t bar_tma;
   uint64_t bar_mma;
+  uint64_t drain_bar;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -32,13 +33,14 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
   SelfTestSmem& s = *reinterpret_cast<SelfTestSmem*>(
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  WaitCtx wc{&s.abort_flag, status_dev, 15};
+  WaitCtx wc{&s.abort_flag, status_dev, 15, kWaitLimitCycles};
   constexpr uint32_t kCols = 256;
 
   if (tid == 0) {
     s.abort_flag = 0;
     mbar_init(&s.bar_tma, 1);
     mbar_init(&s.bar_mma, 1);
+    mbar_init(&s.drain_bar, 1);
     fence_mbar_init();
   }
   if (warp == 0) {
@@ -100,8 +102,8 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
   // ---- issue the MMAs
   if (tid == 0) {
     tc_fence_after();
-    bool ok = mbar_wait(wc, &s.bar_tma, 0, 1);
-    if (ok) {
+    mbar_wait(wc, &s.bar_tma, 0, 1);
+    {
       tc_fence_after();
       const uint32_t sa = smem_u32(s.a), sb = smem_u32(s.b);
       if (mode == 0 || mode == 2) {
@@ -147,9 +149,9 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
   __syncwarp();
 
   // ---- epilogue: TMEM -> registers -> global
-  const bool done = mbar_wait(wc, &s.bar_mma, 0, 2);
+  mbar_wait(wc, &s.bar_mma, 0, 2);
   tc_fence_after();
-  if (done) {
+  {
 #pragma unroll 1
     for (int cb = 0; cb < 4; ++cb) {
       uint32_t r[32];
@@ -170,7 +172,58 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
   }
   tc_fence_before();
   __syncthreads();
+  if (s.abort_flag) {
+    drain_after_abort(tid == 0, &s.drain_bar);
+    __syncthreads();
+  }
   if (warp == 0) tmem_dealloc(tm, kCols);
+}
+
+// A wait that nobody satisfies, with a caller-chosen (short) limit: the safe way to see the expiry path of the
+// kernels' bounded waits at work.  Warp 2 waits on an mbarrier without arrivals; the other warps wait on a second
+// barrier that warp 2 would arrive on afterwards.  Expected: warp 2's wait gives up after `limit` cycles, writes
+// (14 << 12) + 5 to the status word and raises the abort flag; the other warps' waits stop at once; the CTA runs to
+// its end, releases its tensor memory and writes 1 to `done`.  Nothing traps, faults or spins without a bound.
+struct ExpirySmem {
+  uint64_t never, after, drain_bar;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(128) wait_expiry_kernel(int* status_dev, int* done, long long limit) {
+  __shared__ ExpirySmem s;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  WaitCtx wc{&s.abort_flag, status_dev, 14, limit};
+  if (tid == 0) {
+    s.abort_flag = 0;
+    mbar_init(&s.never, 1);
+    mbar_init(&s.after, 1);
+    mbar_init(&s.drain_bar, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&s.tmem_base, 64);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = s.tmem_base;
+  if (warp == 2) {
+    mbar_wait(wc, &s.never, 0, 5);
+  } else {
+    // would be released by warp 2 in a run without the expiry; here the raised flag ends the wait
+    WaitCtx wc_long{&s.abort_flag, status_dev, 14, kWaitLimitCycles};
+    mbar_wait(wc_long, &s.after, 0, 6);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (s.abort_flag) {
+    drain_after_abort(tid == 0, &s.drain_bar);
+    __syncthreads();
+  }
+  if (warp == 0) tmem_dealloc(tm, 64);
+  if (tid == 0) *done = 1;
 }
 
 }  // namespace fq
@@ -187,10 +240,25 @@ extern "C" FQ_API int fq_selftest_umma(const void* a, const void* b, float* d, i
   if ((rc = make_tmap_rows_heads_dim(&mb128, b, 128, 1, 128, 128, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mb64, b, 128, 1, 128, 64, 64)) != FQ_OK) return rc;
   const size_t smem = sizeof(SelfTestSmem) + 1024;
-  FQ_CHECK_CUDA(cudaFuncSetAttribute(selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  {
+    static std::atomic<unsigned long long> done{0};
+    const int rc_attr = set_smem_limit_once(reinterpret_cast<const void*>(selftest_kernel), static_cast<int>(smem), &done);
+    if (rc_attr != FQ_OK) return rc_attr;
+  }
   selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(ma128, ma64, mb128, mb64,
                                                                          static_cast<const __nv_bfloat16*>(a), d, mode,
                                                                          status_dev);
+  FQ_CHECK_CUDA(cudaGetLastError());
+  return FQ_OK;
+}
+
+extern "C" FQ_API int fq_selftest_wait_expiry(int32_t* status_dev, int32_t* done_dev, long long limit_cycles,
+                                              void* stream) {
+  using namespace fq;
+  FQ_CHECK_ARG(status_dev && done_dev, "fq_selftest_wait_expiry: null pointer");
+  FQ_CHECK_ARG(limit_cycles > 0 && limit_cycles <= 100000000LL,
+               "fq_selftest_wait_expiry: the limit must be between 1 and 1e8 cycles (this test is meant to end at once)");
+  wait_expiry_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(status_dev, done_dev, limit_cycles);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }

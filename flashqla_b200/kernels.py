@@ -31,7 +31,12 @@ def make_plan(B: int, T: int, cu_seqlens, device, host=None) -> SeqPlan:
         raise ValueError(
             f"The batch size is expected to be 1 rather than {B} when using `cu_seqlens`."
             f"Please flatten variable-length inputs before processing.")
-    return plan_packed(cu_seqlens, device, host=host)
+    plan = plan_packed(cu_seqlens, device, host=host)
+    if plan.total_tokens > T:
+        # the tail-chunk stores of the kernels are plain pointer writes: a sequence that ends past the tensors would
+        # write out of bounds
+        raise ValueError(f"cu_seqlens[-1] = {plan.total_tokens} exceeds the {T} tokens of the packed tensors")
+    return plan
 
 
 def chunk_local_cumsum(g: torch.Tensor, chunk_size: int = CHUNK, reverse: bool = False, cu_seqlens=None,
@@ -94,6 +99,13 @@ def check_status(status: torch.Tensor, what: str) -> None:
         raise _lib.FlashQLAError(f"{what}: device-side wait timed out (code {st:#x})")
 
 
+def _tile_alloc(plan: SeqPlan, B: int, T: int):
+    """Allocator of the [B,T,H,64] tile tensors.  Rows past the last sequence (packed tensors longer than
+    cu_seqlens[-1]) are never written by the tile kernel, but the last tail tile of the recurrence kernels covers them
+    and masks them by multiplication: they must hold finite values, so such batches start from zeros."""
+    return torch.zeros if plan.total_tokens < B * T else torch.empty
+
+
 def kkt_solve_gated(k, q, b, g_cum, scale, plan: SeqPlan, A=None, want_pg=True):
     """A (gate-free inverse, computed unless given), A_g and P_g tiles, bf16 [B,T,H,64] each."""
     _require_cuda(k, q, b, g_cum)
@@ -109,8 +121,9 @@ def kkt_solve_gated(k, q, b, g_cum, scale, plan: SeqPlan, A=None, want_pg=True):
         A = torch.empty(B, T, H, CHUNK, dtype=k.dtype, device=k.device)
     else:
         A = A.contiguous()
-    Ag = torch.empty(B, T, H, CHUNK, dtype=k.dtype, device=k.device)
-    Pg = torch.empty(B, T, H, CHUNK, dtype=k.dtype, device=k.device) if want_pg else None
+    alloc = _tile_alloc(plan, B, T)
+    Ag = alloc(B, T, H, CHUNK, dtype=k.dtype, device=k.device)
+    Pg = alloc(B, T, H, CHUNK, dtype=k.dtype, device=k.device) if want_pg else None
     cu_p, off_p = plan.ptrs()
     rc = _lib.load().fq_kkt_solve_gated(k.data_ptr(), q.data_ptr(), bf.data_ptr(), g_cum.data_ptr(), A.data_ptr(),
                                         Ag.data_ptr(), None if Pg is None else Pg.data_ptr(), int(a_is_input), B, T, H,
@@ -133,9 +146,10 @@ def kkt_solve_fused(k, q, b, g, scale, plan: SeqPlan, want_A=True):
     bf = b.contiguous() if b.dtype == torch.float32 else b.float().contiguous()
     gf = g.contiguous() if g.dtype == torch.float32 else g.float().contiguous()
     g_cum = torch.empty_like(gf)
-    Ag = torch.empty(B, T, H, CHUNK, dtype=k.dtype, device=k.device)
-    Pg = torch.empty_like(Ag)
-    A = torch.empty_like(Ag) if want_A else None
+    alloc = _tile_alloc(plan, B, T)
+    Ag = alloc(B, T, H, CHUNK, dtype=k.dtype, device=k.device)
+    Pg = alloc(B, T, H, CHUNK, dtype=k.dtype, device=k.device)
+    A = alloc(B, T, H, CHUNK, dtype=k.dtype, device=k.device) if want_A else None
     cu_p, off_p = plan.ptrs()
     rc = _lib.load().fq_kkt_solve_fused(k.data_ptr(), q.data_ptr(), bf.data_ptr(), gf.data_ptr(), g_cum.data_ptr(),
                                         None if A is None else A.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), B, T, H, Hg,

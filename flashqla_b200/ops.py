@@ -87,12 +87,13 @@ def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None,
 
 
 def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, initial_state=None, cu_seqlens=None,
-                               _gated_tiles=None, _plan=None):
+                               _gated_tiles=None, _plan=None, _want_dh0=None):
     """Backward pipeline (chunk/__init__.py:70-113).  ``g`` is the cumsum returned by the forward,
-    ``A`` the tensor returned by the forward.  Returns ``(dq, dk, dv, db, dg, dh0)``."""
+    ``A`` the tensor returned by the forward.  Returns ``(dq, dk, dv, db, dg, dh0)``; ``dh0`` is None when
+    neither ``dht`` nor ``initial_state`` is given (``_want_dh0`` overrides that rule)."""
     from . import bwd  # the backward kernels live in their own module
     return bwd.chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht, scale, initial_state, cu_seqlens,
-                                          gated_tiles=_gated_tiles, plan=_plan)
+                                          gated_tiles=_gated_tiles, plan=_plan, want_dh0=_want_dh0)
 
 
 class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
@@ -127,9 +128,14 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     def backward(ctx, do, dht):
         q, k, v, g_cum, beta, A, initial_state, cu_seqlens = ctx.saved_tensors[:8]
         tiles = tuple(ctx.saved_tensors[8:10]) if ctx.keep_tiles else None
+        # a gradient for the initial state is formed only if one was passed in and asks for it: returning a tensor
+        # for an input that was None (initial_state=None with output_final_state=True, the first segment of a
+        # truncated back-propagation) is an autograd error
+        need_dh0 = initial_state is not None and ctx.needs_input_grad[6]
         dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(
             q=q, k=k, v=v, g=g_cum, beta=beta, A=A, do=do, dht=dht, scale=ctx.scale,
-            initial_state=initial_state, cu_seqlens=cu_seqlens, _gated_tiles=tiles, _plan=ctx.plan)
+            initial_state=initial_state, cu_seqlens=cu_seqlens, _gated_tiles=tiles, _plan=ctx.plan,
+            _want_dh0=need_dh0)
         return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dg.to(ctx.g_dtype), db.to(ctx.beta_dtype),
                 None, dh0, None, None, None)
 

@@ -14,12 +14,18 @@
  *   - variable-length batches: B == 1, `cu_seqlens` = int32 [n_seq+1] token offsets,
  *     `chunk_offsets` = int32 [n_seq+1] prefix sums of ceil(len/64); both NULL for dense batches
  *     (then n_seq == B and every sequence has T tokens);
- *   - the work is enqueued on `stream` (a cudaStream_t); nothing synchronises, nothing is
- *     allocated, no global mutable state is kept apart from per-device constant caches;
+ *   - the work is enqueued on `stream` (a cudaStream_t); nothing synchronises and nothing is allocated.
+ *     The only state the library keeps between calls are per-device caches that are written once and never
+ *     change afterwards (which kernels had their shared-memory limit raised, the SM count, the device address of
+ *     the built-in scratch array of fq_gdr_bwd_chunk_gva_noalloc); they are filled under a mutex or with atomic,
+ *     idempotent updates, so first calls from several host threads are safe.  A host thread's first call that
+ *     builds tensor maps re-selects the current device through the runtime (cudaSetDevice) to bind the device's
+ *     primary context to the thread: let each thread make its first call outside stream capture;
  *   - return value: 0 on success, negative FQ_ERR_* otherwise; fq_last_error() gives a message
  *     for the calling thread;
  *   - `status_dev` (may be NULL): int32 in device memory, must be 0 on entry; a kernel whose
- *     bounded wait expires stores a non-zero code there and drains instead of hanging.
+ *     bounded wait expires stores a non-zero code there ((kernel id << 12) + wait site; the first expiry wins),
+ *     stops waiting and runs to its end instead of hanging; the outputs of such a launch are meaningless.
  */
 #ifndef FLASHQLA_H_
 #define FLASHQLA_H_
@@ -258,10 +264,28 @@ FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void* v, const v
                             float scale, int32_t* status_dev, void* stream);
 
 /*
+ * fp32 correction of dg at the two ends of every sequence, applied between fq_gdr_bwd_chunk and the reverse
+ * fq_chunk_cumsum.  dg of a chunk's last token contains gamma_last * sum(dS o S0) over the 128 x 128 state;
+ * fq_gdr_bwd_chunk forms it from the bf16 copies h / dh.  For a sequence's first chunk S0 is the caller's fp32 h0, for
+ * its last chunk dS is the caller's fp32 dht: this adds the products with the rounding residuals (h0 - bf16(h0),
+ * dht - bf16(dht)) to dg_cum in place, which makes the term exact for one-chunk sequences.  h0 / dht may be NULL.
+ * The reference keeps dS in fp32 registers inside its one serial kernel
+ * (flash_qla/ops/gated_delta_rule/chunk/hopper/fused_bwd.py:335-357); this is what the split into two kernels owes.
+ *   h, dh [total_chunks,H,128(v),128(k)] bf16; h0, dht [n_seq,H,128,128] fp32; g_cumsum, dg_cum [B,T,H] fp32.
+ */
+FQ_API int fq_dg_boundary_fix(const float* h0, const float* dht, const void* h, const void* dh, const float* g_cumsum,
+                              float* dg_cum, int B, int T, int H, const int32_t* cu_seqlens,
+                              const int32_t* chunk_offsets, int n_seq, int total_chunks, void* stream);
+
+/*
  * out[r, hg, :] = sum of in[r, hg*G .. hg*G+G-1, :] (G = H / Hg), bf16 in/out, fp32 accumulation.
  * Replaces group_reduce_vector, flash_qla/ops/utils/group_reduce.py:60-79.
  */
 FQ_API int fq_group_reduce(const void* in, void* out, long long rows, int H, int Hg, void* stream);
+/* The same for two tensors of one shape in ONE launch (dq and dk of the backward, which the reference sums with
+ * two calls, flash_qla/ops/gated_delta_rule/chunk/__init__.py:104-107). */
+FQ_API int fq_group_reduce_pair(const void* in_a, void* out_a, const void* in_b, void* out_b, long long rows, int H,
+                                int Hg, void* stream);
 
 /*
  * y = x * rsqrt(sum(x^2 over the last dim) + eps) for rows of 128 bf16 values, and its backward
@@ -293,12 +317,14 @@ FQ_API int fq_gdr_recurrent(const void* q, const void* k, const void* v, const f
  * buffers were all planned in advance and whose allocator is frozen, or a host that would
  * otherwise pay a device-synchronising cudaMalloc per call).
  *   - limit: B*T*H <= 65536; larger problems return FQ_ERR_WORKSPACE with a message;
+ *   - cost: the 32 MiB array is part of the library image, so every GPU on which the library is loaded holds it
+ *     from load until the process exits, whether or not this entry point is ever called;
  *   - the first call on each device resolves the array's device address and configures the kernel;
- *     make that first call outside any stream capture;
+ *     make that first call outside any stream capture (and see the note on a thread's first call above);
  *   - all calls share the one array and it keeps the previous call's contents: nothing in it has to
  *     be cleared (every row is rewritten before it is read), but two calls that overlap on the GPU
  *     (different streams, or different host threads) race on it; serialise them;
- *   - it calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - it allocates nothing: no cudaMalloc, no cudaFree of a buffer, no allocating library routine.
  */
 FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k, const void* v, const void* A, const void* Ag,
                                         const void* Pg, const void* dout, const void* h, const void* dh,
@@ -313,6 +339,15 @@ FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k, const void
  * csrc/selftest.cu.  No counterpart in the reference; used by the GPU tests only.
  */
 FQ_API int fq_selftest_umma(const void* a, const void* b, float* d, int mode, int32_t* status_dev, void* stream);
+
+/*
+ * Self-test of the bounded waits: launches one small CTA in which one warp waits, for at most `limit_cycles`
+ * (1 .. 1e8), on an mbarrier that nothing completes.  Expected: *status_dev (0 on entry) becomes
+ * (14 << 12) + 5 = 0xE005, the other warps' waits end as soon as the abort flag is up, the CTA releases its
+ * tensor memory and writes 1 to *done_dev; the context stays usable.  No counterpart in the reference (its
+ * TileLang kernels wait without a bound); used by the GPU tests only.
+ */
+FQ_API int fq_selftest_wait_expiry(int32_t* status_dev, int32_t* done_dev, long long limit_cycles, void* stream);
 
 #ifdef __cplusplus
 }

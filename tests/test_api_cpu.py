@@ -65,6 +65,19 @@ def test_planner_takes_a_host_copy_of_cu_seqlens():
         planner.plan_packed(cu.clone(), "cpu", host=torch.tensor([0, 3], dtype=torch.int32))
 
 
+def test_plan_checks_the_sequence_end_against_the_tensors():
+    """cu_seqlens[-1] beyond the packed tensors is refused (the kernels' tail stores are plain pointer writes);
+    shorter is allowed, and the tile tensors of such a batch start from zeros."""
+    from flashqla_b200 import kernels
+    cu = torch.tensor([0, 100, 300], dtype=torch.int32)
+    with pytest.raises(ValueError, match="exceeds"):
+        kernels.make_plan(1, 256, cu, "cpu")
+    assert kernels._tile_alloc(kernels.make_plan(1, 300, cu, "cpu"), 1, 300) is torch.empty
+    assert kernels._tile_alloc(kernels.make_plan(1, 320, cu, "cpu"), 1, 320) is torch.zeros
+    with pytest.raises(ValueError, match="batch size"):
+        kernels.make_plan(2, 300, cu, "cpu")
+
+
 def test_public_operator_validation():
     import flash_qla
     q = torch.zeros(2, 64, 2, 128, dtype=torch.bfloat16)

@@ -9,17 +9,13 @@ import os
 import pytest
 import torch
 
-from conftest import load_golden
+from conftest import check_close, load_golden
 from oracle import gdr_oracle as orc
 
 pytestmark = pytest.mark.gpu
 os.environ.setdefault("FLASHQLA_CHECK_STATUS", "1")
 
 TOL = 1e-2
-# dg contains gamma_last * sum(dS o S0) per chunk, evaluated from the bf16 copies of both states that
-# travel between the kernels.  With h0 ~ randn and a sequence of one short chunk that term dominates
-# dg and its rounding shows; such cases get the reference's own 2e-2 bound for dg.
-TOL_DG_SHORT = 2e-2
 NAMES = ["dq", "dk", "dv", "db", "dg", "dh0"]
 
 
@@ -68,19 +64,14 @@ def test_backward_vs_oracle(B, T, Hq, Hv, cu, dist):
     gc = orc.chunk_local_cumsum(g, cu_t)
     ref = orc.gdr_bwd(q.float(), k.float(), v.float(), gc, beta, do.float(), dht, None, h0, cu_t)
     got = run_bwd(q, k, v, g, beta, h0, do, dht, cu_t)
-    errs = {n: orc.rel_to_max(x, r) for n, x, r in zip(NAMES, got, ref)}
-    tol = {n: TOL for n in NAMES}
-    if T < 64 and dist == "reftest":
-        tol["dg"] = TOL_DG_SHORT
-    assert all(errs[n] < tol[n] for n in NAMES), str({k_: f'{v_:.2e}' for k_, v_ in errs.items()})
+    check_close(got, ref, TOL, NAMES)
 
 
 @pytest.mark.parametrize("name", ["dense_tail_bf16", "varlen_gva_reftest_bf16"])
 def test_backward_vs_reference_fixture(name):
     z = load_golden(name)
     got = run_bwd(z["q"], z["k"], z["v"], z["g"], z["beta"], z["h0"], z["do"], z["dht"], z.get("cu_seqlens"))
-    errs = {n: orc.rel_to_max(x, z[n]) for n, x in zip(NAMES, got)}
-    assert all(e < TOL for e in errs.values()), str({k_: f'{v_:.2e}' for k_, v_ in errs.items()})
+    check_close(got, [z[n] for n in NAMES], TOL, NAMES)
 
 
 @pytest.mark.parametrize("recompute_tiles", [False, True])
@@ -98,8 +89,32 @@ def test_autograd_entry(recompute_tiles, monkeypatch):
     gc = orc.chunk_local_cumsum(g, None)
     ref = orc.gdr_bwd(q.float(), k.float(), v.float(), gc, beta, do.float(), dht, None, h0, None)
     got = [leaves[0].grad, leaves[1].grad, leaves[2].grad, leaves[4].grad, leaves[3].grad, leaves[5].grad]
-    errs = {n: orc.rel_to_max(x.float().cpu(), r) for n, x, r in zip(NAMES, got, ref)}
-    assert all(e < TOL for e in errs.values()), str({k_: f'{v_:.2e}' for k_, v_ in errs.items()})
+    check_close(got, ref, TOL, NAMES)
+
+
+@pytest.mark.parametrize("with_h0,with_final", [(False, True), (True, False), (False, False)])
+def test_autograd_optional_states(with_h0, with_final):
+    """initial_state=None and / or output_final_state=False through the differentiable entry: the first segment of
+    a truncated back-propagation (no initial state, final state handed on) must not return a gradient for the
+    missing input, and a missing final state means a zero state gradient at the end."""
+    import flash_qla
+    q, k, v, g, beta, h0, do, dht = make_inputs(7, 2, 200, 2, 4)
+    dev = "cuda"
+    leaves = [x.to(dev).requires_grad_() for x in (q, k, v, g, beta)]
+    h0_leaf = h0.to(dev).requires_grad_() if with_h0 else None
+    o, fs = flash_qla.chunk_gated_delta_rule(*leaves, initial_state=h0_leaf, output_final_state=with_final)
+    assert (fs is not None) == with_final
+    loss = (o.float() * do.to(dev).float()).sum()
+    if with_final:
+        loss = loss + (fs * dht.to(dev)).sum()
+    loss.backward()
+    gc = orc.chunk_local_cumsum(g, None)
+    ref = orc.gdr_bwd(q.float(), k.float(), v.float(), gc, beta, do.float(), dht if with_final else None, None,
+                      h0 if with_h0 else None, None)
+    got = [leaves[0].grad, leaves[1].grad, leaves[2].grad, leaves[4].grad, leaves[3].grad]
+    check_close(got, ref[:5], TOL, NAMES[:5])
+    if with_h0:
+        check_close([h0_leaf.grad], [ref[5]], TOL, ["dh0"])
 
 
 CP_CASES = [
@@ -124,8 +139,7 @@ def test_backward_context_parallel(B, T, Hq, Hv, cu, dist, pc, monkeypatch):
     gc = orc.chunk_local_cumsum(g, cu_t)
     ref = orc.gdr_bwd(q.float(), k.float(), v.float(), gc, beta, do.float(), dht, None, h0, cu_t)
     got = run_bwd(q, k, v, g, beta, h0, do, dht, cu_t)
-    errs = {n: orc.rel_to_max(x, r) for n, x, r in zip(NAMES, got, ref)}
-    assert all(e < TOL for e in errs.values()), str({k_: f'{v_:.2e}' for k_, v_ in errs.items()})
+    check_close(got, ref, TOL, NAMES)
 
 
 def test_backward_is_reproducible():
@@ -139,3 +153,34 @@ def test_backward_is_reproducible():
             assert torch.equal(got[i], ref[i]), NAMES[i]
         for i in (3, 4):
             assert (got[i] - ref[i]).abs().max() <= 1e-5 * ref[i].abs().max()
+
+
+def test_repeated_forward_backward_is_race_free():
+    """200 forward + backward passes of one packed, grouped-head batch that runs context parallel (pieces of three
+    chunks; the zero-gate head takes the transition-matrix route): every pass must leave the status word at zero and
+    reproduce o, final_state, dq, dk, dv and dh0 bit for bit (dg and dbeta, summed with atomics, to 1e-5).  The
+    reference guards its kernels the same way with 1000 repetitions (tests/test_gdr.py:203,362 of FlashQLA)."""
+    from flashqla_b200 import kernels, ops
+    old = ops._FORCE_PIECE_CHUNKS
+    ops._FORCE_PIECE_CHUNKS = 3
+    try:
+        cu = [0, 1, 64, 65, 700, 700, 1500, 2900]
+        cu_t = torch.tensor(cu, dtype=torch.int32, device="cuda")
+        q, k, v, g, beta, h0, do, dht = (x.cuda() for x in make_inputs(17, 1, cu[-1], 2, 4, "reftest", len(cu) - 1))
+
+        def one_pass():
+            gc, A, o, _, fs = ops.chunk_gated_delta_rule_fwd(q, k, v, g, beta, None, h0, cu_t, True, False, True)
+            outs = ops.chunk_gated_delta_rule_bwd(q, k, v, gc, beta, A, do, dht, None, h0, cu_t)
+            return [o, fs] + list(outs)
+
+        names = ["o", "final_state"] + NAMES
+        ref = one_pass()   # FLASHQLA_CHECK_STATUS=1: every pass reads the status word and raises if it is not zero
+        for rep in range(200):
+            got = one_pass()
+            for n, x, r in zip(names, got, ref):
+                if n in ("db", "dg"):
+                    assert (x - r).abs().max() <= 1e-5 * r.abs().max(), f"{n} differs in repetition {rep}"
+                else:
+                    assert torch.equal(x, r), f"{n} differs in repetition {rep}"
+    finally:
+        ops._FORCE_PIECE_CHUNKS = old

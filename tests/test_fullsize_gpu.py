@@ -11,6 +11,7 @@ import os
 import pytest
 import torch
 
+from conftest import check_close
 from oracle import gdr_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -143,3 +144,89 @@ def test_config4_packed_varlen_full_size():
                 got[5][si:si + 1, sl])
         for n, x, r in zip(("dq", "dk", "dv", "db", "dg", "dh0"), mine, ref):
             assert orc.rel_to_max(x.float().cpu(), r) < TOL_BF16, f"{n} of sequence {si}"
+
+
+def _c5_inputs(T, H, seed):
+    q, k, v, g, beta, h0 = _inputs(seed, 1, T, H, H)
+    gen = torch.Generator(device="cuda").manual_seed(seed + 1000)
+    do = torch.randn(1, T, H, 128, device="cuda", generator=gen).bfloat16()
+    dht = 0.01 * torch.randn(1, H, 128, 128, device="cuda", generator=gen)
+    return q, k, v, g, beta, h0, do, dht
+
+
+def test_config5_one_rank_share():
+    """B=1, T=131072, Hq=Hv=8: the share of one rank when the 1M-token sequence of the long-context configuration
+    is split over 8 GPUs.  Forward and backward of the whole problem; one head against the oracle run on that head
+    alone (forward and backward in full)."""
+    from flashqla_b200 import ops
+    T, H = 131072, 8
+    q, k, v, g, beta, h0, do, dht = _c5_inputs(T, H, 21)
+    scale = 128 ** -0.5
+    gc, A, o, _, fs = ops.chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale, h0, None, True, False, True)
+    got = ops.chunk_gated_delta_rule_bwd(q, k, v, gc, beta, A, do, dht, scale, h0, None)
+    torch.cuda.synchronize()
+    h = 5
+    sl = slice(h, h + 1)
+    cpu = lambda x: x.float().cpu()
+    gcr, _, o_ref, _, fs_ref = orc.gdr_fwd(cpu(q[:, :, sl]), cpu(k[:, :, sl]), cpu(v[:, :, sl]), g[:, :, sl].cpu(),
+                                           beta[:, :, sl].cpu(), scale, h0[:, sl].cpu(), None)
+    check_close([o[:, :, sl], fs[:, sl]], [o_ref, fs_ref], {"o": TOL_BF16, "final_state": TOL_FP32}, ["o", "final_state"])
+    ref = orc.gdr_bwd(cpu(q[:, :, sl]), cpu(k[:, :, sl]), cpu(v[:, :, sl]), gcr, beta[:, :, sl].cpu(), cpu(do[:, :, sl]),
+                      dht[:, sl].cpu(), scale, h0[:, sl].cpu(), None)
+    mine = [got[0][:, :, sl], got[1][:, :, sl], got[2][:, :, sl], got[3][:, :, sl], got[4][:, :, sl], got[5][:, sl]]
+    check_close(mine, ref, TOL_BF16, ["dq", "dk", "dv", "db", "dg", "dh0"])
+
+
+def test_config5_full_length():
+    """B=1, T=1048576, Hq=Hv=8 on one GPU (16384 chunks per head, 131072 units): one head of the forward against the
+    oracle's forward AND backward on that head in full; context parallel on = off; and the backward as a whole through
+    size-independent properties: linearity in (do, dht), one pass = two half passes chained through the state and
+    its gradient."""
+    from flashqla_b200 import ops
+    T, H = 1 << 20, 8
+    q, k, v, g, beta, h0, do, dht = _c5_inputs(T, H, 23)
+    scale = 128 ** -0.5
+    gc, A, o, _, fs = ops.chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale, h0, None, True, False, True)
+    torch.cuda.synchronize()
+    # (1) one head against the oracle
+    h = 2
+    sl = slice(h, h + 1)
+    cpu = lambda x: x.float().cpu()
+    _, _, o_ref, _, fs_ref = orc.gdr_fwd(cpu(q[:, :, sl]), cpu(k[:, :, sl]), cpu(v[:, :, sl]), g[:, :, sl].cpu(),
+                                         beta[:, :, sl].cpu(), scale, h0[:, sl].cpu(), None)
+    check_close([o[:, :, sl], fs[:, sl]], [o_ref, fs_ref], {"o": TOL_BF16, "final_state": TOL_FP32}, ["o", "final_state"])
+    del o_ref
+    # (2) context parallel off gives the same result
+    _, _, o_ser, _, fs_ser = ops.chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale, h0, None, True, False, False)
+    check_close([o, fs], [o_ser, fs_ser], {"o": TOL_BF16, "final_state": TOL_FP32}, ["o", "final_state"], "cp on/off: ")
+    del o_ser
+    # (3) backward: linearity in (do, dht)
+    names = ("dq", "dk", "dv", "db", "dg", "dh0")
+    got = ops.chunk_gated_delta_rule_bwd(q, k, v, gc, beta, A, do, dht, scale, h0, None)
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    do2 = torch.randn(1, T, H, 128, device="cuda", generator=gen).bfloat16()
+    dht2 = 0.01 * torch.randn(1, H, 128, 128, device="cuda", generator=gen)
+    got2 = ops.chunk_gated_delta_rule_bwd(q, k, v, gc, beta, A, do2, dht2, scale, h0, None)
+    dos = (do.float() + do2.float()).bfloat16()
+    gots = ops.chunk_gated_delta_rule_bwd(q, k, v, gc, beta, A, dos, dht + dht2, scale, h0, None)
+    check_close([a.float() + b.float() for a, b in zip(got, got2)], gots, TOL_LIN, names, "linearity: ")
+    # (3b) the same head's six gradients against the oracle's backward on that head in full (16384 chunk steps)
+    gcr = orc.chunk_local_cumsum(g[:, :, sl].cpu(), None)
+    ref = orc.gdr_bwd(cpu(q[:, :, sl]), cpu(k[:, :, sl]), cpu(v[:, :, sl]), gcr, beta[:, :, sl].cpu(), cpu(do[:, :, sl]),
+                      dht[:, sl].cpu(), scale, h0[:, sl].cpu(), None)
+    mine = [got[0][:, :, sl], got[1][:, :, sl], got[2][:, :, sl], got[3][:, :, sl], got[4][:, :, sl], got[5][:, sl]]
+    check_close(mine, ref, TOL_BF16, names, "head vs oracle: ")
+    del ref
+    del got2, gots, do2, dos
+    # (4) backward: two half passes chained through the state (forward) and its gradient (backward)
+    Th = T // 2
+    first = lambda x: x[:, :Th].contiguous()
+    second = lambda x: x[:, Th:].contiguous()
+    gc1, A1, _, _, s1 = ops.chunk_gated_delta_rule_fwd(first(q), first(k), first(v), first(g), first(beta), scale, h0, None,
+                                                       True, False, True)
+    gc2, A2, _, _, _ = ops.chunk_gated_delta_rule_fwd(second(q), second(k), second(v), second(g), second(beta), scale, s1, None,
+                                                      True, False, True)
+    b2 = ops.chunk_gated_delta_rule_bwd(second(q), second(k), second(v), gc2, second(beta), A2, second(do), dht, scale, s1, None)
+    b1 = ops.chunk_gated_delta_rule_bwd(first(q), first(k), first(v), gc1, first(beta), A1, first(do), b2[5], scale, h0, None)
+    chained = [torch.cat([x1, x2], 1) for x1, x2 in zip(b1[:5], b2[:5])] + [b1[5]]
+    check_close(chained, got, TOL_BF16, names, "two half passes: ")

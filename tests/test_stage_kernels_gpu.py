@@ -65,3 +65,28 @@ def test_kkt_solve(B, T, Hq, Hv, cu):
     # bf16 output: half an ulp of the largest entry (1.0 on the diagonal) is 2^-9
     assert (A - A_ref).abs().max().item() < 6e-3
     assert orc.rel_to_max(A, A_ref) < 6e-3
+
+
+def test_bounded_wait_expires_and_the_context_survives():
+    """A wait that nothing satisfies gives up after its limit, reports (kernel id << 12) + site through the status
+    word, releases the other waits of the CTA, frees the tensor memory and lets the kernel end; the next ordinary
+    call on the device works.  The limit is passed in (1e6 cycles, about half a millisecond): nothing traps, faults
+    or spins without a bound."""
+    from flashqla_b200 import _lib, kernels
+    lib = _lib.load()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    done = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = lib.fq_selftest_wait_expiry(status.data_ptr(), done.data_ptr(), 1_000_000, kernels._stream())
+    _lib.check(rc, "fq_selftest_wait_expiry")
+    torch.cuda.synchronize()
+    assert int(done.item()) == 1
+    assert int(status.item()) == (14 << 12) + 5
+    # limits outside the accepted range are refused on the host
+    assert lib.fq_selftest_wait_expiry(status.data_ptr(), done.data_ptr(), 0, kernels._stream()) == -1
+    assert lib.fq_selftest_wait_expiry(status.data_ptr(), done.data_ptr(), 10 ** 10, kernels._stream()) == -1
+    # the device is fine afterwards: a tensor-core self-test (fresh tensor-memory allocation) passes
+    a = torch.randn(128, 128, device="cuda").bfloat16()
+    b = torch.randn(128, 128, device="cuda").bfloat16()
+    d = kernels.selftest_umma(a, b, 0)
+    ref = a.float() @ b.float().t()
+    assert (d - ref).abs().max().item() < 1e-2 * ref.abs().max().item()

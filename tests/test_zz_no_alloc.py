@@ -4,8 +4,9 @@ fq_gdr_bwd_chunk_gva_noalloc serves callers that may not allocate device memory 
 runs (a pre-planned step with a frozen allocator, or a host that would otherwise pay a
 device-synchronising cudaMalloc per call): it keeps the per-V-head dq / dk partial results in an
 array inside the library instead of in two caller-allocated buffers.  The test drives both entry
-points through the C ABI on the same inputs and compares dq, dk, dv, dg and dbeta, twice in a row
-(the second call reuses the array with the first call's contents still in it).
+points through the C ABI on the same inputs, twice in a row (the second call reuses the array with the
+first call's contents still in it): dq, dk and dv must agree bitwise, dg and dbeta to 1e-5 of their maximum (they
+are summed with shared-memory atomics, whose order is not fixed).
 
 This file is named so that pytest collects it last.
 """
@@ -16,7 +17,7 @@ from oracle import gdr_oracle as orc
 
 pytestmark = pytest.mark.gpu
 
-TOL = 1e-2  # same rel-to-max bound as the other backward tests
+TOL = 1e-5  # dg and dbeta only (sums by shared-memory atomics); dq, dk and dv are compared bitwise
 
 
 def _inputs(seed, B, T, Hq, Hv, cu):
@@ -34,7 +35,10 @@ def _inputs(seed, B, T, Hq, Hv, cu):
     return q, k, v, g, beta, do, h0, dht
 
 
-@pytest.mark.parametrize("B,T,Hq,Hv,cu", [(2, 200, 2, 4, None), (1, 500, 1, 4, [0, 130, 131, 500])])
+# the third case sits exactly on the size limit B*T*H = 65536; the fourth follows it with a small packed batch, so the
+# array then still holds the big case's rows
+@pytest.mark.parametrize("B,T,Hq,Hv,cu", [(2, 200, 2, 4, None), (1, 500, 1, 4, [0, 130, 131, 500]), (1, 8192, 2, 8, None),
+                                          (1, 300, 2, 4, [0, 7, 71, 300])])
 def test_noalloc_matches_regular_entry_point(B, T, Hq, Hv, cu):
     from flashqla_b200 import _lib, kernels, ops
     lib = _lib.load()
@@ -79,10 +83,14 @@ def test_noalloc_matches_regular_entry_point(B, T, Hq, Hv, cu):
         dv = torch.full_like(v, float("nan"))
         _lib.check(lib.fq_gdr_bwd_chunk_gva_noalloc(*common_args(dq, dk, dv, dg, db)), "fq_gdr_bwd_chunk_gva_noalloc")
         torch.cuda.synchronize()
-        for name, got, ref in (("dq", dq, dq_ref), ("dk", dk, dk_ref), ("dv", dv, dv_ref), ("dg", dg, dg_ref),
-                               ("db", db, db_ref)):
+        # the same kernel computes dq, dk and dv in the same order on both paths: every bit must agree
+        for name, got, ref in (("dq", dq, dq_ref), ("dk", dk, dk_ref), ("dv", dv, dv_ref)):
             assert torch.isfinite(got.float()).all(), f"{name} (call {call})"
-            assert orc.rel_to_max(got.float().cpu(), ref.float().cpu()) < TOL, f"{name} (call {call})"
+            assert torch.equal(got, ref), f"{name} (call {call}): not bitwise equal to the regular entry point"
+        for name, got, ref in (("dg", dg, dg_ref), ("db", db, db_ref)):
+            assert torch.isfinite(got).all(), f"{name} (call {call})"
+            err = orc.rel_to_max(got.cpu(), ref.cpu())
+            assert err < TOL, f"{name} (call {call}): rel-to-max {err:.2e}, max-abs {(got - ref).abs().max().item():.3e}"
 
 
 def test_noalloc_rejects_oversized_problem():
