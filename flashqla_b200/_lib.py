@@ -30,6 +30,7 @@ SIGNATURES = {
     "fq_cp_transition_plan": [_vp] * 7 + [_i32] * 2 + [_vp],
     "fq_cp_plan": [_vp] * 12 + [_i32] * 3 + [_f32, _i32, _vp],
     "fq_cp_chain": [_vp] * 4 + [_i32] * 3 + [_vp],
+    "fq_cp_chain_ex": [_vp] * 6 + [_i32] * 4 + [_vp],
     "fq_gdr_bwd_dh_cp_ex": [_vp] * 15 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "fq_cp_transition_plan_reverse": [_vp] * 7 + [_i32] * 2 + [_vp],
     "fq_cp_chain_reverse": [_vp] * 5 + [_i32] * 3 + [_vp],

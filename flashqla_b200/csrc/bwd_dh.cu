@@ -99,7 +99,9 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const int warm = warm_code & 0xFFFFFF;
   const bool use_dht = (warm_code >> 30) & 1, use_piece_dht = (warm_code >> 29) & 1;
   if ((warm_code >> 27) & 1) return;  // nothing to do: leave before any barrier or tensor memory is set up
-  const int total = nchunks > 0 ? nchunks + warm : 0;  // iteration `it` handles chunk n = total - 1 - it of the piece
+  // iteration `it` handles chunk n = total - 1 - it of the piece.  An EMPTY piece with a replay (warm > 0) only walks
+  // the chunks behind it: its dh0 slot receives the state gradient at that point of the sequence.
+  const int total = (nchunks > 0 || warm > 0) ? nchunks + warm : 0;
   // tokens available from the piece start to the end of its sequence (bounds the length of replayed chunks)
   const int avail = p.seq_end ? __ldg(p.seq_end + seq) - tok_begin : seq_len;
   WaitCtx wc{&s.abort_flag, p.status_dev, 2, kWaitLimitCycles};

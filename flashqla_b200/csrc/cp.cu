@@ -193,7 +193,8 @@ constexpr int kChainLd = kChainCols + 8;  // row stride of the state slice: conf
 template <bool kReverse>
 __global__ void __launch_bounds__(256) cp_chain_kernel(const float* __restrict__ add, const float* __restrict__ tmat,
                                                       float* __restrict__ out, const int* __restrict__ flags,
-                                                      const int* __restrict__ seq_piece_offsets, int H) {
+                                                      const int* __restrict__ seq_piece_offsets, int H, int compose,
+                                                      const float* __restrict__ init) {
   __shared__ float sx[kDim * kChainLd];
   const int seq = blockIdx.x / H, h = blockIdx.x - seq * H, c0 = blockIdx.y * kChainCols;
   if (__ldg(flags + seq * H + h) == 0) return;
@@ -202,15 +203,30 @@ __global__ void __launch_bounds__(256) cp_chain_kernel(const float* __restrict__
   const int m0 = warp * 16;
   const size_t mat = static_cast<size_t>(kDim) * kDim;
   const int steps = p1 - p0 - 1;
+  if (init != nullptr) {
+    // the chain starts from a given state (gradient) of this head instead of from B (C) of its first piece: every
+    // step, the first included, applies its transition matrix
+    const float* src = init + static_cast<size_t>(h) * mat;
+    for (int i = threadIdx.x; i < kDim * kChainCols; i += 256) {
+      const int row = i / kChainCols, col = i - row * kChainCols;
+      sx[row * kChainLd + col] = __ldg(src + static_cast<size_t>(row) * kDim + c0 + col);
+    }
+    __syncthreads();
+  }
   for (int st = 0; st < steps; ++st) {
     const int r = kReverse ? p1 - 1 - st : p0 + st;  // piece whose (T, add) pair this step applies
-    // accumulators start from B_r (C_r): rows m0+g and m0+g+8, column pairs c0 + 8 n + 2 t
-    const float* B = add + (static_cast<size_t>(r) * H + h) * mat;
+    // accumulators start from B_r (C_r): rows m0+g and m0+g+8, column pairs c0 + 8 n + 2 t.  compose: the chain of
+    // the transition matrices alone, X_1 = T_first, X_{r+1} = T_r X_r (the first step starts from T, later ones from 0)
+    const float* B = (compose ? tmat : add) + (static_cast<size_t>(r) * H + h) * mat;
+    const bool have_b = !compose || st == 0;
     float acc[kChainCols / 8][4];
 #pragma unroll
     for (int n = 0; n < kChainCols / 8; ++n) {
-      const float2 lo = __ldg(reinterpret_cast<const float2*>(B + static_cast<size_t>(m0 + g) * kDim + c0 + 8 * n + 2 * t));
-      const float2 hi = __ldg(reinterpret_cast<const float2*>(B + static_cast<size_t>(m0 + g + 8) * kDim + c0 + 8 * n + 2 * t));
+      float2 lo = make_float2(0.f, 0.f), hi = lo;
+      if (have_b) {
+        lo = __ldg(reinterpret_cast<const float2*>(B + static_cast<size_t>(m0 + g) * kDim + c0 + 8 * n + 2 * t));
+        hi = __ldg(reinterpret_cast<const float2*>(B + static_cast<size_t>(m0 + g + 8) * kDim + c0 + 8 * n + 2 * t));
+      }
       acc[n][0] = lo.x; acc[n][1] = lo.y; acc[n][2] = hi.x; acc[n][3] = hi.y;
     }
     float acc1[kChainCols / 8][4], acc2[kChainCols / 8][4];
@@ -218,7 +234,7 @@ __global__ void __launch_bounds__(256) cp_chain_kernel(const float* __restrict__
     for (int n = 0; n < kChainCols / 8; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc1[n][e] = acc2[n][e] = 0.f;
-    if (st > 0) {
+    if (st > 0 || init != nullptr) {
       const float* Tm = tmat + (static_cast<size_t>(r) * H + h) * mat;
       float ta[16][4];  // the A fragments of all sixteen k-steps: one round trip to L2 per step of the chain
 #pragma unroll
@@ -312,7 +328,7 @@ extern "C" FQ_API int fq_cp_chain(const float* bt, float* h0_piece, const int32_
   FQ_CHECK_ARG(n_pieces > 0 && n_seq > 0 && H > 0, "fq_cp_chain: bad arguments");
   dim3 grid(static_cast<unsigned>(n_seq) * H, kDim / kChainCols);
   const float* tmat = bt + static_cast<size_t>(n_pieces) * H * kDim * kDim;
-  cp_chain_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(bt, tmat, h0_piece, flags, seq_piece_offsets, H);
+  cp_chain_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(bt, tmat, h0_piece, flags, seq_piece_offsets, H, 0, nullptr);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }
@@ -339,7 +355,7 @@ extern "C" FQ_API int fq_cp_chain_reverse(const float* c, const float* tmat, flo
   FQ_CHECK_ARG(c && tmat && dht_piece && flags && seq_piece_offsets, "fq_cp_chain_reverse: null tensor");
   FQ_CHECK_ARG(n_pieces > 0 && n_seq > 0 && H > 0, "fq_cp_chain_reverse: bad arguments");
   dim3 grid(static_cast<unsigned>(n_seq) * H, kDim / kChainCols);
-  cp_chain_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(c, tmat, dht_piece, flags, seq_piece_offsets, H);
+  cp_chain_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(c, tmat, dht_piece, flags, seq_piece_offsets, H, 0, nullptr);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }
@@ -358,6 +374,22 @@ extern "C" FQ_API int fq_cp_plan(const float* g_cumsum, const int32_t* piece_sta
   cp_plan_kernel<<<static_cast<unsigned>(n_seq) * H, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       g_cumsum, piece_start, piece_end, chunks_before, chunks_after, last_chunk_len, seq_piece_offsets, flags, codes,
       pass1_codes, codes_rev, pass1_rev, n_pieces, H, threshold, w_cap);
+  FQ_CHECK_CUDA(cudaGetLastError());
+  return FQ_OK;
+}
+
+extern "C" FQ_API int fq_cp_chain_ex(const float* add, const float* tmat, float* out, const int32_t* flags,
+                                     const int32_t* seq_piece_offsets, const float* init, int n_seq, int H, int reverse,
+                                     int compose, void* stream) {
+  using namespace fq;
+  FQ_CHECK_ARG(tmat && out && flags && seq_piece_offsets, "fq_cp_chain_ex: null tensor");
+  FQ_CHECK_ARG(add != nullptr || compose, "fq_cp_chain_ex: the additive terms are missing");
+  FQ_CHECK_ARG(!(compose && (reverse || init)), "fq_cp_chain_ex: compose goes with neither reverse nor init");
+  FQ_CHECK_ARG(n_seq > 0 && H > 0, "fq_cp_chain_ex: bad arguments");
+  dim3 grid(static_cast<unsigned>(n_seq) * H, kDim / kChainCols);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (reverse) cp_chain_kernel<true><<<grid, 256, 0, st>>>(add, tmat, out, flags, seq_piece_offsets, H, 0, init);
+  else cp_chain_kernel<false><<<grid, 256, 0, st>>>(add, tmat, out, flags, seq_piece_offsets, H, compose, init);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
 }

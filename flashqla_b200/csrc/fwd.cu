@@ -120,7 +120,9 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   const int warm = warm_code & 0xFFFFFF;
   const bool use_h0 = (warm_code >> 30) & 1, use_piece_h0 = (warm_code >> 29) & 1, transition = (warm_code >> 28) & 1,
              skip = (warm_code >> 27) & 1;
-  const int total = (nchunks > 0 && !skip) ? warm + nchunks : 0;  // iterations; iteration `it` handles chunk n = it - warm
+  // iterations; iteration `it` handles chunk n = it - warm.  An EMPTY piece with a replay (warm > 0) is a state-only
+  // run over the chunks in front of it: its final state is the state at that point of the sequence.
+  const int total = ((nchunks > 0 || warm > 0) && !skip) ? warm + nchunks : 0;
   if (skip) return;  // nothing to do for this (entry, head): leave before any barrier or tensor memory is set up
   WaitCtx wc{&s.abort_flag, p.status_dev, 1, kWaitLimitCycles};
 

@@ -119,7 +119,9 @@ FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, const void* A
  *   h0_index[i]  slot of h0 to start from when the replay reaches the sequence start (NULL = i);
  *   ht_index[i]  slot of ht to write, negative for non-terminal pieces (NULL = i);
  *   warmup[i*H+h] = w | (1<<30 if the replay starts at the sequence start): the CTA first replays the
- *                 w whole chunks before the piece (nothing stored) from h0 (bit 30) or from zero.
+ *                 w whole chunks before the piece (nothing stored) from h0 (bit 30) or from zero.  A piece may be
+ *                 EMPTY (two equal boundaries): with w > 0 it is a state-only run over the w chunks in front of it and
+ *                 its ht slot receives the state at that point of the sequence.
  * Replaces intra_card_cp_preprocess + correct_initial_states,
  * flash_qla/ops/gated_delta_rule/chunk/cp_context.py:106-163 and chunk/hopper/cp_fwd.py:256-309:
  * instead of computing per-piece end states in a separate pass and chaining them, every piece
@@ -181,6 +183,25 @@ FQ_API int fq_cp_plan(const float* g_cumsum, const int32_t* piece_start, const i
  */
 FQ_API int fq_cp_chain(const float* bt, float* h0_piece, const int32_t* flags, const int32_t* seq_piece_offsets,
                        int n_pieces, int n_seq, int H, void* stream);
+
+/*
+ * The chain kernel behind fq_cp_chain / fq_cp_chain_reverse with its two further modes; `add` and `tmat` are given
+ * separately ([n_pieces,H,128,128] fp32 each, indexed by piece), `out` has one slot per piece:
+ *   reverse == 0: out[r+1] = T_r out[r] + add[r] for the pieces r of every flagged (sequence, head); the first step
+ *                 takes add alone (the first piece's end state already contains the sequence's initial state);
+ *   reverse != 0: out[r-1] = T_r^T out[r] + add[r] from the last piece down; the first step takes add alone;
+ *   init    (optional, [H,128,128] fp32): the chain starts from this state (gradient) instead, and every step, the
+ *                 first included, applies its transition matrix;
+ *   compose != 0 (forward only, add unused): the product of the transition matrices alone, out[first+1] = T_first,
+ *                 out[r+1] = T_r out[r] - the K x K transition of a whole run of pieces.
+ * seq_piece_offsets may name one piece more than exists (offsets [0, P+1] over P pieces): the forward chain then also
+ * delivers the state after the last piece in out[P].  This is how one GPU's share of a sequence is summarised as
+ * (end state from zero, transition matrix) for the exchange between GPUs; the reference chains the same pair between
+ * the pieces of one card (flash_qla/ops/gated_delta_rule/chunk/hopper/cp_fwd.py:144-165).
+ */
+FQ_API int fq_cp_chain_ex(const float* add, const float* tmat, float* out, const int32_t* flags,
+                          const int32_t* seq_piece_offsets, const float* init, int n_seq, int H, int reverse, int compose,
+                          void* stream);
 
 /*
  * Gate scan for context-parallel pieces (counterpart of get_warmup_chunks,
