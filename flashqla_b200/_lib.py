@@ -59,7 +59,7 @@ def load():
     """Return the loaded library, loading it on first use."""
     global _lib
     if _lib is not None:
-        return _lib
+        return _lib if _recorder is None else _RecordingLib(_lib, _recorder)
     with _lock:
         if _lib is None:
             if not os.path.exists(LIB_PATH):
@@ -72,7 +72,71 @@ def load():
                 fn.argtypes = argtypes
                 fn.restype = _RESTYPES.get(name, _i32)
             _lib = lib
-    return _lib
+    return _lib if _recorder is None else _RecordingLib(_lib, _recorder)
+
+
+class LaunchRecorder:
+    """Optional per-launch timing for benchmarks and profiling: while a recorder is active (``with
+    _lib.record_launches() as rec:``), every C-ABI call is bracketed by two CUDA events on the current stream.
+    ``rec.summary()`` (after a synchronise) gives {entry point: (calls, total ms)}; calls of one entry point within a
+    step are numbered (``fq_gdr_fwd_cp_ex#0`` is the state pass, ``#1`` the final pass).  Costs two event records per
+    launch; off by default."""
+
+    def __init__(self):
+        self.events = []      # (name, start, stop)
+        self._step_counts = {}
+
+    def new_step(self):
+        self._step_counts = {}
+
+    def wrap(self, name, fn):
+        import torch
+
+        def call(*args):
+            i = self._step_counts.get(name, 0)
+            self._step_counts[name] = i + 1
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            rc = fn(*args)
+            e1.record()
+            self.events.append((f"{name}#{i}" if i or name in _MULTI else name, e0, e1))
+            return rc
+        return call
+
+    def summary(self):
+        out = {}
+        for name, e0, e1 in self.events:
+            n, ms = out.get(name, (0, 0.0))
+            out[name] = (n + 1, ms + e0.elapsed_time(e1))
+        return out
+
+
+_MULTI = {"fq_gdr_fwd_cp_ex", "fq_gdr_bwd_dh_cp_ex", "fq_gdr_fwd", "fq_gdr_fwd_cp"}
+_NOT_LAUNCHES = {"fq_version", "fq_last_error"}
+_recorder = None
+
+
+class _RecordingLib:
+    def __init__(self, lib, rec):
+        self._lib, self._rec = lib, rec
+
+    def __getattr__(self, name):
+        fn = getattr(self._lib, name)
+        if name in _NOT_LAUNCHES:
+            return fn
+        return self._rec.wrap(name, fn)
+
+
+class record_launches:
+    def __enter__(self):
+        global _recorder
+        _recorder = LaunchRecorder()
+        return _recorder
+
+    def __exit__(self, *exc):
+        global _recorder
+        _recorder = None
+        return False
 
 
 def check(rc: int, what: str) -> None:
