@@ -219,6 +219,9 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     // tiles are written again in this unit's second round, after the syncs below
     if (tid == kStoreTid) tma_store_wait_read<0>();
     __syncthreads();  // the previous unit's shared-memory reads are complete
+    // after an expiry no further unit is started (every thread reads the flag here, after the barrier and before any
+    // wait of this unit, so all of them see the same value)
+    if (s.abort_flag) break;
 
     if (tid == 0 && iter == 0) load_b(chunk, h, 2, b_kt, b_qt, b_at, b_pg);  // later units: requested a unit ahead
     if (tid < kChunk) {

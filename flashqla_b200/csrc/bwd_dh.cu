@@ -135,6 +135,8 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       for (int it = 0; it < total; ++it) {
         const int n = total - 1 - it, st = it & 1;
         if (it >= 2) mbar_wait(wc, &s.empty[st], ((it >> 1) + 1) & 1, 1);
+        // after an expiry the other roles run through without waiting; no further tiles are requested then
+        if (s.abort_flag) break;
         mbar_arrive_expect_tx(&s.full[st], kDhStageBytes);
         const int row = tok_begin + n * kChunk;
         tma_load_3d(s.kq[st], &map_k, &s.full[st], 0, hg, row);

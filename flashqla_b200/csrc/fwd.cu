@@ -1,22 +1,27 @@
 // Fused GDN forward: inter-chunk state recurrence + chunk outputs, one persistent CTA per
-// (sequence piece, V-head).  The chunk-parallel operand tiles A_g = A o G o beta_col and
-// P_g = scale * G o (Q K^T) come from the pre-kernel (kkt_solve.cu); this kernel carries only what is
-// serial.  The state is kept TRANSPOSED in tensor memory (S^T: lane = v, column = k), so the
-// products on the critical chain have M = 128:
+// (sequence piece, V-head).  The chunk-parallel operand tile A_g = A o G o beta_col comes from the
+// pre-kernel (kkt_solve.cu); this kernel carries what is serial and forms the second gated tile
+// P_g = scale * G o (Q K^T) itself: the tensor core has the room, the tile never touches HBM unless a backward asks for
+// it, and the pre-kernel neither reads q nor pays for the tile.  The state is kept TRANSPOSED in tensor memory
+// (S^T: lane = v, column = k), so the products on the critical chain have M = 128:
 //
 //   U    [128 x 64]  = S^T_bf16 K^T
 //   VD   [128 x 64]  = V^T A_g^T - (gamma o U)^T A_g^T = V_d^T     (the V term is state independent:
 //                                                                  its A operand is the V tile as loaded)
 //   S   += V'^T K                                                  V' = rho o V_d; S pre-scaled by gamma_last
 //   OI   [64 x 128]  = Q S,   OX [64 x 128] = P_g V_d              natural orientation (row = token)
+//   QK   [128 x 64]  = [K; Q] K^T of the NEXT chunk                rows 64-127 = Q K^T -> P_g.  It is parked in the
+//                                                                  columns of U between this chunk's V_d products and
+//                                                                  the next chunk's U
 //
 // Per chunk:  o = scale*gamma o OI + OX,   S <- gamma_last S + K^T V'.
 // W^T = -(gamma o U)^T and V'^T are handed to the tensor core as A operands in TENSOR memory (bf16 pairs written over
 // the accumulators they come from); the bf16 state and V_d^T stay in shared memory (they are B operands, and the
 // state leaves by TMA).  The issuing warp runs its loop with all lanes and issues through one elected lane.
 // Warp roles (16 warps): 0 TMA producer, 1 UMMA issuer, 2-3 gate loader, 4-11 chain group
-// (TMEM state -> bf16 operand + decay, then -gamma o U, then V_d / V'), 12-15 output tile
-// (row-contiguous stores straight from the accumulators).
+// (TMEM state -> bf16 operand + decay, then -gamma o U, then V_d / V'), 12-15 output group: warps 14-15 (the two that
+// can read TMEM lanes 64-127) turn Q K^T of the chunk ahead into its P_g tile, then all four lay the finished chunk's o
+// rows down in a staging tile that leaves by TMA.
 //
 // Context parallel: a CTA may own a piece of a sequence.  It then first replays `w` whole chunks
 // that precede the piece (state only, nothing stored) starting from a zero state - or from the
@@ -34,11 +39,11 @@ namespace fq {
 
 constexpr int kFwdThreads = 512;
 constexpr int kGateStages = 4;
-constexpr uint32_t kStageBytes = 32768 + 16384 + 8192 + 8192;
+constexpr uint32_t kStageBytes = 32768 + 16384 + 8192;  // k | q, v, A_g
 
 // TMEM column map (512 columns allocated)
 constexpr uint32_t kColS = 0;     // fp32 state S^T, 128 columns
-constexpr uint32_t kColUQ = 128;  // U^T, 64 columns
+constexpr uint32_t kColUQ = 128;  // U^T, 64 columns; between two chunks' use: [K; Q] K^T of the chunk ahead
 constexpr uint32_t kColVD = 192;  // V_d^T, 64 columns
 constexpr uint32_t kColOI = 256;  // Q S      [64 x 128] (M = 64: rows in lanes 0-15 of every 32-lane quarter)
 constexpr uint32_t kColOX = 384;  // P_g V_d  [64 x 128]
@@ -47,13 +52,14 @@ struct FwdSmem {
   unsigned char kq[2][32768];  // per stage, two 128-row x 128-byte regions (d 0-63 | d 64-127); rows 0-63 k, 64-127 q
   unsigned char v[2][16384];   // per stage, two 64-row x 128-byte regions (v 0-63 | v 64-127)
   unsigned char a[2][8192];    // per stage, A_g tile [64 i][64 j]
-  unsigned char pg[2][8192];   // per stage, P_g tile [64 i][64 j]
+  unsigned char pg[2][8192];   // P_g tile [64 i][64 j] of chunk c in buffer c & 1, written by the output warps
   unsigned char sbf[32768];    // bf16 S^T [128 v][128 k] as two 128-row regions
   unsigned char vd[16384];     // V_d^T             [128 v][64 i]
   unsigned char ostage[16384]; // o tile of a whole chunk [64 c][128 v] as two 64-row regions (v 0-63 | 64-127): TMA store
   float gate[kGateStages][4][kChunk];  // g, exp(g), exp(g_last - g), beta
   uint64_t full[2], empty[2], gate_full[kGateStages], gate_empty[kGateStages];
-  uint64_t uq_done, vd_done, s_done, o_done;
+  uint64_t uq_done, vd_done, s_done, o_done, qk_done;
+  uint64_t pq_ready;
   uint64_t s_ready, s_scaled, w_ready, vp_ready, o_free;
   uint64_t drain_bar;  // only used by drain_after_abort
   uint32_t tmem_base;
@@ -75,6 +81,7 @@ struct FwdParams {
   const int* piece_map; // [n_entries] piece of each grid entry, or nullptr (= entry); warmup and ht_index are per entry
   const float* h0_piece;  // [n_pieces, H, 128, 128] corrected start states (bit 29) or nullptr
   __nv_bfloat16* o;     // [rows, H, 128] or nullptr
+  __nv_bfloat16* pg_out;  // [rows, H, 64] or nullptr: the P_g tiles, kept for the backward (only written together with o)
   __nv_bfloat16* h_out; // [total_chunks, H, 128(v), 128(k)] TRANSPOSED state before each chunk, or nullptr
                         // (written by TMA straight from the bf16 operand buffer)
   int H, Hg;
@@ -131,6 +138,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     for (int i = 0; i < 2; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
     for (int i = 0; i < kGateStages; ++i) { mbar_init(&s.gate_full[i], 64); mbar_init(&s.gate_empty[i], 12); }
     mbar_init(&s.uq_done, 1); mbar_init(&s.vd_done, 1); mbar_init(&s.s_done, 1); mbar_init(&s.o_done, 1);
+    mbar_init(&s.qk_done, 1); mbar_init(&s.pq_ready, 4);
     mbar_init(&s.s_ready, 8); mbar_init(&s.s_scaled, 8); mbar_init(&s.w_ready, 8); mbar_init(&s.vp_ready, 8);
     mbar_init(&s.o_free, 4);
     mbar_init(&s.drain_bar, 1);
@@ -153,6 +161,9 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       for (int it = 0; it < total; ++it) {
         const int st = it & 1;
         if (it >= 2) mbar_wait(wc, &s.empty[st], ((it >> 1) + 1) & 1, 1);
+        // after an expiry the other roles run through without waiting; no further tiles are requested then (this
+        // thread takes part in no barrier, and the byte counts of tiles that nobody waits for must not pile up)
+        if (s.abort_flag) break;
         mbar_arrive_expect_tx(&s.full[st], kStageBytes);
         const int row = tok_begin + (it - warm) * kChunk;
         tma_load_3d(s.kq[st], &map_k, &s.full[st], 0, hg, row);
@@ -162,7 +173,6 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tma_load_3d(s.v[st], &map_v, &s.full[st], 0, h, row);
         tma_load_3d(s.v[st] + 8192, &map_v, &s.full[st], 64, h, row);
         tma_load_3d(s.a[st], &map_a, &s.full[st], 0, h, row);
-        tma_load_3d(s.pg[st], &map_pg, &s.full[st], 0, h, row);
       }
     }
   } else if (warp == 1) {
@@ -182,6 +192,18 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const uint64_t d_kmn0 = umma_desc_sw128(smem_u32(s.kq[0]), 16384, 1024);
       const uint64_t d_a0 = umma_desc_sw128(smem_u32(s.a[0]), 16, 1024);
       const uint64_t d_pg0 = umma_desc_sw128(smem_u32(s.pg[0]), 16, 1024);
+      // [K; Q] K^T of chunk `c` (stage c & 1) into the U columns: A = the whole 128-row k | q tile, B = its first 64
+      // rows (k); rows 64-127 of the result are Q K^T.  Every barrier of this kernel completes exactly one phase per
+      // iteration, replayed chunks included (their arrivals are trivial), so the phase of iteration `it` is it & 1.
+      auto issue_qk = [&](int c) {
+        const uint64_t d = desc_add(d_kq0, (c & 1) * 32768);
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(tm + kColUQ, desc_add(d, kq_off(kk)), desc_add(d, kq_off(kk)), id64, kk > 0);
+        }
+        __syncwarp();
+      };
       for (int it = 0; it < total; ++it) {
         const int st = it & 1;
         const uint32_t ph = it & 1;
@@ -191,6 +213,17 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                        d_pg = desc_add(d_pg0, st * 8192);
         mbar_wait(wc, &s.full[st], (it >> 1) & 1, 2);
         tc_fence_after();
+        if (want_o) {
+          if (it == 0) {  // the first chunk has no earlier iteration to issue its Q K^T from
+            if (do_o) issue_qk(0);
+            if (elect_one()) umma_commit(&s.qk_done);
+            __syncwarp();
+          }
+          // the output group has read this chunk's Q K^T out of the U columns (normally long ago: it was issued behind
+          // the previous chunk's V_d products); waited for in replayed chunks too, which keeps that group within one
+          // phase of this warp
+          mbar_wait(wc, &s.pq_ready, ph, 22);
+        }
         mbar_wait_spin(wc, &s.s_ready, ph, 3);
         tc_fence_after();
         if (elect_one()) {
@@ -214,10 +247,10 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             umma_ss(tm + kColVD, desc_add(d_vmn, kk * 2048), desc_add(d_a, kk * 32), id64_amn, kk > 0);
         }
         __syncwarp();
-        if (do_o) {  // OI = Q S: the accumulators of the previous chunk must have been drained
+        if (want_o) {  // OI = Q S: the accumulators of the previous chunk must have been drained
           if (it > 0) mbar_wait(wc, &s.o_free, (it - 1) & 1, 4);
           tc_fence_after();
-          if (elect_one()) {
+          if (do_o && elect_one()) {
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk)
               umma_ss(tm + kColOI, desc_add(d_kq, 8192 + kq_off(kk)), desc_add(d_sbf, kq_off(kk)), id_o, kk > 0);
@@ -233,6 +266,17 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           umma_commit(&s.vd_done);
         }
         __syncwarp();
+        if (want_o && it + 1 < total) {
+          // the U columns are dead from here until the next chunk's U: [K; Q] K^T of the next chunk goes there (its
+          // tiles are in the other stage); it runs while the chain group forms V'
+          if (it + 1 >= warm) {
+            mbar_wait(wc, &s.full[st ^ 1], ((it + 1) >> 1) & 1, 24);
+            tc_fence_after();
+            issue_qk(it + 1);
+          }
+          if (elect_one()) umma_commit(&s.qk_done);
+          __syncwarp();
+        }
         mbar_wait_spin(wc, &s.vp_ready, ph, 7);
         mbar_wait_spin(wc, &s.s_scaled, ph, 9);
         tc_fence_after();
@@ -435,13 +479,75 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------------ output tile
-    // o[c][:] = scale * gamma_c * OI[c][:] + OX[c][:]; thread (lane < 16) owns token row c = 16 * quarter + lane
-    const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32;
-    const int c = 16 * (warp & 3) + (lane & 15);
+    // ------------------------------------------------------------------ output group (4 warps)
+    // o[c][:] = scale * gamma_c * OI[c][:] + OX[c][:]; thread (lane < 16) owns token row c = 16 * quarter + lane.
+    // Before the finished chunk is drained, warps 14-15 - the two that can read TMEM lanes 64-127 - turn Q K^T of the
+    // chunk AHEAD (parked in the U columns) into its P_g tile: P_g[r][j] = scale * exp(g_r - g_j) * (q_r . k_j), j <= r.
+    const int q4 = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(q4) * 32;
+    const int c = 16 * q4 + (lane & 15);
+    constexpr float kLog2e = 1.4426950408889634f;
+    const float log2_scale = log2f(p.scale);
+    auto ahead = [&](int ci) {
+      const int n = ci - warm, gs = ci & (kGateStages - 1);
+      mbar_wait(wc, &s.gate_full[gs], (ci >> 2) & 1, 19);
+      if (!kStateOnly) mbar_wait(wc, &s.qk_done, ci & 1, 20);
+      if (!kStateOnly && n >= 0 && q4 >= 2) {
+        tc_fence_after();
+        const int len = min(kChunk, seq_len - n * kChunk);
+        const int r = 32 * (q4 - 2) + lane;   // token row; TMEM lane 64 + r
+        const bool tile_store = p.pg_out != nullptr;
+        if (tile_store) {  // the TMA stores of the earlier tiles have read their buffers
+          if (tid == 448) tma_store_wait_read<0>();
+          asm volatile("bar.sync 4, 64;" ::: "memory");
+        }
+        const float gr = kLog2e * s.gate[gs][0][r] + log2_scale;
+        unsigned char* tile = s.pg[ci & 1];
+        __nv_bfloat16* grow = tile_store ? p.pg_out + (static_cast<size_t>(tok_begin + n * kChunk + r) * p.H + h) * kChunk
+                                         : nullptr;
+        const bool whole = len == kChunk;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t qk[32];
+          tmem_ld32(tmem_addr(tm, lane_base, kColUQ + 32 * half), qk);
+          tmem_wait_ld();
+#pragma unroll
+          for (int pc = 0; pc < 4; ++pc) {
+            const int j0 = 32 * half + 8 * pc;
+            uint4 x = make_uint4(0, 0, 0, 0);
+            if (j0 <= r) {
+              const float4 ga = *reinterpret_cast<const float4*>(&s.gate[gs][0][j0]);
+              const float4 gb = *reinterpret_cast<const float4*>(&s.gate[gs][0][j0 + 4]);
+              const float gj[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+              float y[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                y[e] = (j0 + e <= r) ? exp2f(gr - kLog2e * gj[e]) * __uint_as_float(qk[8 * pc + e]) : 0.f;
+              x = make_uint4(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]), pack_bf16(y[4], y[5]), pack_bf16(y[6], y[7]));
+            }
+            *reinterpret_cast<uint4*>(tile + sw128(r, (4 * half + pc) * 16)) = x;
+            // a tail chunk's tile must not reach past the sequence end: its valid rows go out one by one
+            if (tile_store && !whole && r < len) *(reinterpret_cast<uint4*>(grow) + 4 * half + pc) = x;
+          }
+        }
+        fence_async_smem();
+        if (tile_store) {
+          asm volatile("bar.sync 4, 64;" ::: "memory");  // both warps have written (and fenced) their rows
+          if (whole && tid == 448) {
+            tma_store_3d(&map_pg, tile, 0, h, tok_begin + n * kChunk);
+            tma_store_commit();
+          }
+        }
+        tc_fence_before();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.pq_ready);
+    };
+    if (total > 0) ahead(0);
     for (int it = 0; it < total; ++it) {
       const int n = it - warm, gs = it & (kGateStages - 1);
       const uint32_t ph = it & 1;
+      if (it + 1 < total) ahead(it + 1);
       mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 18);
       mbar_wait(wc, &s.o_done, ph, 21);
       tc_fence_after();
@@ -499,6 +605,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
     }
     if (!kStateOnly && tid == 384) tma_store_wait_all<0>();
+    if (!kStateOnly && tid == 448) tma_store_wait_all<0>();
   }
 
   tc_fence_before();
@@ -512,7 +619,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
 }  // namespace fq
 
-extern "C" FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, const void* Ag, const void* Pg,
+extern "C" FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, const void* Ag, void* Pg,
                                  const float* g_cumsum, const float* beta, const float* h0, float* ht,
                                  const int32_t* ht_index, void* o, void* h_out, int B, int T, int H, int Hg,
                                  const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq, int total_chunks,
@@ -521,7 +628,7 @@ extern "C" FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, co
                        cu_seqlens, chunk_offsets, n_seq, total_chunks, scale, status_dev, stream);
 }
 
-extern "C" FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v, const void* Ag, const void* Pg,
+extern "C" FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v, const void* Ag, void* Pg,
                                     const float* g_cumsum, const float* beta, const float* h0, float* ht,
                                     const int32_t* ht_index,
                                     const int32_t* h0_index, const int32_t* warmup, void* o, void* h_out, int B, int T,
@@ -531,7 +638,7 @@ extern "C" FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v,
                           h_out, B, T, H, Hg, cu_seqlens, chunk_offsets, n_seq, total_chunks, scale, status_dev, stream);
 }
 
-extern "C" FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void* v, const void* Ag, const void* Pg,
+extern "C" FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void* v, const void* Ag, void* Pg,
                                        const float* g_cumsum, const float* beta, const float* h0, float* ht,
                                        const int32_t* ht_index, const int32_t* h0_index, const int32_t* warmup,
                                        const int32_t* piece_map, int n_entries, const float* h0_piece, void* o,
@@ -544,7 +651,6 @@ extern "C" FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void*
   FQ_CHECK_ARG(piece_map == nullptr || (o == nullptr && h_out == nullptr),
                "fq_gdr_fwd: mapped entries are for state-only runs");
   FQ_CHECK_ARG(q && k && v && Ag && g_cumsum && beta, "fq_gdr_fwd: null input tensor");
-  FQ_CHECK_ARG(o == nullptr || Pg != nullptr, "fq_gdr_fwd: P_g is needed when o is requested");
   FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0, "fq_gdr_fwd: bad sizes");
   FQ_CHECK_ARG((cu_seqlens == nullptr) == (chunk_offsets == nullptr),
                "fq_gdr_fwd: cu_seqlens and chunk_offsets must be given together");
@@ -559,7 +665,7 @@ extern "C" FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void*
   if ((rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mv, v, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&ma, Ag, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
-  // in state-only mode (o == NULL) the P_g tile is loaded but never used; A_g stands in for a missing P_g
+  // the P_g tiles are an optional OUTPUT (kept for the backward); without it the map is never dereferenced
   if ((rc = make_tmap_rows_heads_dim(&mpg, Pg ? Pg : Ag, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
   {
     const uint64_t hrows = static_cast<uint64_t>(total_chunks) * H * kDim;
@@ -575,6 +681,7 @@ extern "C" FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void*
   p.g_cum = g_cumsum; p.beta = beta; p.h0 = h0; p.ht = ht; p.ht_index = ht_index; p.h0_index = h0_index;
   p.warmup = warmup; p.piece_map = piece_map; p.h0_piece = h0_piece;
   p.o = static_cast<__nv_bfloat16*>(o); p.h_out = static_cast<__nv_bfloat16*>(h_out);
+  p.pg_out = o ? static_cast<__nv_bfloat16*>(Pg) : nullptr;
   p.H = H; p.Hg = Hg; p.scale = scale;
   p.sa = SeqArgs{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
   p.status_dev = status_dev;

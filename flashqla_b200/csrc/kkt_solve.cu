@@ -500,7 +500,8 @@ extern "C" FQ_API int fq_kkt_solve_fused(const void* k, const void* q, const flo
                                          void* A, void* Ag, void* Pg, int B, int T, int H, int Hg,
                                          const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
                                          int total_chunks, float scale, void* stream) {
-  FQ_CHECK_ARG(g && g_cumsum && Ag && Pg, "fq_kkt_solve_fused: null tensor");
+  FQ_CHECK_ARG(g && g_cumsum && Ag, "fq_kkt_solve_fused: null tensor");
+  FQ_CHECK_ARG(Pg == nullptr || q != nullptr, "fq_kkt_solve_fused: P_g needs q");
   return kkt_launch(k, q, beta, g, g_cumsum, A, Ag, Pg, 0, B, T, H, Hg, cu_seqlens, chunk_offsets, n_seq, total_chunks,
                     scale, stream);
 }

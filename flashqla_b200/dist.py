@@ -142,7 +142,9 @@ class CudaImpl:
         from . import kernels
         plan = kernels.make_plan(1, k.shape[1], None, q.device)
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        g_cum, A, Ag, Pg = kernels.kkt_solve_fused(k, q, beta, g, scale, plan, want_A=want_grad)
+        g_cum, A, Ag, _ = kernels.kkt_solve_fused(k, q, beta, g, scale, plan, want_A=want_grad)
+        # the forward recurrence fills P_g (an input of the backward kernels)
+        Pg = torch.empty_like(Ag) if want_grad else None
         bf = beta.contiguous() if beta.dtype == torch.float32 else beta.float().contiguous()
         return dict(q=q, k=k, v=v, beta=bf, g_cum=g_cum, A=A, Ag=Ag, Pg=Pg, scale=float(scale), plan=plan,
                     H=v.shape[2], Hg=k.shape[2], Tl=k.shape[1])

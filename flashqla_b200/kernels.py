@@ -132,9 +132,10 @@ def kkt_solve_gated(k, q, b, g_cum, scale, plan: SeqPlan, A=None, want_pg=True):
     return A, Ag, Pg
 
 
-def kkt_solve_fused(k, q, b, g, scale, plan: SeqPlan, want_A=True):
-    """Chunk-local cumsum of the raw log gate `g`, A, A_g and P_g in one launch.  Returns (g_cumsum, A, A_g, P_g).
-    `want_A=False` (A is None then) skips the store of the gate-free inverse, which only the backward reads."""
+def kkt_solve_fused(k, q, b, g, scale, plan: SeqPlan, want_A=True, want_pg=False):
+    """Chunk-local cumsum of the raw log gate `g`, A and A_g in one launch.  Returns (g_cumsum, A, A_g, P_g).
+    `want_A=False` (A is None then) skips the store of the gate-free inverse, which only the backward reads.  P_g is
+    None unless `want_pg`: the forward recurrence forms that tile itself (and stores it for a backward)."""
     _require_cuda(k, q, b, g)
     if k.dtype != torch.bfloat16:
         raise _lib.FlashQLAError("kkt_solve_fused: only bfloat16 keys are supported")
@@ -148,12 +149,12 @@ def kkt_solve_fused(k, q, b, g, scale, plan: SeqPlan, want_A=True):
     g_cum = torch.empty_like(gf)
     alloc = _tile_alloc(plan, B, T)
     Ag = alloc(B, T, H, CHUNK, dtype=k.dtype, device=k.device)
-    Pg = alloc(B, T, H, CHUNK, dtype=k.dtype, device=k.device)
+    Pg = alloc(B, T, H, CHUNK, dtype=k.dtype, device=k.device) if want_pg else None
     A = alloc(B, T, H, CHUNK, dtype=k.dtype, device=k.device) if want_A else None
     cu_p, off_p = plan.ptrs()
     rc = _lib.load().fq_kkt_solve_fused(k.data_ptr(), q.data_ptr(), bf.data_ptr(), gf.data_ptr(), g_cum.data_ptr(),
-                                        None if A is None else A.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), B, T, H, Hg,
-                                        cu_p, off_p, plan.n_seq,
+                                        None if A is None else A.data_ptr(), Ag.data_ptr(),
+                                        None if Pg is None else Pg.data_ptr(), B, T, H, Hg, cu_p, off_p, plan.n_seq,
                                         plan.total_chunks, float(scale), _stream())
     _lib.check(rc, "fq_kkt_solve_fused")
     return g_cum, A, Ag, Pg
@@ -227,8 +228,10 @@ def cp_correct_states(q, k, v, ag, g, b, scale, h0, cp, warm: CpWarm, status=Non
 
 def fused_gdr_fwd(q, k, v, ag, pg, g, b, scale, initial_state=None, output_final_state=True, output_h=False,
                   output_o=True, plan: SeqPlan | None = None, cp=None, warmup=None, status=None, h0_piece=None):
-    """Fused forward recurrence.  g is the chunk-local cumsum, ag / pg the gated tiles from kkt_solve_gated.
-    With a CpPlan `cp` (and its `warmup` table) every piece of a sequence runs as its own CTA.
+    """Fused forward recurrence.  g is the chunk-local cumsum, ag the gated tile A_g from kkt_solve_fused / _gated.
+    `pg`: None, or a [B,T,H,64] bf16 tensor that RECEIVES the P_g tiles the kernel forms (kept for the backward;
+    only written when o is produced).  With a CpPlan `cp` (and its `warmup` table) every piece of a sequence runs as
+    its own CTA.
 
     Returns (o or None, hT or None, final_state or None).  hT holds the state before every chunk
     TRANSPOSED ([..., H, V, K]): the kernel stores it by TMA straight from its bf16 operand buffer and the

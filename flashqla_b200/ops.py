@@ -54,7 +54,7 @@ def l2norm(x: torch.Tensor, dim: int = -1, eps: float = 1e-6) -> torch.Tensor:
 
 
 def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None, cu_seqlens=None,
-                               output_final_state=True, output_h=False, auto_cp=True, _return_tiles=False, _plan=None,
+                               output_final_state=True, output_h=False, auto_cp=True, _return_tiles=None, _plan=None,
                                _want_A=True):
     """Forward pipeline (chunk/__init__.py:17-67): [cumsum + K K^T + solve + gated tiles] -> fused recurrence.
 
@@ -66,8 +66,10 @@ def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None,
     if scale is None:
         scale = K ** -0.5
     plan = _plan if _plan is not None else make_plan(B, T, cu_seqlens, q.device)
-    # the cumsum of g is formed in the same launch; A is only stored if a backward may follow
-    g_cum, A, Ag, Pg = kernels.kkt_solve_fused(k, q, beta, g, scale, plan, want_A=_want_A)
+    # the cumsum of g is formed in the same launch; A is only stored if a backward may follow.  The second gated tile
+    # P_g is formed inside the recurrence kernel, which also stores it when the caller keeps the tiles for a backward.
+    g_cum, A, Ag, _ = kernels.kkt_solve_fused(k, q, beta, g, scale, plan, want_A=_want_A)
+    Pg = kernels._tile_alloc(plan, B, T)(B, T, H, kernels.CHUNK, dtype=k.dtype, device=k.device) if _return_tiles else None
     status = kernels._status_tensor(q.device) if _DEBUG_STATUS else None
     cp = warm = None
     if auto_cp:
@@ -81,8 +83,8 @@ def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None,
         kernels.check_status(status, "fq_gdr_fwd")
     if h is not None:
         h = h.transpose(-1, -2)  # stored [.., V, K] by the kernel; the interface is [.., K, V]
-    if _return_tiles:
-        return g_cum, A, o, h, final_state, (Ag, Pg)
+    if _return_tiles is not None:
+        return g_cum, A, o, h, final_state, ((Ag, Pg) if _return_tiles else None)
     return g_cum, A, o, h, final_state
 
 
@@ -108,8 +110,8 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
         needs_bwd = any(ctx.needs_input_grad)
         g_cum, A, o, _, final_state, tiles = chunk_gated_delta_rule_fwd(
             q=q, k=k, v=v, g=g, beta=beta, scale=scale, initial_state=initial_state,
-            output_final_state=output_final_state, output_h=False, cu_seqlens=cu_seqlens, _return_tiles=True,
-            _plan=plan, _want_A=needs_bwd)
+            output_final_state=output_final_state, output_h=False, cu_seqlens=cu_seqlens,
+            _return_tiles=needs_bwd and not _RECOMPUTE_TILES, _plan=plan, _want_A=needs_bwd)
         if not needs_bwd:
             return o.to(q.dtype), final_state
         ctx.plan = plan  # the backward reuses the forward's sequence plan (no second look at cu_seqlens)

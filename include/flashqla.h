@@ -88,8 +88,9 @@ FQ_API int fq_kkt_solve_gated(const void* k, const void* q, const float* beta, c
  * fq_chunk_cumsum + fq_kkt_solve_gated in one launch: `g` is the RAW log gate [B,T,H] fp32, its chunk-local
  * inclusive sum is formed per (chunk, V-head) inside the kernel (a warp scan), used for the gated tiles and written
  * to g_cumsum [B,T,H] fp32.  Saves the separate pass of flash_qla/ops/utils/cumsum.py:131-165 over g.
- * A may be NULL: the recurrence kernels read only A_g and P_g, A is an input of the backward alone, so a forward that
- * will not be differentiated (prefill) need not write it.
+ * A may be NULL: the recurrence kernels do not read it, A is an input of the backward alone, so a forward that
+ * will not be differentiated (prefill) need not write it.  Pg (and with it q) may be NULL: fq_gdr_fwd forms the
+ * P_g tiles itself and can store them for the backward, which is cheaper than forming them here.
  */
 FQ_API int fq_kkt_solve_fused(const void* k, const void* q, const float* beta, const float* g, float* g_cumsum, void* A,
                               void* Ag, void* Pg, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
@@ -100,14 +101,17 @@ FQ_API int fq_kkt_solve_fused(const void* k, const void* q, const float* beta, c
  * and writes o = scale*exp(g) o (Q S) + P_g V_d per chunk.
  * Replaces fused_gdr_fwd, flash_qla/ops/gated_delta_rule/chunk/hopper/fused_fwd.py:535-658
  * (and, with o == NULL and h_out != NULL, the state-only fused_gdr_h of hopper/prepare_h.py:461-558).
- *   q,k [B,T,Hg,128] bf16; v [B,T,H,128] bf16; Ag, Pg [B,T,H,64] bf16 from fq_kkt_solve_gated
- *   (Pg may be NULL when o is NULL); g_cumsum, beta [B,T,H] fp32 (g_cumsum from fq_chunk_cumsum);
+ *   q,k [B,T,Hg,128] bf16; v [B,T,H,128] bf16; Ag [B,T,H,64] bf16 from fq_kkt_solve_gated / _fused;
+ *   Pg [B,T,H,64] bf16 or NULL: an OUTPUT - the kernel forms P_g = scale * G o (Q K^T) of every chunk on its tensor
+ *   core (the reference does the same inside its serial kernel, hopper/fused_fwd.py:300-350) and, if Pg is given
+ *   together with o, stores the tiles for fq_gdr_bwd_dh / fq_gdr_bwd_chunk (rows past a sequence end are not written);
+ *   g_cumsum, beta [B,T,H] fp32 (g_cumsum from fq_chunk_cumsum);
  *   h0   [n_seq,H,128,128] fp32 initial states, or NULL for zeros;
  *   ht   [*,H,128,128] fp32 final states, or NULL; sequence i writes slot ht_index[i]
  *        (negative = skip; ht_index == NULL means slot i);
  *   o    [B,T,H,128] bf16 or NULL;   h_out [total_chunks,H,128,128] bf16 (state BEFORE each chunk) or NULL.
  */
-FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, const void* Ag, const void* Pg,
+FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, const void* Ag, void* Pg,
                       const float* g_cumsum, const float* beta, const float* h0, float* ht, const int32_t* ht_index,
                       void* o, void* h_out, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
                       const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale, int32_t* status_dev,
@@ -127,7 +131,7 @@ FQ_API int fq_gdr_fwd(const void* q, const void* k, const void* v, const void* A
  * instead of computing per-piece end states in a separate pass and chaining them, every piece
  * warms its own state up inside the fused kernel.
  */
-FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v, const void* Ag, const void* Pg,
+FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v, const void* Ag, void* Pg,
                          const float* g_cumsum, const float* beta, const float* h0, float* ht, const int32_t* ht_index,
                          const int32_t* h0_index, const int32_t* warmup, void* o, void* h_out, int B, int T, int H,
                          int Hg, const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq, int total_chunks,
@@ -142,7 +146,7 @@ FQ_API int fq_gdr_fwd_cp(const void* q, const void* k, const void* v, const void
  * of the (ht, mt) correction of flash_qla/ops/gated_delta_rule/chunk/hopper/cp_fwd.py:256-309, used for heads
  * whose gate decays too slowly for a replay.
  */
-FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void* v, const void* Ag, const void* Pg,
+FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void* v, const void* Ag, void* Pg,
                             const float* g_cumsum, const float* beta, const float* h0, float* ht,
                             const int32_t* ht_index, const int32_t* h0_index, const int32_t* warmup,
                             const int32_t* piece_map, int n_entries, const float* h0_piece, void* o, void* h_out, int B,
