@@ -168,77 +168,19 @@ __device__ __forceinline__ void load_gates(float* sg, const float* __restrict__ 
   sg[tid + 32] = kLog2e * b;
 }
 
-// kSingle: every QK head has one V head (G == 1); the gates are then loaded with the tiles and P_g leaves before
-// the solve, so that the Q K^T fragments are dead while K K^T is formed and inverted.
-template <bool kSingle>
-__global__ void __launch_bounds__(128, 6) kkt_solve_kernel(const __nv_bfloat16* __restrict__ k,
-                                                       const float* __restrict__ beta,
-                                                       __nv_bfloat16* __restrict__ A, int H, int Hg, SeqArgs sa,
-                                                       const __nv_bfloat16* __restrict__ q,
-                                                       const float* __restrict__ g_cum,
-                                                       __nv_bfloat16* __restrict__ Ag, __nv_bfloat16* __restrict__ Pg,
-                                                       float scale, const __nv_bfloat16* __restrict__ A_in,
-                                                       float* __restrict__ g_cum_out) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  KktSmem& s = *reinterpret_cast<KktSmem*>(smem_raw);
+// The per-V-head part shared by both kernels: with K K^T (raw, lower block triangle) in s.kk, for each of the G V-heads of
+// the QK head - gates and beta into shared memory, the block inverse X in s.x (or A fetched when it is an input), then A
+// and / or A_g stored, and P_g from the Q K^T fragments `qk` when asked for.  kSingle: G == 1 and the caller has already
+// loaded beta and the gates.
+template <bool kSingle, class Smem>
+__device__ __forceinline__ void solve_heads(Smem& s, const ChunkPos& p, const float (&qk)[8][4], const float* __restrict__ beta,
+                                            __nv_bfloat16* __restrict__ A, int H, int Hg, int hg,
+                                            const float* __restrict__ g_cum, __nv_bfloat16* __restrict__ Ag,
+                                            __nv_bfloat16* __restrict__ Pg, float scale,
+                                            const __nv_bfloat16* __restrict__ A_in, float* __restrict__ g_cum_out) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int hg = blockIdx.y;
   const int G = H / Hg;
-  const ChunkPos p = chunk_lookup(sa, blockIdx.x);
-
-  // ---- K and Q tiles -> shared by asynchronous 16-byte copies (rows past the sequence end are zero-filled)
-  {
-    const __nv_bfloat16* src = k + (static_cast<size_t>(p.tok0) * Hg + hg) * kDim;
-    const __nv_bfloat16* qsrc = Pg ? q + (static_cast<size_t>(p.tok0) * Hg + hg) * kDim : nullptr;
-#pragma unroll
-    for (int it = 0; it < 8; ++it) {
-      const int idx = it * 128 + tid;  // 16-byte piece index: 16 per row
-      const int row = idx >> 4, piece = idx & 15;
-      const int ok = row < p.len;
-      const size_t off = static_cast<size_t>(ok ? row : 0) * Hg * kDim + piece * 8;
-      cp_async16(&s.k[row * kKLd + piece * 8], src + off, ok ? 16 : 0);
-      if (Pg) cp_async16(&s.q[row * kKLd + piece * 8], qsrc + off, ok ? 16 : 0);
-    }
-    if (kSingle && tid < kChunk) {
-      s.beta[tid] = (tid < p.len) ? __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hg) : 0.f;
-      if (Ag || Pg) load_gates(s.g, g_cum, g_cum_out, static_cast<size_t>(p.tok0) * H + hg, H, p.len, tid);
-    }
-    cp_async_wait_all();
-  }
-  __syncthreads();
-
-  // ---- Q K^T (registers) and K K^T (fp32, to shared), lower block triangle only, one pass each
-  float qk[8][4];
-  {
-    const int m0 = warp * 16;
-    const int ntiles = 2 * warp + 2;
-    if (Pg) {
-      gram_pass(qk, s.q, s.k, m0, ntiles, lane);
-      if (kSingle)
-        // the warp's own rows of the Q tile are dead once its Q K^T fragments are formed: staging for P_g
-        store_pg(qk, s.g, Pg + (static_cast<size_t>(p.tok0) * H + hg) * kChunk, static_cast<size_t>(H) * kChunk, warp, lane,
-                 p.len, scale, &s.q[m0 * kKLd]);
-    }
-    if (A_in == nullptr) {
-      float acc[8][4];
-      gram_pass(acc, s.k, s.k, m0, ntiles, lane);
-      __syncthreads();  // every warp is done reading the Q and K tiles, whose storage kk and x reuse
-      {  // the two 16x16 blocks above the diagonal that the 32x32 block products read must be zero
-        const int blk = tid >> 6, idx = tid & 63;
-        *reinterpret_cast<float4*>(&s.x[(32 * blk + (idx >> 2)) * kFLd + 32 * blk + 16 + 4 * (idx & 3)]) =
-            make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (j < ntiles) {
-          *reinterpret_cast<float2*>(&s.kk[(m0 + g) * kFLd + j * 8 + 2 * t]) = make_float2(acc[j][0], acc[j][1]);
-          *reinterpret_cast<float2*>(&s.kk[(m0 + g + 8) * kFLd + j * 8 + 2 * t]) = make_float2(acc[j][2], acc[j][3]);
-        }
-      }
-    }
-  }
-
   for (int hi = 0; hi < G; ++hi) {
     const int hv = hg * G + hi;
     __syncthreads();  // kk complete, tiles read (first pass) / previous head's stores done
@@ -450,6 +392,216 @@ __global__ void __launch_bounds__(128, 6) kkt_solve_kernel(const __nv_bfloat16* 
   }
 }
 
+// kSingle: every QK head has one V head (G == 1); the gates are then loaded with the tiles and P_g leaves before
+// the solve, so that the Q K^T fragments are dead while K K^T is formed and inverted.
+template <bool kSingle>
+__global__ void __launch_bounds__(128, 6) kkt_solve_kernel(const __nv_bfloat16* __restrict__ k,
+                                                       const float* __restrict__ beta,
+                                                       __nv_bfloat16* __restrict__ A, int H, int Hg, SeqArgs sa,
+                                                       const __nv_bfloat16* __restrict__ q,
+                                                       const float* __restrict__ g_cum,
+                                                       __nv_bfloat16* __restrict__ Ag, __nv_bfloat16* __restrict__ Pg,
+                                                       float scale, const __nv_bfloat16* __restrict__ A_in,
+                                                       float* __restrict__ g_cum_out) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  KktSmem& s = *reinterpret_cast<KktSmem*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int hg = blockIdx.y;
+  const int G = H / Hg;
+  const ChunkPos p = chunk_lookup(sa, blockIdx.x);
+
+  // ---- K and Q tiles -> shared by asynchronous 16-byte copies (rows past the sequence end are zero-filled)
+  {
+    const __nv_bfloat16* src = k + (static_cast<size_t>(p.tok0) * Hg + hg) * kDim;
+    const __nv_bfloat16* qsrc = Pg ? q + (static_cast<size_t>(p.tok0) * Hg + hg) * kDim : nullptr;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int idx = it * 128 + tid;  // 16-byte piece index: 16 per row
+      const int row = idx >> 4, piece = idx & 15;
+      const int ok = row < p.len;
+      const size_t off = static_cast<size_t>(ok ? row : 0) * Hg * kDim + piece * 8;
+      cp_async16(&s.k[row * kKLd + piece * 8], src + off, ok ? 16 : 0);
+      if (Pg) cp_async16(&s.q[row * kKLd + piece * 8], qsrc + off, ok ? 16 : 0);
+    }
+    if (kSingle && tid < kChunk) {
+      s.beta[tid] = (tid < p.len) ? __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hg) : 0.f;
+      if (Ag || Pg) load_gates(s.g, g_cum, g_cum_out, static_cast<size_t>(p.tok0) * H + hg, H, p.len, tid);
+    }
+    cp_async_wait_all();
+  }
+  __syncthreads();
+
+  // ---- Q K^T (registers) and K K^T (fp32, to shared), lower block triangle only, one pass each
+  float qk[8][4];
+  {
+    const int m0 = warp * 16;
+    const int ntiles = 2 * warp + 2;
+    if (Pg) {
+      gram_pass(qk, s.q, s.k, m0, ntiles, lane);
+      if (kSingle)
+        // the warp's own rows of the Q tile are dead once its Q K^T fragments are formed: staging for P_g
+        store_pg(qk, s.g, Pg + (static_cast<size_t>(p.tok0) * H + hg) * kChunk, static_cast<size_t>(H) * kChunk, warp, lane,
+                 p.len, scale, &s.q[m0 * kKLd]);
+    }
+    if (A_in == nullptr) {
+      float acc[8][4];
+      gram_pass(acc, s.k, s.k, m0, ntiles, lane);
+      __syncthreads();  // every warp is done reading the Q and K tiles, whose storage kk and x reuse
+      {  // the two 16x16 blocks above the diagonal that the 32x32 block products read must be zero
+        const int blk = tid >> 6, idx = tid & 63;
+        *reinterpret_cast<float4*>(&s.x[(32 * blk + (idx >> 2)) * kFLd + 32 * blk + 16 + 4 * (idx & 3)]) =
+            make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j < ntiles) {
+          *reinterpret_cast<float2*>(&s.kk[(m0 + g) * kFLd + j * 8 + 2 * t]) = make_float2(acc[j][0], acc[j][1]);
+          *reinterpret_cast<float2*>(&s.kk[(m0 + g + 8) * kFLd + j * 8 + 2 * t]) = make_float2(acc[j][2], acc[j][3]);
+        }
+      }
+    }
+  }
+
+  solve_heads<kSingle>(s, p, qk, beta, A, H, Hg, hg, g_cum, Ag, Pg, scale, A_in, g_cum_out);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The forward's tile kernel on the Blackwell path (neither P_g nor a given A: only k is read).  Persistent CTAs of four
+// warps walk the (chunk, QK-head) units; per unit
+//   - the K tile [64 x 128] arrives by TMA (two 128-byte-swizzled halves, no padding, no per-thread copies),
+//   - K K^T [64 x 64] is ONE group of eight tcgen05 products (M = 64, N = 64, K = 16 each) into 64 columns of tensor
+//     memory that the CTA holds for its whole life,
+//   - the accumulator rows come back with tcgen05.ld (row r in lane r & 15 of warp r >> 4) and are laid down in
+//     shared memory for the block inverse; rows past the sequence end are written as zeros, so whatever the tile
+//     held there (the next sequence's tokens) never enters the arithmetic,
+//   - solve_heads() does the rest (the 16 x 16 substitutions and the small block products stay on CUDA cores / the
+//     warp-level tensor path: they are 16-wide, far below a tcgen05 tile).
+// The gates and beta of the unit are fetched while the tile is in flight.
+struct KktTcSmem {
+  union {  // the K tile is dead once K K^T is formed; the inverse X (fp32) then takes its place
+    unsigned char ktile[16384];  // two 64-row x 128-byte regions (d 0-63 | d 64-127), 128-byte swizzle
+    float x[kChunk * kFLd];
+  };
+  float kk[kChunk * kFLd];
+  float beta[kChunk];
+  float g[kChunk];
+  uint64_t bar_tma, bar_mma, drain_bar;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <bool kSingle>
+__global__ void __launch_bounds__(128, 6)
+kkt_solve_tc_kernel(const __grid_constant__ CUtensorMap map_k, const float* __restrict__ beta,
+                    __nv_bfloat16* __restrict__ A, int H, int Hg, SeqArgs sa, const float* __restrict__ g_cum,
+                    __nv_bfloat16* __restrict__ Ag, float scale, float* __restrict__ g_cum_out, int total_chunks,
+                    int* status_dev) {
+  extern __shared__ unsigned char smem_dyn[];
+  KktTcSmem& s = *reinterpret_cast<KktTcSmem*>(
+      reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  WaitCtx wc{&s.abort_flag, status_dev, 4, kWaitLimitCycles};
+  if (tid == 0) {
+    s.abort_flag = 0;
+    mbar_init(&s.bar_tma, 1);
+    mbar_init(&s.bar_mma, 1);
+    mbar_init(&s.drain_bar, 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&map_k);
+  }
+  if (warp == 0) {
+    tmem_alloc(&s.tmem_base, 64);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = s.tmem_base;
+  constexpr uint32_t idesc = umma_idesc(64, 64, false, false, true);
+  const uint32_t sk = smem_u32(s.ktile);
+  const long long units = static_cast<long long>(total_chunks) * Hg;
+  uint32_t phase = 0;
+  float qk_unused[8][4];  // solve_heads' P_g input; never read here (no P_g)
+#pragma unroll 1
+  for (long long u = blockIdx.x; u < units; u += gridDim.x) {
+    if (s.abort_flag) break;  // read by every thread after the barrier that ended the previous unit
+    const int chunk = static_cast<int>(u / Hg), hg = static_cast<int>(u - static_cast<long long>(chunk) * Hg);
+    const ChunkPos p = chunk_lookup(sa, chunk);
+    if (tid == 0) {
+      mbar_arrive_expect_tx(&s.bar_tma, 16384);
+      tma_load_3d(s.ktile, &map_k, &s.bar_tma, 0, hg, p.tok0);
+      tma_load_3d(s.ktile + 8192, &map_k, &s.bar_tma, 64, hg, p.tok0);
+    }
+    if (kSingle && tid < kChunk) {  // beta and the gates while the tile is in flight
+      s.beta[tid] = (tid < p.len) ? __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hg) : 0.f;
+      if (Ag) load_gates(s.g, g_cum, g_cum_out, static_cast<size_t>(p.tok0) * H + hg, H, p.len, tid);
+    }
+    mbar_wait(wc, &s.bar_tma, phase, 1);
+    if (warp == 0) {
+      tc_fence_after();
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {  // K K^T: A and B are the same K-major tile
+          const uint64_t d = umma_desc_sw128(sk + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024);
+          umma_ss(tm, d, d, idesc, kk > 0);
+        }
+        umma_commit(&s.bar_mma);
+      }
+      __syncwarp();
+    }
+    mbar_wait(wc, &s.bar_mma, phase, 2);
+    phase ^= 1;
+    tc_fence_after();
+    {
+      // accumulator row r = 16 warp + lane (lanes 0-15) -> s.kk; only the lower block triangle is read later
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tmem_addr(tm, warp * 32, 0), r0);
+      tmem_ld32(tmem_addr(tm, warp * 32, 32), r1);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncthreads();  // every warp is past its reads of tensor memory and nobody reads the K tile any more: x may be written
+      if (lane < 16) {
+        const int r = 16 * warp + lane;
+        const bool live = r < p.len;
+        float* dst = &s.kk[r * kFLd];
+#pragma unroll
+        for (int c4 = 0; c4 < 8; ++c4) {
+          if (c4 < 4 * (warp + 1)) {
+            float4 v0 = make_float4(__uint_as_float(r0[4 * c4]), __uint_as_float(r0[4 * c4 + 1]), __uint_as_float(r0[4 * c4 + 2]),
+                                    __uint_as_float(r0[4 * c4 + 3]));
+            if (!live) v0 = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4*>(dst + 4 * c4) = v0;
+          }
+        }
+#pragma unroll
+        for (int c4 = 0; c4 < 8; ++c4) {
+          if (8 + c4 < 4 * (warp + 1)) {
+            float4 v1 = make_float4(__uint_as_float(r1[4 * c4]), __uint_as_float(r1[4 * c4 + 1]), __uint_as_float(r1[4 * c4 + 2]),
+                                    __uint_as_float(r1[4 * c4 + 3]));
+            if (!live) v1 = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4*>(dst + 32 + 4 * c4) = v1;
+          }
+        }
+      }
+      {  // the two 16x16 blocks above the diagonal that the 32x32 block products read must be zero
+        const int blk = tid >> 6, idx = tid & 63;
+        *reinterpret_cast<float4*>(&s.x[(32 * blk + (idx >> 2)) * kFLd + 32 * blk + 16 + 4 * (idx & 3)]) =
+            make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    solve_heads<kSingle>(s, p, qk_unused, beta, A, H, Hg, hg, g_cum, Ag, nullptr, scale, nullptr, g_cum_out);
+    __syncthreads();  // the unit's reads of x are done: the next tile may land there
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (s.abort_flag) {
+    drain_after_abort(warp == 0 && elect_one(), &s.drain_bar);
+    __syncthreads();
+  }
+  if (warp == 0) tmem_dealloc(tm, 64);
+}
+
 }  // namespace fq
 
 static int kkt_launch(const void* k, const void* q, const float* beta, const float* g_cumsum, float* g_cum_out, void* A,
@@ -477,6 +629,29 @@ static int kkt_launch(const void* k, const void* q, const float* beta, const flo
     static std::atomic<unsigned long long> done1{0};
     const int rc_attr = set_smem_limit_once(reinterpret_cast<const void*>(kkt_solve_kernel<false>), static_cast<int>(sizeof(KktSmem)), &done1);
     if (rc_attr != FQ_OK) return rc_attr;
+  }
+  if (!a_is_input && Pg == nullptr) {
+    // the forward's case (only k is read): TMA + tcgen05 front end, persistent CTAs
+    CUtensorMap mk;
+    const uint64_t rows = static_cast<uint64_t>(B) * static_cast<uint64_t>(T);
+    FQ_CHECK_ARG(rows > 0 && rows < (1ull << 31), "fq_kkt_solve: token count out of range");
+    int rc = make_tmap_rows_heads_dim(&mk, k, rows, Hg, kDim, kChunk, 64);
+    if (rc != FQ_OK) return rc;
+    const int smem = static_cast<int>(sizeof(KktTcSmem) + 1024);
+    {
+      static std::atomic<unsigned long long> done0{0}, done1{0};
+      if ((rc = set_smem_limit_once(reinterpret_cast<const void*>(kkt_solve_tc_kernel<true>), smem, &done0)) != FQ_OK) return rc;
+      if ((rc = set_smem_limit_once(reinterpret_cast<const void*>(kkt_solve_tc_kernel<false>), smem, &done1)) != FQ_OK) return rc;
+    }
+    const long long units = static_cast<long long>(total_chunks) * Hg;
+    const long long cap = 6LL * sm_count();
+    const unsigned grid_tc = static_cast<unsigned>(units < cap ? units : cap);
+    auto kern_tc = (H == Hg) ? kkt_solve_tc_kernel<true> : kkt_solve_tc_kernel<false>;
+    kern_tc<<<grid_tc, 128, smem, static_cast<cudaStream_t>(stream)>>>(mk, beta, static_cast<__nv_bfloat16*>(A), H, Hg, sa, g_cumsum,
+                                                                      static_cast<__nv_bfloat16*>(Ag), scale, g_cum_out,
+                                                                      total_chunks, nullptr);
+    FQ_CHECK_CUDA(cudaGetLastError());
+    return FQ_OK;
   }
   dim3 grid(total_chunks, Hg);
   auto kern = (H == Hg) ? kkt_solve_kernel<true> : kkt_solve_kernel<false>;
