@@ -487,7 +487,7 @@ def sequence_parallel_run(bn, w, steps, warmup, check=True):
 
     def step():
         if world == 1:   # the whole sequence on one GPU: the plain operator (tiles kept for the backward, as autograd does)
-            gc, A, o, _, fs, tiles = ops.chunk_gated_delta_rule_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], scale, None, None,
+            gc, A, o, _, fs, tiles, _ = ops.chunk_gated_delta_rule_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], scale, None, None,
                                                                     True, False, True, _return_tiles=True)
             ops.chunk_gated_delta_rule_bwd(d["q"], d["k"], d["v"], gc, d["beta"], A, d["do"], None, scale, None, None,
                                            _gated_tiles=tiles)

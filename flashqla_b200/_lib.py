@@ -45,6 +45,8 @@ SIGNATURES = {
     "fq_l2norm_bwd": [_vp, _vp, _vp, ctypes.c_longlong, _f32, _vp],
     "fq_kkt_solve_gated": [_vp] * 7 + [_i32] * 5 + [_vp, _vp, _i32, _i32, _f32, _vp],
     "fq_kkt_solve_fused": [_vp] * 8 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp],
+    "fq_kkt_solve_fused_act": [_vp] * 5 + [_i32, _i32] + [_vp] * 4 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp],
+    "fq_gate_act_bwd": [_vp] * 6 + [_i32, _i32] + [_vp] * 4 + [ctypes.c_longlong, _i32, _vp],
     "fq_selftest_umma": [_vp, _vp, _vp, _i32, _vp, _vp],
     "fq_selftest_wait_expiry": [_vp, _vp, ctypes.c_longlong, _vp],
 }

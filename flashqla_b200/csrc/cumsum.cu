@@ -142,6 +142,79 @@ extern "C" FQ_API int fq_dg_boundary_fix(const float* h0, const float* dht, cons
   return FQ_OK;
 }
 
+namespace fq {
+// Backward of the gate / beta activations that fq_kkt_solve_fused_act applies (same modes): dg, db are the gradients
+// w.r.t. the ACTIVATED log gate and beta, the outputs those w.r.t. the raw inputs; for gate mode 2 also the per-head
+// sums dA_log[h] += sum dg * g and ddt_bias[h] += sum dg * dg/dz (shared-memory partial sums, one atomic per head and CTA).
+__global__ void __launch_bounds__(256) gate_act_bwd_kernel(const float* __restrict__ dg, const float* __restrict__ db,
+                                                          const float* __restrict__ g_raw, const float* __restrict__ beta_raw,
+                                                          const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                                                          int gate_mode, int beta_mode, float* __restrict__ dg_raw,
+                                                          float* __restrict__ db_raw, float* __restrict__ dA_log,
+                                                          float* __restrict__ ddt_bias, long long total, int H) {
+  extern __shared__ float part[];  // [2 * H]
+  const bool sums = gate_mode == 2 && (dA_log != nullptr || ddt_bias != nullptr);
+  if (sums) {
+    for (int i = threadIdx.x; i < 2 * H; i += blockDim.x) part[i] = 0.f;
+    __syncthreads();
+  }
+  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int h = static_cast<int>(idx % H);
+    const float d = dg[idx];
+    float out = d;
+    if (gate_mode == 1) {
+      out = d / (1.f + __expf(g_raw[idx]));  // d logsigmoid(x) / dx = sigmoid(-x)
+    } else if (gate_mode == 2) {
+      const float ea = __expf(__ldg(A_log + h));
+      const float z = g_raw[idx] + (dt_bias ? __ldg(dt_bias + h) : 0.f);
+      const float sp = z > 20.f ? z : log1pf(__expf(z));
+      const float dz = -ea / (1.f + __expf(-z));          // d g / d z
+      out = d * dz;
+      if (sums) {
+        atomicAdd(&part[h], d * (-ea * sp));              // d g / d A_log = g
+        atomicAdd(&part[H + h], out);
+      }
+    }
+    dg_raw[idx] = out;
+    if (db_raw != nullptr) {
+      float o2 = db[idx];
+      if (beta_mode == 1) {
+        const float sg = 1.f / (1.f + __expf(-beta_raw[idx]));
+        o2 *= sg * (1.f - sg);
+      }
+      db_raw[idx] = o2;
+    }
+  }
+  if (sums) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      if (dA_log) atomicAdd(dA_log + i, part[i]);
+      if (ddt_bias) atomicAdd(ddt_bias + i, part[H + i]);
+    }
+  }
+}
+}  // namespace fq
+
+extern "C" FQ_API int fq_gate_act_bwd(const float* dg, const float* db, const float* g_raw, const float* beta_raw,
+                                      const float* A_log, const float* dt_bias, int gate_mode, int beta_mode, float* dg_raw,
+                                      float* db_raw, float* dA_log, float* ddt_bias, long long rows, int H, void* stream) {
+  using namespace fq;
+  FQ_CHECK_ARG(dg && g_raw && dg_raw && rows >= 0 && H > 0 && H <= 4096, "fq_gate_act_bwd: bad arguments");
+  FQ_CHECK_ARG(db_raw == nullptr || (db != nullptr && beta_raw != nullptr), "fq_gate_act_bwd: dbeta needs db and beta_raw");
+  FQ_CHECK_ARG(gate_mode >= 0 && gate_mode <= 2 && beta_mode >= 0 && beta_mode <= 1, "fq_gate_act_bwd: bad mode");
+  FQ_CHECK_ARG(gate_mode != 2 || A_log != nullptr, "fq_gate_act_bwd: gate mode 2 needs A_log");
+  if (rows == 0) return FQ_OK;
+  const long long total = rows * H;
+  const long long blocks = (total + 255) / 256;
+  const long long cap = 8LL * sm_count();
+  gate_act_bwd_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 2 * H * sizeof(float),
+                        static_cast<cudaStream_t>(stream)>>>(dg, db, g_raw, beta_raw, A_log, dt_bias, gate_mode, beta_mode,
+                                                             dg_raw, db_raw, dA_log, ddt_bias, total, H);
+  FQ_CHECK_CUDA(cudaGetLastError());
+  return FQ_OK;
+}
+
 extern "C" FQ_API int fq_chunk_cumsum(const float* g, float* out, int B, int T, int H, const int32_t* cu_seqlens,
                                       const int32_t* chunk_offsets, int n_seq, int total_chunks, int reverse,
                                       void* stream) {

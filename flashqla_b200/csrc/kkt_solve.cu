@@ -141,21 +141,42 @@ __device__ __forceinline__ void store_pg(const float (&qk)[8][4], const float* g
   }
 }
 
+// Optional activations of the caller's raw gate / beta inputs, applied while the values are loaded (the elementwise
+// passes a caller otherwise runs before the operator):
+//   gate_mode 0: g is the log gate          1: g = logsigmoid(x)          2: g = -exp(A_log[h]) * softplus(x + dt_bias[h])
+//   beta_mode 0: beta as given              1: beta = sigmoid(x); the activated values are also written to beta_out
+//                                              ([rows, H] fp32), which the recurrence kernels read
+struct GateAct {
+  int gate_mode;
+  int beta_mode;
+  const float* A_log;    // [H], mode 2
+  const float* dt_bias;  // [H] or nullptr, mode 2
+  float* beta_out;       // [rows, H], beta_mode 1
+};
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(__expf(z)); }
+__device__ __forceinline__ float act_gate(const GateAct& a, float x, int h) {
+  if (a.gate_mode == 1) return fminf(x, 0.f) - log1pf(__expf(-fabsf(x)));
+  if (a.gate_mode == 2) return -__expf(__ldg(a.A_log + h)) * softplus_f(x + (a.dt_bias ? __ldg(a.dt_bias + h) : 0.f));
+  return x;
+}
+__device__ __forceinline__ float act_beta(const GateAct& a, float x) { return a.beta_mode == 1 ? 1.f / (1.f + __expf(-x)) : x; }
+
 // Gate values of one (chunk, head) into shared memory, times log2(e): exp(g_i - g_j) = exp2(g2_i - g2_j).  Called by
 // warps 0 and 1.  With `g_cum_out` the input is the RAW log gate: warp 0 forms the chunk-local inclusive sum (two tokens
 // per lane, shuffle scan) and also stores it, so that no separate prefix-sum pass over g is needed
 // (chunk_local_cumsum, flash_qla/ops/utils/cumsum.py:131-165, folded into this kernel).  Rows past the sequence end
 // get the last valid sum.
 __device__ __forceinline__ void load_gates(float* sg, const float* __restrict__ g_in, float* __restrict__ g_cum_out,
-                                           size_t base, int H, int len, int tid) {
+                                           size_t base, int H, int len, int tid, const GateAct& act = GateAct{0, 0, nullptr, nullptr, nullptr},
+                                           int head = 0) {
   constexpr float kLog2e = 1.4426950408889634f;
   if (g_cum_out == nullptr) {
     sg[tid] = kLog2e * __ldg(g_in + base + static_cast<size_t>(min(tid, len - 1)) * H);
     return;
   }
   if (tid >= 32) return;
-  float a = (tid < len) ? __ldg(g_in + base + static_cast<size_t>(tid) * H) : 0.f;
-  float b = (tid + 32 < len) ? __ldg(g_in + base + static_cast<size_t>(tid + 32) * H) : 0.f;
+  float a = (tid < len) ? act_gate(act, __ldg(g_in + base + static_cast<size_t>(tid) * H), head) : 0.f;
+  float b = (tid + 32 < len) ? act_gate(act, __ldg(g_in + base + static_cast<size_t>(tid + 32) * H), head) : 0.f;
 #pragma unroll
   for (int d = 1; d < 32; d <<= 1) {
     const float ya = __shfl_up_sync(0xffffffffu, a, d), yb = __shfl_up_sync(0xffffffffu, b, d);
@@ -177,7 +198,8 @@ __device__ __forceinline__ void solve_heads(Smem& s, const ChunkPos& p, const fl
                                             __nv_bfloat16* __restrict__ A, int H, int Hg, int hg,
                                             const float* __restrict__ g_cum, __nv_bfloat16* __restrict__ Ag,
                                             __nv_bfloat16* __restrict__ Pg, float scale,
-                                            const __nv_bfloat16* __restrict__ A_in, float* __restrict__ g_cum_out) {
+                                            const __nv_bfloat16* __restrict__ A_in, float* __restrict__ g_cum_out,
+                                            const GateAct& act = GateAct{0, 0, nullptr, nullptr, nullptr}) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int G = H / Hg;
@@ -186,8 +208,13 @@ __device__ __forceinline__ void solve_heads(Smem& s, const ChunkPos& p, const fl
     __syncthreads();  // kk complete, tiles read (first pass) / previous head's stores done
     if (!kSingle) {
       if (tid < kChunk) {
-        s.beta[tid] = (tid < p.len) ? __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hv) : 0.f;
-        if (Ag || Pg) load_gates(s.g, g_cum, g_cum_out, static_cast<size_t>(p.tok0) * H + hv, H, p.len, tid);
+        float bv = 0.f;
+        if (tid < p.len) {
+          bv = act_beta(act, __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hv));
+          if (act.beta_out) act.beta_out[static_cast<size_t>(p.tok0 + tid) * H + hv] = bv;
+        }
+        s.beta[tid] = bv;
+        if (Ag || Pg) load_gates(s.g, g_cum, g_cum_out, static_cast<size_t>(p.tok0) * H + hv, H, p.len, tid, act, hv);
       }
       __syncthreads();
     }
@@ -496,7 +523,7 @@ __global__ void __launch_bounds__(128, 6)
 kkt_solve_tc_kernel(const __grid_constant__ CUtensorMap map_k, const float* __restrict__ beta,
                     __nv_bfloat16* __restrict__ A, int H, int Hg, SeqArgs sa, const float* __restrict__ g_cum,
                     __nv_bfloat16* __restrict__ Ag, float scale, float* __restrict__ g_cum_out, int total_chunks,
-                    int* status_dev) {
+                    int* status_dev, const GateAct act) {
   extern __shared__ unsigned char smem_dyn[];
   KktTcSmem& s = *reinterpret_cast<KktTcSmem*>(
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023)));
@@ -534,8 +561,13 @@ kkt_solve_tc_kernel(const __grid_constant__ CUtensorMap map_k, const float* __re
       tma_load_3d(s.ktile + 8192, &map_k, &s.bar_tma, 64, hg, p.tok0);
     }
     if (kSingle && tid < kChunk) {  // beta and the gates while the tile is in flight
-      s.beta[tid] = (tid < p.len) ? __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hg) : 0.f;
-      if (Ag) load_gates(s.g, g_cum, g_cum_out, static_cast<size_t>(p.tok0) * H + hg, H, p.len, tid);
+      float bv = 0.f;
+      if (tid < p.len) {
+        bv = act_beta(act, __ldg(beta + static_cast<size_t>(p.tok0 + tid) * H + hg));
+        if (act.beta_out) act.beta_out[static_cast<size_t>(p.tok0 + tid) * H + hg] = bv;
+      }
+      s.beta[tid] = bv;
+      if (Ag) load_gates(s.g, g_cum, g_cum_out, static_cast<size_t>(p.tok0) * H + hg, H, p.len, tid, act, hg);
     }
     mbar_wait(wc, &s.bar_tma, phase, 1);
     if (warp == 0) {
@@ -590,7 +622,7 @@ kkt_solve_tc_kernel(const __grid_constant__ CUtensorMap map_k, const float* __re
             make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
-    solve_heads<kSingle>(s, p, qk_unused, beta, A, H, Hg, hg, g_cum, Ag, nullptr, scale, nullptr, g_cum_out);
+    solve_heads<kSingle>(s, p, qk_unused, beta, A, H, Hg, hg, g_cum, Ag, nullptr, scale, nullptr, g_cum_out, act);
     __syncthreads();  // the unit's reads of x are done: the next tile may land there
   }
   tc_fence_before();
@@ -606,7 +638,8 @@ kkt_solve_tc_kernel(const __grid_constant__ CUtensorMap map_k, const float* __re
 
 static int kkt_launch(const void* k, const void* q, const float* beta, const float* g_cumsum, float* g_cum_out, void* A,
                       void* Ag, void* Pg, int a_is_input, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
-                      const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale, void* stream) {
+                      const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale, void* stream,
+                      fq::GateAct act = fq::GateAct{0, 0, nullptr, nullptr, nullptr}) {
   using namespace fq;
   FQ_CHECK_ARG(k && beta && (A || (Ag && !a_is_input)), "fq_kkt_solve: null tensor");
   FQ_CHECK_ARG((Ag == nullptr && Pg == nullptr) || (g_cumsum != nullptr), "fq_kkt_solve: A_g / P_g need the gate cumsum");
@@ -649,7 +682,7 @@ static int kkt_launch(const void* k, const void* q, const float* beta, const flo
     auto kern_tc = (H == Hg) ? kkt_solve_tc_kernel<true> : kkt_solve_tc_kernel<false>;
     kern_tc<<<grid_tc, 128, smem, static_cast<cudaStream_t>(stream)>>>(mk, beta, static_cast<__nv_bfloat16*>(A), H, Hg, sa, g_cumsum,
                                                                       static_cast<__nv_bfloat16*>(Ag), scale, g_cum_out,
-                                                                      total_chunks, nullptr);
+                                                                      total_chunks, nullptr, act);
     FQ_CHECK_CUDA(cudaGetLastError());
     return FQ_OK;
   }
@@ -686,4 +719,18 @@ extern "C" FQ_API int fq_kkt_solve(const void* k, const float* beta, void* A, in
                                    int total_chunks, void* stream) {
   return fq_kkt_solve_gated(k, nullptr, beta, nullptr, A, nullptr, nullptr, 0, B, T, H, Hg, cu_seqlens, chunk_offsets, n_seq,
                             total_chunks, 0.f, stream);
+}
+
+extern "C" FQ_API int fq_kkt_solve_fused_act(const void* k, const float* beta_raw, const float* g_raw, const float* A_log,
+                                             const float* dt_bias, int gate_mode, int beta_mode, float* g_cumsum,
+                                             float* beta_out, void* A, void* Ag, int B, int T, int H, int Hg,
+                                             const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
+                                             int total_chunks, float scale, void* stream) {
+  FQ_CHECK_ARG(g_raw && g_cumsum && Ag && beta_raw, "fq_kkt_solve_fused_act: null tensor");
+  FQ_CHECK_ARG(gate_mode >= 0 && gate_mode <= 2 && beta_mode >= 0 && beta_mode <= 1, "fq_kkt_solve_fused_act: bad mode");
+  FQ_CHECK_ARG(gate_mode != 2 || A_log != nullptr, "fq_kkt_solve_fused_act: gate mode 2 needs A_log");
+  FQ_CHECK_ARG(beta_mode == 0 || beta_out != nullptr, "fq_kkt_solve_fused_act: an activated beta needs beta_out");
+  fq::GateAct act{gate_mode, beta_mode, A_log, dt_bias, beta_mode ? beta_out : nullptr};
+  return kkt_launch(k, nullptr, beta_raw, g_raw, g_cumsum, A, Ag, nullptr, 0, B, T, H, Hg, cu_seqlens, chunk_offsets, n_seq,
+                    total_chunks, scale, stream, act);
 }

@@ -160,6 +160,55 @@ def kkt_solve_fused(k, q, b, g, scale, plan: SeqPlan, want_A=True, want_pg=False
     return g_cum, A, Ag, Pg
 
 
+def kkt_solve_fused_act(k, b_raw, g_raw, scale, plan: SeqPlan, gate_mode: int, beta_mode: int, A_log=None, dt_bias=None,
+                        want_A=True):
+    """kkt_solve_fused with the gate / beta activations applied inside the kernel (modes as in include/flashqla.h).
+    Returns (g_cumsum of the activated gate, activated beta (the input itself for beta_mode 0), A, A_g)."""
+    _require_cuda(k, b_raw, g_raw)
+    if k.dtype != torch.bfloat16:
+        raise _lib.FlashQLAError("kkt_solve_fused_act: only bfloat16 keys are supported")
+    B, T, Hg, K = k.shape
+    H = b_raw.shape[-1]
+    k = k.contiguous()
+    bf = b_raw.contiguous() if b_raw.dtype == torch.float32 else b_raw.float().contiguous()
+    gf = g_raw.contiguous() if g_raw.dtype == torch.float32 else g_raw.float().contiguous()
+    p = lambda t: None if t is None else t.float().contiguous().data_ptr()
+    al = None if A_log is None else A_log.float().contiguous()
+    db_ = None if dt_bias is None else dt_bias.float().contiguous()
+    g_cum = torch.empty_like(gf)
+    beta_act = (torch.zeros_like(bf) if plan.total_tokens < B * T else torch.empty_like(bf)) if beta_mode else bf
+    alloc = _tile_alloc(plan, B, T)
+    Ag = alloc(B, T, H, CHUNK, dtype=k.dtype, device=k.device)
+    A = alloc(B, T, H, CHUNK, dtype=k.dtype, device=k.device) if want_A else None
+    cu_p, off_p = plan.ptrs()
+    rc = _lib.load().fq_kkt_solve_fused_act(k.data_ptr(), bf.data_ptr(), gf.data_ptr(), None if al is None else al.data_ptr(),
+                                            None if db_ is None else db_.data_ptr(), int(gate_mode), int(beta_mode),
+                                            g_cum.data_ptr(), beta_act.data_ptr() if beta_mode else None,
+                                            None if A is None else A.data_ptr(), Ag.data_ptr(), B, T, H, Hg, cu_p, off_p,
+                                            plan.n_seq, plan.total_chunks, float(scale), _stream())
+    _lib.check(rc, "fq_kkt_solve_fused_act")
+    return g_cum, beta_act, A, Ag
+
+
+def gate_act_bwd(dg, db, g_raw, b_raw, gate_mode: int, beta_mode: int, A_log=None, dt_bias=None):
+    """Backward of the in-kernel activations.  Returns (dg_raw, db_raw, dA_log or None, ddt_bias or None)."""
+    H = dg.shape[-1]
+    rows = dg.numel() // H
+    gf = g_raw.contiguous() if g_raw.dtype == torch.float32 else g_raw.float().contiguous()
+    bf = b_raw.contiguous() if b_raw.dtype == torch.float32 else b_raw.float().contiguous()
+    dg, db = dg.contiguous(), db.contiguous()
+    dg_raw, db_raw = torch.empty_like(dg), torch.empty_like(db)
+    al = None if A_log is None else A_log.float().contiguous()
+    bi = None if dt_bias is None else dt_bias.float().contiguous()
+    dA = torch.zeros(H, dtype=torch.float32, device=dg.device) if gate_mode == 2 else None
+    dB = torch.zeros(H, dtype=torch.float32, device=dg.device) if (gate_mode == 2 and dt_bias is not None) else None
+    p = lambda t: None if t is None else t.data_ptr()
+    rc = _lib.load().fq_gate_act_bwd(dg.data_ptr(), db.data_ptr(), gf.data_ptr(), bf.data_ptr(), p(al), p(bi), int(gate_mode),
+                                     int(beta_mode), dg_raw.data_ptr(), db_raw.data_ptr(), p(dA), p(dB), rows, H, _stream())
+    _lib.check(rc, "fq_gate_act_bwd")
+    return dg_raw, db_raw, dA, dB
+
+
 def sm_count(device) -> int:
     return torch.cuda.get_device_properties(device).multi_processor_count
 

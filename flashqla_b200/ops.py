@@ -55,7 +55,7 @@ def l2norm(x: torch.Tensor, dim: int = -1, eps: float = 1e-6) -> torch.Tensor:
 
 def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None, cu_seqlens=None,
                                output_final_state=True, output_h=False, auto_cp=True, _return_tiles=None, _plan=None,
-                               _want_A=True):
+                               _want_A=True, _act=None):
     """Forward pipeline (chunk/__init__.py:17-67): [cumsum + K K^T + solve + gated tiles] -> fused recurrence.
 
     Returns ``(g_cumsum, A, o, h, final_state)``; ``A`` is the gate-free inverse (opaque, only
@@ -68,7 +68,13 @@ def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None,
     plan = _plan if _plan is not None else make_plan(B, T, cu_seqlens, q.device)
     # the cumsum of g is formed in the same launch; A is only stored if a backward may follow.  The second gated tile
     # P_g is formed inside the recurrence kernel, which also stores it when the caller keeps the tiles for a backward.
-    g_cum, A, Ag, _ = kernels.kkt_solve_fused(k, q, beta, g, scale, plan, want_A=_want_A)
+    if _act is None:
+        g_cum, A, Ag, _ = kernels.kkt_solve_fused(k, q, beta, g, scale, plan, want_A=_want_A)
+    else:
+        # g / beta are RAW inputs: the tile kernel applies the activations; from here on `beta` is the activated one
+        gate_mode, beta_mode, A_log, dt_bias = _act
+        g_cum, beta, A, Ag = kernels.kkt_solve_fused_act(k, beta, g, scale, plan, gate_mode, beta_mode, A_log, dt_bias,
+                                                         want_A=_want_A)
     Pg = kernels._tile_alloc(plan, B, T)(B, T, H, kernels.CHUNK, dtype=k.dtype, device=k.device) if _return_tiles else None
     status = kernels._status_tensor(q.device) if _DEBUG_STATUS else None
     cp = warm = None
@@ -84,7 +90,7 @@ def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None,
     if h is not None:
         h = h.transpose(-1, -2)  # stored [.., V, K] by the kernel; the interface is [.., K, V]
     if _return_tiles is not None:
-        return g_cum, A, o, h, final_state, ((Ag, Pg) if _return_tiles else None)
+        return g_cum, A, o, h, final_state, ((Ag, Pg) if _return_tiles else None), beta
     return g_cum, A, o, h, final_state
 
 
@@ -100,26 +106,32 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
 
 class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     """Autograd glue (chunk/__init__.py:116-180): saves (q, k, v, g_cumsum, beta, A, h0, cu_seqlens) and, unless
-    FLASHQLA_RECOMPUTE_TILES=1, the gated tiles A_g and P_g; neither o nor the per-chunk states are kept."""
+    FLASHQLA_RECOMPUTE_TILES=1, the gated tiles A_g and P_g; neither o nor the per-chunk states are kept.
+    With ``gate_mode`` / ``beta_mode`` != 0 the inputs g / beta are raw pre-activations (see ``chunk_gated_delta_rule``):
+    the activations run inside the tile kernel and their derivatives inside one elementwise backward kernel."""
 
     @staticmethod
     @torch.amp.custom_fwd(device_type="cuda")
     def forward(ctx, q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None,
-                plan=None):
+                plan=None, A_log=None, dt_bias=None, gate_mode=0, beta_mode=0):
         # without a gradient to come (inference / prefill) neither A nor anything else is kept
         needs_bwd = any(ctx.needs_input_grad)
-        g_cum, A, o, _, final_state, tiles = chunk_gated_delta_rule_fwd(
+        act = (gate_mode, beta_mode, A_log, dt_bias) if (gate_mode or beta_mode) else None
+        g_cum, A, o, _, final_state, tiles, beta_act = chunk_gated_delta_rule_fwd(
             q=q, k=k, v=v, g=g, beta=beta, scale=scale, initial_state=initial_state,
             output_final_state=output_final_state, output_h=False, cu_seqlens=cu_seqlens,
-            _return_tiles=needs_bwd and not _RECOMPUTE_TILES, _plan=plan, _want_A=needs_bwd)
+            _return_tiles=needs_bwd and not _RECOMPUTE_TILES, _plan=plan, _want_A=needs_bwd, _act=act)
         if not needs_bwd:
             return o.to(q.dtype), final_state
         ctx.plan = plan  # the backward reuses the forward's sequence plan (no second look at cu_seqlens)
         ctx.keep_tiles = not _RECOMPUTE_TILES
+        ctx.act = act is not None
+        ctx.modes = (gate_mode, beta_mode)
+        extra = (g, beta, A_log, dt_bias) if act is not None else ()
         if ctx.keep_tiles:
-            ctx.save_for_backward(q, k, v, g_cum, beta, A, initial_state, cu_seqlens, *tiles)
+            ctx.save_for_backward(q, k, v, g_cum, beta_act, A, initial_state, cu_seqlens, *tiles, *extra)
         else:
-            ctx.save_for_backward(q, k, v, g_cum, beta, A, initial_state, cu_seqlens)
+            ctx.save_for_backward(q, k, v, g_cum, beta_act, A, initial_state, cu_seqlens, *extra)
         ctx.scale = scale
         ctx.g_dtype = g.dtype
         ctx.beta_dtype = beta.dtype
@@ -129,7 +141,11 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     @torch.amp.custom_bwd(device_type="cuda")
     def backward(ctx, do, dht):
         q, k, v, g_cum, beta, A, initial_state, cu_seqlens = ctx.saved_tensors[:8]
-        tiles = tuple(ctx.saved_tensors[8:10]) if ctx.keep_tiles else None
+        n = 8
+        tiles = None
+        if ctx.keep_tiles:
+            tiles = tuple(ctx.saved_tensors[8:10])
+            n = 10
         # a gradient for the initial state is formed only if one was passed in and asks for it: returning a tensor
         # for an input that was None (initial_state=None with output_final_state=True, the first segment of a
         # truncated back-propagation) is an autograd error
@@ -138,18 +154,31 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             q=q, k=k, v=v, g=g_cum, beta=beta, A=A, do=do, dht=dht, scale=ctx.scale,
             initial_state=initial_state, cu_seqlens=cu_seqlens, _gated_tiles=tiles, _plan=ctx.plan,
             _want_dh0=need_dh0)
+        dA_log = ddt_bias = None
+        if ctx.act:
+            g_raw, b_raw, A_log, dt_bias = ctx.saved_tensors[n:n + 4]
+            dg, db, dA_log, ddt_bias = kernels.gate_act_bwd(dg, db, g_raw, b_raw, ctx.modes[0], ctx.modes[1], A_log, dt_bias)
+            if dA_log is not None:
+                dA_log = dA_log.to(A_log.dtype)
+            if ddt_bias is not None:
+                ddt_bias = ddt_bias.to(dt_bias.dtype)
         return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dg.to(ctx.g_dtype), db.to(ctx.beta_dtype),
-                None, dh0, None, None, None)
+                None, dh0, None, None, None, dA_log, ddt_bias, None, None)
 
 
 @torch.compiler.disable
 def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
-                           use_qk_l2norm_in_kernel=False, cu_seqlens=None, head_first=False, cu_seqlens_cpu=None):
+                           use_qk_l2norm_in_kernel=False, cu_seqlens=None, head_first=False, cu_seqlens_cpu=None,
+                           use_gate_in_kernel=False, A_log=None, dt_bias=None, use_beta_sigmoid_in_kernel=False):
     """Public, differentiable entry (chunk/__init__.py:183-237).  Returns ``(o, final_state)``.
 
-    ``cu_seqlens_cpu`` (not in the reference) is an optional host copy of ``cu_seqlens``; with it the variable-length
-    schedule is made without reading the device tensor back, so the call neither synchronises nor blocks capture into
-    a CUDA graph."""
+    Not in the reference:
+    ``cu_seqlens_cpu`` is an optional host copy of ``cu_seqlens``; with it the variable-length schedule is made
+    without reading the device tensor back, so the call neither synchronises nor blocks capture into a CUDA graph.
+    ``use_gate_in_kernel``: ``g`` is the RAW gate input and the activation runs inside the tile kernel:
+    ``g = logsigmoid(g)`` or, when ``A_log`` ([H]) is given, ``g = -exp(A_log) * softplus(g + dt_bias)`` (``dt_bias`` [H]
+    optional); ``use_beta_sigmoid_in_kernel``: ``beta`` is raw and ``sigmoid`` runs in the kernel.  Gradients flow to
+    the raw inputs (and to ``A_log`` / ``dt_bias``)."""
     assert q.dtype == k.dtype == v.dtype
     assert q.dtype != torch.float32, (
         "ChunkGatedDeltaRuleFunction does not support float32. Please use bfloat16 or float16.")
@@ -160,7 +189,8 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
         # extra elementwise pass per tensor; autograd casts the gradients the same way), so the arithmetic is bfloat16.
         o, final_state = chunk_gated_delta_rule(q.bfloat16(), k.bfloat16(), v.bfloat16(), g, beta, scale, initial_state,
                                                 output_final_state, use_qk_l2norm_in_kernel, cu_seqlens, head_first,
-                                                cu_seqlens_cpu)
+                                                cu_seqlens_cpu, use_gate_in_kernel, A_log, dt_bias,
+                                                use_beta_sigmoid_in_kernel)
         return o.to(torch.float16), final_state
     if q.dtype != torch.bfloat16:
         raise _lib.FlashQLAError("the sm_100a kernels take bfloat16 (or float16, computed as bfloat16) q/k/v")
@@ -173,11 +203,15 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
             raise ValueError(
                 f"The number of initial states is expected to be equal to the number of input sequences, "
                 f"i.e., {len(cu_seqlens) - 1} rather than {initial_state.shape[0]}.")
+    if A_log is not None and not use_gate_in_kernel:
+        raise ValueError("A_log / dt_bias are only used with use_gate_in_kernel=True")
     if scale is None:
         scale = k.shape[-1] ** -0.5
     if use_qk_l2norm_in_kernel:
         q = l2norm(q)
         k = l2norm(k)
+    gate_mode = (2 if A_log is not None else 1) if use_gate_in_kernel else 0
+    beta_mode = 1 if use_beta_sigmoid_in_kernel else 0
     plan = make_plan(q.shape[0], q.shape[1], cu_seqlens, q.device, host=cu_seqlens_cpu)
     return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
-                                             plan)
+                                             plan, A_log, dt_bias, gate_mode, beta_mode)

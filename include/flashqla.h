@@ -97,6 +97,28 @@ FQ_API int fq_kkt_solve_fused(const void* k, const void* q, const float* beta, c
                               const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale, void* stream);
 
 /*
+ * fq_kkt_solve_fused (without P_g) that also applies the activations of the caller's RAW gate and beta inputs while it
+ * loads them, so that the elementwise passes a caller otherwise runs before the operator disappear
+ * (flash_qla/ops/gated_delta_rule/chunk/__init__.py:30 takes an already activated g; the l2norm half of the same idea
+ * is flash_qla/utils/math.py:7-21):
+ *   gate_mode 0: g_raw is the log gate;  1: g = logsigmoid(g_raw);  2: g = -exp(A_log[h]) * softplus(g_raw + dt_bias[h])
+ *             (A_log [H] fp32; dt_bias [H] fp32 or NULL);
+ *   beta_mode 0: beta_raw is beta;  1: beta = sigmoid(beta_raw), also written to beta_out [B,T,H] fp32, which is what
+ *             the recurrence and backward kernels then take as beta.
+ * g_cumsum [B,T,H] receives the chunk-local sum of the ACTIVATED gate.  fq_gate_act_bwd is the backward of the
+ * activations: dg / db (w.r.t. the activated values, as fq_gdr_bwd_chunk + the reverse fq_chunk_cumsum deliver them)
+ * -> dg_raw / db_raw, and for gate mode 2 the per-head sums dA_log, ddt_bias ([H] fp32, ADDED to: zero them first;
+ * either may be NULL).  db / beta_raw / db_raw may be NULL together.
+ */
+FQ_API int fq_kkt_solve_fused_act(const void* k, const float* beta_raw, const float* g_raw, const float* A_log,
+                                  const float* dt_bias, int gate_mode, int beta_mode, float* g_cumsum, float* beta_out,
+                                  void* A, void* Ag, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
+                                  const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale, void* stream);
+FQ_API int fq_gate_act_bwd(const float* dg, const float* db, const float* g_raw, const float* beta_raw, const float* A_log,
+                           const float* dt_bias, int gate_mode, int beta_mode, float* dg_raw, float* db_raw, float* dA_log,
+                           float* ddt_bias, long long rows, int H, void* stream);
+
+/*
  * Fused forward recurrence: per (sequence, V-head) walks the chunks, carries the fp32 K x V state
  * and writes o = scale*exp(g) o (Q S) + P_g V_d per chunk.
  * Replaces fused_gdr_fwd, flash_qla/ops/gated_delta_rule/chunk/hopper/fused_fwd.py:535-658

@@ -184,3 +184,48 @@ def test_repeated_forward_backward_is_race_free():
                     assert torch.equal(x, r), f"{n} differs in repetition {rep}"
     finally:
         ops._FORCE_PIECE_CHUNKS = old
+
+
+@pytest.mark.parametrize("gate_mode,beta_sigmoid,cu", [(1, True, None), (2, True, None), (2, False, [0, 100, 101, 470]), (1, False, None)])
+def test_gate_activations_in_kernel(gate_mode, beta_sigmoid, cu):
+    """use_gate_in_kernel / use_beta_sigmoid_in_kernel: raw gate and beta inputs, activations applied inside the tile
+    kernel, their derivatives inside the backward.  Reference: the oracle on torch-activated inputs, with torch.autograd
+    carrying the oracle's dg / dbeta through the activations (fp32).  Tolerance 1e-2 rel-to-max as elsewhere."""
+    import flash_qla
+    torch.manual_seed(23)
+    B, T, Hq, Hv = (2, 200, 2, 4) if cu is None else (1, cu[-1], 2, 4)
+    N = B if cu is None else len(cu) - 1
+    q = orc.l2norm(torch.randn(B, T, Hq, 128)).bfloat16()
+    k = orc.l2norm(torch.randn(B, T, Hq, 128)).bfloat16()
+    v = torch.randn(B, T, Hv, 128).bfloat16()
+    g_raw = torch.randn(B, T, Hv)
+    b_raw = torch.randn(B, T, Hv)
+    A_log = torch.log(torch.empty(Hv).uniform_(0.5, 4.0))
+    dt_bias = 0.5 * torch.randn(Hv)
+    h0, dht = 0.1 * torch.randn(N, Hv, 128, 128), 0.01 * torch.randn(N, Hv, 128, 128)
+    do = torch.randn(B, T, Hv, 128).bfloat16()
+    cu_t = None if cu is None else torch.tensor(cu, dtype=torch.int32)
+    # reference: activations in torch (differentiable), operator maths in the oracle
+    leaves = [x.clone().requires_grad_() for x in (g_raw, b_raw, A_log, dt_bias)]
+    g_act = torch.nn.functional.logsigmoid(leaves[0]) if gate_mode == 1 else \
+        -leaves[2].exp() * torch.nn.functional.softplus(leaves[0] + leaves[3])
+    b_act = leaves[1].sigmoid() if beta_sigmoid else leaves[1]
+    gcr, _, o_ref, _, fs_ref = orc.gdr_fwd(q.float(), k.float(), v.float(), g_act.detach(), b_act.detach(), None, h0, cu_t)
+    ref = orc.gdr_bwd(q.float(), k.float(), v.float(), gcr, b_act.detach(), do.float(), dht, None, h0, cu_t)
+    torch.autograd.backward([g_act, b_act], [ref[4], ref[3]])
+    # operator with raw inputs
+    dev = "cuda"
+    kw = {}
+    ins = [x.to(dev).requires_grad_() for x in (q, k, v, g_raw, b_raw, h0)]
+    if gate_mode == 2:
+        kw = dict(A_log=A_log.to(dev).requires_grad_(), dt_bias=dt_bias.to(dev).requires_grad_())
+    o, fs = flash_qla.chunk_gated_delta_rule(ins[0], ins[1], ins[2], ins[3], ins[4], initial_state=ins[5],
+                                             output_final_state=True, cu_seqlens=None if cu is None else cu_t.to(dev),
+                                             use_gate_in_kernel=True, use_beta_sigmoid_in_kernel=beta_sigmoid, **kw)
+    check_close([o, fs], [o_ref, fs_ref], {"o": 1e-2, "final_state": 5e-3}, ["o", "final_state"])
+    ((o.float() * do.to(dev).float()).sum() + (fs * dht.to(dev)).sum()).backward()
+    got = [ins[0].grad, ins[1].grad, ins[2].grad, ins[4].grad, ins[3].grad, ins[5].grad]
+    want = [ref[0], ref[1], ref[2], leaves[1].grad, leaves[0].grad, ref[5]]
+    check_close(got, want, TOL, ["dq", "dk", "dv", "db_raw", "dg_raw", "dh0"])
+    if gate_mode == 2:
+        check_close([kw["A_log"].grad, kw["dt_bias"].grad], [leaves[2].grad, leaves[3].grad], TOL, ["dA_log", "ddt_bias"])
