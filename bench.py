@@ -490,7 +490,7 @@ def sequence_parallel_run(bn, w, steps, warmup, check=True):
             gc, A, o, _, fs, tiles, _ = ops.chunk_gated_delta_rule_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], scale, None, None,
                                                                     True, False, True, _return_tiles=True)
             ops.chunk_gated_delta_rule_bwd(d["q"], d["k"], d["v"], gc, d["beta"], A, d["do"], None, scale, None, None,
-                                           _gated_tiles=tiles)
+                                           _gated_tiles=tiles[:2])
             return
         o, fs, saved = fqd.cp_forward(d["q"], d["k"], d["v"], d["g"], d["beta"], scale, None, None, impl=impl)
         fqd.cp_backward(saved, d["do"], None, None, impl=impl)

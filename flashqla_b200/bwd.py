@@ -12,9 +12,11 @@ from .planner import plan_cp
 
 
 def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, initial_state=None, cu_seqlens=None,
-                               gated_tiles=None, plan=None, want_dh0=None):
+                               gated_tiles=None, plan=None, want_dh0=None, h_saved=None):
     """``gated_tiles`` = (A_g, P_g) as produced by the forward for the same inputs; when given, the pass that
-    rebuilds them from ``A`` is skipped (the autograd function keeps them unless FLASHQLA_RECOMPUTE_TILES=1)."""
+    rebuilds them from ``A`` is skipped (the autograd function keeps them unless FLASHQLA_RECOMPUTE_TILES=1).
+    ``h_saved``: the bf16 state before every chunk as the forward kernel stored it ([.., V, K]); when given, the state
+    pass that recomputes it is skipped."""
     kernels._require_cuda(q, k, v, g, beta, A, do)
     if q.dtype != torch.bfloat16:
         raise _lib.FlashQLAError("chunk_gated_delta_rule_bwd: only bfloat16 q/k/v are supported")
@@ -52,9 +54,12 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
         # gate scans in both directions; pairs that would replay too far start from corrected states / gradients
         warm = kernels.cp_warmup(g, cp, H, with_reverse=True)
         h0_piece, tmats = kernels.cp_correct_states(q, k, v, Ag, g, bt, scale, h0, cp, warm, status, return_bt=True)
-    _, h, _ = kernels.fused_gdr_fwd(q, k, v, Ag, None, g, bt, scale, initial_state=h0, output_final_state=False,
-                                    output_h=True, output_o=False, plan=plan, cp=cp, warmup=warm, status=status,
-                                    h0_piece=h0_piece)
+    if h_saved is not None:
+        h = h_saved
+    else:
+        _, h, _ = kernels.fused_gdr_fwd(q, k, v, Ag, None, g, bt, scale, initial_state=h0, output_final_state=False,
+                                        output_h=True, output_o=False, plan=plan, cp=cp, warmup=warm, status=status,
+                                        h0_piece=h0_piece)
     # 2. reverse recurrence of the state gradient
     dh = torch.empty_like(h)
     if want_dh0 is None:

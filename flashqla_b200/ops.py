@@ -17,6 +17,10 @@ _FORCE_PIECE_CHUNKS = int(os.environ["FLASHQLA_PIECE_CHUNKS"]) if "FLASHQLA_PIEC
 # The autograd function keeps the gated operand tiles A_g and P_g (2 x [B,T,H,64] bf16) for the backward, which then
 # skips the pass that rebuilds them; set FLASHQLA_RECOMPUTE_TILES=1 to keep only A, like the reference does.
 _RECOMPUTE_TILES = os.environ.get("FLASHQLA_RECOMPUTE_TILES", "0") == "1"
+# It also keeps the bf16 state before every chunk (32 KiB per chunk and V-head, written by the forward kernel on its way)
+# when that tensor stays below this budget, so that the backward need not recompute it with a second state pass; larger
+# problems (and FLASHQLA_KEEP_STATES_MB=0) recompute like the reference does.
+_KEEP_STATES_BYTES = int(float(os.environ.get("FLASHQLA_KEEP_STATES_MB", "2048")) * (1 << 20))
 
 
 class _L2NormFunction(torch.autograd.Function):
@@ -55,7 +59,7 @@ def l2norm(x: torch.Tensor, dim: int = -1, eps: float = 1e-6) -> torch.Tensor:
 
 def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None, cu_seqlens=None,
                                output_final_state=True, output_h=False, auto_cp=True, _return_tiles=None, _plan=None,
-                               _want_A=True, _act=None):
+                               _want_A=True, _act=None, _keep_h=False):
     """Forward pipeline (chunk/__init__.py:17-67): [cumsum + K K^T + solve + gated tiles] -> fused recurrence.
 
     Returns ``(g_cumsum, A, o, h, final_state)``; ``A`` is the gate-free inverse (opaque, only
@@ -82,26 +86,28 @@ def chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None,
         cp = plan_cp(plan, B, T, H, kernels.sm_count(q.device), q.device, piece_chunks=_FORCE_PIECE_CHUNKS)
         if cp is not None:
             warm = kernels.cp_warmup(g_cum, cp, H)
+    keep_h = _keep_h and plan.total_chunks * H * K * v.shape[-1] * 2 <= _KEEP_STATES_BYTES
     o, h, final_state = kernels.fused_gdr_fwd(q, k, v, Ag, Pg, g_cum, beta, scale, initial_state=initial_state,
-                                              output_final_state=output_final_state, output_h=output_h,
+                                              output_final_state=output_final_state, output_h=output_h or keep_h,
                                               plan=plan, cp=cp, warmup=warm, status=status)
     if status is not None:
         kernels.check_status(status, "fq_gdr_fwd")
+    h_kernel = h if keep_h else None  # [.., V, K] as the kernels store and read it
     if h is not None:
-        h = h.transpose(-1, -2)  # stored [.., V, K] by the kernel; the interface is [.., K, V]
+        h = h.transpose(-1, -2) if output_h else None  # the interface is [.., K, V]
     if _return_tiles is not None:
-        return g_cum, A, o, h, final_state, ((Ag, Pg) if _return_tiles else None), beta
+        return g_cum, A, o, h, final_state, ((Ag, Pg, h_kernel) if _return_tiles else None), beta
     return g_cum, A, o, h, final_state
 
 
 def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, initial_state=None, cu_seqlens=None,
-                               _gated_tiles=None, _plan=None, _want_dh0=None):
+                               _gated_tiles=None, _plan=None, _want_dh0=None, _h_saved=None):
     """Backward pipeline (chunk/__init__.py:70-113).  ``g`` is the cumsum returned by the forward,
     ``A`` the tensor returned by the forward.  Returns ``(dq, dk, dv, db, dg, dh0)``; ``dh0`` is None when
     neither ``dht`` nor ``initial_state`` is given (``_want_dh0`` overrides that rule)."""
     from . import bwd  # the backward kernels live in their own module
     return bwd.chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht, scale, initial_state, cu_seqlens,
-                                          gated_tiles=_gated_tiles, plan=_plan, want_dh0=_want_dh0)
+                                          gated_tiles=_gated_tiles, plan=_plan, want_dh0=_want_dh0, h_saved=_h_saved)
 
 
 class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
@@ -120,7 +126,8 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
         g_cum, A, o, _, final_state, tiles, beta_act = chunk_gated_delta_rule_fwd(
             q=q, k=k, v=v, g=g, beta=beta, scale=scale, initial_state=initial_state,
             output_final_state=output_final_state, output_h=False, cu_seqlens=cu_seqlens,
-            _return_tiles=needs_bwd and not _RECOMPUTE_TILES, _plan=plan, _want_A=needs_bwd, _act=act)
+            _return_tiles=needs_bwd and not _RECOMPUTE_TILES, _plan=plan, _want_A=needs_bwd, _act=act,
+            _keep_h=needs_bwd and not _RECOMPUTE_TILES)
         if not needs_bwd:
             return o.to(q.dtype), final_state
         ctx.plan = plan  # the backward reuses the forward's sequence plan (no second look at cu_seqlens)
@@ -128,8 +135,12 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
         ctx.act = act is not None
         ctx.modes = (gate_mode, beta_mode)
         extra = (g, beta, A_log, dt_bias) if act is not None else ()
+        ctx.keep_h = False
         if ctx.keep_tiles:
-            ctx.save_for_backward(q, k, v, g_cum, beta_act, A, initial_state, cu_seqlens, *tiles, *extra)
+            Ag, Pg, h_kernel = tiles
+            ctx.keep_h = h_kernel is not None
+            kept = (Ag, Pg, h_kernel) if ctx.keep_h else (Ag, Pg)
+            ctx.save_for_backward(q, k, v, g_cum, beta_act, A, initial_state, cu_seqlens, *kept, *extra)
         else:
             ctx.save_for_backward(q, k, v, g_cum, beta_act, A, initial_state, cu_seqlens, *extra)
         ctx.scale = scale
@@ -143,9 +154,13 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
         q, k, v, g_cum, beta, A, initial_state, cu_seqlens = ctx.saved_tensors[:8]
         n = 8
         tiles = None
+        h_saved = None
         if ctx.keep_tiles:
             tiles = tuple(ctx.saved_tensors[8:10])
             n = 10
+            if ctx.keep_h:
+                h_saved = ctx.saved_tensors[10]
+                n = 11
         # a gradient for the initial state is formed only if one was passed in and asks for it: returning a tensor
         # for an input that was None (initial_state=None with output_final_state=True, the first segment of a
         # truncated back-propagation) is an autograd error
@@ -153,7 +168,7 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
         dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(
             q=q, k=k, v=v, g=g_cum, beta=beta, A=A, do=do, dht=dht, scale=ctx.scale,
             initial_state=initial_state, cu_seqlens=cu_seqlens, _gated_tiles=tiles, _plan=ctx.plan,
-            _want_dh0=need_dh0)
+            _want_dh0=need_dh0, _h_saved=h_saved)
         dA_log = ddt_bias = None
         if ctx.act:
             g_raw, b_raw, A_log, dt_bias = ctx.saved_tensors[n:n + 4]
