@@ -1,6 +1,7 @@
 // Chunk-local prefix / suffix sum of the log-gate.  HBM-bound: 8 bytes per (token, head).
 // One thread owns one (chunk, head) column of 64 tokens; consecutive threads own consecutive
-// heads, so every load and store of a warp covers contiguous head runs of the [tokens, H] rows.
+// heads, so every load and store of a warp covers contiguous head runs of the [tokens, H] rows (whole 32-byte
+// sectors from H = 8 on).
 #include "flashqla.h"
 #include "host.cuh"
 #include "seq.cuh"
@@ -17,22 +18,34 @@ __global__ void __launch_bounds__(256) chunk_cumsum_kernel(const float* __restri
   const size_t base = static_cast<size_t>(p.tok0) * H + h;
   const float* src = g + base;
   float* dst = out + base;
-  float v[kChunk];
-#pragma unroll
-  for (int i = 0; i < kChunk; ++i) v[i] = (i < p.len) ? src[static_cast<size_t>(i) * H] : 0.f;
+  // Sixteen rows at a time: the sixteen loads are independent (in flight together), the running sum is carried across the
+  // four blocks.  A thread then needs about forty registers, so the SM holds its full complement of warps - with all 64
+  // rows in registers (143 registers) it held an eighth of them and the kernel ran at the latency of its own loads.
   float acc = 0.f;
-  if (!reverse) {
+#pragma unroll 1
+  for (int blk = 0; blk < kChunk / 16; ++blk) {
+    const int r0 = reverse ? kChunk - 16 * (blk + 1) : 16 * blk;
+    if (!reverse && r0 >= p.len) break;
+    if (reverse && r0 >= p.len) continue;
+    float v[16];
 #pragma unroll
-    for (int i = 0; i < kChunk; ++i) {
-      acc += v[i];
-      if (i < p.len) dst[static_cast<size_t>(i) * H] = acc;
-    }
-  } else {
+    for (int i = 0; i < 16; ++i) v[i] = (r0 + i < p.len) ? __ldg(src + static_cast<size_t>(r0 + i) * H) : 0.f;
+    if (!reverse) {
 #pragma unroll
-    for (int i = kChunk - 1; i >= 0; --i) {
-      acc += v[i];
-      if (i < p.len) dst[static_cast<size_t>(i) * H] = acc;
+      for (int i = 0; i < 16; ++i) {
+        acc += v[i];
+        v[i] = acc;
+      }
+    } else {
+#pragma unroll
+      for (int i = 15; i >= 0; --i) {
+        acc += v[i];
+        v[i] = acc;
+      }
     }
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (r0 + i < p.len) dst[static_cast<size_t>(r0 + i) * H] = v[i];
   }
 }
 
@@ -158,8 +171,12 @@ __global__ void __launch_bounds__(256) gate_act_bwd_kernel(const float* __restri
     for (int i = threadIdx.x; i < 2 * H; i += blockDim.x) part[i] = 0.f;
     __syncthreads();
   }
-  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
-       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+  // when the grid stride is a multiple of H every thread stays on one head: its two sums then live in registers and
+  // reach shared memory once, instead of two shared-memory atomics per element
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const bool one_head = sums && (stride % H) == 0;
+  float acc_a = 0.f, acc_b = 0.f;
+  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
     const int h = static_cast<int>(idx % H);
     const float d = dg[idx];
     float out = d;
@@ -171,8 +188,11 @@ __global__ void __launch_bounds__(256) gate_act_bwd_kernel(const float* __restri
       const float sp = z > 20.f ? z : log1pf(__expf(z));
       const float dz = -ea / (1.f + __expf(-z));          // d g / d z
       out = d * dz;
-      if (sums) {
-        atomicAdd(&part[h], d * (-ea * sp));              // d g / d A_log = g
+      if (one_head) {
+        acc_a += d * (-ea * sp);                          // d g / d A_log = g
+        acc_b += out;
+      } else if (sums) {
+        atomicAdd(&part[h], d * (-ea * sp));
         atomicAdd(&part[H + h], out);
       }
     }
@@ -185,6 +205,11 @@ __global__ void __launch_bounds__(256) gate_act_bwd_kernel(const float* __restri
       }
       db_raw[idx] = o2;
     }
+  }
+  if (one_head) {
+    const int h = static_cast<int>((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) % H);
+    atomicAdd(&part[h], acc_a);
+    atomicAdd(&part[H + h], acc_b);
   }
   if (sums) {
     __syncthreads();
