@@ -353,14 +353,14 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const float gL = s.gate[gs][1][kChunk - 1];
         const bool store_h = (p.h_out != nullptr) && (n >= 0);
         constexpr bool state_only = kStateOnly;  // then the chain takes the bf16 state from tensor memory
-        if (p.h_out != nullptr && !state_only) {  // the previous chunk's TMA store must have read the operand buffer
-          if (tid == 128) tma_store_wait_read<0>();
-          asm volatile("bar.sync 2, 256;" ::: "memory");
-        }
         // both 32-column pieces are loaded before anything is stored, so only one TMEM round trip is exposed
         uint32_t r0[32], r1[32];
         tmem_ld32(tmem_addr(tm, lane_base, kColS + 64 * hf), r0);
         tmem_ld32(tmem_addr(tm, lane_base, kColS + 64 * hf + 32), r1);
+        if (p.h_out != nullptr && !state_only) {  // the previous chunk's TMA store must have read the operand buffer;
+          if (tid == 128) tma_store_wait_read<0>();  // waited for while the state is on its way from tensor memory
+          asm volatile("bar.sync 2, 256;" ::: "memory");
+        }
         tmem_wait_ld();
         uint32_t pk[32];
 #pragma unroll
