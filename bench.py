@@ -68,7 +68,7 @@ BWD_BYTES_PER_UNIT = 7 * 16384 + 1024
 FWD_MFLOP, BWD_MFLOP, BWD_CHUNK_MFLOP = 10.49, 31.46, 26.21
 # DRAM traffic per unit from ncu captures of the profiling cases (dram__bytes_read.sum + dram__bytes_write.sum over the
 # units of the captured launch; traffic grows in proportion to the units, so a full launch is units x this figure)
-NCU_TRAFFIC_PER_UNIT = {"gdr_fwd_kernel": 674940416 / 8192, "kkt_solve_kernel": 378400000 / 8192,
+NCU_TRAFFIC_PER_UNIT = {"gdr_fwd_kernel": 604.4e6 / 8192, "kkt_solve_tc_kernel": 178.7e6 / 8192,
                         "gdr_bwd_chunk_kernel": 183.0e3}
 
 
@@ -367,13 +367,13 @@ def fwd_blocks(w, ms_step, kernel_ms, peaks, how):
     roof["step_achieved"] = alg / (ms_step * 1e-3) / 1e9
     roof["step_frac"] = roof["step_achieved"] / peaks["hbm_gbs"]
     roof["step_tensor_frac"] = units * FWD_MFLOP * 1e6 / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"]
-    # the tile kernel's own input / output: k, q per QK head; g, beta in; g_cumsum, A_g, P_g out per V-head
-    kkt_own = units * (2 * 16384 * Hq // Hv + 2 * 8192 + 3 * 256)
-    kkt = hbm_block("kkt_solve_kernel", kkt_ms, kkt_own, peaks, how,
-                    traffic=units * NCU_TRAFFIC_PER_UNIT["kkt_solve_kernel"] if same else None,
-                    extra={"bytes_are": "the kernel's own inputs and outputs (k, q, g, beta; g_cumsum, A_g, P_g); its "
+    # the tile kernel's own input / output: k per QK head; g, beta in; g_cumsum, A_g out per V-head
+    kkt_own = units * (16384 * Hq // Hv + 8192 + 3 * 256)
+    kkt = hbm_block("kkt_solve_tc_kernel", kkt_ms, kkt_own, peaks, how,
+                    traffic=units * NCU_TRAFFIC_PER_UNIT["kkt_solve_tc_kernel"] if same else None,
+                    extra={"bytes_are": "the kernel's own inputs and outputs (k, g, beta; g_cumsum, A_g); its "
                                         "outputs are intermediates of the forward, so they do not count in step_frac"})
-    return roof, {"kkt_solve_kernel": kkt}
+    return roof, {"kkt_solve_tc_kernel": kkt}
 
 
 def bwd_blocks(w, ms_step, kernel_ms, peaks, how):
