@@ -337,8 +337,10 @@ def measure_forward(bn, w, d, steps, warmup):
     return ms, kernel_ms, launches, ms_stage
 
 
-def measure_fwd_bwd(bn, w, d, steps, warmup):
-    """Forward + backward through the differentiable operator and torch.autograd."""
+def measure_fwd_bwd(bn, w, d, steps, warmup, graph=False):
+    """Forward + backward through the differentiable operator and torch.autograd.  ``graph``: additionally capture the
+    step in a CUDA graph and time its replay (a step of a few hundred microseconds is bound by the host's launch rate
+    otherwise); returns a fourth value then, the replay's ms per step or None when the capture failed."""
     import flashqla_b200 as fq
     scale = 128 ** -0.5
     leaves = [d[k_].detach().requires_grad_() for k_ in ("q", "k", "v", "g", "beta", "h0")]
@@ -350,7 +352,28 @@ def measure_fwd_bwd(bn, w, d, steps, warmup):
                                           initial_state=leaves[5], output_final_state=True)
         torch.autograd.backward([o, fs], [d["do"], d["dht"]])
 
-    return bn.timed(step, steps, warmup)
+    if not graph:
+        return bn.timed(step, steps, warmup)
+    eager = bn.timed(step, steps, warmup, record=False)
+    replay_ms, cg = None, None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg):
+            step()
+    except Exception as exc:  # the eager figure stands
+        cg = None
+        print(f"[bench] CUDA graph capture of the fwd+bwd step failed: {exc}", file=sys.stderr, flush=True)
+    # the replay is timed between barriers: every rank takes part, or none does
+    if bn.max_over_ranks([0.0 if cg is not None else 1.0])[0] == 0.0:
+        replay_ms = bn.timed(cg.replay, steps, warmup, record=False)[0]
+    return eager + (replay_ms,)
 
 
 def fwd_blocks(w, ms_step, kernel_ms, peaks, how):
@@ -532,9 +555,12 @@ def multi_gpu_blocks(bn, t1_c3_ms):
     gen = torch.Generator(device=dev).manual_seed(400 + rank)
     d["h0"] = 0.1 * torch.randn(Bl, Hvl, 128, 128, device=dev, generator=gen)
     d["dht"] = 0.01 * torch.randn(Bl, Hvl, 128, 128, device=dev, generator=gen)
-    ms, _, _ = measure_fwd_bwd(bn, w3, d, 50, 3)
-    ms = bn.max_over_ranks([ms])[0]
+    ms_eager, _, _, ms_graph = measure_fwd_bwd(bn, w3, d, 50, 3, graph=True)
+    ms_eager, ms_graph = bn.max_over_ranks([ms_eager, ms_graph if ms_graph is not None else float("inf")])
+    ms = min(ms_eager, ms_graph)
     res["c3_sharded"] = {"scaling": "strong", "workload": w3["desc"], "ms_per_step": ms,
+                         "launch": "CUDA graph replay of the captured fwd+bwd step" if ms == ms_graph else "eager",
+                         "ms_per_step_eager": ms_eager, "ms_per_step_graph": ms_graph if ms_graph != float("inf") else None,
                          "tokens_per_s": w3["B"] * w3["T"] / (ms * 1e-3), "ms_per_step_1gpu": t1_c3_ms,
                          "efficiency_vs_1gpu": t1_c3_ms / (world * ms), "collective": "none (units are independent)",
                          "units_per_rank": Bl * Hql, "shard": f"B={Bl} Hq={Hql} Hv={Hvl} per rank"}

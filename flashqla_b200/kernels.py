@@ -14,7 +14,15 @@ from .planner import SeqPlan, plan_dense, plan_packed
 CHUNK = 64
 
 
+try:  # the raw handle of the current stream without building a torch.cuda.Stream object (15 us -> under 1 us per launch)
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+except AttributeError:  # pragma: no cover - a torch without that binding
+    _raw_stream = None
+
+
 def _stream() -> int:
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
