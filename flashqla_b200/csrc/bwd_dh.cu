@@ -223,15 +223,11 @@ gdr_bwd_dh_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       const int len = min(kChunk, avail - n * kChunk);
       const size_t row = static_cast<size_t>(tok_begin) + n * kChunk;
       const float gl = __ldg(p.g_cum + (row + len - 1) * p.H + h);
-      float gi = gl, bi = 0.f;
-      if (t < len) {
-        gi = __ldg(p.g_cum + (row + t) * p.H + h);
-        bi = __ldg(p.beta + (row + t) * p.H + h);
-      }
+      // (beta is folded into the A_g tile by the pre-kernel: this kernel never reads it)
+      const float gi = (t < len) ? __ldg(p.g_cum + (row + t) * p.H + h) : gl;
       s.gate[gs][0][t] = gi;
       s.gate[gs][1][t] = fast_exp(gi);
       s.gate[gs][2][t] = (t < len) ? fast_exp(gl - gi) : 0.f;
-      s.gate[gs][3][t] = bi;
       mbar_arrive(&s.gate_full[gs]);
     }
   } else if (warp < 8) {

@@ -56,7 +56,7 @@ struct FwdSmem {
   unsigned char sbf[32768];    // bf16 S^T [128 v][128 k] as two 128-row regions
   unsigned char vd[16384];     // V_d^T             [128 v][64 i]
   unsigned char ostage[16384]; // o tile of a whole chunk [64 c][128 v] as two 64-row regions (v 0-63 | 64-127): TMA store
-  float gate[kGateStages][4][kChunk];  // g, exp(g), exp(g_last - g), beta
+  float gate[kGateStages][4][kChunk];  // g, exp(g), exp(g_last - g), (unused)
   uint64_t full[2], empty[2], gate_full[kGateStages], gate_empty[kGateStages];
   uint64_t uq_done, vd_done, s_done, o_done, qk_done;
   uint64_t pq_ready;
@@ -305,15 +305,11 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const int len = min(kChunk, seq_len - n * kChunk);  // replayed chunks (n < 0) are always whole
       const long long row = static_cast<long long>(tok_begin) + static_cast<long long>(n) * kChunk;
       const float gl = __ldg(p.g_cum + (row + len - 1) * p.H + h);
-      float gi = gl, bi = 0.f;
-      if (t < len) {
-        gi = __ldg(p.g_cum + (row + t) * p.H + h);
-        bi = __ldg(p.beta + (row + t) * p.H + h);
-      }
+      // (beta is folded into the A_g tile by the pre-kernel: this kernel never reads it)
+      const float gi = (t < len) ? __ldg(p.g_cum + (row + t) * p.H + h) : gl;
       s.gate[gs][0][t] = gi;
       s.gate[gs][1][t] = fast_exp(gi);
       s.gate[gs][2][t] = (t < len) ? fast_exp(gl - gi) : 0.f;
-      s.gate[gs][3][t] = bi;
       mbar_arrive(&s.gate_full[gs]);
     }
   } else if (warp < 12) {
