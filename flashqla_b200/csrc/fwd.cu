@@ -33,6 +33,7 @@
 #include "flashqla.h"
 #include "host.cuh"
 #include "seq.cuh"
+#include "fwd_params.cuh"
 
 namespace fq {
 
@@ -64,30 +65,6 @@ struct FwdSmem {
   uint64_t drain_bar;  // only used by drain_after_abort
   uint32_t tmem_base;
   int abort_flag;
-};
-
-struct FwdParams {
-  const float* g_cum;   // [rows, H] chunk-local cumsum of the log gate
-  const float* beta;    // [rows, H]
-  const float* h0;      // [n_h0, H, 128, 128] or nullptr
-  float* ht;            // [n_out, H, 128, 128] or nullptr
-  const int* ht_index;  // [n_seq] slot in ht per piece (negative: do not write) or nullptr (= piece index)
-  const int* h0_index;  // [n_seq] slot in h0 per piece or nullptr (= piece index)
-  const int* warmup;    // [n_entries, H] chunks to replay before the piece; bit 30 set = the replay starts at the
-                        //            sequence start (use h0), else start from zero.  nullptr = {0 | bit 30}.
-                        //            bit 29: start from h0_piece[piece] (no replay); bit 28: transition run (S = I and
-                        //            the V tile ignored: the final state is the piece's transition matrix);
-                        //            bit 27: nothing to do for this (entry, head)
-  const int* piece_map; // [n_entries] piece of each grid entry, or nullptr (= entry); warmup and ht_index are per entry
-  const float* h0_piece;  // [n_pieces, H, 128, 128] corrected start states (bit 29) or nullptr
-  __nv_bfloat16* o;     // [rows, H, 128] or nullptr
-  __nv_bfloat16* pg_out;  // [rows, H, 64] or nullptr: the P_g tiles, kept for the backward (only written together with o)
-  __nv_bfloat16* h_out; // [total_chunks, H, 128(v), 128(k)] TRANSPOSED state before each chunk, or nullptr
-                        // (written by TMA straight from the bf16 operand buffer)
-  int H, Hg;
-  float scale;
-  SeqArgs sa;
-  int* status_dev;
 };
 
 __device__ __forceinline__ uint32_t kq_off(int kk) { return (kk >> 2) * 16384 + (kk & 3) * 32; }
@@ -694,6 +671,8 @@ extern "C" FQ_API int fq_gdr_fwd_cp_ex(const void* q, const void* k, const void*
   }
   const long long ctas = static_cast<long long>(n_entries) * H;
   FQ_CHECK_ARG(ctas < (1ll << 31), "fq_gdr_fwd: too many (sequence, head) pairs");
+  if (o != nullptr && h_out != nullptr)  // a forward that keeps its states for a backward: the variant built for that
+    return launch_gdr_fwd_train(mq, mk, mv, ma, mpg, mh, mo, p, static_cast<unsigned>(ctas), static_cast<cudaStream_t>(stream));
   auto kern = (o != nullptr) ? gdr_fwd_kernel<false> : gdr_fwd_kernel<true>;
   kern<<<static_cast<unsigned>(ctas), kFwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, ma, mpg, mh, mo, p);
   FQ_CHECK_CUDA(cudaGetLastError());
