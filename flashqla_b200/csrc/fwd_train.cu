@@ -521,14 +521,14 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       mbar_wait(wc, &s.gate_full[gs], (it >> 2) & 1, 18);
       mbar_wait(wc, &s.o_done, ph, 21);
       tc_fence_after();
-      bool staged = false, oi_released = false;
+      bool staged = false, oi_released = false, whole = false;
       if (!kStateOnly && n >= 0) {
-        const int len = min(kChunk, seq_len - n * kChunk);
-        // A whole chunk leaves through a shared-memory tile and two TMA stores (coalesced, and off the load/store
-        // pipe that the chain group needs); a tail chunk is written row by row so that nothing past the sequence end
-        // is touched.
-        staged = len == kChunk;
-        if (staged) {  // the previous chunk's TMA store has read the tile
+        // The chunk is transposed into a shared-memory tile; a whole chunk leaves by two TMA stores (coalesced, and off
+        // the load/store pipe that the chain group needs), of a tail chunk only the rows below the sequence end are
+        // copied out.
+        staged = true;
+        whole = seq_len - n * kChunk >= kChunk;
+        {  // the previous chunk's TMA store has read the tile
           if (tid == 384) tma_store_wait_read<0>();
           asm volatile("bar.sync 3, 128;" ::: "memory");
         }
@@ -551,7 +551,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           uint32_t ox[32];
           tmem_ld32(tmem_addr(tm, lane_base, kColOX + 32 * half), ox);
           tmem_wait_ld();
-          if (staged) {
+          {
 #pragma unroll
             for (int i4 = 0; i4 < 8; ++i4) {
               const float4 gm = *reinterpret_cast<const float4*>(&s.gate[gs][3][32 * half + 4 * i4]);
@@ -564,16 +564,6 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 *reinterpret_cast<__nv_bfloat16*>(tile + sw128(32 * half + i, bcol)) = two.x;
                 *reinterpret_cast<__nv_bfloat16*>(tile + sw128(32 * half + i + 1, bcol)) = two.y;
               }
-            }
-          } else {  // tail chunk: straight to global memory, rows below the sequence end only
-            __nv_bfloat16* dst = p.o + (static_cast<size_t>(tok_begin + n * kChunk) * p.H + h) * kDim + col;
-            const size_t row_stride = static_cast<size_t>(p.H) * kDim;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int cc = 32 * half + i;
-              if (cc < len)
-                dst[static_cast<size_t>(cc) * row_stride] =
-                    __float2bfloat16_rn(s.gate[gs][3][cc] * __uint_as_float(oi[i]) + __uint_as_float(ox[i]));
             }
           }
         }
@@ -588,12 +578,23 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
       if (staged) {
         fence_async_smem();
-        asm volatile("bar.sync 3, 128;" ::: "memory");  // all four warps have written (and fenced) their rows
-        if (tid == 384) {
-          const int row0 = tok_begin + n * kChunk;
-          tma_store_3d(&map_o, s.ostage, 0, h, row0);
-          tma_store_3d(&map_o, s.ostage + 8192, 64, h, row0);
-          tma_store_commit();
+        asm volatile("bar.sync 3, 128;" ::: "memory");  // all four warps have written (and fenced) their columns
+        const int row0 = tok_begin + n * kChunk;
+        if (whole) {
+          if (tid == 384) {
+            tma_store_3d(&map_o, s.ostage, 0, h, row0);
+            tma_store_3d(&map_o, s.ostage + 8192, 64, h, row0);
+            tma_store_commit();
+          }
+        } else {
+          // tail chunk: only the rows below the sequence end may be written; they are copied out of the tile, 16 bytes
+          // per thread and step (a row is 16 such pieces)
+          const int len = seq_len - n * kChunk;
+          for (int idx = tid - 384; idx < len * 16; idx += 128) {
+            const int row = idx >> 4, piece = idx & 15;
+            const uint4 x = *reinterpret_cast<const uint4*>(s.ostage + (piece >> 3) * 8192 + sw128(row, (piece & 7) * 16));
+            *(reinterpret_cast<uint4*>(p.o + (static_cast<size_t>(row0 + row) * p.H + h) * kDim) + piece) = x;
+          }  // (the barrier at the start of the next drain keeps the tile until every thread has copied its pieces)
         }
       }
     }
