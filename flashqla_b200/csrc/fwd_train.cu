@@ -21,7 +21,7 @@
 //    while the chain group converts the new state, and its P_g tile - formed by the two gate warps, which are the spare
 //    warps that can read TMEM lanes 64-127 - has the whole next chunk's time: the tile is off the chain and does
 //    not queue behind the output group's drain.
-// Measured on config 3 (forward with stored states): 0.346 ms against 0.456 ms for the arrangement of fwd.cu; without
+// Measured on config 3 (forward with stored states): 0.322 ms against 0.456 ms for the arrangement of fwd.cu; without
 // stored states this arrangement is the slower one (config 2: 0.68 ms against 0.63 ms), hence two kernels.
 //
 // Warp roles (16 warps): 0 TMA producer, 1 UMMA issuer, 2-3 gate loader + P_g tile, 4-11 chain group
