@@ -402,7 +402,7 @@ def fwd_blocks(w, ms_step, kernel_ms, peaks, how):
 def bwd_blocks(w, ms_step, kernel_ms, peaks, how):
     B, T, Hq, Hv = w["B"], w["T"], w["Hq"], w["Hv"]
     units = B * ((T + 63) // 64) * Hv
-    chunk_ms = pick(kernel_ms, "fq_gdr_bwd_chunk")
+    chunk_ms = pick(kernel_ms, "fq_gdr_bwd_chunk_grouped", "fq_gdr_bwd_chunk")
     blk = tensor_block("gdr_bwd_chunk_kernel", chunk_ms, units * BWD_CHUNK_MFLOP * 1e6, peaks, how,
                        traffic=units * NCU_TRAFFIC_PER_UNIT["gdr_bwd_chunk_kernel"])
     alg = units * (unit_bytes(FWD_BYTES_PER_UNIT, Hq, Hv) + unit_bytes(BWD_BYTES_PER_UNIT, Hq, Hv))

@@ -37,6 +37,7 @@ SIGNATURES = {
     "fq_gdr_bwd_dh": [_vp] * 10 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "fq_gdr_bwd_dh_cp": [_vp] * 14 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "fq_gdr_bwd_chunk": [_vp] * 16 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
+    "fq_gdr_bwd_chunk_grouped": [_vp] * 16 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "fq_gdr_bwd_chunk_gva_noalloc": [_vp] * 16 + [_i32] * 4 + [_vp, _vp, _i32, _i32, _f32, _vp, _vp],
     "fq_group_reduce": [_vp, _vp, ctypes.c_longlong, _i32, _i32, _vp],
     "fq_group_reduce_pair": [_vp, _vp, _vp, _vp, ctypes.c_longlong, _i32, _i32, _vp],

@@ -93,16 +93,18 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
                                      cp.out_index_bwd.data_ptr(), cp.seq_end.data_ptr(), warm.codes_rev.data_ptr(),
                                      dht_piece.data_ptr(), *tail)
     _lib.check(rc, "fq_gdr_bwd_dh")
-    # 3. chunk-parallel gradients
-    dq_h = torch.empty(B, T, H, K, dtype=q.dtype, device=dev)
-    dk_h = torch.empty(B, T, H, K, dtype=q.dtype, device=dev)
+    # 3. chunk-parallel gradients; with grouped value heads the kernel sums dq / dk over the V-heads of every QK head itself
+    #    (flash_qla/ops/gated_delta_rule/chunk/__init__.py:107-110 does it with a separate kernel)
+    dq = torch.empty(B, T, Hg, K, dtype=q.dtype, device=dev)
+    dk = torch.empty(B, T, Hg, K, dtype=q.dtype, device=dev)
     dg_c = torch.empty(B, T, H, dtype=torch.float32, device=dev)
     db = torch.empty(B, T, H, dtype=torch.float32, device=dev)
     dv = torch.empty_like(v)
-    rc = lib.fq_gdr_bwd_chunk(q.data_ptr(), k.data_ptr(), v.data_ptr(), A.data_ptr(), Ag.data_ptr(), Pg.data_ptr(),
-                              do.data_ptr(), h.data_ptr(), dh.data_ptr(), g.data_ptr(), bt.data_ptr(), dq_h.data_ptr(),
-                              dk_h.data_ptr(), dv.data_ptr(), dg_c.data_ptr(), db.data_ptr(), B, T, H, Hg, cu_p, off_p, plan.n_seq,
-                              plan.total_chunks, float(scale), st_p, kernels._stream())
+    entry = lib.fq_gdr_bwd_chunk_grouped if Hg < H else lib.fq_gdr_bwd_chunk
+    rc = entry(q.data_ptr(), k.data_ptr(), v.data_ptr(), A.data_ptr(), Ag.data_ptr(), Pg.data_ptr(),
+               do.data_ptr(), h.data_ptr(), dh.data_ptr(), g.data_ptr(), bt.data_ptr(), dq.data_ptr(),
+               dk.data_ptr(), dv.data_ptr(), dg_c.data_ptr(), db.data_ptr(), B, T, H, Hg, cu_p, off_p, plan.n_seq,
+               plan.total_chunks, float(scale), st_p, kernels._stream())
     _lib.check(rc, "fq_gdr_bwd_chunk")
     # 3b. the whole-state dot product in dg of a sequence's first / last chunk, corrected with the fp32 initial state /
     #     final-state gradient (the chunk kernel used their bf16 copies)
@@ -110,16 +112,7 @@ def chunk_gated_delta_rule_bwd(q, k, v, g, beta, A, do, dht=None, scale=None, in
         rc = lib.fq_dg_boundary_fix(pp(h0), pp(dht_c), h.data_ptr(), dh.data_ptr(), g.data_ptr(), dg_c.data_ptr(), B, T, H,
                                     cu_p, off_p, plan.n_seq, plan.total_chunks, kernels._stream())
         _lib.check(rc, "fq_dg_boundary_fix")
-    # 4. sum the V-heads of every QK head
-    if Hg < H:
-        dq = torch.empty(B, T, Hg, K, dtype=q.dtype, device=dev)
-        dk = torch.empty(B, T, Hg, K, dtype=q.dtype, device=dev)
-        rc = lib.fq_group_reduce_pair(dq_h.data_ptr(), dq.data_ptr(), dk_h.data_ptr(), dk.data_ptr(), B * T, H, Hg,
-                                      kernels._stream())
-        _lib.check(rc, "fq_group_reduce_pair")
-    else:
-        dq, dk = dq_h, dk_h
-    # 5. d/d(cumsum) -> d/d(raw gate)
+    # 4. d/d(cumsum) -> d/d(raw gate)
     dg = kernels.chunk_local_cumsum(dg_c, reverse=True, plan=plan)
     if status is not None:
         kernels.check_status(status, "backward kernels")

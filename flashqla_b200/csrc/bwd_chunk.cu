@@ -71,12 +71,14 @@ struct BwdChunkSmem {
 struct BwdChunkParams {
   const float* g_cum;
   const float* beta;
-  __nv_bfloat16* dq;  // [rows, H, 128]
-  __nv_bfloat16* dk;  // [rows, H, 128]
+  __nv_bfloat16* dq;  // [rows, Hout, 128]
+  __nv_bfloat16* dk;  // [rows, Hout, 128]
   float* dg;          // [rows, H]
   float* db;          // [rows, H]
   __nv_bfloat16* dv;  // [rows, H, 128]
   int H, Hg, total_chunks;
+  int Hout;     // H: dq / dk per V-head;  Hg (grouped): the kernel sums the V-heads of a QK head itself - a CTA then
+                // takes the heads of a group one after the other, stores the first head's tile and adds the others'
   float scale;
   SeqArgs sa;
   int* status_dev;
@@ -84,6 +86,20 @@ struct BwdChunkParams {
 
 __device__ __forceinline__ uint32_t off64(int kk) { return (kk >> 2) * 8192 + (kk & 3) * 32; }
 __device__ __forceinline__ uint32_t off128(int kk) { return (kk >> 2) * 16384 + (kk & 3) * 32; }
+
+// Eight bf16 values of a tail chunk's row: stored, or (grouped output, later heads of a group) added to what the same
+// thread stored for the earlier heads - the sum is formed in fp32 and rounded once, as the tile path does.
+__device__ __forceinline__ void row_out(__nv_bfloat16* dst, uint4 x, bool accum) {
+  uint4* ptr = reinterpret_cast<uint4*>(dst);
+  if (accum) {
+    const uint4 o = *ptr;
+    x.x = pack_bf16(bf16_lo(o.x) + bf16_lo(x.x), bf16_hi(o.x) + bf16_hi(x.x));
+    x.y = pack_bf16(bf16_lo(o.y) + bf16_lo(x.y), bf16_hi(o.y) + bf16_hi(x.y));
+    x.z = pack_bf16(bf16_lo(o.z) + bf16_lo(x.z), bf16_hi(o.z) + bf16_hi(x.z));
+    x.w = pack_bf16(bf16_lo(o.w) + bf16_lo(x.w), bf16_hi(o.w) + bf16_hi(x.w));
+  }
+  *ptr = x;
+}
 
 // sum over the 16 lanes of a half warp (lanes 0-15 and 16-31 reduce separately)
 __device__ __forceinline__ float half_warp_sum(float x) {
@@ -183,9 +199,13 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
     if (part != 0) tma_load_3d(dpg, &map_pg, &s.bar_tma_b, 0, h, r0);
   };
-  // Units (chunk, head) are walked with a stride of one grid; the index pair is stepped without divisions.
-  int chunk = static_cast<int>(blockIdx.x) / p.H, h = static_cast<int>(blockIdx.x) - chunk * p.H;
-  const int step_c = static_cast<int>(gridDim.x) / p.H, step_h = static_cast<int>(gridDim.x) - step_c * p.H;
+  // Units (chunk, head) are walked with a stride of one grid; the index pair is stepped without divisions.  Grouped
+  // output: the stride runs over (chunk, QK head) pairs and the V-heads of the pair follow one another (index j).
+  const bool grouped = p.Hout != p.H;
+  const int Hw = grouped ? p.Hg : p.H, Gw = grouped ? heads_per_group : 1;
+  int oc = static_cast<int>(blockIdx.x) / Hw, oh = static_cast<int>(blockIdx.x) - oc * Hw, j = 0;
+  const int step_c = static_cast<int>(gridDim.x) / Hw, step_h = static_cast<int>(gridDim.x) - step_c * Hw;
+  int chunk = oc, h = oh * Gw;
   if (tid == 0 && chunk < p.total_chunks) load_a(chunk, h);
 
   // raw gate values of a unit: threads 0-63 fetch them one unit ahead, so that the loads are not waited for
@@ -204,9 +224,15 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   if (tid < kChunk && chunk < p.total_chunks) fetch_gates(chunk, h);
 #pragma unroll 1
   for (int iter = 0; chunk < p.total_chunks; ++iter) {
-    int nchunk = chunk + step_c, nh = h + step_h;  // this CTA's next unit
-    if (nh >= p.H) { nh -= p.H; ++nchunk; }
+    int noc = oc, noh = oh, nj = j + 1;  // this CTA's next unit
+    if (nj >= Gw) {
+      nj = 0; noc = oc + step_c; noh = oh + step_h;
+      if (noh >= Hw) { noh -= Hw; ++noc; }
+    }
+    const int nchunk = noc, nh = noh * Gw + nj;
     const bool has_next = nchunk < p.total_chunks;
+    const bool accum = grouped && j > 0;   // dq / dk of this unit are added to the group's
+    const int ho = grouped ? h / heads_per_group : h;
     const int hg = h / heads_per_group;
     const ChunkPos cp = chunk_lookup(p.sa, chunk);
     const int len = cp.len;
@@ -645,7 +671,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
       }
       // dq
-      __nv_bfloat16* dst = p.dq + (static_cast<size_t>(cp.tok0 + row) * p.H + h) * kDim + 64 * hf;
+      __nv_bfloat16* dst = p.dq + (static_cast<size_t>(cp.tok0 + row) * p.Hout + ho) * kDim + 64 * hf;
       {
         tmem_ld32(tmem_addr(tm, lane_base, kBcColQ + 64 * hf + 32 * pc), r);
         tmem_wait_ld();
@@ -659,7 +685,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             x.w = pack_bf16(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
             // whole chunk: into the Q tile (dead since this round's products completed), stored by TMA below
             if (whole) *reinterpret_cast<uint4*>(b_qt + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = x;
-            else *reinterpret_cast<uint4*>(dst + 32 * pc + 8 * ch) = x;
+            else row_out(dst + 32 * pc + 8 * ch, x, accum);
           }
         }
       }
@@ -668,8 +694,14 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     fence_async_smem();
     __syncthreads();
     if (whole && tid == kStoreTid) {
-      tma_store_3d(&map_dq, b_qt, 0, h, cp.tok0);
-      tma_store_3d(&map_dq, b_qt + 8192, 64, h, cp.tok0);
+      if (accum) {  // the group's earlier tiles (stored or added by this thread) are complete in global memory
+        tma_store_wait_all<0>();
+        tma_reduce_add_3d(&map_dq, b_qt, 0, ho, cp.tok0);
+        tma_reduce_add_3d(&map_dq, b_qt + 8192, 64, ho, cp.tok0);
+      } else {
+        tma_store_3d(&map_dq, b_qt, 0, ho, cp.tok0);
+        tma_store_3d(&map_dq, b_qt + 8192, 64, ho, cp.tok0);
+      }
       tma_store_commit();
     }
 
@@ -754,7 +786,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     mma_phase ^= 1;
     tc_fence_after();
     {
-      __nv_bfloat16* dst = p.dk + (static_cast<size_t>(cp.tok0 + row) * p.H + h) * kDim + 64 * hf;
+      __nv_bfloat16* dst = p.dk + (static_cast<size_t>(cp.tok0 + row) * p.Hout + ho) * kDim + 64 * hf;
       {
         uint32_t r[32];
         tmem_ld32(tmem_addr(tm, lane_base, kBcColK + 64 * hf + 32 * pc), r);
@@ -769,7 +801,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             x.w = pack_bf16(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
             // whole chunk: into the K tile (dead since this round's products completed), stored by TMA below
             if (whole) *reinterpret_cast<uint4*>(b_kt + hf * 8192 + sw128(row, (4 * pc + ch) * 16)) = x;
-            else *reinterpret_cast<uint4*>(dst + 32 * pc + 8 * ch) = x;
+            else row_out(dst + 32 * pc + 8 * ch, x, accum);
           }
         }
       }
@@ -778,8 +810,13 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     fence_async_smem();
     __syncthreads();
     if (whole && tid == kStoreTid) {
-      tma_store_3d(&map_dk, b_kt, 0, h, cp.tok0);
-      tma_store_3d(&map_dk, b_kt + 8192, 64, h, cp.tok0);
+      if (accum) {  // (the wait before this unit's dq tile covered the group's earlier dk tiles as well)
+        tma_reduce_add_3d(&map_dk, b_kt, 0, ho, cp.tok0);
+        tma_reduce_add_3d(&map_dk, b_kt + 8192, 64, ho, cp.tok0);
+      } else {
+        tma_store_3d(&map_dk, b_kt, 0, ho, cp.tok0);
+        tma_store_3d(&map_dk, b_kt + 8192, 64, ho, cp.tok0);
+      }
       tma_store_commit();
     }
     if (tid < kChunk) {
@@ -802,6 +839,7 @@ gdr_bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       t = b_at; b_at = b_dvp; b_dvp = t;
       t = b_pg; b_pg = b_t12; b_t12 = t;
     }
+    oc = noc; oh = noh; j = nj;
     chunk = nchunk;
     h = nh;
   }
@@ -866,14 +904,13 @@ static int launch_group_reduce(const void* in0, void* out0, const void* in1, voi
 
 }  // namespace fq
 
-extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void* v, const void* A, const void* Ag,
-                                       const void* Pg, const void* dout, const void* h, const void* dh,
-                                       const float* g_cumsum, const float* beta, void* dq, void* dk, void* dv, float* dg,
-                                       float* db,
-                                       int B, int T, int H, int Hg, const int32_t* cu_seqlens,
-                                       const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
-                                       int32_t* status_dev, void* stream) {
+static int bwd_chunk_launch(const void* q, const void* k, const void* v, const void* A, const void* Ag, const void* Pg,
+                            const void* dout, const void* h, const void* dh, const float* g_cumsum, const float* beta,
+                            void* dq, void* dk, void* dv, float* dg, float* db, int B, int T, int H, int Hg,
+                            const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq, int total_chunks,
+                            float scale, int32_t* status_dev, void* stream, bool grouped) {
   using namespace fq;
+  const int Hout = grouped ? Hg : H;
   FQ_CHECK_ARG(q && k && v && A && Ag && Pg && dout && dv && h && dh && g_cumsum && beta && dq && dk && dg && db,
                "fq_gdr_bwd_chunk: null tensor");
   FQ_CHECK_ARG(B > 0 && T >= 0 && H > 0 && Hg > 0 && H % Hg == 0 && n_seq > 0 && total_chunks >= 0,
@@ -897,14 +934,14 @@ extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void*
   if ((rc = make_tmap_rows_heads_dim(&mpg, Pg, rows, H, kChunk, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mh, h, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdh, dh, hrows, 1, kDim, kDim, 64)) != FQ_OK) return rc;
-  if ((rc = make_tmap_rows_heads_dim(&mdq, dq, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
-  if ((rc = make_tmap_rows_heads_dim(&mdk, dk, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdq, dq, rows, Hout, kDim, kChunk, 64)) != FQ_OK) return rc;
+  if ((rc = make_tmap_rows_heads_dim(&mdk, dk, rows, Hout, kDim, kChunk, 64)) != FQ_OK) return rc;
   if ((rc = make_tmap_rows_heads_dim(&mdv, dv, rows, H, kDim, kChunk, 64)) != FQ_OK) return rc;
   BwdChunkParams p;
   p.g_cum = g_cumsum; p.beta = beta;
   p.dq = static_cast<__nv_bfloat16*>(dq); p.dk = static_cast<__nv_bfloat16*>(dk); p.dg = dg; p.db = db;
   p.dv = static_cast<__nv_bfloat16*>(dv);
-  p.H = H; p.Hg = Hg; p.total_chunks = total_chunks; p.scale = scale;
+  p.H = H; p.Hg = Hg; p.Hout = Hout; p.total_chunks = total_chunks; p.scale = scale;
   p.sa = SeqArgs{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
   p.status_dev = status_dev;
   const size_t smem = sizeof(BwdChunkSmem) + 1024;
@@ -913,12 +950,33 @@ extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void*
     const int rc_attr = set_smem_limit_once(reinterpret_cast<const void*>(gdr_bwd_chunk_kernel), static_cast<int>(smem), &done0);
     if (rc_attr != FQ_OK) return rc_attr;
   }
-  const long long units = static_cast<long long>(total_chunks) * H;
+  const long long units = static_cast<long long>(total_chunks) * Hout;  // strides of the unit walk (see the kernel)
   const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
   gdr_bwd_chunk_kernel<<<grid, kBcThreads, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mdo, ma, mag, mpg, mh,
                                                                                       mdh, mdq, mdk, mdv, p);
   FQ_CHECK_CUDA(cudaGetLastError());
   return FQ_OK;
+}
+
+extern "C" FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void* v, const void* A, const void* Ag,
+                                       const void* Pg, const void* dout, const void* h, const void* dh,
+                                       const float* g_cumsum, const float* beta, void* dq, void* dk, void* dv, float* dg,
+                                       float* db,
+                                       int B, int T, int H, int Hg, const int32_t* cu_seqlens,
+                                       const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
+                                       int32_t* status_dev, void* stream) {
+  return bwd_chunk_launch(q, k, v, A, Ag, Pg, dout, h, dh, g_cumsum, beta, dq, dk, dv, dg, db, B, T, H, Hg, cu_seqlens,
+                          chunk_offsets, n_seq, total_chunks, scale, status_dev, stream, false);
+}
+
+extern "C" FQ_API int fq_gdr_bwd_chunk_grouped(const void* q, const void* k, const void* v, const void* A, const void* Ag,
+                                               const void* Pg, const void* dout, const void* h, const void* dh,
+                                               const float* g_cumsum, const float* beta, void* dq, void* dk, void* dv,
+                                               float* dg, float* db, int B, int T, int H, int Hg,
+                                               const int32_t* cu_seqlens, const int32_t* chunk_offsets, int n_seq,
+                                               int total_chunks, float scale, int32_t* status_dev, void* stream) {
+  return bwd_chunk_launch(q, k, v, A, Ag, Pg, dout, h, dh, g_cumsum, beta, dq, dk, dv, dg, db, B, T, H, Hg, cu_seqlens,
+                          chunk_offsets, n_seq, total_chunks, scale, status_dev, stream, true);
 }
 
 extern "C" FQ_API int fq_group_reduce(const void* in, void* out, long long rows, int H, int Hg, void* stream) {
@@ -1026,7 +1084,7 @@ extern "C" FQ_API int fq_gdr_bwd_chunk_gva_noalloc(const void* q, const void* k,
   p.g_cum = g_cumsum; p.beta = beta;
   p.dq = dq_h; p.dk = dk_h; p.dg = dg; p.db = db;
   p.dv = static_cast<__nv_bfloat16*>(dv);
-  p.H = H; p.Hg = Hg; p.total_chunks = total_chunks; p.scale = scale;
+  p.H = H; p.Hg = Hg; p.Hout = H; p.total_chunks = total_chunks; p.scale = scale;
   p.sa = SeqArgs{T, cu_seqlens, chunk_offsets, n_seq, (T + kChunk - 1) / kChunk};
   p.status_dev = status_dev;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -311,6 +311,21 @@ FQ_API int fq_gdr_bwd_chunk(const void* q, const void* k, const void* v, const v
                             float scale, int32_t* status_dev, void* stream);
 
 /*
+ * fq_gdr_bwd_chunk with the sum over the V-heads of every QK head done inside the kernel: dq, dk are [B,T,Hg,128]
+ * (the reference sums them after its kernel with group_reduce_vector,
+ * flash_qla/ops/gated_delta_rule/chunk/__init__.py:107-110; tests/ref_gdr.py:694-698).
+ * A CTA takes the V-heads of a (chunk, QK head) pair one after the other, stores the first head's tile and ADDS the
+ * others' (TMA reduce; tail chunks row by row), in that fixed order: for two V-heads per QK head the result is
+ * bit-identical to fq_gdr_bwd_chunk + fq_group_reduce_pair, and the [B,T,H,128] per-head copies are never written.
+ */
+FQ_API int fq_gdr_bwd_chunk_grouped(const void* q, const void* k, const void* v, const void* A, const void* Ag,
+                                    const void* Pg, const void* dout, const void* h, const void* dh,
+                                    const float* g_cumsum, const float* beta, void* dq, void* dk, void* dv, float* dg,
+                                    float* db, int B, int T, int H, int Hg, const int32_t* cu_seqlens,
+                                    const int32_t* chunk_offsets, int n_seq, int total_chunks, float scale,
+                                    int32_t* status_dev, void* stream);
+
+/*
  * fp32 correction of dg at the two ends of every sequence, applied between fq_gdr_bwd_chunk and the reverse
  * fq_chunk_cumsum.  dg of a chunk's last token contains gamma_last * sum(dS o S0) over the 128 x 128 state;
  * fq_gdr_bwd_chunk forms it from the bf16 copies h / dh.  For a sequence's first chunk S0 is the caller's fp32 h0, for

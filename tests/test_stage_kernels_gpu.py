@@ -90,3 +90,75 @@ def test_bounded_wait_expires_and_the_context_survives():
     d = kernels.selftest_umma(a, b, 0)
     ref = a.float() @ b.float().t()
     assert (d - ref).abs().max().item() < 1e-2 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("B,T,Hq,Hv,cu", [(2, 256, 2, 4, None), (1, 500, 1, 2, [0, 130, 131, 500]), (1, 2048, 2, 8, None),
+                                          (1, 300, 1, 3, [0, 7, 71, 300])])
+def test_bwd_chunk_grouped_sums_the_value_heads_in_the_kernel(B, T, Hq, Hv, cu):
+    """fq_gdr_bwd_chunk_grouped (dq, dk summed over the V-heads of a QK head inside the kernel: TMA reduce for whole
+    chunks, row by row for tails) against fq_gdr_bwd_chunk + fq_group_reduce_pair.  Two V-heads per QK head: bitwise
+    equal (one rounding of an exact two-term sum on both paths); more: the partial sums are rounded to bf16 one
+    more time per head, so 2^-7 of the maximum is allowed."""
+    from oracle import gdr_oracle as orc
+    from flashqla_b200 import _lib, kernels, ops
+    lib = _lib.load()
+    torch.manual_seed(33)
+    dev = "cuda"
+    n_seq = B if cu is None else len(cu) - 1
+    q = orc.l2norm(torch.randn(B, T, Hq, 128)).bfloat16().to(dev)
+    k = orc.l2norm(torch.randn(B, T, Hq, 128)).bfloat16().to(dev)
+    v = torch.randn(B, T, Hv, 128).bfloat16().to(dev)
+    g = torch.nn.functional.logsigmoid(torch.randn(B, T, Hv)).to(dev)
+    beta = torch.randn(B, T, Hv).sigmoid().to(dev)
+    do = torch.randn(B, T, Hv, 128).bfloat16().to(dev)
+    h0 = (0.1 * torch.randn(n_seq, Hv, 128, 128)).to(dev)
+    dht = (0.01 * torch.randn(n_seq, Hv, 128, 128)).to(dev)
+    cu_t = None if cu is None else torch.tensor(cu, dtype=torch.int32, device=dev)
+    plan = kernels.make_plan(B, T, cu_t, q.device)
+    scale = 128 ** -0.5
+    gc, A, _, _, _ = ops.chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale, h0, cu_t, True, False, False)
+    _, Ag, Pg = kernels.kkt_solve_gated(k, q, beta, gc, scale, plan, A=A)
+    _, h, _ = kernels.fused_gdr_fwd(q, k, v, Ag, None, gc, beta, scale, initial_state=h0, output_final_state=False,
+                                    output_h=True, output_o=False, plan=plan)
+    dh = torch.empty_like(h)
+    cu_p, off_p = plan.ptrs()
+    st = kernels._stream()
+    _lib.check(lib.fq_gdr_bwd_dh(q.data_ptr(), k.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), do.data_ptr(), gc.data_ptr(),
+                                 beta.data_ptr(), dht.data_ptr(), None, dh.data_ptr(), B, T, Hv, Hq, cu_p, off_p, plan.n_seq,
+                                 plan.total_chunks, scale, None, st), "fq_gdr_bwd_dh")
+
+    def args(dq, dk, dv, dg, db):
+        return (q.data_ptr(), k.data_ptr(), v.data_ptr(), A.data_ptr(), Ag.data_ptr(), Pg.data_ptr(), do.data_ptr(),
+                h.data_ptr(), dh.data_ptr(), gc.data_ptr(), beta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                dg.data_ptr(), db.data_ptr(), B, T, Hv, Hq, cu_p, off_p, plan.n_seq, plan.total_chunks, scale, None, st)
+
+    dq_h = torch.empty(B, T, Hv, 128, dtype=torch.bfloat16, device=dev)
+    dk_h = torch.empty_like(dq_h)
+    dg_r, db_r, dv_r = torch.empty(B, T, Hv, device=dev), torch.empty(B, T, Hv, device=dev), torch.empty_like(v)
+    _lib.check(lib.fq_gdr_bwd_chunk(*args(dq_h, dk_h, dv_r, dg_r, db_r)), "fq_gdr_bwd_chunk")
+    dq_r = torch.empty(B, T, Hq, 128, dtype=torch.bfloat16, device=dev)
+    dk_r = torch.empty_like(dq_r)
+    _lib.check(lib.fq_group_reduce_pair(dq_h.data_ptr(), dq_r.data_ptr(), dk_h.data_ptr(), dk_r.data_ptr(), B * T, Hv, Hq, st),
+               "fq_group_reduce_pair")
+    dq = torch.full((B, T, Hq, 128), float("nan"), dtype=torch.bfloat16, device=dev)
+    dk = torch.full_like(dq, float("nan"))
+    dg, db, dv = torch.empty(B, T, Hv, device=dev), torch.empty(B, T, Hv, device=dev), torch.full_like(v, float("nan"))
+    _lib.check(lib.fq_gdr_bwd_chunk_grouped(*args(dq, dk, dv, dg, db)), "fq_gdr_bwd_chunk_grouped")
+    torch.cuda.synchronize()
+    valid = torch.zeros(B, T, dtype=torch.bool, device=dev)
+    if cu is None:
+        valid[:] = True
+    else:
+        valid[0, :cu[-1]] = True
+    assert torch.equal(dv[valid], dv_r[valid]), "dv"
+    for name, got, ref in (("dq", dq, dq_r), ("dk", dk, dk_r)):
+        got, ref = got[valid], ref[valid]
+        assert torch.isfinite(got.float()).all(), name
+        if Hv // Hq == 2:
+            assert torch.equal(got, ref), f"{name}: not bitwise equal to the two-kernel path"
+        else:
+            err = (got.float() - ref.float()).abs().max().item() / ref.float().abs().max().item()
+            assert err < 2 ** -7, f"{name}: rel-to-max {err:.2e}"
+    for name, got, ref in (("dg", dg, dg_r), ("db", db, db_r)):
+        err = orc.rel_to_max(got[valid].cpu(), ref[valid].cpu())
+        assert err < 1e-5, f"{name}: rel-to-max {err:.2e}"
