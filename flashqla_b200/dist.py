@@ -147,7 +147,7 @@ class CudaImpl:
         Pg = torch.empty_like(Ag) if want_grad else None
         bf = beta.contiguous() if beta.dtype == torch.float32 else beta.float().contiguous()
         return dict(q=q, k=k, v=v, beta=bf, g_cum=g_cum, A=A, Ag=Ag, Pg=Pg, scale=float(scale), plan=plan,
-                    H=v.shape[2], Hg=k.shape[2], Tl=k.shape[1])
+                    H=v.shape[2], Hg=k.shape[2], Tl=k.shape[1], want_grad=want_grad)
 
     def _pieces(self, c):
         from . import kernels
@@ -313,14 +313,21 @@ class CudaImpl:
         dev = c["q"].device
         cp = plan_cp(c["plan"], 1, c["Tl"], c["H"], kernels.sm_count(dev), dev)
         warm = kernels.cp_warmup(c["g_cum"], cp, c["H"]) if cp is not None else None
-        o, _, fs = kernels.fused_gdr_fwd(c["q"], c["k"], c["v"], c["Ag"], c["Pg"], c["g_cum"], c["beta"], c["scale"],
-                                         initial_state=h_in, output_final_state=want_final, plan=c["plan"], cp=cp, warmup=warm)
+        # a forward whose backward follows keeps the bf16 state before every chunk when it fits the budget of the
+        # single-GPU operator (FLASHQLA_KEEP_STATES_MB): the backward then skips its state pass
+        from .ops import _KEEP_STATES_BYTES
+        keep_h = c["want_grad"] and c["plan"].total_chunks * c["H"] * 128 * 128 * 2 <= _KEEP_STATES_BYTES
+        o, h, fs = kernels.fused_gdr_fwd(c["q"], c["k"], c["v"], c["Ag"], c["Pg"], c["g_cum"], c["beta"], c["scale"],
+                                         initial_state=h_in, output_final_state=want_final, output_h=keep_h, plan=c["plan"],
+                                         cp=cp, warmup=warm)
+        c["h"] = h
         return o, fs
 
     def backward(self, c, do, e_in, h_in):
         from . import bwd
         return bwd.chunk_gated_delta_rule_bwd(c["q"], c["k"], c["v"], c["g_cum"], c["beta"], c["A"], do, e_in, c["scale"], h_in,
-                                              None, gated_tiles=(c["Ag"], c["Pg"]), plan=c["plan"], want_dh0=True)
+                                              None, gated_tiles=(c["Ag"], c["Pg"]), plan=c["plan"], want_dh0=True,
+                                              h_saved=c.get("h"))
 
 
 # --------------------------------------------------------------------------------------------------------------------

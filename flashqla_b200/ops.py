@@ -20,7 +20,7 @@ _RECOMPUTE_TILES = os.environ.get("FLASHQLA_RECOMPUTE_TILES", "0") == "1"
 # It also keeps the bf16 state before every chunk (32 KiB per chunk and V-head, written by the forward kernel on its way)
 # when that tensor stays below this budget, so that the backward need not recompute it with a second state pass; larger
 # problems (and FLASHQLA_KEEP_STATES_MB=0) recompute like the reference does.
-_KEEP_STATES_BYTES = int(float(os.environ.get("FLASHQLA_KEEP_STATES_MB", "2048")) * (1 << 20))
+_KEEP_STATES_BYTES = int(float(os.environ.get("FLASHQLA_KEEP_STATES_MB", "8192")) * (1 << 20))
 
 
 class _L2NormFunction(torch.autograd.Function):
