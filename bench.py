@@ -509,11 +509,11 @@ def sequence_parallel_run(bn, w, steps, warmup, check=True):
         torch.cuda.empty_cache()
 
     def step():
-        if world == 1:   # the whole sequence on one GPU: the plain operator (tiles kept for the backward, as autograd does)
+        if world == 1:   # the whole sequence on one GPU: the plain operator (tiles and states kept for the backward, as autograd does)
             gc, A, o, _, fs, tiles, _ = ops.chunk_gated_delta_rule_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], scale, None, None,
-                                                                    True, False, True, _return_tiles=True)
+                                                                    True, False, True, _return_tiles=True, _keep_h=True)
             ops.chunk_gated_delta_rule_bwd(d["q"], d["k"], d["v"], gc, d["beta"], A, d["do"], None, scale, None, None,
-                                           _gated_tiles=tiles[:2])
+                                           _gated_tiles=tiles[:2], _h_saved=tiles[2])
             return
         o, fs, saved = fqd.cp_forward(d["q"], d["k"], d["v"], d["g"], d["beta"], scale, None, None, impl=impl)
         fqd.cp_backward(saved, d["do"], None, None, impl=impl)
