@@ -337,6 +337,29 @@ def measure_forward(bn, w, d, steps, warmup):
     return ms, kernel_ms, launches, ms_stage
 
 
+def graph_replay_ms(bn, step, steps, warmup):
+    """ms per step of `step` captured once in a CUDA graph and replayed, or None when the capture failed on any rank
+    (the replay is timed between barriers: every rank takes part, or none does)."""
+    cg = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg):
+            step()
+    except Exception as exc:  # the eager figure stands
+        cg = None
+        print(f"[bench] CUDA graph capture of the step failed: {exc}", file=sys.stderr, flush=True)
+    if bn.max_over_ranks([0.0 if cg is not None else 1.0])[0] != 0.0:
+        return None
+    return bn.timed(cg.replay, steps, warmup, record=False)[0]
+
+
 def measure_fwd_bwd(bn, w, d, steps, warmup, graph=False):
     """Forward + backward through the differentiable operator and torch.autograd.  ``graph``: additionally capture the
     step in a CUDA graph and time its replay (a step of a few hundred microseconds is bound by the host's launch rate
@@ -355,24 +378,7 @@ def measure_fwd_bwd(bn, w, d, steps, warmup, graph=False):
     if not graph:
         return bn.timed(step, steps, warmup)
     eager = bn.timed(step, steps, warmup, record=False)
-    replay_ms, cg = None, None
-    try:
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for _ in range(3):
-                step()
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        cg = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(cg):
-            step()
-    except Exception as exc:  # the eager figure stands
-        cg = None
-        print(f"[bench] CUDA graph capture of the fwd+bwd step failed: {exc}", file=sys.stderr, flush=True)
-    # the replay is timed between barriers: every rank takes part, or none does
-    if bn.max_over_ranks([0.0 if cg is not None else 1.0])[0] == 0.0:
-        replay_ms = bn.timed(cg.replay, steps, warmup, record=False)[0]
+    replay_ms = graph_replay_ms(bn, step, steps, warmup)
     return eager + (replay_ms,)
 
 
@@ -520,6 +526,14 @@ def sequence_parallel_run(bn, w, steps, warmup, check=True):
 
     ms, _, _ = bn.timed(step, steps, warmup, record=False)
     ms = bn.max_over_ranks([ms])[0]
+    out["ms_per_step_eager"] = ms
+    if world > 1 and os.environ.get("FQ_BENCH_SP_GRAPH", "0") == "1":
+        # the step (kernels and NCCL collectives) captured once and replayed: shows what the host's launch rate costs
+        ms_g = graph_replay_ms(bn, step, steps, warmup)
+        if ms_g is not None:
+            ms_g = bn.max_over_ranks([ms_g])[0]
+            out["ms_per_step_graph"] = ms_g
+            ms = min(ms, ms_g)
     out.update({"ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "steps": steps,
                 "exchange": "all_gather of per-rank (end state from zero, transition matrix) in the forward and of the "
                             "left-edge state gradient in the backward; no halo, no serial hand-over",
