@@ -314,7 +314,7 @@ gdr_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       tmem_wait_st();
     }
     for (int it = 0; it < total; ++it) {
-      const int n = it - warm, st = it & 1, gs = it & (kGateStages - 1);
+      const int n = it - warm, gs = it & (kGateStages - 1);
       const uint32_t ph = it & 1;
       // ---- state -> bf16 operand, optional h, decay
       if (it > 0) {
