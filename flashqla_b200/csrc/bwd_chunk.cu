@@ -88,8 +88,9 @@ __device__ __forceinline__ uint32_t off64(int kk) { return (kk >> 2) * 8192 + (k
 __device__ __forceinline__ uint32_t off128(int kk) { return (kk >> 2) * 16384 + (kk & 3) * 32; }
 
 // Eight bf16 values of a tail chunk's row: stored, or (grouped output, later heads of a group) added to what the same
-// thread stored for the earlier heads - the sum is formed in fp32 and rounded once, as the tile path does.
-__device__ __forceinline__ void row_out(__nv_bfloat16* dst, uint4 x, bool accum) {
+// thread stored for the earlier heads - the sum is formed in fp32 and rounded once, as the tile path does.  Kept out
+// of line: only tail chunks come here, and the kernel's loop body is large as it is.
+static __device__ __noinline__ void row_out(__nv_bfloat16* dst, uint4 x, bool accum) {
   uint4* ptr = reinterpret_cast<uint4*>(dst);
   if (accum) {
     const uint4 o = *ptr;
